@@ -1,0 +1,268 @@
+/*
+ * b200const.h -- C ABI of the B200 constant-folding shim.
+ *
+ * This is the boundary a host compiler binds to in order to run the
+ * vpux::Const::ContentAttr transformation chain (constant folding of weight
+ * tensors) and the weight-compression codec on an NVIDIA B200 (sm_100a).
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, never
+ * throws, and returns 0 on success or a negative B200C_ERR_* code.  The text of
+ * the error (the message the reference would have put into VPUX_THROW) is kept
+ * per calling thread and read with b200c_last_error().
+ *
+ * There is no CPU implementation behind these calls: when no CUDA device is
+ * usable every compute entry point fails with B200C_ERR_CUDA.
+ *
+ * Reference interfaces are cited by their path inside openvinotoolkit/npu_plugin.
+ */
+#ifndef B200CONST_H_
+#define B200CONST_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200C_MAX_RANK 8
+
+/* ---- element types ------------------------------------------------------
+ * dtype = (class << 8) | bit width.  Integer signedness follows MLIR:
+ * signless (i8), signed (si8), unsigned (ui8).  The reference treats signless
+ * integers as unsigned when it reads values
+ * (src/vpux_compiler/include/vpux/compiler/dialect/const/utils/content.hpp:253-299).
+ */
+#define B200C_CLS_FLOAT 1
+#define B200C_CLS_BFLOAT 2
+#define B200C_CLS_INT 3  /* signless */
+#define B200C_CLS_SINT 4 /* signed   */
+#define B200C_CLS_UINT 5 /* unsigned */
+#define B200C_DTYPE(cls, bits) (((cls) << 8) | (bits))
+#define B200C_DTYPE_BITS(dt) ((dt)&0xFF)
+#define B200C_DTYPE_CLASS(dt) (((dt) >> 8) & 0xFF)
+
+#define B200C_F64 B200C_DTYPE(B200C_CLS_FLOAT, 64)
+#define B200C_F32 B200C_DTYPE(B200C_CLS_FLOAT, 32)
+#define B200C_F16 B200C_DTYPE(B200C_CLS_FLOAT, 16)
+#define B200C_BF16 B200C_DTYPE(B200C_CLS_BFLOAT, 16)
+#define B200C_I1 B200C_DTYPE(B200C_CLS_INT, 1)
+#define B200C_UI1 B200C_DTYPE(B200C_CLS_UINT, 1)
+#define B200C_I4 B200C_DTYPE(B200C_CLS_INT, 4)
+#define B200C_SI4 B200C_DTYPE(B200C_CLS_SINT, 4)
+#define B200C_UI4 B200C_DTYPE(B200C_CLS_UINT, 4)
+#define B200C_I8 B200C_DTYPE(B200C_CLS_INT, 8)
+#define B200C_SI8 B200C_DTYPE(B200C_CLS_SINT, 8)
+#define B200C_UI8 B200C_DTYPE(B200C_CLS_UINT, 8)
+#define B200C_I16 B200C_DTYPE(B200C_CLS_INT, 16)
+#define B200C_SI16 B200C_DTYPE(B200C_CLS_SINT, 16)
+#define B200C_UI16 B200C_DTYPE(B200C_CLS_UINT, 16)
+#define B200C_I32 B200C_DTYPE(B200C_CLS_INT, 32)
+#define B200C_SI32 B200C_DTYPE(B200C_CLS_SINT, 32)
+#define B200C_UI32 B200C_DTYPE(B200C_CLS_UINT, 32)
+#define B200C_I64 B200C_DTYPE(B200C_CLS_INT, 64)
+#define B200C_SI64 B200C_DTYPE(B200C_CLS_SINT, 64)
+#define B200C_UI64 B200C_DTYPE(B200C_CLS_UINT, 64)
+
+/* ---- quantisation kinds (mlir::quant::UniformQuantized[PerAxis]Type) ---- */
+#define B200C_Q_NONE 0
+#define B200C_Q_PER_TENSOR 1
+#define B200C_Q_PER_AXIS 2
+
+/*
+ * Tensor type: what vpux::NDTypeInterface carries for a constant
+ * (shape, element type, DimsOrder).  For a quantised element type `dtype` is
+ * the normalised storage integer (si8/ui8/si4/ui4,
+ * src/vpux_compiler/src/utils/quantization.cpp:47-54) and the q* fields hold
+ * the quantisation parameters.  `scales`/`zps` are borrowed, `nq` entries each
+ * (1 for per-tensor).  `order[k]` is the logical dimension stored at memory
+ * position k, k = 0 being the outermost (DimsOrder::toPermutation); NHWC is
+ * {0,2,3,1}.
+ */
+typedef struct b200c_type {
+    int32_t dtype;
+    int32_t rank;
+    int64_t shape[B200C_MAX_RANK];
+    uint8_t order[B200C_MAX_RANK];
+    int32_t qkind;
+    int32_t qaxis;
+    int32_t qexpressed; /* dtype of the expressed type (f32/f16) */
+    int32_t _pad;
+    int64_t qmin, qmax; /* storageTypeMin / storageTypeMax */
+    int64_t nq;
+    const double* scales;
+    const int64_t* zps;
+} b200c_type;
+
+/* ---- transformation kinds: one per reference attribute mnemonic ----------
+ * (src/vpux_compiler/tblgen/vpux/compiler/dialect/const/attributes.td)       */
+enum b200c_xform_kind {
+    B200C_X_CONVERT_ELEM_TYPE = 1, /* type.dtype (+quant none)                 */
+    B200C_X_QUANT_CAST = 2,        /* type.q*; type.dtype == 0 -> strip quant   */
+    B200C_X_DEQUANTIZE = 3,
+    B200C_X_RESCALE = 4,      /* f = scale                                       */
+    B200C_X_ADD = 5,          /* f = bias                                        */
+    B200C_X_REORDER = 6,      /* a[0..rank) = new order permutation              */
+    B200C_X_SUBVIEW = 7,      /* a = offset, b = shape                           */
+    B200C_X_PAD_WITH_ZERO = 8, /* a = padBefore, b = padAfter                    */
+    B200C_X_BIT_PACK = 9,     /* i0 = width (4)                                  */
+    B200C_X_GET_SPARSITY_MAP = 10,
+    B200C_X_SPARSIFY = 11,    /* i0 = compressOutputType, aux = numActualElements */
+    B200C_X_SWIZZLE_CONSTANT = 12, /* i0 = swizzle key, i1 = arch (3 = VPUX37XX)  */
+    B200C_X_RESHAPE = 13,     /* b = new shape, n = new rank                     */
+    B200C_X_CHANGE_SHAPE_AND_ELEM_TYPE = 14, /* b = shape, type = element type   */
+    B200C_X_BROADCAST = 15,   /* i0 = axis, i1 = value                           */
+    B200C_X_TRANSPOSE = 16,   /* a = order permutation                           */
+    B200C_X_REVERSE = 17,     /* i0 = axis                                       */
+    B200C_X_EXPAND_DILATED = 18, /* a[0..1] = dilations                          */
+    /* Synthetic producer step with no reference counterpart: per-channel
+     * (axis 0) quantisation of a float tensor.  i0 = scheme:
+     *   0: symmetric int8  scale = max|w|/127, zp = 0, round-half-even, clamp [-127,127]
+     *   1: asymmetric u4   scale = (max-min)/15, zp = clamp(rint(-min/scale),0,15)
+     * side0 / side1 receive the per-channel f32 scales / i32 zero points
+     * (same residency as the fold output).  The result holds the integral
+     * values in f32 storage; follow it with ConvertElemType + QuantCast.      */
+    B200C_X_QUANTIZE_SYNTH = 100
+};
+
+#define B200C_QSYNTH_SYM_I8 0
+#define B200C_QSYNTH_ASYM_U4 1
+
+typedef struct b200c_xform {
+    int32_t kind;
+    int32_t n;                  /* entries used in a[] / b[]                    */
+    int64_t a[B200C_MAX_RANK];
+    int64_t b[B200C_MAX_RANK];
+    double f;
+    int64_t i0, i1;
+    b200c_type type;
+    const int64_t* aux;
+    int64_t naux;
+    void* side0;
+    void* side1;
+} b200c_xform;
+
+/* ---- return codes --------------------------------------------------------- */
+#define B200C_OK 0
+#define B200C_NOT_SMALLER 1       /* compress: the reference's mlir::failure()   */
+#define B200C_ERR_INVALID (-1)    /* malformed descriptor / argument             */
+#define B200C_ERR_THROW (-2)      /* the reference would VPUX_THROW here         */
+#define B200C_ERR_CUDA (-3)       /* CUDA runtime failure or no device           */
+#define B200C_ERR_NOMEM (-4)      /* device or host allocation failed            */
+#define B200C_ERR_CAPACITY (-5)   /* output buffer too small                     */
+#define B200C_ERR_UNSUPPORTED (-6) /* valid in the reference, not built here     */
+
+/* ---- context ----------------------------------------------------------------
+ * One context per (host thread, device).  It owns a CUDA stream, a growing
+ * scratch arena and pinned staging memory.  Calls on different contexts may
+ * run concurrently (the reference folds from many threads at once:
+ * src/vpux_compiler/src/dialect/VPUIP/graph-schema/export.cpp:465 and
+ * src/vpux_compiler/src/dialect/const/utils/constant_folding_in_background.cpp:57-100);
+ * calls on one context are serialised by an internal mutex.                   */
+typedef struct b200c_ctx b200c_ctx;
+int b200c_create(int device, b200c_ctx** out);
+void b200c_destroy(b200c_ctx* ctx);
+/* Use `stream` (a cudaStream_t) for all later work of this context; NULL
+ * restores the context's own stream.                                          */
+int b200c_set_stream(b200c_ctx* ctx, void* stream);
+void* b200c_get_stream(b200c_ctx* ctx);
+int b200c_synchronize(b200c_ctx* ctx);
+/* Number of kernels of this library launched through the context so far.     */
+int64_t b200c_launch_count(b200c_ctx* ctx);
+/* Thread-local message of the last failing call on this thread.              */
+const char* b200c_last_error(void);
+const char* b200c_version(void);
+
+/* ---- type inference -----------------------------------------------------------
+ * Const::ContentAttr::inferFinalType
+ * (src/vpux_compiler/src/dialect/const/attributes/content.cpp:373-381) and each
+ * attribute's inferOutputType.  `out->scales` / `out->zps` must point to
+ * caller storage of `out->nq` entries on entry when the result can be
+ * per-axis quantised; on return nq is the count written.  Pure host code.     */
+int b200c_infer_type(const b200c_type* in, const b200c_xform* chain, int n, b200c_type* out);
+
+/* Index at which ContentAttr::addTransformation inserts a new transformation
+ * (getInsertionPosition, content.cpp:268-299): NONE before PREFERRED_LAST before
+ * LAST; a second LAST is an error.  `kinds` are the b200c_xform_kind values of
+ * the existing list.                                                          */
+int b200c_insert_position(const int32_t* kinds, int n, int32_t new_kind, int* pos);
+
+/* Byte size of a tensor of this type: NDTypeInterface::getTotalAllocSize
+ * (src/vpux_compiler/src/core/type_interfaces.cpp:148-162).                   */
+int64_t b200c_total_alloc_size(const b200c_type* t);
+
+/* ---- folding -------------------------------------------------------------------
+ * Const::ContentAttr::fold() followed by Const::Content::copyTo()
+ * (content.cpp:167-193, src/vpux_compiler/src/dialect/const/utils/content.cpp:184-207),
+ * i.e. what Const::DeclareOp::getContent() + copyTo hands to the constant-folding
+ * pass (src/vpux_compiler/src/dialect/const/passes/constant_folding.cpp:27-77),
+ * the blob writer (export.cpp:465-479) and the compression pass.
+ *
+ *  base/data/nbytes : the base ElementsAttr: type and raw bytes; `is_splat`
+ *                     means `data` holds a single element.
+ *  data_on_device   : `data` is a device pointer on the context's device.
+ *  out/out_cap      : destination; `out_on_device` as above.  The bytes are
+ *                     exactly those copyTo writes; *out_bytes is their count.
+ *                     Bytes of `out` beyond *out_bytes are not touched.
+ *  out_type         : type of the folded Content (may be NULL); pointer rules
+ *                     as for b200c_infer_type.
+ * The call returns after the result is complete (it synchronises the
+ * context's stream) unless out_on_device != 0 and B200C_FOLD_ASYNC is set in
+ * `flags`, in which case data-dependent errors are reported by the next
+ * synchronising call on the context.                                          */
+#define B200C_FOLD_ASYNC 1
+int b200c_fold(b200c_ctx* ctx, const b200c_type* base, const void* data, size_t nbytes, int is_splat,
+               int data_on_device, const b200c_xform* chain, int n, void* out, size_t out_cap, int out_on_device,
+               size_t* out_bytes, b200c_type* out_type, int flags);
+
+/* Per-output-channel count of elements that differ from the sparsify value:
+ * vpux::countNonSparseElementsPerOC (src/vpux_compiler/src/utils/sparsity.cpp:28-72)
+ * applied to the folded content of (base, chain).  counts: host int64[shape[0]].  */
+int b200c_count_nonsparse_per_oc(b200c_ctx* ctx, const b200c_type* base, const void* data, size_t nbytes,
+                                 int is_splat, int data_on_device, const b200c_xform* chain, int n,
+                                 int64_t* counts, int64_t ncounts);
+
+/* ---- weight compression ----------------------------------------------------------
+ * Stands where vpux::BitCompactorCodec::compress calls
+ * btc27::BitCompactor::{GetCompressedSizeBound, CompressArray}
+ * (src/vpux_compiler/src/utils/bit_compactor_codec.cpp:15-42).  The bitstream is
+ * this library's own block format (64-byte blocks, per-block mode selection),
+ * not BitCompactor's: the BitCompactor sources are not part of the reference
+ * tree.  b200c_btc_compress returns B200C_NOT_SMALLER when the stream would not
+ * be smaller than the input, as the reference's codec returns failure.        */
+int b200c_btc_bound(size_t n, size_t* bound);
+int b200c_btc_compress(b200c_ctx* ctx, const void* in, size_t n, int in_on_device, void* out, size_t cap,
+                       int out_on_device, size_t* out_n);
+int b200c_btc_decompress(b200c_ctx* ctx, const void* in, size_t n, int in_on_device, void* out, size_t cap,
+                         int out_on_device, size_t* out_n);
+
+/* Batched form used for whole-model folding: `count` independent buffers that
+ * already reside on the device are compressed with one analysis launch, one
+ * device prefix sum and one emit launch.  sizes/offsets are host arrays;
+ * out_sizes[i] receives the stream length of buffer i (B200C_NOT_SMALLER cases
+ * are reported through not_smaller[i] = 1 and store the input unchanged).     */
+int b200c_btc_compress_batch(b200c_ctx* ctx, int count, const void* const* in_dev, const size_t* sizes,
+                             void* out_dev, size_t out_cap, size_t* out_offsets, size_t* out_sizes,
+                             int32_t* not_smaller);
+
+/* ---- synthetic weights ----------------------------------------------------------
+ * Counter-based seeded generator (Philox-4x32-10 keyed by seed and stream)
+ * used by the benchmark so that inputs never cross PCIe.  dist: 0 = normal
+ * (p0 = sigma), 1 = uniform int8 in [-127,127] with Bernoulli(p0) zeros,
+ * 2 = discretised Laplace(0, p0) clipped to [-127,127] with a fraction p1 of
+ * exact zeros.  dtype: B200C_F32, B200C_F16 or B200C_SI8.                    */
+int b200c_synth_fill(b200c_ctx* ctx, void* dst_dev, int64_t count, int32_t dtype, int32_t dist, double p0,
+                     double p1, uint64_t seed, uint64_t stream_id);
+
+/* ---- device memory helpers (so that callers need no CUDA runtime of their own) */
+int b200c_dev_alloc(b200c_ctx* ctx, size_t n, void** out);
+int b200c_dev_free(b200c_ctx* ctx, void* p);
+int b200c_host_alloc_pinned(size_t n, void** out);
+int b200c_host_free_pinned(void* p);
+int b200c_memcpy_h2d(b200c_ctx* ctx, void* dst_dev, const void* src, size_t n);
+int b200c_memcpy_d2h(b200c_ctx* ctx, void* dst, const void* src_dev, size_t n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200CONST_H_ */

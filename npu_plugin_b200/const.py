@@ -1,0 +1,567 @@
+"""Host-side mirror of the reference's Const dialect API for Python callers.
+
+Names follow vpux::Const (src/vpux_compiler/tblgen/vpux/compiler/dialect/const/attributes.td:72-107):
+ContentAttr with its builder methods (convertElemType, quantCast, dequantize, rescale, add, reorder,
+padWithZero, subview, bitPack, getSparsityMap, sparsify, swizzleConstant, reshape, ...), Content
+(getType, isSplat, copyTo, getValues) and DeclareOp.getContent().  The arithmetic runs in
+libb200const.so on the GPU; this module only marshals descriptors.
+
+A `backend` object supplies infer_type / insert_position / fold / ...; the default is the CUDA
+library.  Tests pass the CPU oracle's backend to run the same chain on both sides.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import _cabi as A
+
+
+class ConstError(RuntimeError):
+    """The reference would have raised VPUX_THROW here; the message is the reference-style text."""
+
+
+class Unsupported(RuntimeError):
+    pass
+
+
+class CudaError(RuntimeError):
+    pass
+
+
+def raise_for(rc, msg):
+    if rc in (A.OK, A.NOT_SMALLER):
+        return rc
+    text = msg.decode() if isinstance(msg, bytes) else str(msg)
+    if rc == A.ERR_THROW:
+        raise ConstError(text)
+    if rc == A.ERR_UNSUPPORTED:
+        raise Unsupported(text)
+    if rc in (A.ERR_CUDA, A.ERR_NOMEM):
+        raise CudaError(text)
+    raise ValueError(f"b200c error {rc}: {text}")
+
+
+# --------------------------------------------------------------------------- DimsOrder
+class DimsOrder(tuple):
+    """Permutation, outermost memory dim first (DimsOrder::toPermutation,
+    src/vpux_compiler/src/core/attributes/dims_order.cpp)."""
+
+    @staticmethod
+    def fromCode(code):
+        digits = []
+        while code:
+            digits.append((code & 0xF) - 1)
+            code >>= 4
+        return DimsOrder(reversed(digits))
+
+    @staticmethod
+    def fromNumDims(n):
+        return DimsOrder(range(n))
+
+    def code(self):
+        c = 0
+        for d in self:
+            c = (c << 4) | (d + 1)
+        return c
+
+    def dimPos(self, d):
+        return self.index(d)
+
+
+DimsOrder.C = DimsOrder((0,))
+DimsOrder.NC = DimsOrder((0, 1))
+DimsOrder.CHW = DimsOrder((0, 1, 2))
+DimsOrder.HWC = DimsOrder((1, 2, 0))
+DimsOrder.NCHW = DimsOrder((0, 1, 2, 3))
+DimsOrder.NHWC = DimsOrder((0, 2, 3, 1))
+DimsOrder.NHCW = DimsOrder((0, 2, 1, 3))
+DimsOrder.OIYX = DimsOrder.NCHW
+DimsOrder.OYXI = DimsOrder.NHWC
+DimsOrder.YXOI = DimsOrder((2, 3, 0, 1))
+DimsOrder.NCDHW = DimsOrder((0, 1, 2, 3, 4))
+DimsOrder.NDHWC = DimsOrder((0, 2, 3, 4, 1))
+
+
+# --------------------------------------------------------------------------- element types
+class Quant:
+    """mlir::quant::UniformQuantizedType / UniformQuantizedPerAxisType."""
+
+    def __init__(self, kind, storage, expressed, scales, zps, axis=0, qmin=None, qmax=None):
+        self.kind = kind
+        self.storage = storage  # normalised storage integer dtype (si8/ui8/si4/ui4)
+        self.expressed = expressed
+        self.scales = [float(s) for s in scales]
+        self.zps = [int(z) for z in zps]
+        self.axis = int(axis)
+        bits = A.dtype_bits(storage)
+        signed = A.dtype_class(storage) == A.CLS_SINT
+        self.qmin = int(qmin) if qmin is not None else (-(1 << (bits - 1)) if signed else 0)
+        self.qmax = int(qmax) if qmax is not None else ((1 << (bits - 1)) - 1 if signed else (1 << bits) - 1)
+
+    def __eq__(self, o):
+        return isinstance(o, Quant) and (self.kind, self.storage, self.expressed, self.scales, self.zps, self.axis,
+                                         self.qmin, self.qmax) == (o.kind, o.storage, o.expressed, o.scales, o.zps,
+                                                                   o.axis, o.qmin, o.qmax)
+
+    def __repr__(self):
+        return (f"Quant(kind={self.kind}, storage={self.storage:#x}, axis={self.axis}, n={len(self.scales)}, "
+                f"range=[{self.qmin},{self.qmax}])")
+
+
+def UniformQuantizedType(storage, expressed, scale, zeroPoint, qmin=None, qmax=None):
+    return Quant(A.Q_PER_TENSOR, storage, expressed, [scale], [zeroPoint], 0, qmin, qmax)
+
+
+def UniformQuantizedPerAxisType(storage, expressed, scales, zeroPoints, axis, qmin=None, qmax=None):
+    return Quant(A.Q_PER_AXIS, storage, expressed, scales, zeroPoints, axis, qmin, qmax)
+
+
+def _np_dtype(dt):
+    m = {A.F64: np.float64, A.F32: np.float32, A.F16: np.float16, A.BF16: np.uint16, A.I8: np.uint8,
+         A.SI8: np.int8, A.UI8: np.uint8, A.I16: np.uint16, A.SI16: np.int16, A.UI16: np.uint16, A.I32: np.uint32,
+         A.SI32: np.int32, A.UI32: np.uint32, A.I64: np.uint64, A.SI64: np.int64, A.UI64: np.uint64}
+    return np.dtype(m[dt])
+
+
+class NDType:
+    """shape + element type (+ DimsOrder): the part of vpux::NDTypeInterface constants use."""
+
+    def __init__(self, shape, elem, order=None):
+        self.shape = tuple(int(s) for s in shape)
+        self.quant = elem if isinstance(elem, Quant) else None
+        self.dtype = elem.storage if isinstance(elem, Quant) else int(elem)
+        self.order = DimsOrder(order) if order is not None else DimsOrder.fromNumDims(len(self.shape))
+
+    @property
+    def rank(self):
+        return len(self.shape)
+
+    def getNumElements(self):
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+    def getElemTypeSize(self):
+        return A.dtype_bits(self.dtype)
+
+    def getTotalAllocSize(self):
+        n = 1 if self.rank == 0 else self.getNumElements()
+        return (self.getElemTypeSize() * n + 7) // 8
+
+    def getMemShape(self):
+        return tuple(self.shape[d] for d in self.order)
+
+    def getElementType(self):
+        return self.quant if self.quant is not None else self.dtype
+
+    def __eq__(self, o):
+        return isinstance(o, NDType) and (self.shape, self.dtype, self.quant, tuple(self.order)) == (
+            o.shape, o.dtype, o.quant, tuple(o.order))
+
+    def __repr__(self):
+        return f"NDType({self.shape}, {self.dtype:#x}, order={tuple(self.order)}, quant={self.quant})"
+
+    # ---- marshalling
+    def to_c(self, keep):
+        t = A.b200c_type()
+        t.dtype = self.dtype
+        t.rank = self.rank
+        for k, s in enumerate(self.shape):
+            t.shape[k] = s
+        for k, d in enumerate(self.order):
+            t.order[k] = d
+        if self.quant is not None:
+            q = self.quant
+            t.qkind, t.qaxis, t.qexpressed = q.kind, q.axis, q.expressed
+            t.qmin, t.qmax = q.qmin, q.qmax
+            t.nq = len(q.scales)
+            sc = (C.c_double * max(1, len(q.scales)))(*q.scales)
+            zp = (C.c_int64 * max(1, len(q.zps)))(*q.zps)
+            keep.extend([sc, zp])
+            t.scales = C.cast(sc, C.POINTER(C.c_double))
+            t.zps = C.cast(zp, C.POINTER(C.c_int64))
+        return t
+
+    @staticmethod
+    def from_c(t):
+        shape = [t.shape[k] for k in range(t.rank)]
+        order = [t.order[k] for k in range(t.rank)]
+        elem = t.dtype
+        if t.qkind != A.Q_NONE:
+            elem = Quant(t.qkind, t.dtype, t.qexpressed, [t.scales[i] for i in range(t.nq)],
+                         [t.zps[i] for i in range(t.nq)], t.qaxis, t.qmin, t.qmax)
+        return NDType(shape, elem, order)
+
+
+def out_type_slot(max_q, keep):
+    """A b200c_type with caller storage for up to max_q quantisation parameters."""
+    t = A.b200c_type()
+    sc = (C.c_double * max(1, max_q))()
+    zp = (C.c_int64 * max(1, max_q))()
+    keep.extend([sc, zp])
+    t.nq = max_q
+    t.scales = C.cast(sc, C.POINTER(C.c_double))
+    t.zps = C.cast(zp, C.POINTER(C.c_int64))
+    return t
+
+
+# --------------------------------------------------------------------------- transformations
+_NAMES = {A.X_CONVERT_ELEM_TYPE: "ConvertElemType", A.X_QUANT_CAST: "QuantCast", A.X_DEQUANTIZE: "Dequantize",
+          A.X_RESCALE: "Rescale", A.X_ADD: "Add", A.X_REORDER: "Reorder", A.X_SUBVIEW: "SubView",
+          A.X_PAD_WITH_ZERO: "PadWithZero", A.X_BIT_PACK: "BitPack", A.X_GET_SPARSITY_MAP: "GetSparsityMap",
+          A.X_SPARSIFY: "Sparsify", A.X_SWIZZLE_CONSTANT: "SwizzleConstant", A.X_RESHAPE: "Reshape",
+          A.X_CHANGE_SHAPE_AND_ELEM_TYPE: "ChangeShapeAndElemType", A.X_BROADCAST: "Broadcast",
+          A.X_TRANSPOSE: "Transpose", A.X_REVERSE: "Reverse", A.X_EXPAND_DILATED: "ExpandDilated",
+          A.X_QUANTIZE_SYNTH: "QuantizeSynth"}
+
+
+class Transform:
+    """One Const::TransformAttrInterface instance."""
+
+    def __init__(self, kind, a=(), b=(), f=0.0, i0=0, i1=0, elem=None, aux=None, side0=None, side1=None):
+        self.kind, self.a, self.b, self.f, self.i0, self.i1 = kind, tuple(a), tuple(b), float(f), int(i0), int(i1)
+        self.elem, self.aux, self.side0, self.side1 = elem, (None if aux is None else [int(v) for v in aux]), side0, side1
+
+    def getTransformationName(self):
+        return _NAMES[self.kind]
+
+    def __repr__(self):
+        return f"#const.{_NAMES[self.kind]}"
+
+    @staticmethod
+    def _ptr(side):
+        if side is None:
+            return None
+        if isinstance(side, np.ndarray):
+            return side.ctypes.data
+        return int(side)
+
+    def to_c(self, keep):
+        x = A.b200c_xform()
+        x.kind = self.kind
+        n = max(len(self.a), len(self.b))
+        x.n = n
+        for k, v in enumerate(self.a):
+            x.a[k] = v
+        for k, v in enumerate(self.b):
+            x.b[k] = v
+        x.f, x.i0, x.i1 = self.f, self.i0, self.i1
+        if self.elem is not None:
+            x.type = NDType((), self.elem).to_c(keep)
+        if self.aux is not None:
+            arr = (C.c_int64 * max(1, len(self.aux)))(*self.aux)
+            keep.append(arr)
+            x.aux = C.cast(arr, C.POINTER(C.c_int64))
+            x.naux = len(self.aux)
+        x.side0 = self._ptr(self.side0)
+        x.side1 = self._ptr(self.side1)
+        return x
+
+
+def chain_to_c(transforms, keep):
+    arr = (A.b200c_xform * max(1, len(transforms)))()
+    for i, t in enumerate(transforms):
+        arr[i] = t.to_c(keep)
+    return arr
+
+
+def max_q_of(base_type, transforms):
+    m = base_type.getNumElements() if base_type.rank else 1
+    m = max([m, 1] + list(base_type.shape))
+    for t in transforms:
+        for v in list(t.a) + list(t.b) + [t.i1]:
+            m = max(m, abs(int(v)))
+        if isinstance(t.elem, Quant):
+            m = max(m, len(t.elem.scales))
+    return min(m, 1 << 24) + 64
+
+
+# --------------------------------------------------------------------------- Content
+class Content:
+    """Result of ContentAttr.fold(): the folded type plus the bytes Content::copyTo writes."""
+
+    def __init__(self, ndtype, raw, written, splat=False):
+        self._type, self._raw, self._written, self._splat = ndtype, raw, written, splat
+
+    def getType(self):
+        return self._type
+
+    def copyTo(self, buf=None):
+        """Bytes copyTo writes into a zero-initialised buffer of getTotalAllocSize bytes."""
+        if buf is None:
+            return self._raw
+        b = np.frombuffer(buf, dtype=np.uint8) if not isinstance(buf, np.ndarray) else buf.view(np.uint8).reshape(-1)
+        b[:self._written] = self._raw[:self._written]
+        return buf
+
+    @property
+    def bytesWritten(self):
+        return self._written
+
+    def getValues(self, np_dtype=None):
+        dt = np.dtype(np_dtype) if np_dtype is not None else _np_dtype(self._type.dtype)
+        if self._type.getElemTypeSize() < 8:
+            raise ConstError(f"Unsupported storage type of size '{self._type.getElemTypeSize()}' bits.")
+        vals = self._raw[:self._type.getNumElements() * _np_dtype(self._type.dtype).itemsize].view(
+            _np_dtype(self._type.dtype))
+        return vals.astype(dt) if dt != vals.dtype else vals
+
+
+# --------------------------------------------------------------------------- backend (CUDA library)
+class CudaBackend:
+    """Calls libb200const.so; one b200c_ctx per backend object."""
+
+    name = "b200"
+
+    def __init__(self, device=0):
+        self.lib = A.load()
+        h = C.c_void_p()
+        raise_for(self.lib.b200c_create(device, C.byref(h)), self.lib.b200c_last_error())
+        self.ctx = h
+        self.device = device
+
+    def close(self):
+        if self.ctx:
+            self.lib.b200c_destroy(self.ctx)
+            self.ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _err(self):
+        return self.lib.b200c_last_error()
+
+    # host-only entry points
+    def infer_type(self, base_type, transforms):
+        keep = []
+        out = out_type_slot(max_q_of(base_type, transforms), keep)
+        bt = base_type.to_c(keep)
+        ch = chain_to_c(transforms, keep)
+        raise_for(self.lib.b200c_infer_type(C.byref(bt), ch, len(transforms), C.byref(out)), self._err())
+        return NDType.from_c(out)
+
+    def insert_position(self, kinds, new_kind):
+        arr = (C.c_int32 * max(1, len(kinds)))(*kinds)
+        pos = C.c_int()
+        raise_for(self.lib.b200c_insert_position(arr, len(kinds), new_kind, C.byref(pos)), self._err())
+        return pos.value
+
+    # compute entry points
+    def fold(self, base_type, data, is_splat, transforms):
+        keep = []
+        bt = base_type.to_c(keep)
+        ch = chain_to_c(transforms, keep)
+        final = self.infer_type(base_type, transforms)
+        # the folded Content can be larger than the attribute's type says only for Sparsify<false>
+        # (never: it is smaller); the inferred size is therefore a safe capacity.
+        cap = max(final.getTotalAllocSize(), 1)
+        out = np.zeros(cap, dtype=np.uint8)
+        ot = out_type_slot(max_q_of(base_type, transforms), keep)
+        nb = C.c_size_t()
+        buf = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        rc = self.lib.b200c_fold(self.ctx, C.byref(bt), buf.ctypes.data, buf.size, int(is_splat), 0, ch,
+                                 len(transforms), out.ctypes.data, cap, 0, C.byref(nb), C.byref(ot), 0)
+        raise_for(rc, self._err())
+        t = NDType.from_c(ot)
+        return Content(t, out[:max(t.getTotalAllocSize(), nb.value)], nb.value)
+
+    def count_nonsparse_per_oc(self, base_type, data, is_splat, transforms):
+        keep = []
+        bt = base_type.to_c(keep)
+        ch = chain_to_c(transforms, keep)
+        t = self.infer_type(base_type, [x for x in transforms])
+        oc = t.shape[0]
+        counts = (C.c_int64 * max(1, oc))()
+        buf = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        rc = self.lib.b200c_count_nonsparse_per_oc(self.ctx, C.byref(bt), buf.ctypes.data, buf.size, int(is_splat), 0,
+                                                   ch, len(transforms), counts, oc)
+        raise_for(rc, self._err())
+        return [counts[i] for i in range(oc)]
+
+    def btc_bound(self, n):
+        b = C.c_size_t()
+        raise_for(self.lib.b200c_btc_bound(n, C.byref(b)), self._err())
+        return b.value
+
+    def btc_compress(self, data):
+        """Returns (stream bytes, not_smaller flag)."""
+        buf = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        cap = self.btc_bound(buf.size)
+        out = np.zeros(cap, dtype=np.uint8)
+        n = C.c_size_t()
+        rc = self.lib.b200c_btc_compress(self.ctx, buf.ctypes.data, buf.size, 0, out.ctypes.data, cap, 0, C.byref(n))
+        raise_for(rc, self._err())
+        return out[:n.value], rc == A.NOT_SMALLER
+
+    def btc_decompress(self, stream, n_out):
+        buf = np.ascontiguousarray(stream).view(np.uint8).reshape(-1)
+        out = np.zeros(max(1, n_out), dtype=np.uint8)
+        n = C.c_size_t()
+        rc = self.lib.b200c_btc_decompress(self.ctx, buf.ctypes.data, buf.size, 0, out.ctypes.data, n_out, 0,
+                                           C.byref(n))
+        raise_for(rc, self._err())
+        return out[:n.value]
+
+    def launch_count(self):
+        return self.lib.b200c_launch_count(self.ctx)
+
+
+_default_backend = None
+
+
+def default_backend():
+    global _default_backend
+    if _default_backend is None:
+        _default_backend = CudaBackend(0)
+    return _default_backend
+
+
+# --------------------------------------------------------------------------- ContentAttr
+class ContentAttr:
+    """Const::ContentAttr: base content + ordered transformation list + inferred final type."""
+
+    def __init__(self, base, base_type, is_splat, transforms, backend):
+        self._base, self._baseType, self._isSplat = base, base_type, is_splat
+        self._transforms = list(transforms)
+        self._backend = backend
+
+    @staticmethod
+    def get(base, base_type=None, is_splat=None, backend=None):
+        """base: numpy array holding the dense (or single splat) element(s); base_type: NDType
+        (defaults to the array's shape and dtype)."""
+        arr = np.ascontiguousarray(base)
+        if base_type is None:
+            m = {np.dtype(np.float32): A.F32, np.dtype(np.float16): A.F16, np.dtype(np.float64): A.F64,
+                 np.dtype(np.int8): A.SI8, np.dtype(np.uint8): A.UI8, np.dtype(np.int16): A.SI16,
+                 np.dtype(np.uint16): A.UI16, np.dtype(np.int32): A.SI32, np.dtype(np.uint32): A.UI32,
+                 np.dtype(np.int64): A.SI64, np.dtype(np.uint64): A.UI64}
+            base_type = NDType(arr.shape, m[arr.dtype])
+        if is_splat is None:
+            is_splat = (arr.size == 1 and base_type.getNumElements() != 1)
+        return ContentAttr(arr, base_type, bool(is_splat), [], backend or default_backend())
+
+    # -- accessors
+    def getBaseContent(self):
+        return self._base
+
+    def getTransformations(self):
+        return list(self._transforms)
+
+    def getType(self):
+        return self._backend.infer_type(self._baseType, self._transforms)
+
+    def withBackend(self, backend):
+        return ContentAttr(self._base, self._baseType, self._isSplat, self._transforms, backend)
+
+    # -- ContentAttr::addTransformation (content.cpp:305-331)
+    def addTransformation(self, t):
+        kinds = [x.kind for x in self._transforms]
+        pos = self._backend.insert_position(kinds, t.kind)
+        ts = list(self._transforms)
+        ts.insert(pos, t)
+        out = ContentAttr(self._base, self._baseType, self._isSplat, ts, self._backend)
+        out.getType()  # inferFinalType runs when the attribute is built; errors surface here
+        return out
+
+    # -- builder methods (attributes.td:72-107)
+    def convertElemType(self, elem):
+        return self.addTransformation(Transform(A.X_CONVERT_ELEM_TYPE, elem=elem))
+
+    def quantCast(self, quant=None):
+        return self.addTransformation(Transform(A.X_QUANT_CAST, elem=quant))
+
+    def dequantize(self):
+        return self.addTransformation(Transform(A.X_DEQUANTIZE))
+
+    def rescale(self, scale):
+        return self.addTransformation(Transform(A.X_RESCALE, f=scale))
+
+    def add(self, bias):
+        return self.addTransformation(Transform(A.X_ADD, f=bias))
+
+    def reorder(self, order):
+        return self.addTransformation(Transform(A.X_REORDER, a=tuple(order)))
+
+    def transpose(self, order):
+        return self.addTransformation(Transform(A.X_TRANSPOSE, a=tuple(order)))
+
+    def reshape(self, shape):
+        return self.addTransformation(Transform(A.X_RESHAPE, b=tuple(shape)))
+
+    def changeShapeAndElemType(self, shape, elem):
+        return self.addTransformation(Transform(A.X_CHANGE_SHAPE_AND_ELEM_TYPE, b=tuple(shape), elem=elem))
+
+    def subview(self, offset, shape):
+        return self.addTransformation(Transform(A.X_SUBVIEW, a=tuple(offset), b=tuple(shape)))
+
+    def padWithZero(self, padBefore, padAfter):
+        return self.addTransformation(Transform(A.X_PAD_WITH_ZERO, a=tuple(padBefore), b=tuple(padAfter)))
+
+    def broadcast(self, axis, value):
+        return self.addTransformation(Transform(A.X_BROADCAST, i0=axis, i1=value))
+
+    def reverse(self, axis):
+        return self.addTransformation(Transform(A.X_REVERSE, i0=axis))
+
+    def bitPack(self, width):
+        return self.addTransformation(Transform(A.X_BIT_PACK, i0=width))
+
+    def getSparsityMap(self):
+        return self.addTransformation(Transform(A.X_GET_SPARSITY_MAP))
+
+    def sparsify(self, compressOutputType, numActualElements=None):
+        return self.addTransformation(Transform(A.X_SPARSIFY, i0=int(bool(compressOutputType)), aux=numActualElements))
+
+    def swizzleConstant(self, swizzleKey, arch=3):
+        return self.addTransformation(Transform(A.X_SWIZZLE_CONSTANT, i0=swizzleKey, i1=arch))
+
+    def quantizeSynth(self, scheme):
+        """Synthetic per-output-channel quantiser (no reference counterpart); the per-channel
+        scales / zero points land in the returned attribute's `.sideScales` / `.sideZeroPoints`."""
+        oc = self.getType().shape[0]
+        s0 = np.zeros(oc, dtype=np.float32)
+        s1 = np.zeros(oc, dtype=np.int32)
+        out = self.addTransformation(Transform(A.X_QUANTIZE_SYNTH, i0=scheme, side0=s0, side1=s1))
+        return out
+
+    @property
+    def sideScales(self):
+        for t in self._transforms:
+            if t.kind == A.X_QUANTIZE_SYNTH:
+                return t.side0
+        return None
+
+    @property
+    def sideZeroPoints(self):
+        for t in self._transforms:
+            if t.kind == A.X_QUANTIZE_SYNTH:
+                return t.side1
+        return None
+
+    # -- ContentAttr::fold (content.cpp:167-193) + copyTo
+    def fold(self):
+        return self._backend.fold(self._baseType, self._base, self._isSplat, self._transforms)
+
+    def countNonSparseElementsPerOC(self):
+        return self._backend.count_nonsparse_per_oc(self._baseType, self._base, self._isSplat, self._transforms)
+
+
+class DeclareOp:
+    """Const::DeclareOp (src/vpux_compiler/src/dialect/const/ops.cpp:88-91): holds a ContentAttr;
+    getContent() folds it."""
+
+    def __init__(self, contentAttr):
+        self._attr = contentAttr
+
+    def getContentAttr(self):
+        return self._attr
+
+    def getType(self):
+        return self._attr.getType()
+
+    def getContent(self):
+        return self._attr.fold()

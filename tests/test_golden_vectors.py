@@ -1,0 +1,398 @@
+"""Known-answer tests taken from the reference's own unit and lit tests for the Const dialect.
+
+Each case cites the reference test it restates (paths inside openvinotoolkit/npu_plugin):
+  UT  = tests/unit/vpux_compiler/dialect/const/content_tests.cpp
+  LIT = tests/lit/NPU/dialect/const/passes/
+They run against the CPU oracle everywhere (this pins the oracle) and, on the GPU box, against the
+CUDA library through the C ABI.
+"""
+import numpy as np
+import pytest
+
+from npu_plugin_b200 import _cabi as A
+from npu_plugin_b200.const import (ConstError, ContentAttr, DimsOrder, NDType, UniformQuantizedPerAxisType,
+                                   UniformQuantizedType)
+
+
+def attr(backend, vals, shape, dtype, np_dtype=None, splat=False):
+    arr = np.asarray(vals, dtype=np_dtype)
+    return ContentAttr.get(arr, NDType(shape, dtype), is_splat=splat, backend=backend)
+
+
+def iota(n, np_dtype):
+    return np.arange(n).astype(np_dtype)
+
+
+# UT:98-121 FromDenseElementsAttr / :356-378 CopyTo style: no transformation
+def test_from_dense_and_copy_to(backend):
+    vals = iota(24, np.float32)
+    c = attr(backend, vals, (1, 2, 3, 4), A.F32).fold()
+    assert c.getType() == NDType((1, 2, 3, 4), A.F32)
+    assert np.array_equal(c.getValues(), vals)
+    assert c.copyTo().tobytes() == vals.tobytes()
+
+
+# UT:419-446 CopyTo_I4: first element lands in the high nibble
+def test_copy_to_i4(backend):
+    c = attr(backend, [1, 7, 10, 15], (4,), A.I8, np.uint8).convertElemType(A.I4).fold()
+    assert c.getType().getTotalAllocSize() == 2
+    assert list(c.copyTo()) == [0x17, 0xAF]
+
+
+# UT:448-477 CopyTo_I1: first element lands in the most significant bit
+def test_copy_to_i1(backend):
+    vals = [0, 0, 0, 1, 0, 0, 1, 1, 1, 1, 1, 1, 1, 1, 1, 0]
+    c = attr(backend, vals, (16,), A.I8, np.uint8).convertElemType(A.I1).fold()
+    assert list(c.copyTo()) == [0x13, 0xFE]
+
+
+# UT:479-503, :505-527 Splat_CopyTo_FP32 / U8
+def test_splat_copy_to(backend):
+    c = attr(backend, [1.0], (8,), A.F32, np.float32, splat=True).fold()
+    assert np.array_equal(c.copyTo().view(np.float32), np.ones(8, np.float32))
+    c = attr(backend, [1], (8,), A.I8, np.uint8, splat=True).fold()
+    assert list(c.copyTo()) == [1] * 8
+
+
+# UT:529-553 Splat_CopyTo_I4 and :555-579 Splat_CopyTo_I1
+def test_splat_copy_to_subbyte(backend):
+    c = attr(backend, [10], (4,), A.I8, np.uint8, splat=True).convertElemType(A.I4).fold()
+    assert list(c.copyTo()) == [0xAA, 0xAA]
+    c = attr(backend, [1], (16,), A.I8, np.uint8, splat=True).convertElemType(A.I1).fold()
+    assert list(c.copyTo()) == [0xFF, 0xFF]
+
+
+# UT:581-606 ConvertElemType f32 -> si32, :608-635 splat
+def test_convert_elem_type(backend):
+    vals = iota(24, np.float32)
+    c = attr(backend, vals, (1, 2, 3, 4), A.F32).convertElemType(A.SI32).fold()
+    assert c.getType() == NDType((1, 2, 3, 4), A.SI32)
+    assert np.array_equal(c.getValues(np.int32), np.arange(24, dtype=np.int32))
+    c = attr(backend, [4.0], (1, 2, 3, 4), A.F32, np.float32, splat=True).convertElemType(A.SI32).fold()
+    assert np.array_equal(c.getValues(np.int32), np.full(24, 4, np.int32))
+
+
+# UT:663-693 Add, and Rescale (CA/rescale.cpp:64-78)
+def test_add_and_rescale(backend):
+    vals = iota(24, np.float32)
+    c = attr(backend, vals, (1, 2, 3, 4), A.F32).add(10).fold()
+    assert np.array_equal(c.getValues(), vals + np.float32(10))
+    c = attr(backend, vals, (1, 2, 3, 4), A.F32).rescale(0.1).fold()
+    assert np.array_equal(c.getValues(), vals * np.float32(0.1))
+
+
+# UT:695-724 QuantCast leaves the values alone
+def test_quant_cast(backend):
+    vals = iota(16, np.uint8)
+    q = UniformQuantizedType(A.UI8, A.F32, 0.078431372549019607, 128, 0, 255)
+    c = attr(backend, vals, (1, 16), A.UI8).quantCast(q).fold()
+    assert c.getType().quant == q
+    assert np.array_equal(c.copyTo(), vals)
+
+
+# UT:726-764 Dequantize, scale 2/254
+def test_dequantize(backend):
+    vals = np.array([((i % 3) - 1) * 127 for i in range(16)], dtype=np.int8)
+    q = UniformQuantizedType(A.SI8, A.F32, 2.0 / 254.0, 0, -127, 127)
+    c = attr(backend, vals, (1, 16), A.SI8).quantCast(q).dequantize().fold()
+    assert c.getType() == NDType((1, 16), A.F32)
+    exp = np.array([float((i % 3) - 1) for i in range(16)], dtype=np.float32)
+    np.testing.assert_allclose(c.getValues(), exp, rtol=4 * np.finfo(np.float32).eps)  # EXPECT_FLOAT_EQ = 4 ulp
+    # the exact reference arithmetic: float((q - zp) * double scale)
+    exact = ((vals.astype(np.int64) - 0).astype(np.float64) * (2.0 / 254.0)).astype(np.float32)
+    assert np.array_equal(c.getValues(), exact)
+
+
+# UT:766-797 Reshape is metadata only
+def test_reshape(backend):
+    vals = iota(18, np.float32)
+    c = attr(backend, vals, (1, 9, 2), A.F32).reshape((1, 3, 3, 2)).fold()
+    assert c.getType().shape == (1, 3, 3, 2)
+    assert np.array_equal(c.getValues(), vals)
+
+
+# UT:868-903 Reorder NCHW -> NHWC, :905-942 ReorderAfterReshape
+@pytest.mark.parametrize("reshape_first", [False, True])
+def test_reorder(backend, reshape_first):
+    N, Cc, H, W = 1, 2, 2, 2
+    vals = iota(N * Cc * H * W, np.float32)
+    if reshape_first:
+        a = attr(backend, vals, (N, Cc * H * W), A.F32).reshape((N, Cc, H, W))
+    else:
+        a = attr(backend, vals, (N, Cc, H, W), A.F32)
+    c = a.reorder(DimsOrder.NHWC).fold()
+    assert c.getType().order == DimsOrder.NHWC and c.getType().shape == (N, Cc, H, W)
+    out = c.getValues()
+    for n in range(N):
+        for ch in range(Cc):
+            for h in range(H):
+                for w in range(W):
+                    assert out[ch + w * Cc + h * Cc * W + n * Cc * W * H] == vals[w + h * W + ch * W * H + n * W * H * Cc]
+
+
+def check_padded(out, exp, buf, pad, zp, act_off=0, orig_off=0):
+    """checkPaddedBuffer, UT:55-80"""
+    IC, IH, IW = buf
+    PC, PH, PW = pad
+    for c in range(IC + 2 * PC):
+        for h in range(IH + 2 * PH):
+            for w in range(IW + 2 * PW):
+                ni = w + h * (IW + 2 * PW) + c * (IW + 2 * PW) * (IH + 2 * PH) + act_off
+                if c < PC or c >= IC + PC or h < PH or h >= IH + PH or w < PW or w >= IW + PW:
+                    assert out[ni] == zp, (c, h, w)
+                else:
+                    oi = (w - PW) + (h - PH) * IW + (c - PC) * IW * IH + orig_off
+                    assert out[ni] == exp[oi], (c, h, w)
+
+
+# UT:944-972 Pad, :974-1000 PadSplat
+def test_pad(backend):
+    vals = iota(6, np.int32)
+    c = attr(backend, vals, (1, 2, 3), A.SI32).padWithZero((1, 1, 1), (1, 1, 1)).fold()
+    assert c.getType().shape == (3, 4, 5)
+    check_padded(c.getValues(np.int32), vals, (1, 2, 3), (1, 1, 1), 0)
+    c = attr(backend, [42], (1, 2, 3), A.SI32, np.int32, splat=True).padWithZero((1, 1, 1), (1, 1, 1)).fold()
+    check_padded(c.getValues(np.int32), np.full(6, 42, np.int32), (1, 2, 3), (1, 1, 1), 0)
+
+
+# UT:1002-1045 PadUniformQuant: the pad value is the zero point (128); storage stays f32, copy-out gives u8
+def test_pad_uniform_quant(backend):
+    OC, IC, IH, IW = 2, 1, 2, 3
+    vals = iota(OC * IC * IH * IW, np.float32)
+    q = UniformQuantizedType(A.UI8, A.F32, 0.078431372549019607, 128, 0, 255)
+    a = attr(backend, vals, (OC, IC, IH, IW), A.F32).convertElemType(A.UI8).quantCast(q)
+    c = a.padWithZero((0, 2, 2, 2), (0, 2, 2, 2)).fold()
+    out = c.copyTo()  # ui8 bytes
+    for oc in range(OC):
+        check_padded(out, vals, (IC, IH, IW), (2, 2, 2), 128, oc * (IC + 4) * (IW + 4) * (IH + 4), oc * IC * IW * IH)
+
+
+# UT:1047-1106 PadPerAxisQuant: padded channels take the edge scales/zero points
+def test_pad_per_axis_quant(backend):
+    OC, IC, IH, IW = 2, 1, 2, 3
+    vals = iota(OC * IC * IH * IW, np.float32)
+    zp = 127
+    q = UniformQuantizedPerAxisType(A.UI8, A.F32, [0.5, 0.5], [zp, zp], 0, 0, 255)
+    a = attr(backend, vals, (OC, IC, IH, IW), A.F32).convertElemType(A.UI8).quantCast(q)
+    a = a.padWithZero((2, 2, 2, 2), (2, 2, 2, 2))
+    t = a.getType()
+    assert t.shape == (6, 5, 6, 7) and t.quant.zps == [zp] * 6 and t.quant.scales == [0.5] * 6
+    out = a.fold().copyTo()
+    ch = IC * IW * IH
+    exp = np.concatenate([np.full(ch * 2, zp, np.float32), vals, np.full(ch * 2, zp, np.float32)])
+    for oc in range(OC + 4):
+        check_padded(out, exp, (IC, IH, IW), (2, 2, 2), zp, oc * (IC + 4) * (IW + 4) * (IH + 4), oc * ch)
+
+
+# UT:1108-1149 SubView, :1203-1231 SubViewSplat
+def test_subview(backend):
+    vals = iota(6, np.int32)
+    c = attr(backend, vals, (1, 2, 3), A.SI32).subview((0, 1, 1), (1, 1, 1)).fold()
+    assert c.getType().shape == (1, 1, 1)
+    assert c.getValues(np.int32)[0] == vals[1 + 1 * 3]
+    c = attr(backend, vals, (1, 2, 3), A.SI32).subview((0, 0, 1), (1, 2, 2)).fold()
+    assert list(c.getValues(np.int32)) == [1, 2, 4, 5]
+    c = attr(backend, [42], (1, 2, 3), A.SI32, np.int32, splat=True).subview((0, 1, 1), (1, 1, 1)).fold()
+    assert c.getValues(np.int32)[0] == 42
+
+
+# UT:1151-1201 SubViewI1: packed bits, bit k of a byte is element k (LSB first)
+def test_subview_i1(backend):
+    IC, IH, IW = 1, 7, 5
+    bits = np.array([i % 2 for i in range(IC * IH * IW)], dtype=np.uint8)
+    packed = np.packbits(bits, bitorder="little")
+    a = ContentAttr.get(packed, NDType((IC, IH, IW), A.I1), is_splat=False, backend=backend)
+    for off, shp in [((0, 1, 1), (1, 1, 1)), ((0, 2, 1), (1, 3, 4))]:
+        c = a.subview(off, shp).fold()
+        raw = c.copyTo()
+        ref = bits.reshape(IC, IH, IW)[off[0]:off[0] + shp[0], off[1]:off[1] + shp[1], off[2]:off[2] + shp[2]]
+        got = np.unpackbits(raw, bitorder="little")[:ref.size]
+        assert np.array_equal(got, ref.reshape(-1))
+
+
+# UT:1233-1262 BitPack: low nibble first
+def test_bit_pack(backend):
+    a = attr(backend, [1, 2, 3, 4, 5, 6], (1, 2, 3), A.SI8, np.int8).bitPack(4)
+    assert a.getType() == NDType((1, 2, 3), A.SI4)
+    assert list(a.fold().copyTo()) == [0x21, 0x43, 0x65]
+
+
+# UT:1264-1306 BitPackQuant
+def test_bit_pack_quant(backend):
+    q = UniformQuantizedType(A.SI8, A.F32, 1.0, 0, -4, 3)
+    a = attr(backend, [1, 2, 3, 1, 2, 3], (1, 2, 3), A.SI8, np.int8).quantCast(q).bitPack(4)
+    assert a.getType().quant == UniformQuantizedType(A.SI4, A.F32, 1.0, 0, -4, 3)
+    assert list(a.fold().copyTo()) == [0x21, 0x13, 0x32]
+
+
+# UT:1308-1340 Transpose 512x40
+def test_transpose(backend):
+    N, Cc = 512, 40
+    vals = iota(N * Cc, np.float32)
+    c = attr(backend, vals, (N, Cc), A.F32).transpose((1, 0)).fold()
+    assert c.getType().shape == (Cc, N)
+    assert np.array_equal(c.getValues().reshape(Cc, N), vals.reshape(N, Cc).T)
+
+
+# UT:1342-1393 BitPackIsLast: ordering and the errors of late insertions
+def test_bit_pack_is_last(backend):
+    a = attr(backend, [1, 2, 3, 4, 5, 6], (1, 1, 2, 3), A.SI8, np.int8).bitPack(4)
+    names = [t.getTransformationName() for t in a.add(17.0).getTransformations()]
+    assert names == ["Add", "BitPack"]
+    names = [t.getTransformationName() for t in a.add(17.0).broadcast(1, 42).getTransformations()]
+    assert names == ["Add", "Broadcast", "BitPack"]
+    with pytest.raises(ConstError):
+        a.dequantize()
+    a.convertElemType(A.SI32)
+    a.padWithZero((0, 1, 2, 3), (0, 3, 2, 1))
+    a.reorder(DimsOrder.NHWC)
+    a.rescale(19.0)
+    a.reshape((1, 2, 3))
+    a.subview((0, 0, 0, 0), (1, 1, 2, 3))
+    a.transpose(DimsOrder.NHWC)
+    with pytest.raises(ConstError):
+        a.swizzleConstant(5, 3)
+    assert a.quantCast(UniformQuantizedType(A.SI8, A.F32, 0.078431372549019607, 0, -4, 3)) is not None
+
+
+# UT:1446-1481 GetSparsityMap, :1483-1527 quantised (zero point 7)
+def test_get_sparsity_map(backend):
+    vals = [0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 0, 11, 0, 13, 14, 15]
+    a = attr(backend, vals, (1, 1, 2, 8), A.UI8, np.uint8).getSparsityMap()
+    assert a.getType() == NDType((1, 1, 1, 128), A.I1)
+    raw = a.fold().copyTo()
+    assert len(raw) == 16 and list(raw[:2]) == [0xFE, 0xEB] and not raw[2:].any()
+    vals = [7, 0, 1, 2, 3, 4, 5, 6, 7, 8, 7, 10, 7, 12, 13, 14]
+    q = UniformQuantizedType(A.UI8, A.F32, 1.0, 7, 0, 14)
+    raw = attr(backend, vals, (1, 1, 2, 8), A.UI8, np.uint8).quantCast(q).getSparsityMap().fold().copyTo()
+    assert list(raw[:2]) == [0xFE, 0xEA] and not raw[2:].any()
+
+
+SPARSE_IN = [0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 0, 11, 0, 13, 14, 15,
+             16, 0, 18, 19, 20, 0, 22, 23, 24, 25, 26, 0, 0, 29, 30, 31]
+SPARSE_OUT = [1, 2, 3, 4, 5, 6, 7, 8, 9, 11, 13, 14, 15, 0, 0, 0,
+              16, 18, 19, 20, 22, 23, 24, 25, 26, 29, 30, 31, 0, 0, 0, 0]
+
+
+# UT:1529-1553 Sparsify
+def test_sparsify(backend):
+    a = attr(backend, SPARSE_IN, (2, 1, 2, 8), A.UI8, np.uint8).sparsify(False)
+    assert a.getType() == NDType((2, 1, 2, 8), A.UI8)  # attribute type is unchanged for compressOutputType=false
+    c = a.fold()
+    assert c.getType() == NDType((32, 1, 1, 1), A.UI8)  # the folded content is flat u8
+    assert list(c.copyTo()[:32]) == SPARSE_OUT
+    b = attr(backend, SPARSE_IN, (2, 1, 2, 8), A.UI8, np.uint8)
+    assert b.countNonSparseElementsPerOC() == [13, 12]
+    c2 = b.sparsify(True, [13, 12]).fold()
+    assert c2.getType() == NDType((32, 1, 1, 1), A.UI8) and list(c2.copyTo()) == SPARSE_OUT
+
+
+# UT:1555-1603 SparsifyQuantized (zero point 16)
+def test_sparsify_quantized(backend):
+    vals = [16, 1, 2, 3, 4, 5, 6, 7, 8, 9, 16, 11, 16, 13, 14, 15,
+            16, 16, 18, 19, 20, 16, 22, 23, 24, 25, 26, 16, 16, 29, 30, 31]
+    exp = [1, 2, 3, 4, 5, 6, 7, 8, 9, 11, 13, 14, 15, 0, 0, 0,
+           18, 19, 20, 22, 23, 24, 25, 26, 29, 30, 31, 0, 0, 0, 0, 0]
+    q = UniformQuantizedType(A.UI8, A.F32, 1.0, 16, 0, 31)
+    c = attr(backend, vals, (2, 1, 2, 8), A.UI8, np.uint8).quantCast(q).sparsify(False).fold()
+    assert list(c.copyTo()[:32]) == exp
+
+
+# UT:1605-1637 PositionRequirement
+def test_position_requirement(backend):
+    a = attr(backend, iota(9, np.float32), (1, 1, 3, 3), A.F32).rescale(10.0)
+    a = a.swizzleConstant(5, 3).sparsify(False).convertElemType(A.F16)
+    names = [t.getTransformationName() for t in a.getTransformations()]
+    assert names == ["Rescale", "ConvertElemType", "Sparsify", "SwizzleConstant"]
+
+
+# LIT constant_folding.mlir:212-222 ConstFoldI4: f16 {1,0,1,2} -> si4 -> bytes [16, 18]
+def test_lit_const_fold_i4(backend):
+    q = UniformQuantizedType(A.SI4, A.F16, 0.0039215686274509803, 0)
+    a = attr(backend, [1.0, 0.0, 1.0, 2.0], (1, 4, 1, 1), A.F16, np.float16)
+    a = a.convertElemType(A.SI4).quantCast(q).reorder(DimsOrder.YXOI)
+    c = a.fold()
+    assert c.getType().getTotalAllocSize() == 2
+    assert list(c.copyTo()) == [16, 18]
+
+
+# LIT constant_folding.mlir:12-30 ConstFold chain on a splat: -1.0 -> f16 -> ui8 must fail the range check
+# of the lazy conversion only when values are read; with 129 (QuantConstFold, :34-52) it folds.
+def test_lit_quant_const_fold(backend):
+    q = UniformQuantizedType(A.UI8, A.F16, 0.0039215686274509803, 0)
+    a = attr(backend, [129], (16, 3, 1, 1), A.UI8, np.uint8, splat=True).quantCast(q).reorder(DimsOrder.YXOI)
+    c = a.fold()
+    assert c.getType().order == DimsOrder.YXOI
+    assert list(c.copyTo()) == [129] * 48
+    d = a.dequantize().fold()  # inserted before nothing LAST: Dequantize goes at the end
+    # expressed type is f16: f32 storage (one rounding) then f16 at copy-out (second rounding)
+    exp = np.float16(np.float32(np.float64(129) * 0.0039215686274509803))
+    assert d.getType().dtype == A.F16
+    assert np.array_equal(d.getValues(), np.full(48, exp, np.float16))
+
+
+# LIT constant_folding_37XX.mlir:13-35: splat-true i1 100x1x1x384 swizzled -> 40960 bits, all 0xFF
+def test_lit_swizzle_subbyte_splat(backend):
+    a = ContentAttr.get(np.array([1], np.uint8), NDType((100, 1, 1, 384), A.I1), is_splat=True, backend=backend)
+    a = a.swizzleConstant(5, 3)
+    assert a.getType() == NDType((40960, 1, 1, 1), A.I1)
+    raw = a.fold().copyTo()
+    assert len(raw) == 5120 and (raw == 0xFF).all()
+
+
+# LIT constant_folding_37XX.mlir:46-62: long chain then swizzle; first bytes 0x01 00 00 ...
+def test_lit_swizzle_after_chain(backend):
+    q = UniformQuantizedType(A.UI8, A.F16, 1.0, 0, 0, 254)
+    a = attr(backend, [1.0], (32, 1, 1, 1), A.F16, np.float16, splat=True)
+    a = a.convertElemType(A.UI8).quantCast(q).reorder(DimsOrder.NHWC).reorder(DimsOrder.NCHW)
+    a = a.reshape((32, 1, 1, 1)).padWithZero((0, 0, 0, 0), (0, 15, 0, 0)).reorder(DimsOrder.NHWC)
+    a = a.subview((0, 0, 0, 0), (16, 16, 1, 1)).swizzleConstant(5, 3)
+    assert a.getType().shape == (512, 1, 1, 1) and a.getType().dtype == A.UI8
+    raw = a.fold().copyTo()
+    # before swizzling: 16 rows of [1, 0 x15]; 256 bytes -> padded to 512; block 0 has stagger 0
+    exp = np.zeros(512, np.uint8)
+    exp[0:256:16] = 1
+    assert np.array_equal(raw, exp)
+
+
+# LIT constant_folding_37XX.mlir:66-75: 3 bytes -> reshape/broadcast -> 768 bytes after swizzle alignment
+def test_lit_swizzle_shape_mismatch(backend):
+    a = attr(backend, [1, 2, 3], (1, 1, 3, 1), A.UI8, np.uint8).swizzleConstant(5, 3)
+    assert a.getType() == NDType((512, 1, 1, 1), A.UI8)
+    raw = a.fold().copyTo()
+    assert list(raw[:3]) == [1, 2, 3] and not raw[3:].any()
+
+
+# tests/unit/vpux_compiler/utils/swizzling_test.cpp:35-100: deswizzle(swizzle(x)) == x for keys 0..5,
+# aligned and unaligned sizes; swizzled != x once the buffer exceeds the pattern stride (512 B) and key > 0.
+@pytest.mark.parametrize("key", [0, 1, 2, 3, 4, 5])
+@pytest.mark.parametrize("size", [512, 1024, 4096, 16384, 50176, 1000, 5000])
+def test_swizzle_roundtrip(backend, oracle, key, size):
+    rng = np.random.default_rng(key * 100 + size)
+    x = rng.integers(0, 256, size, dtype=np.uint8)
+    a = ContentAttr.get(x, NDType((size, 1, 1, 1), A.UI8), backend=backend).swizzleConstant(key, 3)
+    raw = a.fold().copyTo()
+    padded = np.zeros((size + 511) // 512 * 512, np.uint8)
+    padded[:size] = x
+    assert len(raw) == len(padded)
+    assert np.array_equal(oracle.deswizzle(raw, key), padded)
+    if key > 0 and len(padded) > 512:
+        assert not np.array_equal(raw, padded)
+    if key == 0:
+        assert np.array_equal(raw, padded)
+
+
+# The swizzle address rule itself, independent of both implementations
+# (swizzle_transform.hpp:58-80 + CA/swizzle_transform.cpp:41-79): chunk at address a moves to
+# (a & ~511) + ((a + ((a>>9 & mask) << (9-key))) & 511).
+@pytest.mark.parametrize("key", [1, 3, 5])
+def test_swizzle_address_rule(backend, key):
+    size = 8192
+    x = np.arange(size, dtype=np.uint32).astype(np.uint8) ^ (np.arange(size) >> 8).astype(np.uint8)
+    raw = ContentAttr.get(x, NDType((size, 1, 1, 1), A.UI8), backend=backend).swizzleConstant(key, 3).fold().copyTo()
+    exp = np.zeros(size, np.uint8)
+    for a in range(0, size, 16):
+        stagger = ((a >> 9) & 63 & ((1 << key) - 1)) << (9 - key)
+        dst = (a & ~511) + ((a + stagger) & 511)
+        exp[dst:dst + 16] = x[a:a + 16]
+    assert np.array_equal(raw, exp)
