@@ -21,6 +21,12 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#if defined(__GNUC__)
+#define B200C_API __attribute__((visibility("default")))
+#else
+#define B200C_API
+#endif
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -160,18 +166,18 @@ typedef struct b200c_xform {
  * src/vpux_compiler/src/dialect/const/utils/constant_folding_in_background.cpp:57-100);
  * calls on one context are serialised by an internal mutex.                   */
 typedef struct b200c_ctx b200c_ctx;
-int b200c_create(int device, b200c_ctx** out);
-void b200c_destroy(b200c_ctx* ctx);
+B200C_API int b200c_create(int device, b200c_ctx** out);
+B200C_API void b200c_destroy(b200c_ctx* ctx);
 /* Use `stream` (a cudaStream_t) for all later work of this context; NULL
  * restores the context's own stream.                                          */
-int b200c_set_stream(b200c_ctx* ctx, void* stream);
-void* b200c_get_stream(b200c_ctx* ctx);
-int b200c_synchronize(b200c_ctx* ctx);
+B200C_API int b200c_set_stream(b200c_ctx* ctx, void* stream);
+B200C_API void* b200c_get_stream(b200c_ctx* ctx);
+B200C_API int b200c_synchronize(b200c_ctx* ctx);
 /* Number of kernels of this library launched through the context so far.     */
-int64_t b200c_launch_count(b200c_ctx* ctx);
+B200C_API int64_t b200c_launch_count(b200c_ctx* ctx);
 /* Thread-local message of the last failing call on this thread.              */
-const char* b200c_last_error(void);
-const char* b200c_version(void);
+B200C_API const char* b200c_last_error(void);
+B200C_API const char* b200c_version(void);
 
 /* ---- type inference -----------------------------------------------------------
  * Const::ContentAttr::inferFinalType
@@ -179,17 +185,17 @@ const char* b200c_version(void);
  * attribute's inferOutputType.  `out->scales` / `out->zps` must point to
  * caller storage of `out->nq` entries on entry when the result can be
  * per-axis quantised; on return nq is the count written.  Pure host code.     */
-int b200c_infer_type(const b200c_type* in, const b200c_xform* chain, int n, b200c_type* out);
+B200C_API int b200c_infer_type(const b200c_type* in, const b200c_xform* chain, int n, b200c_type* out);
 
 /* Index at which ContentAttr::addTransformation inserts a new transformation
  * (getInsertionPosition, content.cpp:268-299): NONE before PREFERRED_LAST before
  * LAST; a second LAST is an error.  `kinds` are the b200c_xform_kind values of
  * the existing list.                                                          */
-int b200c_insert_position(const int32_t* kinds, int n, int32_t new_kind, int* pos);
+B200C_API int b200c_insert_position(const int32_t* kinds, int n, int32_t new_kind, int* pos);
 
 /* Byte size of a tensor of this type: NDTypeInterface::getTotalAllocSize
  * (src/vpux_compiler/src/core/type_interfaces.cpp:148-162).                   */
-int64_t b200c_total_alloc_size(const b200c_type* t);
+B200C_API int64_t b200c_total_alloc_size(const b200c_type* t);
 
 /* ---- folding -------------------------------------------------------------------
  * Const::ContentAttr::fold() followed by Const::Content::copyTo()
@@ -211,14 +217,14 @@ int64_t b200c_total_alloc_size(const b200c_type* t);
  * `flags`, in which case data-dependent errors are reported by the next
  * synchronising call on the context.                                          */
 #define B200C_FOLD_ASYNC 1
-int b200c_fold(b200c_ctx* ctx, const b200c_type* base, const void* data, size_t nbytes, int is_splat,
+B200C_API int b200c_fold(b200c_ctx* ctx, const b200c_type* base, const void* data, size_t nbytes, int is_splat,
                int data_on_device, const b200c_xform* chain, int n, void* out, size_t out_cap, int out_on_device,
                size_t* out_bytes, b200c_type* out_type, int flags);
 
 /* Per-output-channel count of elements that differ from the sparsify value:
  * vpux::countNonSparseElementsPerOC (src/vpux_compiler/src/utils/sparsity.cpp:28-72)
  * applied to the folded content of (base, chain).  counts: host int64[shape[0]].  */
-int b200c_count_nonsparse_per_oc(b200c_ctx* ctx, const b200c_type* base, const void* data, size_t nbytes,
+B200C_API int b200c_count_nonsparse_per_oc(b200c_ctx* ctx, const b200c_type* base, const void* data, size_t nbytes,
                                  int is_splat, int data_on_device, const b200c_xform* chain, int n,
                                  int64_t* counts, int64_t ncounts);
 
@@ -230,10 +236,10 @@ int b200c_count_nonsparse_per_oc(b200c_ctx* ctx, const b200c_type* base, const v
  * not BitCompactor's: the BitCompactor sources are not part of the reference
  * tree.  b200c_btc_compress returns B200C_NOT_SMALLER when the stream would not
  * be smaller than the input, as the reference's codec returns failure.        */
-int b200c_btc_bound(size_t n, size_t* bound);
-int b200c_btc_compress(b200c_ctx* ctx, const void* in, size_t n, int in_on_device, void* out, size_t cap,
+B200C_API int b200c_btc_bound(size_t n, size_t* bound);
+B200C_API int b200c_btc_compress(b200c_ctx* ctx, const void* in, size_t n, int in_on_device, void* out, size_t cap,
                        int out_on_device, size_t* out_n);
-int b200c_btc_decompress(b200c_ctx* ctx, const void* in, size_t n, int in_on_device, void* out, size_t cap,
+B200C_API int b200c_btc_decompress(b200c_ctx* ctx, const void* in, size_t n, int in_on_device, void* out, size_t cap,
                          int out_on_device, size_t* out_n);
 
 /* Batched form used for whole-model folding: `count` independent buffers that
@@ -241,7 +247,7 @@ int b200c_btc_decompress(b200c_ctx* ctx, const void* in, size_t n, int in_on_dev
  * device prefix sum and one emit launch.  sizes/offsets are host arrays;
  * out_sizes[i] receives the stream length of buffer i (B200C_NOT_SMALLER cases
  * are reported through not_smaller[i] = 1 and store the input unchanged).     */
-int b200c_btc_compress_batch(b200c_ctx* ctx, int count, const void* const* in_dev, const size_t* sizes,
+B200C_API int b200c_btc_compress_batch(b200c_ctx* ctx, int count, const void* const* in_dev, const size_t* sizes,
                              void* out_dev, size_t out_cap, size_t* out_offsets, size_t* out_sizes,
                              int32_t* not_smaller);
 
@@ -251,16 +257,16 @@ int b200c_btc_compress_batch(b200c_ctx* ctx, int count, const void* const* in_de
  * (p0 = sigma), 1 = uniform int8 in [-127,127] with Bernoulli(p0) zeros,
  * 2 = discretised Laplace(0, p0) clipped to [-127,127] with a fraction p1 of
  * exact zeros.  dtype: B200C_F32, B200C_F16 or B200C_SI8.                    */
-int b200c_synth_fill(b200c_ctx* ctx, void* dst_dev, int64_t count, int32_t dtype, int32_t dist, double p0,
+B200C_API int b200c_synth_fill(b200c_ctx* ctx, void* dst_dev, int64_t count, int32_t dtype, int32_t dist, double p0,
                      double p1, uint64_t seed, uint64_t stream_id);
 
 /* ---- device memory helpers (so that callers need no CUDA runtime of their own) */
-int b200c_dev_alloc(b200c_ctx* ctx, size_t n, void** out);
-int b200c_dev_free(b200c_ctx* ctx, void* p);
-int b200c_host_alloc_pinned(size_t n, void** out);
-int b200c_host_free_pinned(void* p);
-int b200c_memcpy_h2d(b200c_ctx* ctx, void* dst_dev, const void* src, size_t n);
-int b200c_memcpy_d2h(b200c_ctx* ctx, void* dst, const void* src_dev, size_t n);
+B200C_API int b200c_dev_alloc(b200c_ctx* ctx, size_t n, void** out);
+B200C_API int b200c_dev_free(b200c_ctx* ctx, void* p);
+B200C_API int b200c_host_alloc_pinned(size_t n, void** out);
+B200C_API int b200c_host_free_pinned(void* p);
+B200C_API int b200c_memcpy_h2d(b200c_ctx* ctx, void* dst_dev, const void* src, size_t n);
+B200C_API int b200c_memcpy_d2h(b200c_ctx* ctx, void* dst, const void* src_dev, size_t n);
 
 #ifdef __cplusplus
 }

@@ -130,7 +130,8 @@ SYMBOLS = {
     "b200c_memcpy_d2h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
 }
 
-LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc", "libb200const.so")
+LIB_PATH = os.environ.get("B200C_LIBRARY_PATH") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc",
+                                                                "libb200const.so")
 _lib = None
 
 

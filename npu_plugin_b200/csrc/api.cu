@@ -1,0 +1,560 @@
+// C ABI of the library (include/b200const.h): context management, memory helpers and the entry
+// points that drive the planner and the codec.  No exception crosses this file's boundary.
+#include "../../include/b200const.h"
+#include "plan.h"
+
+#include <cstdlib>
+#include <cstring>
+#include <memory>
+#include <string>
+
+namespace b200c {
+
+static thread_local std::string t_lastError;
+
+// ---------------------------------------------------------------------------- memory
+void* devMalloc(Context* ctx, size_t bytes) {
+    if (bytes == 0) bytes = 1;
+#ifdef B200C_HOST_EMULATION
+    if (B2_EMU(ctx)) {
+        void* p = std::malloc(bytes);
+        if (!p) throw NoMem("host allocation failed");
+        return p;
+    }
+#endif
+    (void)ctx;
+    void* p = nullptr;
+    const cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        throw NoMem(std::string("cudaMalloc of ") + std::to_string(bytes) + " bytes: " + cudaGetErrorString(e));
+    }
+    return p;
+}
+
+void devFree(Context* ctx, void* p) {
+    if (!p) return;
+#ifdef B200C_HOST_EMULATION
+    if (B2_EMU(ctx)) {
+        std::free(p);
+        return;
+    }
+#endif
+    (void)ctx;
+    cudaFree(p);
+}
+
+void copyH2D(Context* ctx, void* dst, const void* src, size_t n) {
+    if (n == 0) return;
+    if (B2_EMU(ctx)) {
+        std::memcpy(dst, src, n);
+        return;
+    }
+    B2_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, ctx->stream));
+}
+void copyD2H(Context* ctx, void* dst, const void* src, size_t n) {
+    if (n == 0) return;
+    if (B2_EMU(ctx)) {
+        std::memcpy(dst, src, n);
+        return;
+    }
+    B2_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToHost, ctx->stream));
+}
+void copyD2D(Context* ctx, void* dst, const void* src, size_t n) {
+    if (n == 0) return;
+    if (B2_EMU(ctx)) {
+        std::memmove(dst, src, n);
+        return;
+    }
+    B2_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToDevice, ctx->stream));
+}
+void fillBytes(Context* ctx, void* dst, int value, size_t n) {
+    if (n == 0) return;
+    if (B2_EMU(ctx)) {
+        std::memset(dst, value, n);
+        return;
+    }
+    B2_CUDA(cudaMemsetAsync(dst, value, n, ctx->stream));
+}
+void syncStream(Context* ctx) {
+    if (B2_EMU(ctx)) return;
+    B2_CUDA(cudaStreamSynchronize(ctx->stream));
+}
+
+static const char* errText(int code) {
+    switch (code) {
+    case E_CAST_RANGE:
+        return "Can not safely cast a value: it is outside the range of the target element type";
+    case E_CAST_INEXACT:
+        return "Can not safely cast a value: the conversion to the floating point type is not exact";
+    case E_OOB:
+        return "Out-of-bound access";
+    case E_SPARSE_OVERFLOW:
+        return "Sparsify: more non-sparse elements than numActualElements allows";
+    case E_CODEC:
+        return "codec: malformed stream or output capacity exceeded";
+    default:
+        return "unknown device-side error";
+    }
+}
+
+void checkDeviceError(Context* ctx) {
+    int code = E_NONE;
+    if (B2_EMU(ctx)) {
+        code = *ctx->errWord;
+        *ctx->errWord = E_NONE;
+    } else {
+        B2_CUDA(cudaMemcpyAsync(ctx->errHost, ctx->errWord, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+        B2_CUDA(cudaStreamSynchronize(ctx->stream));
+        code = *ctx->errHost;
+        if (code != E_NONE) {
+            B2_CUDA(cudaMemsetAsync(ctx->errWord, 0, sizeof(int), ctx->stream));
+        }
+    }
+    if (code != E_NONE) throw RefThrow(errText(code));
+}
+
+// ---------------------------------------------------------------------------- arena
+Arena::~Arena() {
+    releaseAll();
+}
+
+void Arena::releaseAll() {
+    for (auto& b : _blocks) devFree(_ctx, b.ptr);
+    _blocks.clear();
+}
+
+void* Arena::alloc(size_t bytes, size_t align) {
+    if (bytes == 0) bytes = 1;
+    for (auto& b : _blocks) {
+        const size_t at = (b.used + align - 1) / align * align;
+        if (at + bytes <= b.size) {
+            b.used = at + bytes;
+            return b.ptr + at;
+        }
+    }
+    const size_t minBlock = 64ull << 20;
+    const size_t size = std::max(minBlock, (bytes + align + 4095) / 4096 * 4096);
+    Block nb;
+    nb.ptr = static_cast<char*>(devMalloc(_ctx, size));
+    nb.size = size;
+    nb.used = bytes;
+    _blocks.push_back(nb);
+    return nb.ptr;
+}
+
+void Arena::reset() {
+    // keep the largest block only when fragmentation grew: several blocks are merged into one
+    if (_blocks.size() > 4) {
+        size_t total = 0;
+        for (auto& b : _blocks) total += b.size;
+        for (auto& b : _blocks) devFree(_ctx, b.ptr);
+        _blocks.clear();
+        Block nb;
+        nb.ptr = static_cast<char*>(devMalloc(_ctx, total));
+        nb.size = total;
+        nb.used = 0;
+        _blocks.push_back(nb);
+    }
+    for (auto& b : _blocks) b.used = 0;
+}
+
+size_t Arena::reserved() const {
+    size_t t = 0;
+    for (auto& b : _blocks) t += b.size;
+    return t;
+}
+
+// ---------------------------------------------------------------------------- error mapping
+template <class F>
+static int guarded(F&& body) {
+    try {
+        body();
+        return B200C_OK;
+    } catch (const RefThrow& e) {
+        t_lastError = e.what();
+        return B200C_ERR_THROW;
+    } catch (const NotBuilt& e) {
+        t_lastError = e.what();
+        return B200C_ERR_UNSUPPORTED;
+    } catch (const BadArg& e) {
+        t_lastError = e.what();
+        return B200C_ERR_INVALID;
+    } catch (const CudaFail& e) {
+        t_lastError = e.what();
+        return B200C_ERR_CUDA;
+    } catch (const NoMem& e) {
+        t_lastError = e.what();
+        return B200C_ERR_NOMEM;
+    } catch (const Capacity& e) {
+        t_lastError = e.what();
+        return B200C_ERR_CAPACITY;
+    } catch (const std::bad_alloc&) {
+        t_lastError = "host allocation failed";
+        return B200C_ERR_NOMEM;
+    } catch (const std::exception& e) {
+        t_lastError = e.what();
+        return B200C_ERR_INVALID;
+    }
+}
+
+static std::vector<Transformation> chainFromC(const b200c_xform* chain, int n) {
+    if (n < 0 || (n > 0 && chain == nullptr)) throw BadArg("bad transformation list");
+    std::vector<Transformation> xs;
+    xs.reserve(n);
+    for (int i = 0; i < n; ++i) xs.push_back(xformFromC(chain[i]));
+    return xs;
+}
+
+// After an asynchronous failure the arena and the error word must be left clean for the next call.
+struct CallScope {
+    Context* ctx;
+    std::unique_lock<std::mutex> lock;
+    explicit CallScope(Context* c): ctx(c), lock(c->mu) {
+        if (!B2_EMU(ctx)) {
+            const cudaError_t e = cudaSetDevice(ctx->device);
+            if (e != cudaSuccess) throw CudaFail(std::string("cudaSetDevice: ") + cudaGetErrorString(e));
+        }
+        ctx->arena.reset();
+    }
+};
+
+}  // namespace b200c
+
+using namespace b200c;
+
+extern "C" {
+
+const char* b200c_last_error(void) {
+    return t_lastError.c_str();
+}
+
+const char* b200c_version(void) {
+#ifdef B200C_HOST_EMULATION
+    return "b200const 0.1 (host-emulation debug build)";
+#else
+    return "b200const 0.1 (sm_100a)";
+#endif
+}
+
+int b200c_create(int device, b200c_ctx** out) {
+    return guarded([&] {
+        if (!out) throw BadArg("null output pointer");
+        auto ctx = std::make_unique<Context>();
+        ctx->device = device;
+#ifdef B200C_HOST_EMULATION
+        const char* emu = std::getenv("B200C_EMULATE");
+        ctx->emulated = emu && emu[0] == '1';
+#endif
+        if (B2_EMU(ctx)) {
+            ctx->errWord = static_cast<int*>(std::calloc(1, sizeof(int)));
+            ctx->errHost = ctx->errWord;
+        } else {
+            int count = 0;
+            cudaError_t e = cudaGetDeviceCount(&count);
+            if (e != cudaSuccess || count == 0) {
+                cudaGetLastError();
+                throw CudaFail(std::string("no usable CUDA device: ") + (e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0"));
+            }
+            if (device < 0 || device >= count) throw BadArg("device index out of range");
+            B2_CUDA(cudaSetDevice(device));
+            cudaDeviceProp prop;
+            B2_CUDA(cudaGetDeviceProperties(&prop, device));
+            ctx->smCount = prop.multiProcessorCount;
+            ctx->l2Bytes = static_cast<size_t>(prop.l2CacheSize);
+            B2_CUDA(cudaStreamCreateWithFlags(&ctx->ownStream, cudaStreamNonBlocking));
+            ctx->stream = ctx->ownStream;
+            B2_CUDA(cudaMalloc(&ctx->errWord, sizeof(int)));
+            B2_CUDA(cudaMemset(ctx->errWord, 0, sizeof(int)));
+            B2_CUDA(cudaMallocHost(&ctx->errHost, sizeof(int)));
+            *ctx->errHost = 0;
+        }
+        *out = reinterpret_cast<b200c_ctx*>(ctx.release());
+    });
+}
+
+void b200c_destroy(b200c_ctx* h) {
+    if (!h) return;
+    Context* ctx = reinterpret_cast<Context*>(h);
+    if (B2_EMU(ctx)) {
+        std::free(ctx->errWord);
+    } else {
+        cudaSetDevice(ctx->device);
+        cudaStreamSynchronize(ctx->stream);
+        if (ctx->errWord) cudaFree(ctx->errWord);
+        if (ctx->errHost) cudaFreeHost(ctx->errHost);
+    }
+    ctx->arena.releaseAll();  // frees the blocks while the device is still current
+    if (!B2_EMU(ctx) && ctx->ownStream) cudaStreamDestroy(ctx->ownStream);
+    delete ctx;
+}
+
+int b200c_set_stream(b200c_ctx* h, void* stream) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        ctx->stream = stream ? static_cast<cudaStream_t>(stream) : ctx->ownStream;
+    });
+}
+
+void* b200c_get_stream(b200c_ctx* h) {
+    return h ? static_cast<void*>(reinterpret_cast<Context*>(h)->stream) : nullptr;
+}
+
+int b200c_synchronize(b200c_ctx* h) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        if (!B2_EMU(ctx)) B2_CUDA(cudaSetDevice(ctx->device));
+        syncStream(ctx);
+        checkDeviceError(ctx);
+    });
+}
+
+int64_t b200c_launch_count(b200c_ctx* h) {
+    return h ? reinterpret_cast<Context*>(h)->launches : 0;
+}
+
+int b200c_infer_type(const b200c_type* in, const b200c_xform* chain, int n, b200c_type* out) {
+    return guarded([&] {
+        if (!in || !out) throw BadArg("null type pointer");
+        const TensorType t = inferChain(typeFromC(*in), chainFromC(chain, n));
+        typeToC(t, out);
+    });
+}
+
+int b200c_insert_position(const int32_t* kinds, int n, int32_t new_kind, int* pos) {
+    return guarded([&] {
+        if (n < 0 || (n > 0 && !kinds) || !pos) throw BadArg("bad arguments");
+        *pos = insertPosition(std::vector<int>(kinds, kinds + n), new_kind);
+    });
+}
+
+int64_t b200c_total_alloc_size(const b200c_type* t) {
+    int64_t r = -1;
+    guarded([&] {
+        if (!t) throw BadArg("null type pointer");
+        r = typeFromC(*t).allocBytes();
+    });
+    return r;
+}
+
+// Stage the base content on the device (or use it in place) and build the planner.
+static std::unique_ptr<Planner> makePlanner(Context* ctx, const b200c_type* base, const void* data, size_t nbytes,
+                                            int is_splat, int data_on_device) {
+    if (!base) throw BadArg("null base type");
+    const TensorType bt = typeFromC(*base);
+    if (bt.quantized()) throw BadArg("the base content cannot have a quantised element type");
+    if (nbytes > 0 && !data) throw BadArg("null data pointer");
+    const void* dev = data;
+    if (!data_on_device) {
+        void* d = ctx->arena.alloc(nbytes ? nbytes : 1);
+        copyH2D(ctx, d, data, nbytes);
+        dev = d;
+    }
+    return std::make_unique<Planner>(ctx, bt, dev, nbytes, is_splat != 0);
+}
+
+int b200c_fold(b200c_ctx* h, const b200c_type* base, const void* data, size_t nbytes, int is_splat, int data_on_device,
+               const b200c_xform* chain, int n, void* out, size_t out_cap, int out_on_device, size_t* out_bytes,
+               b200c_type* out_type, int flags) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        CallScope scope(ctx);
+        if (!out && out_cap > 0) throw BadArg("null output pointer");
+        const auto xs = chainFromC(chain, n);
+        auto plan = makePlanner(ctx, base, data, nbytes, is_splat, data_on_device);
+        void* devOut = out;
+        if (!out_on_device) devOut = ctx->arena.alloc(out_cap ? out_cap : 1);
+        const size_t wrote = plan->run(xs, devOut, out_cap);
+        if (!out_on_device) copyD2H(ctx, out, devOut, wrote);
+        for (const auto& so : plan->sideOutputs()) {
+            if (out_on_device) {
+                copyD2D(ctx, so.user, so.dev, so.bytes);
+            } else {
+                copyD2H(ctx, so.user, so.dev, so.bytes);
+            }
+        }
+        if (out_bytes) *out_bytes = wrote;
+        if (out_type) typeToC(plan->state().type, out_type);
+        const bool async = out_on_device && (flags & B200C_FOLD_ASYNC);
+        if (!async) {
+            syncStream(ctx);
+            checkDeviceError(ctx);
+        }
+    });
+}
+
+int b200c_count_nonsparse_per_oc(b200c_ctx* h, const b200c_type* base, const void* data, size_t nbytes, int is_splat,
+                                 int data_on_device, const b200c_xform* chain, int n, int64_t* counts,
+                                 int64_t ncounts) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        CallScope scope(ctx);
+        const auto xs = chainFromC(chain, n);
+        auto plan = makePlanner(ctx, base, data, nbytes, is_splat, data_on_device);
+        plan->runNoCopy(xs);
+        const auto v = plan->countNonSparse();
+        if (static_cast<int64_t>(v.size()) > ncounts || (!counts && !v.empty())) throw Capacity("counts array too small");
+        std::copy(v.begin(), v.end(), counts);
+    });
+}
+
+// ---------------------------------------------------------------------------- codec
+int b200c_btc_bound(size_t n, size_t* bound) {
+    if (!bound) return B200C_ERR_INVALID;
+    *bound = codecBound(n);
+    return B200C_OK;
+}
+
+int b200c_btc_compress(b200c_ctx* h, const void* in, size_t n, int in_on_device, void* out, size_t cap,
+                       int out_on_device, size_t* out_n) {
+    bool notSmaller = false;
+    const int rc = guarded([&] {
+        if (!h) throw BadArg("null context");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        CallScope scope(ctx);
+        if (n == 0) refThrow("BitCompactorCodec::compress: Empty input data vector");
+        if (!in || !out || !out_n) throw BadArg("null pointer");
+        if (cap < codecBound(n)) throw Capacity("output capacity below b200c_btc_bound(n)");
+        const unsigned char* devIn = static_cast<const unsigned char*>(in);
+        if (!in_on_device) {
+            void* d = ctx->arena.alloc(n);
+            copyH2D(ctx, d, in, n);
+            devIn = static_cast<const unsigned char*>(d);
+        }
+        unsigned char* devOut = static_cast<unsigned char*>(out);
+        if (!out_on_device) devOut = static_cast<unsigned char*>(ctx->arena.alloc(cap));
+        CodecBuf buf{devIn, n};
+        CodecResult res{};
+        codecCompressBatch(ctx, 1, &buf, devOut, cap, /*rawFallback=*/false, &res);
+        if (!out_on_device) {
+            copyD2H(ctx, out, devOut + res.offset, res.size);
+            syncStream(ctx);
+        }
+        *out_n = res.size;
+        notSmaller = res.notSmaller;
+    });
+    return rc != B200C_OK ? rc : (notSmaller ? B200C_NOT_SMALLER : B200C_OK);
+}
+
+int b200c_btc_decompress(b200c_ctx* h, const void* in, size_t n, int in_on_device, void* out, size_t cap,
+                         int out_on_device, size_t* out_n) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        CallScope scope(ctx);
+        if (!in || !out_n || (!out && cap)) throw BadArg("null pointer");
+        const unsigned char* devIn = static_cast<const unsigned char*>(in);
+        if (!in_on_device) {
+            void* d = ctx->arena.alloc(n ? n : 1);
+            copyH2D(ctx, d, in, n);
+            devIn = static_cast<const unsigned char*>(d);
+        }
+        unsigned char* devOut = static_cast<unsigned char*>(out);
+        if (!out_on_device) devOut = static_cast<unsigned char*>(ctx->arena.alloc(cap ? cap : 1));
+        const size_t total = codecDecompress(ctx, devIn, n, devOut, cap);
+        if (!out_on_device) {
+            copyD2H(ctx, out, devOut, total);
+            syncStream(ctx);
+        }
+        *out_n = total;
+    });
+}
+
+int b200c_btc_compress_batch(b200c_ctx* h, int count, const void* const* in_dev, const size_t* sizes, void* out_dev,
+                             size_t out_cap, size_t* out_offsets, size_t* out_sizes, int32_t* not_smaller) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        CallScope scope(ctx);
+        if (count < 0 || (count > 0 && (!in_dev || !sizes || !out_dev || !out_offsets || !out_sizes))) {
+            throw BadArg("bad batch arguments");
+        }
+        std::vector<CodecBuf> bufs(count);
+        for (int i = 0; i < count; ++i) bufs[i] = CodecBuf{static_cast<const unsigned char*>(in_dev[i]), sizes[i]};
+        std::vector<CodecResult> res(count);
+        codecCompressBatch(ctx, count, bufs.data(), static_cast<unsigned char*>(out_dev), out_cap, /*rawFallback=*/true,
+                           res.data());
+        for (int i = 0; i < count; ++i) {
+            out_offsets[i] = res[i].offset;
+            out_sizes[i] = res[i].size;
+            if (not_smaller) not_smaller[i] = res[i].notSmaller ? 1 : 0;
+        }
+    });
+}
+
+// ---------------------------------------------------------------------------- synthetic weights
+int b200c_synth_fill(b200c_ctx* h, void* dst_dev, int64_t count, int32_t dtype, int32_t dist, double p0, double p1,
+                     uint64_t seed, uint64_t stream_id) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        if (!B2_EMU(ctx)) B2_CUDA(cudaSetDevice(ctx->device));
+        if (count > 0 && !dst_dev) throw BadArg("null destination");
+        if (dist < 0 || dist > 2) throw BadArg("unknown distribution");
+        launchSynthFill(ctx, dst_dev, count, dtype, dist, p0, p1, seed, stream_id);
+    });
+}
+
+// ---------------------------------------------------------------------------- memory helpers
+int b200c_dev_alloc(b200c_ctx* h, size_t n, void** out) {
+    return guarded([&] {
+        if (!h || !out) throw BadArg("null pointer");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        if (!B2_EMU(ctx)) B2_CUDA(cudaSetDevice(ctx->device));
+        *out = devMalloc(ctx, n);
+    });
+}
+int b200c_dev_free(b200c_ctx* h, void* p) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        if (!B2_EMU(ctx)) B2_CUDA(cudaSetDevice(ctx->device));
+        devFree(ctx, p);
+    });
+}
+int b200c_host_alloc_pinned(size_t n, void** out) {
+    return guarded([&] {
+        if (!out) throw BadArg("null pointer");
+        void* p = nullptr;
+        const cudaError_t e = cudaMallocHost(&p, n ? n : 1);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            throw NoMem(std::string("cudaMallocHost: ") + cudaGetErrorString(e));
+        }
+        *out = p;
+    });
+}
+int b200c_host_free_pinned(void* p) {
+    return guarded([&] {
+        if (p) B2_CUDA(cudaFreeHost(p));
+    });
+}
+int b200c_memcpy_h2d(b200c_ctx* h, void* dst_dev, const void* src, size_t n) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        if (!B2_EMU(ctx)) B2_CUDA(cudaSetDevice(ctx->device));
+        copyH2D(ctx, dst_dev, src, n);
+        syncStream(ctx);
+    });
+}
+int b200c_memcpy_d2h(b200c_ctx* h, void* dst, const void* src_dev, size_t n) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        if (!B2_EMU(ctx)) B2_CUDA(cudaSetDevice(ctx->device));
+        copyD2H(ctx, dst, src_dev, n);
+        syncStream(ctx);
+    });
+}
+
+}  // extern "C"

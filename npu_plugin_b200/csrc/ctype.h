@@ -1,0 +1,174 @@
+// Host-side model of a constant's type and of one transformation, shared by the type-inference
+// code and the fold planner.  Mirrors what vpux::NDTypeInterface exposes for ranked tensors
+// (src/vpux_compiler/src/core/type_interfaces.cpp) without any MLIR dependency.
+#pragma once
+
+#include "../../include/b200const.h"
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace b200c {
+
+// An error the reference would raise with VPUX_THROW; carried to the C ABI as B200C_ERR_THROW.
+struct RefThrow : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+// Valid in the reference but not built here; B200C_ERR_UNSUPPORTED.
+struct NotBuilt : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+// Malformed descriptor; B200C_ERR_INVALID.
+struct BadArg : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+struct CudaFail : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+struct NoMem : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+struct Capacity : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+
+[[noreturn]] inline void refThrow(const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    throw RefThrow(buf);
+}
+
+inline int dtBits(int dt) {
+    return B200C_DTYPE_BITS(dt);
+}
+inline int dtClass(int dt) {
+    return B200C_DTYPE_CLASS(dt);
+}
+inline bool dtIsFloat(int dt) {
+    return dtClass(dt) == B200C_CLS_FLOAT || dtClass(dt) == B200C_CLS_BFLOAT;
+}
+inline bool dtIsInt(int dt) {
+    const int c = dtClass(dt);
+    return c == B200C_CLS_INT || c == B200C_CLS_SINT || c == B200C_CLS_UINT;
+}
+inline bool dtValid(int dt) {
+    const int b = dtBits(dt);
+    switch (dtClass(dt)) {
+    case B200C_CLS_FLOAT:
+        return b == 16 || b == 32 || b == 64;
+    case B200C_CLS_BFLOAT:
+        return b == 16;
+    case B200C_CLS_INT:
+    case B200C_CLS_SINT:
+    case B200C_CLS_UINT:
+        return b == 1 || b == 4 || b == 8 || b == 16 || b == 32 || b == 64;
+    default:
+        return false;
+    }
+}
+inline int64_t roundUp(int64_t v, int64_t a) {
+    return (v + a - 1) / a * a;
+}
+
+struct QuantInfo {
+    int kind = B200C_Q_NONE;
+    int axis = 0;
+    int expressed = 0;
+    int64_t qmin = 0, qmax = 0;
+    std::vector<double> scales;
+    std::vector<int64_t> zps;
+};
+
+struct TensorType {
+    int dtype = 0;  // for quantised types: the normalised storage integer
+    std::vector<int64_t> shape;
+    std::vector<int> order;  // order[k] = logical dim at memory position k, outermost first
+    QuantInfo q;
+
+    int rank() const {
+        return static_cast<int>(shape.size());
+    }
+    bool quantized() const {
+        return q.kind != B200C_Q_NONE;
+    }
+    int64_t count() const {
+        int64_t n = 1;
+        for (auto d : shape) n *= d;
+        return n;
+    }
+    int bits() const {
+        return dtBits(dtype);
+    }
+    bool identityOrder() const {
+        for (int k = 0; k < rank(); ++k)
+            if (order[k] != k) return false;
+        return true;
+    }
+    void setIdentityOrder() {
+        order.resize(shape.size());
+        for (size_t k = 0; k < shape.size(); ++k) order[k] = static_cast<int>(k);
+    }
+    std::vector<int64_t> memOrder(const std::vector<int64_t>& logical) const {
+        std::vector<int64_t> m(logical.size());
+        for (size_t k = 0; k < logical.size(); ++k) m[k] = logical[order[k]];
+        return m;
+    }
+    std::vector<int64_t> memShape() const {
+        return memOrder(shape);
+    }
+    int memPosOf(int logicalDim) const {
+        for (int k = 0; k < rank(); ++k)
+            if (order[k] == logicalDim) return k;
+        throw BadArg("logical dim not in order");
+    }
+    // getTotalAllocSize: bits x count rounded up to bytes (rank 0 holds one element)
+    int64_t allocBytes() const {
+        return (static_cast<int64_t>(bits()) * (rank() == 0 ? 1 : count()) + 7) / 8;
+    }
+};
+
+struct Transformation {
+    int kind = 0;
+    std::vector<int64_t> a, b;
+    double f = 0;
+    int64_t i0 = 0, i1 = 0;
+    bool hasType = false;
+    TensorType type;  // element type only (rank 0)
+    bool hasAux = false;
+    std::vector<int64_t> aux;
+    void* side0 = nullptr;
+    void* side1 = nullptr;
+};
+
+enum class PositionReq { None, PreferredLast, Last };
+
+// descriptor <-> model
+TensorType typeFromC(const b200c_type& c, bool elemOnly = false);
+void typeToC(const TensorType& t, b200c_type* c);
+Transformation xformFromC(const b200c_xform& c);
+
+// inferOutputType of one transformation / of a whole list (ContentAttr::inferFinalType)
+TensorType inferOne(const Transformation& x, const TensorType& in);
+TensorType inferChain(const TensorType& base, const std::vector<Transformation>& chain);
+
+PositionReq positionOf(int kind);
+bool acceptsSubByteStorage(int kind);
+int insertPosition(const std::vector<int>& kinds, int newKind);
+
+// helpers the planner also needs
+TensorType withShape(const TensorType& in, const std::vector<int64_t>& shape);
+TensorType withShapeAndElem(const TensorType& in, const std::vector<int64_t>& shape, int dtype, const QuantInfo& q);
+int64_t sparsifyValue(const TensorType& t);
+
+constexpr int64_t kSwizzleSizeAlign = 512;  // SWIZZLING_SIZE_ALIGNMENT_VPUX37XX
+constexpr int kArchVPUX37XX = 3;            // VPU::ArchKind::VPUX37XX
+constexpr int64_t kWeightSetAlign = 16;     // VPU_WEIGHT_SET_BYTE_ALIGNMENT (nce_invariant.hpp:39)
+
+}  // namespace b200c

@@ -1,0 +1,83 @@
+// Fold planner interface; see plan.cu.
+#pragma once
+
+#include "runtime.h"
+
+#include <vector>
+
+namespace b200c {
+
+// Host-side form of a view (GenParams with growable lists).
+struct View {
+    const void* src = nullptr;  // device pointer
+    size_t srcBytes = 0;
+    int srcTag = T_NONE;  // C type of the source elements; T_NONE for bit-packed storage
+    int rank = 0;
+    long long shape[kMaxDims] = {0};
+    long long stride[kMaxDims] = {0};
+    long long base = 0;
+    std::vector<FillBox> boxes;
+    std::vector<ValueOp> ops;
+};
+
+// What Const::Content carries: logical type, storage element type, splat flag, and here the lazy view.
+struct ContentState {
+    TensorType type;
+    int storage = 0;
+    bool splat = false;
+    View view;
+};
+
+struct SideOutput {
+    const void* dev;
+    void* user;
+    size_t bytes;
+};
+
+int tagOfStorage(int dtype);
+
+class Planner {
+public:
+    Planner(Context* ctx, const TensorType& baseType, const void* devData, size_t nbytes, bool splat);
+
+    // fold + copyTo into dst (device); returns bytes written
+    size_t run(const std::vector<Transformation>& chain, void* dst, size_t cap);
+    // fold only (for count queries)
+    void runNoCopy(const std::vector<Transformation>& chain);
+    std::vector<int64_t> countNonSparse();
+
+    const ContentState& state() const {
+        return _s;
+    }
+    const std::vector<SideOutput>& sideOutputs() const {
+        return _sides;
+    }
+
+private:
+    void apply(const Transformation& x);
+    void materialize();
+    const void* denseAs(int tag);
+    GenParams paramsFor(const View& v) const;
+    int curTag() const;
+    void* uploadTable(const void* host, size_t bytes);
+    void needByteStorage(const char* what);
+    void quantizeSynth(const Transformation& x, const TensorType& outType);
+    void getSparsityMap(const TensorType& outType, int swizzleKey);
+    void sparsify(const Transformation& x);
+    void subviewBits(const Transformation& x, const TensorType& outType);
+    void swizzle(const Transformation& x, const TensorType& outType);
+    size_t emitCopyTo(void* dst, size_t cap, int swizzleKey, int64_t totalBytes);
+
+    Context* _ctx;
+    ContentState _s;
+    std::vector<std::vector<char>> _staging;
+    std::vector<SideOutput> _sides;
+    bool _afterBitPack = false;
+    void* _finalDst = nullptr;
+    size_t _finalCap = 0;
+    bool _isLast = false;
+    bool _wroteFinal = false;
+    size_t _finalBytes = 0;
+};
+
+}  // namespace b200c

@@ -1,0 +1,140 @@
+// Per-context runtime state: stream, scratch arena, error word, launch accounting.
+#pragma once
+
+#include "ctype.h"
+#include "view.h"
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <mutex>
+#include <string>
+#include <vector>
+
+namespace b200c {
+
+#define B2_CUDA(call)                                                                              \
+    do {                                                                                           \
+        cudaError_t e_ = (call);                                                                   \
+        if (e_ != cudaSuccess) {                                                                   \
+            throw ::b200c::CudaFail(std::string(#call) + ": " + cudaGetErrorString(e_));           \
+        }                                                                                          \
+    } while (0)
+
+// Debug build only (B200C_HOST_EMULATION): kernels written as per-unit functions can be run on the
+// host to exercise the planner without a GPU.  The shipped library is never built with this macro,
+// and B2_EMU() is then the constant false.
+#ifdef B200C_HOST_EMULATION
+#define B2_EMU(ctx) ((ctx)->emulated)
+#else
+#define B2_EMU(ctx) false
+#endif
+
+struct Context;
+
+// Bump allocator over device memory.  Blocks are kept for the life of the context and reused by
+// every call; reset() rewinds to the start.
+class Arena {
+public:
+    explicit Arena(Context* ctx): _ctx(ctx) {
+    }
+    ~Arena();
+    void* alloc(size_t bytes, size_t align = 256);
+    void reset();
+    void releaseAll();
+    size_t reserved() const;
+
+private:
+    struct Block {
+        char* ptr;
+        size_t size, used;
+    };
+    Context* _ctx;
+    std::vector<Block> _blocks;
+};
+
+struct Context {
+    int device = 0;
+    cudaStream_t ownStream = nullptr;
+    cudaStream_t stream = nullptr;
+    std::mutex mu;
+    Arena arena{this};
+    int* errWord = nullptr;      // device
+    int* errHost = nullptr;      // pinned host mirror
+    int64_t launches = 0;
+    int smCount = 148;
+    size_t l2Bytes = 0;
+    bool emulated = false;
+};
+
+// device memory through the context (host malloc under emulation)
+void* devMalloc(Context* ctx, size_t bytes);
+void devFree(Context* ctx, void* p);
+void copyH2D(Context* ctx, void* dst, const void* src, size_t n);
+void copyD2H(Context* ctx, void* dst, const void* src, size_t n);
+void copyD2D(Context* ctx, void* dst, const void* src, size_t n);
+void fillBytes(Context* ctx, void* dst, int value, size_t n);
+void syncStream(Context* ctx);
+// Reads and clears the device error word (synchronises); maps it to a RefThrow.
+void checkDeviceError(Context* ctx);
+
+// ---- kernel entry points (defined in the .cu files) ----------------------------------------
+void launchGeneric(Context* ctx, const GenParams& p);
+
+struct RowStatsParams {
+    GenParams view;       // evaluates the Content before quantisation (outMode unused)
+    int rowDim;           // view dim holding logical dim 0
+    long long rows;
+    long long rowElems;   // elements per row
+    int scheme;
+    float* scales;        // [rows]
+    int* zps;             // [rows]
+};
+void launchRowStats(Context* ctx, const RowStatsParams& p);
+
+// sparsity (GetSparsityMap / Sparsify) on a dense buffer of `tag` elements laid out [OC][work]
+void launchSparsityMap(Context* ctx, const void* src, int tag, long long oc, long long work, long long outBitsPerOC,
+                       unsigned long long sparseBits, void* dstBits, int swizzleKey);
+void launchCountNonSparse(Context* ctx, const void* src, int tag, long long oc, long long work,
+                          unsigned long long sparseBits, long long* counts);
+void launchSparsifyOffsets(Context* ctx, const long long* counts, long long oc, int elemBytes, long long* offsets,
+                           long long* total);
+void launchSparsifyScatter(Context* ctx, const void* src, int tag, long long oc, long long work,
+                           unsigned long long sparseBits, const long long* offsets, void* dst, long long dstBytes,
+                           int swizzleKey, int* err);
+
+// swizzle of an existing byte buffer (16-byte chunks), zero or constant tail
+void launchSwizzleCopy(Context* ctx, const void* src, long long srcBytes, void* dst, long long totalBytes, int key,
+                       int tailByte);
+// SubView on bit-packed i1 storage
+void launchSubViewBits(Context* ctx, const void* src, void* dst, int rank, const long long* outShape,
+                       const long long* inStride, long long base, long long outBits);
+
+// block codec (codec.h, codec_kernels.cu)
+size_t codecBound(size_t n);
+struct CodecJobDev {
+    const unsigned char* in;
+    unsigned long long n, nblocks, nsuper, firstBlock;
+    unsigned long long recordsBytes, streamBytes, outBase, outBytes;
+    int notSmaller;
+    int _pad;
+};
+struct CodecBuf {
+    const unsigned char* in;  // device
+    size_t n;
+};
+struct CodecResult {
+    size_t offset, size;
+    bool notSmaller;
+};
+// Compresses `count` device buffers into outDev; segment i starts at results[i].offset (32-byte
+// aligned).  With rawFallback a buffer whose stream would not be smaller is stored unchanged.
+void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned char* outDev, size_t outCap,
+                        bool rawFallback, CodecResult* results);
+size_t codecDecompress(Context* ctx, const unsigned char* inDev, size_t n, unsigned char* outDev, size_t cap);
+
+// synthetic weights
+void launchSynthFill(Context* ctx, void* dst, long long count, int dtype, int dist, double p0, double p1,
+                     unsigned long long seed, unsigned long long stream);
+
+}  // namespace b200c

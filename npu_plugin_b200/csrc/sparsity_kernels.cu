@@ -1,0 +1,301 @@
+// Sparsity kernels: GetSparsityMap (1 bit per element, LSB first, per-channel rows padded to
+// 128 bits) and Sparsify (per-channel compaction with 16-byte aligned channel starts), restating
+// src/vpux_compiler/src/dialect/const/attributes/get_sparsity_map.cpp:23-107,
+// sparsify.cpp:115-186 and src/vpux_compiler/src/utils/sparsity.cpp:28-72 as count -> scan -> scatter.
+// Inputs are dense [OC][work] buffers of si8/ui8/f16/bf16/f32 elements.
+#include "runtime.h"
+
+#include <algorithm>
+
+namespace b200c {
+
+// element != sparse value, with float semantics for the float types (ov::float16 compares as float)
+B2_HD bool differs(const void* src, long long idx, int tag, unsigned long long sparseBits) {
+    switch (tag) {
+    case T_I8:
+    case T_U8:
+        return static_cast<const unsigned char*>(src)[idx] != static_cast<unsigned char>(sparseBits);
+    case T_F16:
+        return halfBitsToFloat(static_cast<const unsigned short*>(src)[idx]) !=
+               halfBitsToFloat(static_cast<unsigned short>(sparseBits));
+    case T_BF16:
+        return bf16BitsToFloat(static_cast<const unsigned short*>(src)[idx]) !=
+               bf16BitsToFloat(static_cast<unsigned short>(sparseBits));
+    default:
+        return bitsToFloat(static_cast<const unsigned int*>(src)[idx]) !=
+               bitsToFloat(static_cast<unsigned int>(sparseBits));
+    }
+}
+
+// ---------------------------------------------------------------------------- GetSparsityMap
+struct MapParams {
+    const void* src;
+    unsigned char* dst;
+    int tag;
+    long long oc, work, outBytesPerOC;
+    unsigned long long sparseBits;
+    int swizzleKey;
+};
+
+// one output byte: 8 consecutive elements of one channel, element k -> bit k; bytes past the
+// channel's data are the zero fill of the 128-bit alignment
+B2_HD void mapByte(const MapParams& p, long long byteIdx) {
+    const long long oc = byteIdx / p.outBytesPerOC;
+    const long long j = byteIdx - oc * p.outBytesPerOC;
+    unsigned int byte = 0;
+    if (j * 8 < p.work) {
+        const long long first = oc * p.work + j * 8;
+        for (int b = 0; b < 8; ++b) byte |= static_cast<unsigned int>(differs(p.src, first + b, p.tag, p.sparseBits)) << b;
+    }
+    p.dst[swizzleAddr(byteIdx, p.swizzleKey)] = static_cast<unsigned char>(byte);
+}
+
+__global__ void __launch_bounds__(256) sparsityMapKernel(const __grid_constant__ MapParams p, long long bytes) {
+    const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < bytes; i += step) mapByte(p, i);
+}
+
+// 8-bit elements, work % 16 == 0 and 16-byte aligned rows: one 128-bit load -> 16 mask bits per thread.
+// The per-byte "not equal" flags are gathered into a nibble with one multiply.
+__global__ void __launch_bounds__(256) sparsityMapBytesKernel(const __grid_constant__ MapParams p, long long units,
+                                                              long long unitsPerOC, long long dataUnitsPerOC) {
+    const unsigned int sv = static_cast<unsigned int>(p.sparseBits & 0xFF) * 0x01010101u;
+    const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long u = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; u < units; u += step) {
+        const long long oc = u / unitsPerOC;
+        const long long j = u - oc * unitsPerOC;
+        unsigned int mask16 = 0;
+        if (j < dataUnitsPerOC) {
+            const uint4 v = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(p.src) + oc * p.work + j * 16);
+            const unsigned int w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const unsigned int ne = (__vcmpne4(w[i], sv) >> 7) & 0x01010101u;
+                mask16 |= ((ne * 0x01020408u) >> 24 & 0xFu) << (4 * i);
+            }
+        }
+        const long long a = u * 2;  // two output bytes; a 16-byte swizzle chunk is never split
+        *reinterpret_cast<unsigned short*>(p.dst + swizzleAddr(a, p.swizzleKey)) = static_cast<unsigned short>(mask16);
+    }
+}
+
+void launchSparsityMap(Context* ctx, const void* src, int tag, long long oc, long long work, long long outBitsPerOC,
+                       unsigned long long sparseBits, void* dstBits, int swizzleKey) {
+    MapParams p;
+    p.src = src;
+    p.dst = static_cast<unsigned char*>(dstBits);
+    p.tag = tag;
+    p.oc = oc;
+    p.work = work;
+    p.outBytesPerOC = outBitsPerOC / 8;
+    p.sparseBits = sparseBits;
+    p.swizzleKey = swizzleKey;
+    const long long bytes = oc * p.outBytesPerOC;
+    if (bytes <= 0) return;
+#ifdef B200C_HOST_EMULATION
+    if (B2_EMU(ctx)) {
+        for (long long i = 0; i < bytes; ++i) mapByte(p, i);
+        ++ctx->launches;
+        return;
+    }
+#endif
+    const bool fast = tagBytes(tag) == 1 && work % 16 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+                      (reinterpret_cast<uintptr_t>(dstBits) & 1) == 0;
+    if (fast) {
+        const long long unitsPerOC = p.outBytesPerOC / 2, units = oc * unitsPerOC;
+        const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>((units + 255) / 256, ctx->smCount * 8LL)));
+        sparsityMapBytesKernel<<<grid, 256, 0, ctx->stream>>>(p, units, unitsPerOC, work / 16);
+    } else {
+        const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>((bytes + 255) / 256, ctx->smCount * 8LL)));
+        sparsityMapKernel<<<grid, 256, 0, ctx->stream>>>(p, bytes);
+    }
+    B2_CUDA(cudaGetLastError());
+    ++ctx->launches;
+}
+
+// ---------------------------------------------------------------------------- count per channel
+__global__ void __launch_bounds__(256) countNonSparseKernel(const void* __restrict__ src, int tag, long long oc,
+                                                            long long work, unsigned long long sparseBits,
+                                                            long long* __restrict__ counts) {
+    __shared__ long long part[8];
+    for (long long c = blockIdx.x; c < oc; c += gridDim.x) {
+        long long n = 0;
+        const long long first = c * work;
+        if (tagBytes(tag) == 1 && ((reinterpret_cast<uintptr_t>(src) + first) & 15) == 0) {
+            const unsigned int sv = static_cast<unsigned int>(sparseBits & 0xFF) * 0x01010101u;
+            const unsigned char* row = static_cast<const unsigned char*>(src) + first;
+            const long long vec = work / 16;
+            for (long long j = threadIdx.x; j < vec; j += blockDim.x) {
+                const uint4 v = *reinterpret_cast<const uint4*>(row + j * 16);
+                n += (__popc(__vcmpne4(v.x, sv)) + __popc(__vcmpne4(v.y, sv)) + __popc(__vcmpne4(v.z, sv)) +
+                      __popc(__vcmpne4(v.w, sv))) >> 3;
+            }
+            for (long long j = vec * 16 + threadIdx.x; j < work; j += blockDim.x) n += row[j] != (sparseBits & 0xFF);
+        } else {
+            for (long long j = threadIdx.x; j < work; j += blockDim.x) n += differs(src, first + j, tag, sparseBits);
+        }
+        for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xFFFFFFFFu, n, o);
+        if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = n;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            long long t = 0;
+            for (int w = 0; w < 8; ++w) t += part[w];
+            counts[c] = t;
+        }
+        __syncthreads();
+    }
+}
+
+void launchCountNonSparse(Context* ctx, const void* src, int tag, long long oc, long long work,
+                          unsigned long long sparseBits, long long* counts) {
+    if (oc <= 0) return;
+#ifdef B200C_HOST_EMULATION
+    if (B2_EMU(ctx)) {
+        for (long long c = 0; c < oc; ++c) {
+            long long n = 0;
+            for (long long j = 0; j < work; ++j) n += differs(src, c * work + j, tag, sparseBits);
+            counts[c] = n;
+        }
+        ++ctx->launches;
+        return;
+    }
+#endif
+    const int grid = static_cast<int>(std::min<long long>(oc, ctx->smCount * 8LL));
+    countNonSparseKernel<<<grid, 256, 0, ctx->stream>>>(src, tag, oc, work, sparseBits, counts);
+    B2_CUDA(cudaGetLastError());
+    ++ctx->launches;
+}
+
+// ---------------------------------------------------------------------------- channel offsets
+// offsets[c] = sum over earlier channels of align16(count * elemBytes); *total = the full sum.
+// One CTA walks the channels in tiles of 1024 with a shuffle-based block scan (no inter-CTA waits).
+__global__ void __launch_bounds__(1024) sparsifyOffsetsKernel(const long long* __restrict__ counts, long long oc,
+                                                              int elemBytes, long long* __restrict__ offsets,
+                                                              long long* __restrict__ total) {
+    __shared__ long long warpSum[32];
+    __shared__ long long carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (long long tile = 0; tile < oc; tile += blockDim.x) {
+        const long long c = tile + threadIdx.x;
+        const long long mine = c < oc ? ((counts[c] * elemBytes + 15) & ~15ll) : 0;
+        long long incl = mine;
+        for (int o = 1; o < 32; o <<= 1) {
+            const long long t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) warpSum[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            long long w = warpSum[lane];
+            for (int o = 1; o < 32; o <<= 1) {
+                const long long t = __shfl_up_sync(0xFFFFFFFFu, w, o);
+                if (lane >= o) w += t;
+            }
+            warpSum[lane] = w;
+        }
+        __syncthreads();
+        const long long before = carry + (warp ? warpSum[warp - 1] : 0) + incl - mine;
+        if (c < oc) offsets[c] = before;
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) carry = before + mine;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *total = carry;
+}
+
+void launchSparsifyOffsets(Context* ctx, const long long* counts, long long oc, int elemBytes, long long* offsets,
+                           long long* total) {
+#ifdef B200C_HOST_EMULATION
+    if (B2_EMU(ctx)) {
+        long long run = 0;
+        for (long long c = 0; c < oc; ++c) {
+            offsets[c] = run;
+            run += (counts[c] * elemBytes + 15) & ~15ll;
+        }
+        *total = run;
+        ++ctx->launches;
+        return;
+    }
+#endif
+    sparsifyOffsetsKernel<<<1, 1024, 0, ctx->stream>>>(counts, oc, elemBytes, offsets, total);
+    B2_CUDA(cudaGetLastError());
+    ++ctx->launches;
+}
+
+// ---------------------------------------------------------------------------- compaction
+// One CTA per channel keeps the element order: every round takes blockDim consecutive elements,
+// ranks the survivors with ballot/popc inside each warp and a small shared-memory scan across warps.
+__global__ void __launch_bounds__(256) sparsifyScatterKernel(const void* __restrict__ src, int tag, long long oc,
+                                                             long long work, unsigned long long sparseBits,
+                                                             const long long* __restrict__ offsets,
+                                                             unsigned char* __restrict__ dst, long long dstBytes,
+                                                             int swizzleKey, int* err) {
+    __shared__ int warpCount[8];
+    __shared__ long long running;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int eb = tagBytes(tag);
+    for (long long c = blockIdx.x; c < oc; c += gridDim.x) {
+        if (threadIdx.x == 0) running = offsets[c];
+        __syncthreads();
+        for (long long tile = 0; tile < work; tile += blockDim.x) {
+            const long long j = tile + threadIdx.x;
+            const long long idx = c * work + j;
+            const bool keep = j < work && differs(src, idx, tag, sparseBits);
+            const unsigned int votes = __ballot_sync(0xFFFFFFFFu, keep);
+            if (lane == 0) warpCount[warp] = __popc(votes);
+            __syncthreads();
+            int before = __popc(votes & ((1u << lane) - 1u));
+            for (int w = 0; w < warp; ++w) before += warpCount[w];
+            if (keep) {
+                const long long at = running + static_cast<long long>(before) * eb;
+                if (at + eb > dstBytes) {
+                    atomicCAS(err, E_NONE, E_SPARSE_OVERFLOW);
+                } else {
+                    storeRawAt(dst, swizzleAddr(at, swizzleKey), eb, loadRaw(src, idx, tag));
+                }
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int all = 0;
+                for (int w = 0; w < 8; ++w) all += warpCount[w];
+                running += static_cast<long long>(all) * eb;
+            }
+            __syncthreads();
+        }
+    }
+}
+
+void launchSparsifyScatter(Context* ctx, const void* src, int tag, long long oc, long long work,
+                           unsigned long long sparseBits, const long long* offsets, void* dst, long long dstBytes,
+                           int swizzleKey, int* err) {
+    if (oc <= 0 || work <= 0) return;
+#ifdef B200C_HOST_EMULATION
+    if (B2_EMU(ctx)) {
+        const int eb = tagBytes(tag);
+        for (long long c = 0; c < oc; ++c) {
+            long long at = offsets[c];
+            for (long long j = 0; j < work; ++j) {
+                const long long idx = c * work + j;
+                if (!differs(src, idx, tag, sparseBits)) continue;
+                if (at + eb > dstBytes) {
+                    if (*err == E_NONE) *err = E_SPARSE_OVERFLOW;
+                } else {
+                    storeRawAt(dst, swizzleAddr(at, swizzleKey), eb, loadRaw(src, idx, tag));
+                }
+                at += eb;
+            }
+        }
+        ++ctx->launches;
+        return;
+    }
+#endif
+    const int grid = static_cast<int>(std::min<long long>(oc, ctx->smCount * 8LL));
+    sparsifyScatterKernel<<<grid, 256, 0, ctx->stream>>>(src, tag, oc, work, sparseBits, offsets,
+                                                         static_cast<unsigned char*>(dst), dstBytes, swizzleKey, err);
+    B2_CUDA(cudaGetLastError());
+    ++ctx->launches;
+}
+
+}  // namespace b200c
