@@ -1576,9 +1576,11 @@ static Content fold(const Type& baseType, const char* data, size_t nbytes, bool 
 // (stands where BitCompactor is called, src/vpux_compiler/src/utils/bit_compactor_codec.cpp:15-42;
 //  the format is NOT BitCompactor's -- its sources are not in the reference tree).
 //
-// Stream: 16-byte header { 'B','2','B','C', version=1, 0,0,0, u64 n } then one record per
-// 64-byte block of the input (the last block is zero-extended), then zero bytes up to a
-// multiple of 32.  Record = 1 header byte (mode in bits 7..5, parameter w in bits 4..0) + payload:
+// Stream (little endian): 32-byte header { 'B','2','B','C', u32 version = 1, u64 n, u64 nblocks,
+// u32 nsuper, u32 0 }, then an index of nsuper u32 values (byte offset, from the start of the
+// records, of the first record of every group of 64 blocks), then one record per 64-byte block of
+// the input (the last block is zero-extended), then zero bytes up to a multiple of 32.
+// Record = 1 header byte (mode in bits 7..5, parameter w in bits 4..0) + payload:
 //   mode 0 RAW     : 64 bytes
 //   mode 1 CONST   : 1 byte, all 64 bytes equal it
 //   mode 2 PACKU   : 1 byte base (the block minimum as unsigned) + 8*w bytes: (b - base) in w bits, w = 1..7
@@ -1588,7 +1590,8 @@ static Content fold(const Type& baseType, const char* data, size_t nbytes, bool 
 // of a little-endian w-byte word.  Mode choice: smallest record; ties go to the smaller mode id.
 // ---------------------------------------------------------------------------
 namespace codec {
-static const size_t HDR = 16;
+static const size_t HDR = 32;
+static const size_t SUPER = 64;
 static inline uint8_t zigzag(uint8_t b) {
     const int8_t s = static_cast<int8_t>(b);
     return static_cast<uint8_t>((static_cast<uint8_t>(s) << 1) ^ static_cast<uint8_t>(s >> 7));
@@ -1606,7 +1609,14 @@ static inline int bitWidth(uint8_t v) {
 }
 static size_t bound(size_t n) {
     const size_t blocks = (n + 63) / 64;
-    return static_cast<size_t>(alignUp(static_cast<int64_t>(HDR + blocks * 65), 32));
+    const size_t supers = (blocks + SUPER - 1) / SUPER;
+    return static_cast<size_t>(alignUp(static_cast<int64_t>(HDR + 4 * supers + blocks * 65), 32));
+}
+static void put32(uint8_t* p, uint32_t v) {
+    for (int i = 0; i < 4; ++i) p[i] = static_cast<uint8_t>(v >> (8 * i));
+}
+static uint32_t get32(const uint8_t* p) {
+    return p[0] | (uint32_t(p[1]) << 8) | (uint32_t(p[2]) << 16) | (uint32_t(p[3]) << 24);
 }
 struct Choice {
     int mode, w;
@@ -1646,17 +1656,23 @@ static void unpackGroup(const uint8_t* in, int w, uint8_t* v8) {
 }
 static size_t compress(const uint8_t* in, size_t n, uint8_t* out, size_t cap) {
     if (cap < bound(n)) throwf("codec: output capacity below the bound");
+    const size_t blocks = (n + 63) / 64;
+    const size_t supers = (blocks + SUPER - 1) / SUPER;
     std::memset(out, 0, HDR);
     out[0] = 'B';
     out[1] = '2';
     out[2] = 'B';
     out[3] = 'C';
-    out[4] = 1;
-    const uint64_t n64 = n;
-    std::memcpy(out + 8, &n64, 8);
-    size_t o = HDR;
-    const size_t blocks = (n + 63) / 64;
+    put32(out + 4, 1);
+    put32(out + 8, static_cast<uint32_t>(n));
+    put32(out + 12, static_cast<uint32_t>(static_cast<uint64_t>(n) >> 32));
+    put32(out + 16, static_cast<uint32_t>(blocks));
+    put32(out + 20, static_cast<uint32_t>(static_cast<uint64_t>(blocks) >> 32));
+    put32(out + 24, static_cast<uint32_t>(supers));
+    const size_t recordsAt = HDR + 4 * supers;
+    size_t o = recordsAt;
     for (size_t bi = 0; bi < blocks; ++bi) {
+        if (bi % SUPER == 0) put32(out + HDR + 4 * (bi / SUPER), static_cast<uint32_t>(o - recordsAt));
         uint8_t b[64] = {0};
         std::memcpy(b, in + bi * 64, std::min<size_t>(64, n - bi * 64));
         const Choice c = choose(b);
@@ -1701,15 +1717,19 @@ static size_t compress(const uint8_t* in, size_t n, uint8_t* out, size_t cap) {
     return padded;
 }
 static size_t decompress(const uint8_t* in, size_t n, uint8_t* out, size_t cap) {
-    if (n < HDR || in[0] != 'B' || in[1] != '2' || in[2] != 'B' || in[3] != 'C' || in[4] != 1) {
+    if (n < HDR || in[0] != 'B' || in[1] != '2' || in[2] != 'B' || in[3] != 'C' || get32(in + 4) != 1) {
         throwf("codec: bad stream header");
     }
-    uint64_t total = 0;
-    std::memcpy(&total, in + 8, 8);
+    const uint64_t total = get32(in + 8) | (static_cast<uint64_t>(get32(in + 12)) << 32);
     if (total > cap) throwf("codec: output capacity too small");
-    size_t i = HDR;
     const size_t blocks = (total + 63) / 64;
+    const size_t supers = (blocks + SUPER - 1) / SUPER;
+    if (get32(in + 24) != supers) throwf("codec: inconsistent stream header");
+    size_t i = HDR + 4 * supers;
     for (size_t bi = 0; bi < blocks; ++bi) {
+        if (bi % SUPER == 0 && get32(in + HDR + 4 * (bi / SUPER)) != i - (HDR + 4 * supers)) {
+            throwf("codec: index entry does not match the record position");
+        }
         if (i >= n) throwf("codec: truncated stream");
         const int mode = in[i] >> 5, w = in[i] & 31;
         ++i;
