@@ -1,0 +1,410 @@
+#!/usr/bin/env python
+"""Benchmark of the weight-preparation hot path on B200.
+
+Workload (default): whole-model fold of a 7B Llama-shaped decoder with synthetic f16 weights
+(BASELINE.json configs[4]): every linear weight goes through per-output-channel symmetric int8
+quantisation -> ConvertElemType -> QuantCast -> Reorder -> SwizzleConstant(5) and then block
+compression; embedding and RMSNorm gains pass through.  Constants are sharded by tensor over the
+ranks; compressed segments are gathered on rank 0.  A "step" is one pass over the whole model.
+
+  python bench.py --gpus N --steps K --warmup W            # this library (N>1 under torchrun)
+  python bench.py --impl reference ...                      # the CPU path (oracle) on the host cores
+
+Prints ONE JSON line (rank 0).
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+from npu_plugin_b200 import _cabi as A  # noqa: E402
+from npu_plugin_b200.blob import ConstantDecl, ShardFolder, partition  # noqa: E402
+from npu_plugin_b200.const import (DimsOrder, NDType, Transform, UniformQuantizedPerAxisType)  # noqa: E402
+
+HBM_FALLBACK_GBS = 6650.0
+
+
+# ----------------------------------------------------------------------------- workload
+def llama7b_decls(layers=32, hidden=4096, ffn=11008, vocab=32000):
+    """225 linear weights + embedding + 65 RMSNorm gains of a 7B Llama-shaped decoder (shapes only)."""
+    decls = []
+
+    def linear(name, o, i):
+        q = UniformQuantizedPerAxisType(A.SI8, A.F16, [1.0] * o, [0] * o, 0, -127, 127)
+        chain = [Transform(A.X_QUANTIZE_SYNTH, i0=A.QSYNTH_SYM_I8), Transform(A.X_CONVERT_ELEM_TYPE, elem=A.SI8),
+                 Transform(A.X_QUANT_CAST, elem=q), Transform(A.X_REORDER, a=DimsOrder.NHWC),
+                 Transform(A.X_SWIZZLE_CONSTANT, i0=5, i1=3)]
+        decls.append(ConstantDecl(name, NDType((o, i, 1, 1), A.F16), chain, o * i * 2, compress=True))
+
+    for l in range(layers):
+        for n in ("q", "k", "v", "o"):
+            linear(f"l{l}.{n}", hidden, hidden)
+        linear(f"l{l}.gate", ffn, hidden)
+        linear(f"l{l}.up", ffn, hidden)
+        linear(f"l{l}.down", hidden, ffn)
+    linear("lm_head", vocab, hidden)
+    decls.append(ConstantDecl("embedding", NDType((vocab, hidden), A.F16), [], vocab * hidden * 2, compress=False))
+    for l in range(2 * layers + 1):
+        decls.append(ConstantDecl(f"norm{l}", NDType((hidden,), A.F16), [], hidden * 2, compress=False))
+    return decls
+
+
+def algorithmic_bytes(decls, folded_sizes, blob_sizes):
+    """Read-once + write-once bytes of one step: fold (input + folded output + scale tables) and, for
+    compressed constants, codec (folded input + stream output)."""
+    fold = sum(d.nbytes for d in decls) + sum(folded_sizes)
+    fold += sum(4 * d.base_type.shape[0] for d in decls if d.transforms)
+    codec = 0
+    for d, fs, bs in zip(decls, folded_sizes, blob_sizes):
+        if bs is not None:
+            codec += fs + bs
+    return fold, codec
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms",
+                                          "50", "-i", str(self.index)], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, reasons = [], set()
+        try:
+            for line in open(self.path):
+                p = [x.strip() for x in line.split(",")]
+                if len(p) < 9:
+                    continue
+                try:
+                    sm.append(float(p[1]))
+                    out["sm_max_mhz"] = float(p[2])
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out["sm_mhz"] = float(np.median(sm))
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return HBM_FALLBACK_GBS, "fallback"
+
+
+# ----------------------------------------------------------------------------- CPU (reference arm / cpu_baseline)
+def cpu_sample_decls(decls, budget_elems):
+    """A bounded sample of the workload for the host: whole tensors, in model order, up to the budget."""
+    out, total = [], 0
+    for d in decls:
+        if not d.transforms:
+            continue
+        n = d.nbytes // 2
+        if out and total + n > budget_elems:
+            break
+        out.append(d)
+        total += n
+    return out
+
+
+def run_cpu(decls, steps, warmup, budget_elems, threads=None):
+    """Times the CPU restatement of the reference's folding + codec (oracle) on a bounded sample.
+    Returns (GB/s over algorithmic bytes, ms per sample pass, cores, sample description)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle_backend import OracleBackend
+    orc = OracleBackend()
+    cores = orc.set_threads(threads or (os.cpu_count() or 1))
+    sample = cpu_sample_decls(decls, budget_elems)
+    rng = np.random.default_rng(5)
+    data = [rng.normal(0, 0.02, d.base_type.getNumElements()).astype(np.float16) for d in sample]
+    side = [(np.zeros(d.base_type.shape[0], np.float32), np.zeros(d.base_type.shape[0], np.int32)) for d in sample]
+    for d, s in zip(sample, side):
+        for t in d.transforms:
+            if t.kind == A.X_QUANTIZE_SYNTH:
+                t.side0, t.side1 = s
+    times, bytes_step = [], 0
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        b = 0
+        for d, x in zip(sample, data):
+            c = orc.fold(d.base_type, x, False, d.transforms)
+            folded = c.copyTo()
+            stream, _ = orc.btc_compress(folded)
+            b += d.nbytes + folded.size + 4 * d.base_type.shape[0] + folded.size + stream.size
+        dt = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dt)
+            bytes_step = b
+    for d in sample:
+        for t in d.transforms:
+            t.side0 = t.side1 = None
+    sec = float(np.mean(times))
+    desc = f"{len(sample)} linear tensors ({sum(d.nbytes for d in sample) // 2} elements) of the 7B-shape model, fold + codec"
+    return bytes_step / sec / 1e9, sec * 1e3, cores, desc
+
+
+# ----------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layers", type=int, default=32, help="decoder layers of the 7B-shape workload (32 = the named config)")
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cpu-budget", type=int, default=220_000_000, help="elements of the CPU sample")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    decls = llama7b_decls(layers=args.layers)
+    workload = f"llama7b-shape fold: {len([d for d in decls if d.transforms])} linear f16 weights -> sym int8 per-channel " \
+               f"-> Reorder -> Swizzle(5) -> block codec; {len(decls)} constants, layers={args.layers}"
+    config = {"workload": workload, "sharding": "by tensor (LPT)", "l2": "per-step working set (>26 GB at N=1) exceeds L2",
+              "layers": args.layers}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        gbs, ms, cores, desc = run_cpu(decls, max(1, args.steps), max(0, args.warmup), args.cpu_budget)
+        line = {"impl": "reference", "metric": "folded_weight_GBps", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "f16->i8", "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": desc},
+                "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    import torch
+    import torch.distributed as dist
+    from npu_plugin_b200.const import CudaBackend
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    backend = CudaBackend(local_rank)
+    lib, ctx = backend.lib, backend.ctx
+    # a real (non-default) stream shared by torch and the library, so that torch's CUDA events are
+    # recorded on the stream the kernels are launched on (the default stream's handle is 0, which
+    # b200c_set_stream reads as "use the context's own stream")
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    assert stream.cuda_stream != 0
+    lib.b200c_set_stream(ctx, C.c_void_p(stream.cuda_stream))
+
+    owner = partition(decls, world)
+    mine = [d for d, o in zip(decls, owner) if o == rank]
+    folder = ShardFolder(backend, mine)
+
+    # device buffers (torch owns the memory; the library only sees pointers)
+    inputs = [torch.empty(d.nbytes, dtype=torch.uint8, device="cuda") for d in mine]
+    for i, d in enumerate(mine):
+        rc = lib.b200c_synth_fill(ctx, inputs[i].data_ptr(), d.nbytes // 2, A.F16, 0, 0.02 if d.transforms else 1.0, 0.0,
+                                  5, decls.index(d))
+        assert rc == 0, lib.b200c_last_error()
+    in_ptrs = [t.data_ptr() for t in inputs]
+    folded = torch.empty(folder.folded_bytes, dtype=torch.uint8, device="cuda")
+    blob = torch.empty(folder.blob_bound, dtype=torch.uint8, device="cuda")
+    scales = [torch.empty(d.base_type.shape[0], dtype=torch.float32, device="cuda") if d.transforms else None for d in mine]
+    zps = [torch.empty(d.base_type.shape[0], dtype=torch.int32, device="cuda") if d.transforms else None for d in mine]
+    side = [(s.data_ptr(), z.data_ptr()) if s is not None else None for s, z in zip(scales, zps)]
+    # rank 0 assembles the model blob: its own segments plus every other rank's
+    gather_cap = None
+    gathered = None
+
+    seg_info = {}
+
+    def step(timers=None):
+        if timers:
+            timers[0].record(stream)
+        folder.fold(in_ptrs, folded.data_ptr(), True, side)
+        if timers:
+            timers[1].record(stream)
+        segs = folder.compress(folded.data_ptr(), blob.data_ptr(), blob.numel())
+        if timers:
+            timers[2].record(stream)
+        used = max([o + s for _, o, s, _ in segs], default=0)
+        seg_info["segs"], seg_info["used"] = segs, used
+        if world > 1:
+            nonlocal gathered, gather_cap
+            sizes = torch.tensor([used], dtype=torch.int64, device="cuda")
+            all_sizes = [torch.zeros(1, dtype=torch.int64, device="cuda") for _ in range(world)]
+            dist.all_gather(all_sizes, sizes)
+            all_sizes = [int(s.item()) for s in all_sizes]
+            if rank == 0:
+                total = sum(all_sizes)
+                if gathered is None or gathered.numel() < total:
+                    gathered = torch.empty(int(total * 1.05) + 1024, dtype=torch.uint8, device="cuda")
+                at = all_sizes[0]
+                gathered[:at].copy_(blob[:at])
+                reqs = []
+                for r in range(1, world):
+                    if all_sizes[r]:
+                        reqs.append(dist.irecv(gathered[at:at + all_sizes[r]], src=r))
+                    at += all_sizes[r]
+                for q in reqs:
+                    q.wait()
+            elif used:
+                dist.send(blob[:used], dst=0)
+            seg_info["gathered"] = sum(all_sizes)
+        if timers:
+            timers[3].record(stream)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()  # sampled from the warm-up on: the timed region can be shorter than nvidia-smi's start-up
+    for _ in range(max(args.warmup, 0)):
+        step()
+    sync_all()
+    launches0 = backend.launch_count()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin.record(stream)
+    for k in range(args.steps):
+        step(ev[k])
+    t_end.record(stream)
+    sync_all()
+    clocks = sampler.stop()
+    launches = backend.launch_count() - launches0
+    elapsed_ms = t_begin.elapsed_time(t_end)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+        ln = torch.tensor([launches], dtype=torch.int64, device="cuda")
+        dist.all_reduce(ln)
+        launches = int(ln.item())
+    ms_per_step = elapsed_ms / args.steps
+    fold_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in ev]))
+    codec_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in ev]))
+    gather_ms = float(np.mean([e[2].elapsed_time(e[3]) for e in ev]))
+
+    # algorithmic bytes of the whole job (all ranks)
+    blob_sizes_local = {i: s for i, _, s, _ in seg_info["segs"]}
+    fold_b, codec_b = algorithmic_bytes(mine, folder.folded_sizes, [blob_sizes_local.get(i) for i in range(len(mine))])
+    tot = torch.tensor([fold_b, codec_b, sum(1 for _, _, _, c in seg_info["segs"] if c), seg_info["used"]],
+                       dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(tot)
+    fold_all, codec_all, n_compressed, blob_bytes = [float(x) for x in tot.tolist()]
+    value = (fold_all + codec_all) / (ms_per_step * 1e-3) / 1e9
+
+    # roofline of the dominant kernel: the fused fold pass, one launch per linear weight
+    peak, peak_kind = measured_peak()
+    n_fold_launch = len([d for d in mine if d.transforms])
+    fold_local_b, _ = algorithmic_bytes(mine, folder.folded_sizes, [None] * len(mine))
+    achieved = fold_local_b / (fold_ms * 1e-3) / 1e9 if fold_ms > 0 else 0.0
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None, "peak_kind": peak_kind, "kernel": "fold pass (per-tensor quantise+reorder+swizzle)",
+                "launches_per_step": n_fold_launch, "avg_launch_ms": fold_ms / max(1, n_fold_launch),
+                "phase_ms": {"fold": fold_ms, "codec": codec_ms, "gather": gather_ms}}
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            roofline["traffic"] = json.load(f).get("fold_dram_bytes_per_launch")
+    except Exception:
+        pass
+
+    # end to end through the C ABI with host buffers (pinned), copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        host_in = [torch.empty(d.nbytes, dtype=torch.uint8, pin_memory=True) for d in mine]
+        for h, t in zip(host_in, inputs):
+            h.copy_(t)
+        torch.cuda.synchronize()
+        host_blob = torch.empty(blob.numel(), dtype=torch.uint8, pin_memory=True)
+        host_ptrs = [h.data_ptr() for h in host_in]
+
+        def e2e_step():
+            folder.fold(host_ptrs, folded.data_ptr(), False, side)
+            segs = folder.compress(folded.data_ptr(), blob.data_ptr(), blob.numel())
+            used = max([o + s for _, o, s, _ in segs], default=0)
+            host_blob[:used].copy_(blob[:used], non_blocking=True)
+            # uncompressed pass-through constants are part of the blob as well
+            return used
+
+        e2e_step()
+        sync_all()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        used = 0
+        for _ in range(max(1, args.e2e_steps)):
+            used = e2e_step()
+        b.record(stream)
+        sync_all()
+        ems = a.elapsed_time(b) / max(1, args.e2e_steps)
+        if world > 1:
+            t = torch.tensor([ems], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ems = float(t.item())
+        h2d = torch.tensor([sum(d.nbytes for d in mine), used], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(h2d)
+        e2e = {"value": (fold_all + codec_all) / (ems * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ems,
+               "h2d_bytes_per_step": int(h2d[0].item()), "d2h_bytes_per_step": int(h2d[1].item())}
+        del host_in, host_blob
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        gbs, ms, cores, desc = run_cpu(decls, 1, 0, args.cpu_budget)
+        cpu = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": desc, "ms_per_sample": ms}
+
+    if rank == 0:
+        line = {"metric": "folded_weight_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "f16->i8", "data": "synthetic", "config": config, "clocks": clocks,
+                "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu,
+                "bytes": {"fold": fold_all, "codec": codec_all, "blob": blob_bytes, "compressed_tensors": n_compressed},
+                "per_gpu_GBps": value / world}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

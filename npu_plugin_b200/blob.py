@@ -1,0 +1,104 @@
+"""Whole-model constant folding: the B200 counterpart of the reference's blob constant writer.
+
+The reference serialises a model's constants with a parallel loop over every Const::DeclareOp --
+fold(), then copyTo() into an 8-byte aligned buffer (serializeBinaryData,
+src/vpux_compiler/src/dialect/VPUIP/graph-schema/export.cpp:453-493) -- after the weight compression
+pass replaced compressible ones (src/vpux_compiler/src/dialect/VPUIP/passes/compress_weights_btc.cpp:64-72,
+120-136).  Here the declarations of one rank's shard are folded back to back on the device into one
+"folded" arena and then compressed in one batched call; segments that do not shrink, or are below
+the 4 KB gate, stay uncompressed, as the reference leaves them.
+
+Descriptors are marshalled once (prepare) so that a step is only C ABI calls.
+"""
+import ctypes as C
+
+from . import _cabi as A
+from .const import NDType, chain_to_c, out_type_slot, raise_for
+
+MIN_COMPRESS_BYTES = 4096  # MIN_INPUT_SIZE = 4_KB, compress_weights_btc.cpp:120-125
+SEGMENT_ALIGN = 512        # folded segments start on a swizzle-block boundary (>= the 8 bytes of export.cpp:473-476)
+
+
+class ConstantDecl:
+    """One constant: base content (pointer + byte size + type) and its transformation list."""
+
+    def __init__(self, name, base_type, transforms, nbytes, compress=True, is_splat=False):
+        self.name, self.base_type, self.transforms = name, base_type, list(transforms)
+        self.nbytes, self.compress, self.is_splat = int(nbytes), bool(compress), bool(is_splat)
+
+
+def partition(decls, world_size):
+    """Deterministic longest-processing-time assignment of constants to ranks by input bytes."""
+    order = sorted(range(len(decls)), key=lambda i: (-decls[i].nbytes, i))
+    load = [0] * world_size
+    owner = [0] * len(decls)
+    for i in order:
+        r = min(range(world_size), key=lambda k: (load[k], k))
+        owner[i] = r
+        load[r] += decls[i].nbytes
+    return owner
+
+
+class ShardFolder:
+    """Folds and compresses the constants one rank owns.  All buffers are caller-provided device
+    (or pinned host) memory; nothing is allocated per step."""
+
+    def __init__(self, backend, decls):
+        self.b, self.lib, self.ctx = backend, backend.lib, backend.ctx
+        self.decls = decls
+        self._keep = []
+        self._prepared = []
+        self.folded_offsets, self.folded_sizes = [], []
+        at = 0
+        for d in decls:
+            final = backend.infer_type(d.base_type, d.transforms)
+            size = final.getTotalAllocSize()
+            bt = d.base_type.to_c(self._keep)
+            ch = chain_to_c(d.transforms, self._keep)
+            ot = out_type_slot(1, self._keep)
+            self._prepared.append((bt, ch, len(d.transforms), ot))
+            self.folded_offsets.append(at)
+            self.folded_sizes.append(size)
+            at = (at + size + SEGMENT_ALIGN - 1) // SEGMENT_ALIGN * SEGMENT_ALIGN
+        self.folded_bytes = max(at, 1)
+        n = max(1, len(decls))
+        self._in_ptrs = (C.c_void_p * n)()
+        self._sizes = (C.c_size_t * n)()
+        self._out_off = (C.c_size_t * n)()
+        self._out_size = (C.c_size_t * n)()
+        self._not_smaller = (C.c_int32 * n)()
+        self._nb = C.c_size_t()
+        self.comp_idx = [i for i, d in enumerate(decls) if d.compress and self.folded_sizes[i] >= MIN_COMPRESS_BYTES]
+        self.blob_bound = sum((backend.btc_bound(self.folded_sizes[i]) + 31) // 32 * 32 for i in self.comp_idx) + 64
+
+    def fold(self, data_ptrs, folded_ptr, data_on_device=True, side_ptrs=None):
+        """fold() + copyTo() of every constant into folded_ptr + folded_offsets[i] (asynchronous when
+        everything is on the device; errors surface at the next synchronising call)."""
+        lib, ctx = self.lib, self.ctx
+        flags = A.FOLD_ASYNC
+        for i, (bt, ch, n, ot) in enumerate(self._prepared):
+            d = self.decls[i]
+            if side_ptrs is not None and side_ptrs[i] is not None:
+                for k in range(n):
+                    if ch[k].kind == A.X_QUANTIZE_SYNTH:
+                        ch[k].side0, ch[k].side1 = side_ptrs[i]
+            rc = lib.b200c_fold(ctx, C.byref(bt), data_ptrs[i], d.nbytes, int(d.is_splat), int(data_on_device), ch, n,
+                                folded_ptr + self.folded_offsets[i], self.folded_sizes[i], 1, C.byref(self._nb), None,
+                                flags)
+            if rc != A.OK:
+                raise_for(rc, lib.b200c_last_error())
+
+    def compress(self, folded_ptr, blob_ptr, blob_cap):
+        """Batched block compression of the folded segments into blob_ptr.  Returns a list of
+        (decl index, blob offset, size, compressed flag); synchronises."""
+        k = len(self.comp_idx)
+        if k == 0:
+            raise_for(self.lib.b200c_synchronize(self.ctx), self.lib.b200c_last_error())
+            return []
+        for j, i in enumerate(self.comp_idx):
+            self._in_ptrs[j] = folded_ptr + self.folded_offsets[i]
+            self._sizes[j] = self.folded_sizes[i]
+        rc = self.lib.b200c_btc_compress_batch(self.ctx, k, self._in_ptrs, self._sizes, blob_ptr, blob_cap,
+                                               self._out_off, self._out_size, self._not_smaller)
+        raise_for(rc, self.lib.b200c_last_error())
+        return [(i, self._out_off[j], self._out_size[j], not self._not_smaller[j]) for j, i in enumerate(self.comp_idx)]

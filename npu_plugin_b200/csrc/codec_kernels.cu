@@ -15,102 +15,189 @@ size_t codecBound(size_t n) {
     return static_cast<size_t>(roundUp(static_cast<int64_t>(kCodecHeaderBytes + 4 * supers + 65 * blocks), 32));
 }
 
-B2_HD int jobOfBlock(const CodecJobDev* jobs, int njobs, unsigned long long g) {
-    int lo = 0, hi = njobs - 1;
-    while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (jobs[mid].firstBlock <= g) {
-            lo = mid;
-        } else {
-            hi = mid - 1;
-        }
-    }
-    return lo;
-}
+// Blocks are indexed in a padded space in which every buffer starts on a tile boundary
+// (kTileBlocks blocks), so one tile never straddles two buffers.
+constexpr int kTileBlocks = 4096;
+constexpr int kIterBlocks = 64;  // blocks handled per CTA iteration: 256 threads, 4 lanes per block
 
 B2_HD void loadBlock(const CodecJobDev& job, unsigned long long blk, unsigned char* b) {
     const unsigned long long first = blk * kCodecBlock;
     const unsigned char* src = job.in + first;
-#ifdef __CUDA_ARCH__
-    if (first + kCodecBlock <= job.n && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-        uint4* d = reinterpret_cast<uint4*>(b);
-        const uint4* s = reinterpret_cast<const uint4*>(src);
-        d[0] = s[0];
-        d[1] = s[1];
-        d[2] = s[2];
-        d[3] = s[3];
-        return;
-    }
-#endif
     for (int i = 0; i < kCodecBlock; ++i) b[i] = (first + i < job.n) ? src[i] : 0;
 }
 
 // ---------------------------------------------------------------------------- analyze
-B2_HD void analyzeOne(const CodecJobDev* jobs, int njobs, unsigned long long g, unsigned char* headers,
-                      unsigned char* bases, unsigned char* sizes) {
-    const CodecJobDev& job = jobs[jobOfBlock(jobs, njobs, g)];
-    const unsigned long long blk = g - job.firstBlock;
-    if (blk >= job.nblocks) {
-        sizes[g] = 0;
-        headers[g] = 0;
-        bases[g] = 0;
-        return;
+// Four lanes share a 64-byte block: each loads 16 bytes (one coalesced 512-byte request per warp),
+// reduces min / max / zigzag-or / non-zero count with byte-SIMD instructions, and the four partial
+// results are combined with two shuffle steps.
+__device__ __forceinline__ unsigned int zigzag4(unsigned int x) {
+    return ((x << 1) & 0xFEFEFEFEu) ^ (((x >> 7) & 0x01010101u) * 0xFFu);
+}
+
+struct LaneStats {
+    unsigned int mn, mx, zor, nnz;
+};
+
+__device__ __forceinline__ LaneStats statsOf(uint4 v) {
+    LaneStats s;
+    unsigned int m = __vminu4(__vminu4(v.x, v.y), __vminu4(v.z, v.w));
+    m = __vminu4(m, m >> 16);
+    s.mn = __vminu4(m, m >> 8) & 0xFFu;
+    unsigned int M = __vmaxu4(__vmaxu4(v.x, v.y), __vmaxu4(v.z, v.w));
+    M = __vmaxu4(M, M >> 16);
+    s.mx = __vmaxu4(M, M >> 8) & 0xFFu;
+    unsigned int o = zigzag4(v.x) | zigzag4(v.y) | zigzag4(v.z) | zigzag4(v.w);
+    o |= o >> 16;
+    s.zor = (o | (o >> 8)) & 0xFFu;
+    s.nnz = (__popc(__vcmpne4(v.x, 0)) + __popc(__vcmpne4(v.y, 0)) + __popc(__vcmpne4(v.z, 0)) +
+             __popc(__vcmpne4(v.w, 0))) >> 3;
+    return s;
+}
+
+__device__ __forceinline__ LaneStats groupReduce(LaneStats s) {
+#pragma unroll
+    for (int o = 1; o <= 2; o <<= 1) {
+        s.mn = min(s.mn, __shfl_xor_sync(0xFFFFFFFFu, s.mn, o));
+        s.mx = max(s.mx, __shfl_xor_sync(0xFFFFFFFFu, s.mx, o));
+        s.zor |= __shfl_xor_sync(0xFFFFFFFFu, s.zor, o);
+        s.nnz += __shfl_xor_sync(0xFFFFFFFFu, s.nnz, o);
     }
-    alignas(16) unsigned char b[kCodecBlock];
-    loadBlock(job, blk, b);
-    unsigned char h, base;
-    sizes[g] = static_cast<unsigned char>(codecChoose(b, &h, &base));
-    headers[g] = h;
-    bases[g] = base;
+    return s;
 }
 
-__global__ void __launch_bounds__(128) codecAnalyzeKernel(const CodecJobDev* __restrict__ jobs, int njobs,
-                                                          unsigned long long totalBlocks, unsigned char* headers,
-                                                          unsigned char* bases, unsigned char* sizes) {
-    const unsigned long long step = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
-    for (unsigned long long g = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; g < totalBlocks;
-         g += step) {
-        analyzeOne(jobs, njobs, g, headers, bases, sizes);
+// same decision as codecChoose(), from the reduced statistics
+__device__ __forceinline__ int chooseFromStats(LaneStats s, unsigned int* header) {
+    int mode = 0, w = 0, size = 65;
+    if (s.mn == s.mx) {
+        mode = 1;
+        size = 2;
     }
+    const int wu = 32 - __clz(s.mx - s.mn);
+    if (wu >= 1 && wu <= 7 && 2 + 8 * wu < size) {
+        mode = 2;
+        w = wu;
+        size = 2 + 8 * wu;
+    }
+    const int ws = 32 - __clz(s.zor);
+    if (ws >= 1 && ws <= 7 && 1 + 8 * ws < size) {
+        mode = 3;
+        w = ws;
+        size = 1 + 8 * ws;
+    }
+    if (9 + static_cast<int>(s.nnz) < size) {
+        mode = 4;
+        w = 0;
+        size = 9 + static_cast<int>(s.nnz);
+    }
+    *header = static_cast<unsigned int>((mode << 5) | w);
+    return size;
 }
 
-// ---------------------------------------------------------------------------- exclusive scan (u8 -> u64)
-constexpr int kScanThreads = 256;
-constexpr int kScanPerThread = 16;
-constexpr int kScanTile = kScanThreads * kScanPerThread;
-
-__device__ __forceinline__ unsigned int blockReduceSum(unsigned int v, unsigned int* smem) {
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
-    if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
-    __syncthreads();
-    unsigned int t = 0;
-    for (int w = 0; w < kScanThreads / 32; ++w) t += smem[w];
-    __syncthreads();
-    return t;
+__device__ __forceinline__ uint4 loadLane16(const CodecJobDev& job, unsigned long long blk, int lane4, bool vec) {
+    const unsigned long long first = blk * kCodecBlock + static_cast<unsigned long long>(lane4) * 16;
+    if (vec && first + 16 <= job.n) return __ldg(reinterpret_cast<const uint4*>(job.in + first));
+    unsigned int w[4] = {0, 0, 0, 0};
+    for (int i = 0; i < 16; ++i) {
+        if (first + i < job.n) w[i >> 2] |= static_cast<unsigned int>(job.in[first + i]) << (8 * (i & 3));
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-__global__ void __launch_bounds__(kScanThreads) scanTileSumsKernel(const unsigned char* __restrict__ in,
-                                                                   unsigned long long n, unsigned int* tileSums,
-                                                                   unsigned long long ntiles) {
-    __shared__ unsigned int smem[kScanThreads / 32];
-    for (unsigned long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
-        const unsigned long long first = t * kScanTile + static_cast<unsigned long long>(threadIdx.x) * kScanPerThread;
-        unsigned int s = 0;
-        if (first + kScanPerThread <= n) {
-            const uint4 v = *reinterpret_cast<const uint4*>(in + first);
-            s = __vsadu4(v.x, 0) + __vsadu4(v.y, 0) + __vsadu4(v.z, 0) + __vsadu4(v.w, 0);
-        } else {
-            for (int i = 0; i < kScanPerThread; ++i)
-                if (first + i < n) s += in[first + i];
+__global__ void __launch_bounds__(256) codecAnalyzeKernel(const CodecJobDev* __restrict__ jobs,
+                                                          const unsigned int* __restrict__ tileJob,
+                                                          unsigned long long ntiles, unsigned char* __restrict__ headers,
+                                                          unsigned char* __restrict__ bases,
+                                                          unsigned char* __restrict__ sizes,
+                                                          unsigned int* __restrict__ tileSums) {
+    __shared__ unsigned int red[8];
+    const int grp = threadIdx.x >> 2, lane4 = threadIdx.x & 3;
+    for (unsigned long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const CodecJobDev& job = jobs[tileJob[tile]];
+        const bool vec = (reinterpret_cast<uintptr_t>(job.in) & 15) == 0;
+        const unsigned long long tileFirst = (tile - job.firstBlock / kTileBlocks) * kTileBlocks;
+        unsigned int sum = 0;
+        const unsigned long long left = job.nblocks - tileFirst;  // blocks of the buffer from this tile on
+        const int iters = left >= kTileBlocks ? kTileBlocks / kIterBlocks
+                                              : static_cast<int>((left + kIterBlocks - 1) / kIterBlocks);
+        constexpr int UNROLL = 4;  // independent 128-bit loads in flight per thread
+        for (int it0 = 0; it0 < iters; it0 += UNROLL) {
+            uint4 v[UNROLL];
+            bool valid[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const unsigned long long blk = tileFirst + static_cast<unsigned long long>(it0 + u) * kIterBlocks + grp;
+                valid[u] = (it0 + u) < iters && blk < job.nblocks;
+                v[u] = valid[u] ? loadLane16(job, blk, lane4, vec) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                if (it0 + u >= iters) break;
+                LaneStats st;
+                st.mn = 255;
+                st.mx = 0;
+                st.zor = 0;
+                st.nnz = 0;
+                if (valid[u]) st = statsOf(v[u]);
+                st = groupReduce(st);
+                if (lane4 == 0) {
+                    const unsigned long long g =
+                            tile * kTileBlocks + static_cast<unsigned long long>(it0 + u) * kIterBlocks + grp;
+                    unsigned int header = 0;
+                    const int size = valid[u] ? chooseFromStats(st, &header) : 0;
+                    headers[g] = static_cast<unsigned char>(header);
+                    bases[g] = static_cast<unsigned char>(st.mn);
+                    sizes[g] = static_cast<unsigned char>(size);
+                    sum += size;
+                }
+            }
         }
-        const unsigned int total = blockReduceSum(s, smem);
-        if (threadIdx.x == 0) tileSums[t] = total;
+        // the rest of the tile is padding: its sizes must read as zero
+        for (unsigned long long r = static_cast<unsigned long long>(iters) * kIterBlocks + threadIdx.x; r < kTileBlocks;
+             r += blockDim.x) {
+            sizes[tile * kTileBlocks + r] = 0;
+        }
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned int t = 0;
+            for (int w = 0; w < 8; ++w) t += red[w];
+            tileSums[tile] = t;
+        }
+        __syncthreads();
     }
 }
 
-// single CTA: exclusive scan of the tile sums; also stores the grand total at tileOffsets[ntiles]
-__global__ void __launch_bounds__(1024) scanTilesKernel(const unsigned int* __restrict__ tileSums,
-                                                        unsigned long long ntiles, unsigned long long* tileOffsets) {
+// ---------------------------------------------------------------------------- layout
+// Per-buffer record bytes, stream size, "not smaller" flag and output placement (each segment
+// starts on a 32-byte boundary).  tileOffsets is the exclusive prefix sum of the per-tile sums.
+B2_HD void layoutJobs(CodecJobDev* jobs, int njobs, const unsigned long long* tileOffsets, unsigned long long outCap,
+                      int rawFallback, int* err) {
+    unsigned long long run = 0;
+    for (int j = 0; j < njobs; ++j) {
+        CodecJobDev& job = jobs[j];
+        const unsigned long long t0 = job.firstBlock / kTileBlocks;
+        const unsigned long long t1 = t0 + (job.nblocks + kTileBlocks - 1) / kTileBlocks;
+        job.recordsBytes = tileOffsets[t1] - tileOffsets[t0];
+        const unsigned long long raw = kCodecHeaderBytes + 4 * job.nsuper + job.recordsBytes;
+        job.streamBytes = (raw + 31) & ~31ull;
+        job.notSmaller = job.n <= job.streamBytes;  // bit_compactor_codec.cpp:36-39
+        job.outBytes = (rawFallback && job.notSmaller) ? job.n : job.streamBytes;
+        job.outBase = run;
+        run = (run + job.outBytes + 31) & ~31ull;
+        if (job.outBase + job.outBytes > outCap) {
+            if (*err == E_NONE) *err = E_CODEC;
+            job.outBytes = 0;
+        }
+    }
+}
+
+// single CTA: exclusive scan of the tile sums (the device prefix sum behind every record offset),
+// grand total at tileOffsets[ntiles], then the per-buffer layout
+__global__ void __launch_bounds__(1024) codecScanKernel(const unsigned int* __restrict__ tileSums,
+                                                        unsigned long long ntiles, unsigned long long* tileOffsets,
+                                                        CodecJobDev* jobs, int njobs, unsigned long long outCap,
+                                                        int rawFallback, int* err) {
     __shared__ unsigned long long warpSum[32];
     __shared__ unsigned long long carry;
     if (threadIdx.x == 0) carry = 0;
@@ -141,94 +228,11 @@ __global__ void __launch_bounds__(1024) scanTilesKernel(const unsigned int* __re
         if (threadIdx.x == blockDim.x - 1) carry = before + mine;
         __syncthreads();
     }
-    if (threadIdx.x == 0) tileOffsets[ntiles] = carry;
-}
-
-__global__ void __launch_bounds__(kScanThreads) scanScatterKernel(const unsigned char* __restrict__ in,
-                                                                  unsigned long long n,
-                                                                  const unsigned long long* __restrict__ tileOffsets,
-                                                                  unsigned long long* __restrict__ out,
-                                                                  unsigned long long ntiles) {
-    __shared__ unsigned int warpSum[kScanThreads / 32];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (unsigned long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
-        const unsigned long long first = t * kScanTile + static_cast<unsigned long long>(threadIdx.x) * kScanPerThread;
-        unsigned char v[kScanPerThread];
-        unsigned int s = 0;
-        for (int i = 0; i < kScanPerThread; ++i) {
-            v[i] = (first + i < n) ? in[first + i] : 0;
-            s += v[i];
-        }
-        unsigned int incl = s;
-        for (int o = 1; o < 32; o <<= 1) {
-            const unsigned int x = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-            if (lane >= o) incl += x;
-        }
-        if (lane == 31) warpSum[warp] = incl;
-        __syncthreads();
-        unsigned int before = incl - s;
-        for (int w = 0; w < warp; ++w) before += warpSum[w];
-        unsigned long long run = tileOffsets[t] + before;
-        for (int i = 0; i < kScanPerThread; ++i) {
-            if (first + i < n) out[first + i] = run;
-            run += v[i];
-        }
-        __syncthreads();
+    if (threadIdx.x == 0) {
+        tileOffsets[ntiles] = carry;
+        __threadfence_block();
+        layoutJobs(jobs, njobs, tileOffsets, outCap, rawFallback, err);
     }
-    if (blockIdx.x == 0 && threadIdx.x == 0) out[n] = tileOffsets[ntiles];
-}
-
-// Exclusive prefix sum of n byte-sized values into out[0..n]; out[n] is the total.
-static void exclusiveScanU8(Context* ctx, const unsigned char* in, unsigned long long n, unsigned long long* out) {
-#ifdef B200C_HOST_EMULATION
-    if (B2_EMU(ctx)) {
-        unsigned long long run = 0;
-        for (unsigned long long i = 0; i < n; ++i) {
-            out[i] = run;
-            run += in[i];
-        }
-        out[n] = run;
-        ctx->launches += 3;
-        return;
-    }
-#endif
-    const unsigned long long ntiles = (n + kScanTile - 1) / kScanTile;
-    unsigned int* tileSums = static_cast<unsigned int*>(ctx->arena.alloc((ntiles + 1) * sizeof(unsigned int)));
-    unsigned long long* tileOffsets =
-            static_cast<unsigned long long*>(ctx->arena.alloc((ntiles + 1) * sizeof(unsigned long long)));
-    const int grid = static_cast<int>(std::max<unsigned long long>(1, std::min<unsigned long long>(ntiles, ctx->smCount * 8ULL)));
-    scanTileSumsKernel<<<grid, kScanThreads, 0, ctx->stream>>>(in, n, tileSums, ntiles);
-    scanTilesKernel<<<1, 1024, 0, ctx->stream>>>(tileSums, ntiles, tileOffsets);
-    scanScatterKernel<<<grid, kScanThreads, 0, ctx->stream>>>(in, n, tileOffsets, out, ntiles);
-    B2_CUDA(cudaGetLastError());
-    ctx->launches += 3;
-}
-
-// ---------------------------------------------------------------------------- layout
-// Single thread: per-buffer record bytes, stream size, "not smaller" flag and output placement
-// (each segment starts on a 32-byte boundary).
-B2_HD void layoutJobs(CodecJobDev* jobs, int njobs, const unsigned long long* offsets, unsigned long long outCap,
-                      int rawFallback, int* err) {
-    unsigned long long run = 0;
-    for (int j = 0; j < njobs; ++j) {
-        CodecJobDev& job = jobs[j];
-        job.recordsBytes = offsets[job.firstBlock + job.nblocks] - offsets[job.firstBlock];
-        const unsigned long long raw = kCodecHeaderBytes + 4 * job.nsuper + job.recordsBytes;
-        job.streamBytes = (raw + 31) & ~31ull;
-        job.notSmaller = job.n <= job.streamBytes;  // bit_compactor_codec.cpp:36-39
-        job.outBytes = (rawFallback && job.notSmaller) ? job.n : job.streamBytes;
-        job.outBase = run;
-        run = (run + job.outBytes + 31) & ~31ull;
-        if (job.outBase + job.outBytes > outCap) {
-            if (*err == E_NONE) *err = E_CODEC;
-            job.outBytes = 0;
-        }
-    }
-}
-
-__global__ void codecLayoutKernel(CodecJobDev* jobs, int njobs, const unsigned long long* offsets,
-                                  unsigned long long outCap, int rawFallback, int* err) {
-    if (blockIdx.x == 0 && threadIdx.x == 0) layoutJobs(jobs, njobs, offsets, outCap, rawFallback, err);
 }
 
 // ---------------------------------------------------------------------------- emit
@@ -243,50 +247,161 @@ B2_HD void putU64(unsigned char* p, unsigned long long v) {
     putU32(p + 4, static_cast<unsigned int>(v >> 32));
 }
 
-B2_HD void emitOne(const CodecJobDev* jobs, int njobs, unsigned long long g, const unsigned char* headers,
-                   const unsigned char* bases, const unsigned long long* offsets, unsigned char* out,
-                   int rawFallback) {
-    const CodecJobDev& job = jobs[jobOfBlock(jobs, njobs, g)];
-    const unsigned long long blk = g - job.firstBlock;
-    if (blk >= job.nblocks || job.outBytes == 0) return;
-    unsigned char* dst = out + job.outBase;
-    alignas(16) unsigned char b[kCodecBlock];
-    loadBlock(job, blk, b);
-    if (rawFallback && job.notSmaller) {  // segment keeps the input bytes
-        const unsigned long long first = blk * kCodecBlock;
-        for (int i = 0; i < kCodecBlock && first + i < job.n; ++i) dst[first + i] = b[i];
-        return;
-    }
-    const unsigned long long rel = offsets[g] - offsets[job.firstBlock];
-    unsigned char* records = dst + kCodecHeaderBytes + 4 * job.nsuper;
-    codecWriteRecord(b, headers[g], bases[g], records + rel);
-    if (blk % kCodecSuper == 0) putU32(dst + kCodecHeaderBytes + 4 * (blk / kCodecSuper), static_cast<unsigned int>(rel));
-    if (blk == 0) {
-        dst[0] = 'B';
-        dst[1] = '2';
-        dst[2] = 'B';
-        dst[3] = 'C';
-        putU32(dst + 4, 1);
-        putU64(dst + 8, job.n);
-        putU64(dst + 16, job.nblocks);
-        putU32(dst + 24, static_cast<unsigned int>(job.nsuper));
-        putU32(dst + 28, 0);
-    }
-    if (blk + 1 == job.nblocks) {
-        for (unsigned long long a = kCodecHeaderBytes + 4 * job.nsuper + job.recordsBytes; a < job.streamBytes; ++a) dst[a] = 0;
-    }
+B2_HD void writeStreamHeader(const CodecJobDev& job, unsigned char* dst) {
+    dst[0] = 'B';
+    dst[1] = '2';
+    dst[2] = 'B';
+    dst[3] = 'C';
+    putU32(dst + 4, 1);
+    putU64(dst + 8, job.n);
+    putU64(dst + 16, job.nblocks);
+    putU32(dst + 24, static_cast<unsigned int>(job.nsuper));
+    putU32(dst + 28, 0);
 }
 
-__global__ void __launch_bounds__(128) codecEmitKernel(const CodecJobDev* __restrict__ jobs, int njobs,
-                                                       unsigned long long totalBlocks,
+// One CTA per tile of a buffer that is being compressed.  Record offsets inside the tile come from
+// a block-wide exclusive scan of the tile's record sizes added to the tile's global offset.  Every
+// iteration encodes 64 blocks into a shared-memory window laid out like the output (same 16-byte
+// phase), which is then copied out with 128-bit stores.
+__global__ void __launch_bounds__(256) codecEmitKernel(const CodecJobDev* __restrict__ jobs,
+                                                       const unsigned int* __restrict__ tileJob,
+                                                       const unsigned int* __restrict__ emitTiles,
+                                                       unsigned long long nEmitTiles,
                                                        const unsigned char* __restrict__ headers,
                                                        const unsigned char* __restrict__ bases,
-                                                       const unsigned long long* __restrict__ offsets,
-                                                       unsigned char* out, int rawFallback) {
-    const unsigned long long step = static_cast<unsigned long long>(gridDim.x) * blockDim.x;
-    for (unsigned long long g = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; g < totalBlocks;
-         g += step) {
-        emitOne(jobs, njobs, g, headers, bases, offsets, out, rawFallback);
+                                                       const unsigned char* __restrict__ sizes,
+                                                       const unsigned long long* __restrict__ tileOffsets,
+                                                       unsigned char* __restrict__ out) {
+    __shared__ unsigned int relOff[kTileBlocks + 1];                        // record offsets inside the tile
+    __shared__ __align__(16) unsigned char window[kIterBlocks * 65 + 48];   // one iteration's records
+    __shared__ unsigned int warpTot[8];
+    const int grp = threadIdx.x >> 2, lane4 = threadIdx.x & 3;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    for (unsigned long long e = blockIdx.x; e < nEmitTiles; e += gridDim.x) {
+        const unsigned long long tile = emitTiles[e];
+        const CodecJobDev& job = jobs[tileJob[tile]];
+        const bool vec = (reinterpret_cast<uintptr_t>(job.in) & 15) == 0;
+        const unsigned long long jobFirstTile = job.firstBlock / kTileBlocks;
+        const unsigned long long tileFirst = (tile - jobFirstTile) * kTileBlocks;  // first block of the tile in the job
+        unsigned char* dst = out + job.outBase;
+        unsigned char* records = dst + kCodecHeaderBytes + 4 * job.nsuper;
+        const unsigned long long tileRel = tileOffsets[tile] - tileOffsets[jobFirstTile];
+
+        // exclusive scan of the 4096 record sizes: 16 per thread
+        {
+            const unsigned char* sz = sizes + tile * kTileBlocks + threadIdx.x * 16;
+            const uint4 v = *reinterpret_cast<const uint4*>(sz);
+            const unsigned int w[4] = {v.x, v.y, v.z, v.w};
+            unsigned int local[16], s = 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                local[i] = s;
+                s += (w[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+            }
+            unsigned int incl = s;
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned int x = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if (lane >= o) incl += x;
+            }
+            if (lane == 31) warpTot[warp] = incl;
+            __syncthreads();
+            unsigned int before = incl - s;
+            for (int wv = 0; wv < warp; ++wv) before += warpTot[wv];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) relOff[threadIdx.x * 16 + i] = before + local[i];
+            if (threadIdx.x == 255) relOff[kTileBlocks] = before + s;
+            __syncthreads();
+        }
+
+        if (tileFirst == 0 && threadIdx.x == 0) writeStreamHeader(job, dst);
+
+        for (int it = 0; it < kTileBlocks / kIterBlocks; ++it) {
+            const unsigned long long blk0 = tileFirst + static_cast<unsigned long long>(it) * kIterBlocks;
+            if (blk0 >= job.nblocks) break;
+            const unsigned int winStart = relOff[it * kIterBlocks];
+            const unsigned int winEnd = relOff[(it + 1) * kIterBlocks];
+            const unsigned long long outStart = tileRel + winStart;  // offset inside the records area
+            const unsigned int phase = static_cast<unsigned int>(reinterpret_cast<uintptr_t>(records + outStart) & 15);
+            const unsigned long long blk = blk0 + grp;
+            if (blk < job.nblocks) {
+                const unsigned long long g = tile * kTileBlocks + static_cast<unsigned long long>(it) * kIterBlocks + grp;
+                const unsigned int header = headers[g], base = bases[g];
+                const int mode = header >> 5, w = header & 31;
+                unsigned char* rec = window + phase + (relOff[it * kIterBlocks + grp] - winStart);
+                const uint4 v = loadLane16(job, blk, lane4, vec);
+                const unsigned int words[4] = {v.x, v.y, v.z, v.w};
+                if (lane4 == 0) rec[0] = static_cast<unsigned char>(header);
+                if (mode == 0) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) rec[1 + lane4 * 16 + i] = static_cast<unsigned char>(words[i >> 2] >> (8 * (i & 3)));
+                } else if (mode == 1) {
+                    if (lane4 == 0) rec[1] = static_cast<unsigned char>(base);
+                } else if (mode == 2 || mode == 3) {
+                    const int skip = mode == 2 ? 2 : 1;
+                    if (mode == 2 && lane4 == 0) rec[1] = static_cast<unsigned char>(base);
+#pragma unroll
+                    for (int gq = 0; gq < 2; ++gq) {  // two 8-element groups per lane
+                        unsigned long long word = 0;
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            const unsigned int b = (words[gq * 2 + (k >> 2)] >> (8 * (k & 3))) & 0xFFu;
+                            const unsigned long long f = mode == 2 ? ((b - base) & 0xFFu) : zigzag8(b);
+                            word |= f << (k * w);
+                        }
+                        unsigned char* g8 = rec + skip + (lane4 * 2 + gq) * w;
+                        for (int j = 0; j < w; ++j) g8[j] = static_cast<unsigned char>(word >> (8 * j));
+                    }
+                } else {  // sparse: mask bytes then the non-zero bytes in order
+                    unsigned int m16 = 0;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) m16 |= static_cast<unsigned int>(((words[i >> 2] >> (8 * (i & 3))) & 0xFFu) != 0) << i;
+                    rec[1 + lane4 * 2] = static_cast<unsigned char>(m16);
+                    rec[2 + lane4 * 2] = static_cast<unsigned char>(m16 >> 8);
+                    const unsigned int mine = __popc(m16);
+                    // exclusive prefix of the non-zero counts over the four lanes of the group
+                    const unsigned int mask4 = 0xFu << (lane & ~3);
+                    unsigned int incl = mine;
+                    const unsigned int a = __shfl_up_sync(mask4, incl, 1, 4);
+                    if (lane4 >= 1) incl += a;
+                    const unsigned int b2 = __shfl_up_sync(mask4, incl, 2, 4);
+                    if (lane4 >= 2) incl += b2;
+                    unsigned char* nz = rec + 9 + (incl - mine);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const unsigned int b = (words[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+                        if (b != 0) *nz++ = static_cast<unsigned char>(b);
+                    }
+                }
+                if (grp == 0 && lane4 == 0) {
+                    putU32(dst + kCodecHeaderBytes + 4 * (blk0 / kCodecSuper), static_cast<unsigned int>(outStart));
+                }
+            }
+            __syncthreads();
+            // copy the window out: [outStart, outStart + len) of the records area
+            {
+                const unsigned int len = winEnd - winStart;
+                unsigned char* gdst = records + outStart;
+                const unsigned int head = (16 - phase) & 15;  // bytes up to the first 16-byte boundary
+                for (unsigned int i = threadIdx.x; i < len && i < head; i += blockDim.x) gdst[i] = window[phase + i];
+                const unsigned int bodyStart = head < len ? head : len;
+                const unsigned int nvec = (len - bodyStart) / 16;
+                for (unsigned int q = threadIdx.x; q < nvec; q += blockDim.x) {
+                    *reinterpret_cast<uint4*>(gdst + bodyStart + q * 16) =
+                            *reinterpret_cast<const uint4*>(window + phase + bodyStart + q * 16);
+                }
+                for (unsigned int i = bodyStart + nvec * 16 + threadIdx.x; i < len; i += blockDim.x) gdst[i] = window[phase + i];
+            }
+            __syncthreads();
+        }
+        // trailing zero bytes of the stream (32-byte alignment), written by the buffer's last tile
+        if (tileFirst + kTileBlocks >= job.nblocks) {
+            for (unsigned long long a = kCodecHeaderBytes + 4 * job.nsuper + job.recordsBytes + threadIdx.x; a < job.streamBytes;
+                 a += blockDim.x) {
+                dst[a] = 0;
+            }
+        }
+        __syncthreads();
     }
 }
 
@@ -294,7 +409,8 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
                         bool rawFallback, CodecResult* results) {
     if (count <= 0) return;
     std::vector<CodecJobDev> jobs(count);
-    unsigned long long totalBlocks = 0;
+    std::vector<unsigned int> tileJob;
+    unsigned long long ntiles = 0;
     for (int j = 0; j < count; ++j) {
         if (bufs[j].n == 0) refThrow("BitCompactorCodec::compress: Empty input data vector");
         if (bufs[j].n >= (1ull << 32)) throw NotBuilt("codec input of 4 GiB or more");
@@ -303,42 +419,114 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
         jobs[j].n = bufs[j].n;
         jobs[j].nblocks = (bufs[j].n + kCodecBlock - 1) / kCodecBlock;
         jobs[j].nsuper = (jobs[j].nblocks + kCodecSuper - 1) / kCodecSuper;
-        jobs[j].firstBlock = totalBlocks;
-        totalBlocks += jobs[j].nblocks;
+        jobs[j].firstBlock = ntiles * kTileBlocks;
+        const unsigned long long t = (jobs[j].nblocks + kTileBlocks - 1) / kTileBlocks;
+        tileJob.insert(tileJob.end(), t, static_cast<unsigned int>(j));
+        ntiles += t;
     }
+    const unsigned long long padded = ntiles * kTileBlocks;
     CodecJobDev* jobsDev = static_cast<CodecJobDev*>(ctx->arena.alloc(sizeof(CodecJobDev) * count));
-    unsigned char* headers = static_cast<unsigned char*>(ctx->arena.alloc(totalBlocks + 16));
-    unsigned char* bases = static_cast<unsigned char*>(ctx->arena.alloc(totalBlocks + 16));
-    unsigned char* sizes = static_cast<unsigned char*>(ctx->arena.alloc(totalBlocks + 16));
-    unsigned long long* offsets =
-            static_cast<unsigned long long*>(ctx->arena.alloc((totalBlocks + 1) * sizeof(unsigned long long)));
+    unsigned int* tileJobDev = static_cast<unsigned int*>(ctx->arena.alloc(sizeof(unsigned int) * ntiles));
+    unsigned char* headers = static_cast<unsigned char*>(ctx->arena.alloc(padded));
+    unsigned char* bases = static_cast<unsigned char*>(ctx->arena.alloc(padded));
+    unsigned char* sizes = static_cast<unsigned char*>(ctx->arena.alloc(padded));
+    unsigned int* tileSums = static_cast<unsigned int*>(ctx->arena.alloc(sizeof(unsigned int) * (ntiles + 1)));
+    unsigned long long* tileOffsets =
+            static_cast<unsigned long long*>(ctx->arena.alloc(sizeof(unsigned long long) * (ntiles + 1)));
     copyH2D(ctx, jobsDev, jobs.data(), sizeof(CodecJobDev) * count);
+    copyH2D(ctx, tileJobDev, tileJob.data(), sizeof(unsigned int) * ntiles);
 
 #ifdef B200C_HOST_EMULATION
     if (B2_EMU(ctx)) {
-        for (unsigned long long g = 0; g < totalBlocks; ++g) analyzeOne(jobsDev, count, g, headers, bases, sizes);
-        exclusiveScanU8(ctx, sizes, totalBlocks, offsets);
-        layoutJobs(jobsDev, count, offsets, outCap, rawFallback, ctx->errWord);
-        for (unsigned long long g = 0; g < totalBlocks; ++g)
-            emitOne(jobsDev, count, g, headers, bases, offsets, outDev, rawFallback);
+        // serial restatement of the three kernels on the same padded index space
+        for (unsigned long long tile = 0; tile < ntiles; ++tile) {
+            const CodecJobDev& job = jobsDev[tileJobDev[tile]];
+            const unsigned long long tileFirst = (tile - job.firstBlock / kTileBlocks) * kTileBlocks;
+            unsigned int sum = 0;
+            for (int i = 0; i < kTileBlocks; ++i) {
+                const unsigned long long g = tile * kTileBlocks + i, blk = tileFirst + i;
+                sizes[g] = headers[g] = bases[g] = 0;
+                if (blk < job.nblocks) {
+                    unsigned char b[kCodecBlock];
+                    loadBlock(job, blk, b);
+                    sizes[g] = static_cast<unsigned char>(codecChoose(b, &headers[g], &bases[g]));
+                }
+                sum += sizes[g];
+            }
+            tileSums[tile] = sum;
+        }
+        unsigned long long run = 0;
+        for (unsigned long long t = 0; t < ntiles; ++t) {
+            tileOffsets[t] = run;
+            run += tileSums[t];
+        }
+        tileOffsets[ntiles] = run;
+        layoutJobs(jobsDev, count, tileOffsets, outCap, rawFallback, ctx->errWord);
+        for (unsigned long long tile = 0; tile < ntiles; ++tile) {
+            const CodecJobDev& job = jobsDev[tileJobDev[tile]];
+            if (job.outBytes == 0) continue;
+            unsigned char* dst = outDev + job.outBase;
+            const unsigned long long jobFirstTile = job.firstBlock / kTileBlocks;
+            const unsigned long long tileFirst = (tile - jobFirstTile) * kTileBlocks;
+            if (rawFallback && job.notSmaller) {
+                if (tileFirst == 0) std::memcpy(dst, job.in, job.n);
+                continue;
+            }
+            unsigned char* records = dst + kCodecHeaderBytes + 4 * job.nsuper;
+            unsigned long long at = tileOffsets[tile] - tileOffsets[jobFirstTile];
+            if (tileFirst == 0) writeStreamHeader(job, dst);
+            for (int i = 0; i < kTileBlocks; ++i) {
+                const unsigned long long g = tile * kTileBlocks + i, blk = tileFirst + i;
+                if (blk >= job.nblocks) break;
+                unsigned char b[kCodecBlock];
+                loadBlock(job, blk, b);
+                if (blk % kCodecSuper == 0) putU32(dst + kCodecHeaderBytes + 4 * (blk / kCodecSuper), static_cast<unsigned int>(at));
+                codecWriteRecord(b, headers[g], bases[g], records + at);
+                at += sizes[g];
+            }
+            if (tileFirst + kTileBlocks >= job.nblocks) {
+                for (unsigned long long a = kCodecHeaderBytes + 4 * job.nsuper + job.recordsBytes; a < job.streamBytes; ++a) dst[a] = 0;
+            }
+        }
         ctx->launches += 3;
+        std::memcpy(jobs.data(), jobsDev, sizeof(CodecJobDev) * count);
     } else
 #endif
     {
-        const int grid = static_cast<int>(
-                std::max<unsigned long long>(1, std::min<unsigned long long>((totalBlocks + 127) / 128, ctx->smCount * 16ULL)));
-        codecAnalyzeKernel<<<grid, 128, 0, ctx->stream>>>(jobsDev, count, totalBlocks, headers, bases, sizes);
+        const int grid = static_cast<int>(std::max<unsigned long long>(1, std::min<unsigned long long>(ntiles, ctx->smCount * 8ULL)));
+        codecAnalyzeKernel<<<grid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, ntiles, headers, bases, sizes, tileSums);
         B2_CUDA(cudaGetLastError());
-        exclusiveScanU8(ctx, sizes, totalBlocks, offsets);
-        codecLayoutKernel<<<1, 32, 0, ctx->stream>>>(jobsDev, count, offsets, outCap, rawFallback ? 1 : 0, ctx->errWord);
-        codecEmitKernel<<<grid, 128, 0, ctx->stream>>>(jobsDev, count, totalBlocks, headers, bases, offsets, outDev,
-                                                       rawFallback ? 1 : 0);
+        codecScanKernel<<<1, 1024, 0, ctx->stream>>>(tileSums, ntiles, tileOffsets, jobsDev, count, outCap,
+                                                     rawFallback ? 1 : 0, ctx->errWord);
         B2_CUDA(cudaGetLastError());
-        ctx->launches += 3;
+        ctx->launches += 2;
+        copyD2H(ctx, jobs.data(), jobsDev, sizeof(CodecJobDev) * count);
+        syncStream(ctx);
+        checkDeviceError(ctx);
+        // buffers that do not shrink are stored as they are (a device-to-device copy); the others
+        // go through the emit kernel
+        std::vector<unsigned int> emitTiles;
+        for (int j = 0; j < count; ++j) {
+            if (jobs[j].outBytes == 0) continue;
+            if (rawFallback && jobs[j].notSmaller) {
+                copyD2D(ctx, outDev + jobs[j].outBase, jobs[j].in, jobs[j].n);
+                continue;
+            }
+            const unsigned long long t0 = jobs[j].firstBlock / kTileBlocks;
+            const unsigned long long t1 = t0 + (jobs[j].nblocks + kTileBlocks - 1) / kTileBlocks;
+            for (unsigned long long t = t0; t < t1; ++t) emitTiles.push_back(static_cast<unsigned int>(t));
+        }
+        if (!emitTiles.empty()) {
+            unsigned int* emitDev = static_cast<unsigned int*>(ctx->arena.alloc(sizeof(unsigned int) * emitTiles.size()));
+            copyH2D(ctx, emitDev, emitTiles.data(), sizeof(unsigned int) * emitTiles.size());
+            const int egrid = static_cast<int>(std::min<unsigned long long>(emitTiles.size(), ctx->smCount * 4ULL));
+            codecEmitKernel<<<egrid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, emitDev, emitTiles.size(), headers, bases,
+                                                            sizes, tileOffsets, outDev);
+            B2_CUDA(cudaGetLastError());
+            ++ctx->launches;
+            syncStream(ctx);  // emitTiles (pageable) must stay alive until the copy is done
+        }
     }
-    copyD2H(ctx, jobs.data(), jobsDev, sizeof(CodecJobDev) * count);
-    syncStream(ctx);
-    checkDeviceError(ctx);
     for (int j = 0; j < count; ++j) {
         results[j].offset = jobs[j].outBase;
         results[j].size = jobs[j].outBytes;

@@ -8,6 +8,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <memory>
 #include <stdexcept>
 #include <string>
 #include <vector>
@@ -77,13 +78,32 @@ inline int64_t roundUp(int64_t v, int64_t a) {
     return (v + a - 1) / a * a;
 }
 
+// Quantisation parameters.  The scale / zero-point arrays are views: they either borrow the
+// caller's descriptor arrays (valid for the duration of one C ABI call) or point into storage
+// owned through the shared pointers, so copying a type never copies the tables.
 struct QuantInfo {
     int kind = B200C_Q_NONE;
     int axis = 0;
     int expressed = 0;
     int64_t qmin = 0, qmax = 0;
-    std::vector<double> scales;
-    std::vector<int64_t> zps;
+    const double* scales = nullptr;
+    const int64_t* zps = nullptr;
+    size_t n = 0;
+    std::shared_ptr<std::vector<double>> ownScales;
+    std::shared_ptr<std::vector<int64_t>> ownZps;
+
+    void own(std::vector<double> s, std::vector<int64_t> z) {
+        ownScales = std::make_shared<std::vector<double>>(std::move(s));
+        ownZps = std::make_shared<std::vector<int64_t>>(std::move(z));
+        scales = ownScales->data();
+        zps = ownZps->data();
+        n = ownScales->size();
+    }
+    bool zpsAllEqual() const {
+        for (size_t i = 1; i < n; ++i)
+            if (zps[i] != zps[0]) return false;
+        return true;
+    }
 };
 
 struct TensorType {

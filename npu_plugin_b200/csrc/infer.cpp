@@ -38,8 +38,9 @@ TensorType typeFromC(const b200c_type& c, bool elemOnly) {
         t.q.expressed = c.qexpressed;
         t.q.qmin = c.qmin;
         t.q.qmax = c.qmax;
-        t.q.scales.assign(c.scales, c.scales + c.nq);
-        t.q.zps.assign(c.zps, c.zps + c.nq);
+        t.q.scales = c.scales;  // borrowed for the duration of the call
+        t.q.zps = c.zps;
+        t.q.n = static_cast<size_t>(c.nq);
     }
     return t;
 }
@@ -59,13 +60,13 @@ void typeToC(const TensorType& t, b200c_type* c) {
     c->qexpressed = t.q.expressed;
     c->qmin = t.q.qmin;
     c->qmax = t.q.qmax;
-    c->nq = static_cast<int64_t>(t.q.scales.size());
+    c->nq = static_cast<int64_t>(t.q.n);
     if (t.quantized()) {
         if (sc == nullptr || zp == nullptr || cap < c->nq) {
             throw Capacity("output type needs caller storage for " + std::to_string(c->nq) + " quantisation parameters");
         }
-        std::copy(t.q.scales.begin(), t.q.scales.end(), sc);
-        std::copy(t.q.zps.begin(), t.q.zps.end(), zp);
+        if (sc != t.q.scales) std::copy(t.q.scales, t.q.scales + t.q.n, sc);
+        if (zp != t.q.zps) std::copy(t.q.zps, t.q.zps + t.q.n, zp);
     }
 }
 
@@ -97,9 +98,9 @@ static void checkPerAxis(const TensorType& t) {
     if (t.q.axis < 0 || t.q.axis >= t.rank()) {
         refThrow("Quantized axis '%d' is out of main type rank '%d'", t.q.axis, t.rank());
     }
-    if (static_cast<size_t>(t.shape[t.q.axis]) != t.q.scales.size()) {
+    if (static_cast<size_t>(t.shape[t.q.axis]) != t.q.n) {
         refThrow("Number of scales '%zu' in per-axis quantized type do not match the quantized dimension size '%lld'",
-                 t.q.scales.size(), static_cast<long long>(t.shape[t.q.axis]));
+                 t.q.n, static_cast<long long>(t.shape[t.q.axis]));
     }
 }
 
@@ -170,14 +171,15 @@ static TensorType padded(const TensorType& in, const std::vector<int64_t>& befor
         const int64_t front = before[in.q.axis], back = after[in.q.axis];
         if (front != 0 || back != 0) {
             if (front < 0 || back < 0) throw BadArg("negative padding on the quantised axis");
-            const auto& z = in.q.zps;
-            if (std::any_of(z.begin(), z.end(), [&](int64_t v) { return v != z.front(); })) {
-                refThrow("All zero points should be equal");
-            }
-            out.q.scales.insert(out.q.scales.begin(), static_cast<size_t>(front), in.q.scales.front());
-            out.q.scales.insert(out.q.scales.end(), static_cast<size_t>(back), in.q.scales.back());
-            out.q.zps.insert(out.q.zps.begin(), static_cast<size_t>(front), z.front());
-            out.q.zps.insert(out.q.zps.end(), static_cast<size_t>(back), z.back());
+            if (in.q.n == 0) refThrow("Can't get value for expand scales.");
+            if (!in.q.zpsAllEqual()) refThrow("All zero points should be equal");
+            std::vector<double> sc(static_cast<size_t>(front), in.q.scales[0]);
+            sc.insert(sc.end(), in.q.scales, in.q.scales + in.q.n);
+            sc.insert(sc.end(), static_cast<size_t>(back), in.q.scales[in.q.n - 1]);
+            std::vector<int64_t> zp(static_cast<size_t>(front), in.q.zps[0]);
+            zp.insert(zp.end(), in.q.zps, in.q.zps + in.q.n);
+            zp.insert(zp.end(), static_cast<size_t>(back), in.q.zps[in.q.n - 1]);
+            out.q.own(std::move(sc), std::move(zp));
         }
     }
     checkPerAxis(out);
@@ -191,12 +193,13 @@ static TensorType tiled(const TensorType& in, const std::vector<int64_t>& offset
     if (in.q.kind == B200C_Q_PER_AXIS) {
         if (offset.size() != shape.size()) refThrow("Offsets doesn't match shape");
         const int64_t lo = offset[in.q.axis], n = shape[in.q.axis];
-        if (!(lo == 0 && static_cast<size_t>(n) == in.q.scales.size())) {
-            if (lo < 0 || n < 0 || static_cast<size_t>(lo + n) > in.q.scales.size()) {
+        if (!(lo == 0 && static_cast<size_t>(n) == in.q.n)) {
+            if (lo < 0 || n < 0 || static_cast<size_t>(lo + n) > in.q.n) {
                 refThrow("Invalid slice of the quantization parameters");
             }
-            out.q.scales.assign(in.q.scales.begin() + lo, in.q.scales.begin() + lo + n);
-            out.q.zps.assign(in.q.zps.begin() + lo, in.q.zps.begin() + lo + n);
+            out.q.scales = in.q.scales + lo;  // a window into the same table
+            out.q.zps = in.q.zps + lo;
+            out.q.n = static_cast<size_t>(n);
         }
     }
     checkPerAxis(out);
@@ -206,11 +209,8 @@ static TensorType tiled(const TensorType& in, const std::vector<int64_t>& offset
 // getSparsifyValue (src/vpux_compiler/src/utils/sparsity.cpp:12-26)
 int64_t sparsifyValue(const TensorType& t) {
     if (t.q.kind == B200C_Q_NONE) return 0;
-    const auto& z = t.q.zps;
-    if (t.q.kind == B200C_Q_PER_AXIS && std::any_of(z.begin(), z.end(), [&](int64_t v) { return v != z.front(); })) {
-        refThrow("Not all zero-points are equal");
-    }
-    return z.front();
+    if (t.q.kind == B200C_Q_PER_AXIS && !t.q.zpsAllEqual()) refThrow("Not all zero-points are equal");
+    return t.q.zps[0];
 }
 
 // ---------------------------------------------------------------------------- inferOutputType

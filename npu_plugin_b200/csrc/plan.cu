@@ -166,7 +166,7 @@ void Planner::materialize() {
         p.outTag = tag;
         p.outElems = p.outUnits = n;
         p.dataBytes = p.totalBytes = static_cast<long long>(bytes);
-        launchGeneric(_ctx, p);
+        runGeneric(p);
     }
     View nv;
     nv.src = dst;
@@ -196,9 +196,93 @@ const void* Planner::denseAs(int tag) {
         p.outTag = tag;
         p.outElems = p.outUnits = n;
         p.dataBytes = p.totalBytes = static_cast<long long>(bytes);
-        launchGeneric(_ctx, p);
+        runGeneric(p);
     }
     return dst;
+}
+
+
+void Planner::flushPendingStats() {
+    if (!_pending.active) return;
+    _pending.active = false;
+    launchRowStats(_ctx, _pending.stats);
+}
+
+void Planner::runGeneric(const GenParams& p) {
+    flushPendingStats();
+    launchGeneric(_ctx, p);
+}
+
+// The whole remaining chain is "quantise every row, permute inside rows, store bytes/nibbles
+// (swizzled)": hand it to the single-pass kernel.
+bool Planner::tryFusedRowQuant(void* dst, int outMode, int outTag, int swizzleKey, int64_t dataBytes,
+                               int64_t totalBytes) {
+    if (!_pending.active) return false;
+    const View& v = _s.view;
+    const RowStatsParams& st = _pending.stats;
+    if (_s.splat || v.ops.size() != 1 || !v.boxes.empty() || v.src != _pending.src || v.base != 0) return false;
+    const ValueOp& op = v.ops[0];
+    if (op.fscales != st.scales || op.off != 0 || op.dim < 0) return false;
+    const bool sym = st.scheme == B200C_QSYNTH_SYM_I8;
+    if (outMode == 0) {
+        if (!(outTag == T_I8 || (outTag == T_U8 && !sym))) return false;
+    } else if (sym) {
+        return false;  // negative values fail BitPack's unsigned read; the generic pass reports that
+    }
+    if (v.shape[op.dim] != st.rows) return false;
+    // the row dim must be the outermost dim that matters, with rows laid out back to back
+    for (int k = 0; k < op.dim; ++k)
+        if (v.shape[k] != 1) return false;
+    if (st.rows > 1 && v.stride[op.dim] != st.rowElems) return false;
+    // the remaining dims must enumerate the row exactly once (a mixed-radix permutation)
+    std::vector<std::pair<long long, long long>> dims;  // (shape, stride), outermost first
+    for (int k = op.dim + 1; k < v.rank; ++k)
+        if (v.shape[k] != 1) dims.push_back({v.shape[k], v.stride[k]});
+    {
+        auto sorted = dims;
+        std::sort(sorted.begin(), sorted.end(), [](const auto& a, const auto& b) { return a.second < b.second; });
+        long long expect = 1;
+        for (const auto& d : sorted) {
+            if (d.second != expect) return false;
+            expect *= d.first;
+        }
+        if (expect != st.rowElems) return false;
+    }
+    for (size_t k = 0; k + 1 < dims.size();) {  // merge dims that are contiguous in the source
+        if (dims[k].second == dims[k + 1].second * dims[k + 1].first) {
+            dims[k + 1].first *= dims[k].first;
+            dims.erase(dims.begin() + k);
+        } else {
+            ++k;
+        }
+    }
+    if (dims.size() > 3) return false;
+    RowQuantParams rq;
+    std::memset(&rq, 0, sizeof(rq));
+    rq.src = _pending.src;
+    rq.srcTag = _pending.srcTag;
+    rq.rows = st.rows;
+    rq.rowElems = st.rowElems;
+    rq.scheme = st.scheme;
+    rq.scales = st.scales;
+    rq.zps = st.zps;
+    if (dims.size() == 1 || dims.empty()) {
+        rq.irank = 0;
+    } else {
+        rq.irank = static_cast<int>(dims.size());
+        for (size_t k = 0; k < dims.size(); ++k) {
+            rq.ishape[k] = dims[k].first;
+            rq.istride[k] = dims[k].second;
+        }
+    }
+    rq.dst = dst;
+    rq.outMode = outMode;
+    rq.swizzleKey = swizzleKey;
+    rq.dataBytes = dataBytes;
+    rq.totalBytes = totalBytes;
+    _pending.active = false;
+    launchRowQuantFused(_ctx, rq);
+    return true;
 }
 
 // ---------------------------------------------------------------------------- transformations
@@ -303,8 +387,8 @@ void Planner::apply(const Transformation& x) {
             if (outType.rank() != 4) refThrow("Unsupported shape size %d", outType.rank());
             if (outType.q.axis != 0) refThrow("Only per-channel quantization is supported");
             const size_t es = tagBytes(tag);
-            std::vector<char> table(outType.q.zps.size() * es);
-            for (size_t i = 0; i < outType.q.zps.size(); ++i) {
+            std::vector<char> table(outType.q.n * es);
+            for (size_t i = 0; i < outType.q.n; ++i) {
                 const unsigned long long bits = castIntToTag(outType.q.zps[i], tag);
                 std::memcpy(table.data() + i * es, &bits, es);  // little endian
             }
@@ -330,7 +414,9 @@ void Planner::apply(const Transformation& x) {
             if (op.dim >= 0) op.off -= before[op.dim];
         for (auto& b : v.boxes)
             if (b.table) b.tableOff -= before[b.tableDim];
-        v.boxes.push_back(fb);
+        bool widens = false;
+        for (int k = 0; k < v.rank; ++k) widens = widens || shape[k] != inShape[k];
+        if (widens) v.boxes.push_back(fb);  // a zero-width pad fills nothing
         _s.type = outType;
         _s.splat = false;
         return;
@@ -346,11 +432,11 @@ void Planner::apply(const Transformation& x) {
         if (_s.type.q.kind == B200C_Q_PER_AXIS) {
             const auto& q = _s.type.q;
             const int memAxis = _s.type.memPosOf(q.axis);
-            if (static_cast<int64_t>(q.scales.size()) != v.shape[memAxis]) refThrow("Wrong scales size");
+            if (static_cast<int64_t>(q.n) != v.shape[memAxis]) refThrow("Wrong scales size");
             if (_s.type.count() == 0) refThrow("Inner size is zero");
-            op.scales = static_cast<const double*>(uploadTable(q.scales.data(), q.scales.size() * sizeof(double)));
+            op.scales = static_cast<const double*>(uploadTable(q.scales, q.n * sizeof(double)));
             static_assert(sizeof(long long) == sizeof(int64_t), "");
-            op.zps = static_cast<const long long*>(uploadTable(q.zps.data(), q.zps.size() * sizeof(int64_t)));
+            op.zps = static_cast<const long long*>(uploadTable(q.zps, q.n * sizeof(int64_t)));
             op.dim = memAxis;
             op.off = 0;
             _s.splat = false;  // dequantize.cpp:31-40
@@ -443,6 +529,7 @@ void Planner::quantizeSynth(const Transformation& x, const TensorType& outType) 
     const int rowDim = _s.type.memPosOf(0);
     float* scales = static_cast<float*>(_ctx->arena.alloc(std::max<int64_t>(rows, 1) * sizeof(float)));
     int* zps = static_cast<int*>(_ctx->arena.alloc(std::max<int64_t>(rows, 1) * sizeof(int)));
+    flushPendingStats();
     if (rows > 0 && _s.type.count() > 0) {
         RowStatsParams rp;
         rp.view = paramsFor(v);
@@ -452,7 +539,18 @@ void Planner::quantizeSynth(const Transformation& x, const TensorType& outType) 
         rp.scheme = static_cast<int>(x.i0);
         rp.scales = scales;
         rp.zps = zps;
-        launchRowStats(_ctx, rp);
+        const bool rowsContiguous = isPlain(v) && !_s.splat && rowDim == 0 &&
+                                    (v.srcTag == T_F16 || v.srcTag == T_F32) &&
+                                    static_cast<size_t>(rp.rowElems) * tagBytes(v.srcTag) <= rowQuantMaxRowBytes();
+        if (rowsContiguous && !B2_EMU(_ctx)) {
+            _pending.active = true;
+            _pending.stats = rp;
+            _pending.src = v.src;
+            _pending.srcTag = v.srcTag;
+            _pending.rowDim = rowDim;
+        } else {
+            launchRowStats(_ctx, rp);
+        }
     }
     ValueOp op;
     std::memset(&op, 0, sizeof(op));
@@ -688,6 +786,7 @@ size_t Planner::emitCopyTo(void* dst, size_t cap, int swizzleKey, int64_t totalB
                               : (static_cast<int64_t>(dtBits(_s.storage)) * n + 7) / 8;
         if (_afterBitPack) {
             // BitPack output: u8 storage of n/2 bytes, same size as the logical type -> memcpy branch
+            if (tryFusedRowQuant(dst, 1, T_U8, -1, n / 2, n / 2)) return static_cast<size_t>(n / 2);
             GenParams p = paramsFor(v);
             p.dst = dst;
             p.outMode = OUT_BITPACK4;
@@ -695,7 +794,7 @@ size_t Planner::emitCopyTo(void* dst, size_t cap, int swizzleKey, int64_t totalB
             p.outElems = n;
             p.outUnits = n / 2;
             p.dataBytes = p.totalBytes = n / 2;
-            if (p.outUnits) launchGeneric(_ctx, p);
+            if (p.outUnits) runGeneric(p);
             return static_cast<size_t>(n / 2);
         }
         if (alloc < storageBytes) {
@@ -715,7 +814,7 @@ size_t Planner::emitCopyTo(void* dst, size_t cap, int swizzleKey, int64_t totalB
             p.outElems = n;
             p.outUnits = alloc;
             p.dataBytes = p.totalBytes = alloc;
-            launchGeneric(_ctx, p);
+            runGeneric(p);
             return static_cast<size_t>(alloc);
         }
         // same size (or bit-packed storage): plain memcpy of the storage bytes
@@ -743,7 +842,7 @@ size_t Planner::emitCopyTo(void* dst, size_t cap, int swizzleKey, int64_t totalB
     if (_s.splat && totalBytes > 0) {
         // swizzled splat: no swizzle, tail padded with the first output byte (swizzle_transform.cpp:170-188)
         p.totalBytes = dataBytes;
-        if (n > 0) launchGeneric(_ctx, p);
+        if (n > 0) runGeneric(p);
         if (target > dataBytes) {
             unsigned char first = 0;
             if (n > 0) {
@@ -755,7 +854,25 @@ size_t Planner::emitCopyTo(void* dst, size_t cap, int swizzleKey, int64_t totalB
         }
         return static_cast<size_t>(target);
     }
-    if (p.totalBytes > 0) launchGeneric(_ctx, p);
+    if (p.totalBytes > 0 && p.outMode == OUT_RAW && isPlain(v)) {
+        // nothing to compute: a device copy, or the chunk-rotating copy when swizzled
+        if (p.swizzleKey < 0) {
+            copyD2D(_ctx, dst, v.src, static_cast<size_t>(dataBytes));
+            if (p.totalBytes > dataBytes) {
+                fillBytes(_ctx, static_cast<char*>(dst) + dataBytes, 0, static_cast<size_t>(p.totalBytes - dataBytes));
+            }
+        } else {
+            launchSwizzleCopy(_ctx, v.src, dataBytes, dst, p.totalBytes, p.swizzleKey, 0);
+        }
+        return static_cast<size_t>(p.totalBytes);
+    }
+    if (p.totalBytes > 0) {
+        if (p.outMode == OUT_CAST && n > 0 &&
+            tryFusedRowQuant(dst, 0, p.outTag, p.swizzleKey, p.dataBytes, p.totalBytes)) {
+            return static_cast<size_t>(p.totalBytes);
+        }
+        runGeneric(p);
+    }
     return static_cast<size_t>(p.totalBytes);
 }
 

@@ -67,6 +67,19 @@ private:
     void subviewBits(const Transformation& x, const TensorType& outType);
     void swizzle(const Transformation& x, const TensorType& outType);
     size_t emitCopyTo(void* dst, size_t cap, int swizzleKey, int64_t totalBytes);
+    void runGeneric(const GenParams& p);
+    void flushPendingStats();
+    bool tryFusedRowQuant(void* dst, int outMode, int outTag, int swizzleKey, int64_t dataBytes, int64_t totalBytes);
+
+    // QuantizeSynth whose statistics pass has not run yet: if the chain ends in a shape the fused
+    // kernel handles, statistics and quantisation happen in one pass over the tensor
+    struct PendingStats {
+        bool active = false;
+        RowStatsParams stats;
+        const void* src = nullptr;
+        int srcTag = T_NONE;
+        int rowDim = 0;
+    } _pending;
 
     Context* _ctx;
     ContentState _s;

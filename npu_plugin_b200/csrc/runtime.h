@@ -92,6 +92,27 @@ struct RowStatsParams {
 };
 void launchRowStats(Context* ctx, const RowStatsParams& p);
 
+// Fused single-pass quantiser (rowquant_kernels.cu): rows are contiguous in the source; the output
+// keeps the row order and may permute elements inside a row.
+struct RowQuantParams {
+    const void* src;
+    int srcTag;  // T_F16 or T_F32
+    long long rows, rowElems;
+    int scheme;
+    float* scales;
+    int* zps;
+    int irank;  // within-row output map: 0 = identity, else mixed radix ishape/istride (outermost first)
+    long long ishape[3], istride[3];
+    void* dst;
+    int outMode;  // 0: one byte per element, 1: BitPack nibbles
+    int swizzleKey;
+    long long dataBytes, totalBytes;
+    int vecIn, vecOut;  // filled by the launcher
+    long long smemRowElems;
+};
+void launchRowQuantFused(Context* ctx, RowQuantParams p);
+size_t rowQuantMaxRowBytes();
+
 // sparsity (GetSparsityMap / Sparsify) on a dense buffer of `tag` elements laid out [OC][work]
 void launchSparsityMap(Context* ctx, const void* src, int tag, long long oc, long long work, long long outBitsPerOC,
                        unsigned long long sparseBits, void* dstBits, int swizzleKey);

@@ -358,3 +358,49 @@ def test_empty_and_tiny(gpu, oracle):
     for shape in [(0,), (1,), (1, 1, 1, 1), (2, 0, 3)]:
         w = np.zeros(shape, np.float32)
         assert_same(*both(lambda b: ContentAttr.get(w, NDType(shape, A.F32), backend=b).convertElemType(A.F16), gpu, oracle))
+
+
+# ------------------------------------------------------------------ fused quantiser edge cases
+# The single-pass kernel replaces the per-element IEEE division and rint by an FMA-corrected
+# reciprocal and a magic-constant rounding; these rows are built to sit on rounding ties and at the
+# edges of the float range, for every kernel variant (warp rows, register rows, staged rows, scalar tails).
+@pytest.mark.parametrize("npdt,dt", [(np.float16, A.F16), (np.float32, A.F32)])
+@pytest.mark.parametrize("scheme", [A.QSYNTH_SYM_I8, A.QSYNTH_ASYM_U4])
+@pytest.mark.parametrize("rowlen", [16, 100, 1024, 1040, 4096, 11008, 20000])
+def test_fused_quantiser_ties_and_extremes(gpu, oracle, npdt, dt, scheme, rowlen):
+    rng = np.random.default_rng(rowlen + scheme)
+    rows = 9
+    w = rng.normal(0, 1, (rows, rowlen)).astype(np.float32)
+    # row 0: exact multiples of amax/254 -> quotients on .5 ties
+    amax = 3.96875
+    k = rng.integers(-254, 255, rowlen)
+    w[0] = (k * (amax / 254.0))
+    w[0, 0] = amax
+    # row 1: all zero (scale falls back to 1); row 2: a single non-zero
+    w[1] = 0
+    w[2] = 0
+    w[2, rowlen // 2] = -0.5
+    # row 3: tiny magnitudes; row 4: large magnitudes
+    w[3] *= 1e-6
+    w[4] *= 1000.0 if npdt == np.float16 else 1e30
+    # row 5: constant row (asymmetric scale is zero -> 1)
+    w[5] = 0.37
+    if npdt == np.float32:
+        w[6] *= 1e-38  # subnormal products
+        w[7, ::3] = np.float32(1e-45)
+    w = w.astype(npdt)
+    store = A.SI8 if scheme == A.QSYNTH_SYM_I8 else A.UI8
+    qmin, qmax = (-127, 127) if scheme == A.QSYNTH_SYM_I8 else (0, 15)
+
+    def chain(b, swz, pack):
+        a = ContentAttr.get(w.reshape(rows, rowlen, 1, 1), NDType((rows, rowlen, 1, 1), dt), backend=b)
+        a = a.quantizeSynth(scheme).convertElemType(store)
+        a = a.quantCast(UniformQuantizedPerAxisType(store, A.F32, [1.0] * rows, [0] * rows, 0, qmin, qmax))
+        if pack:
+            return a.bitPack(4)
+        return a.swizzleConstant(5, 3) if swz else a
+
+    for swz, pack in [(False, False), (True, False)] + ([(False, True)] if scheme == A.QSYNTH_ASYM_U4 and rowlen % 2 == 0 else []):
+        ag, ao = chain(gpu, swz, pack), chain(oracle, swz, pack)
+        assert_same(ag.fold(), ao.fold())
+        assert np.array_equal(ag.sideScales, ao.sideScales) and np.array_equal(ag.sideZeroPoints, ao.sideZeroPoints)
