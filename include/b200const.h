@@ -221,6 +221,27 @@ B200C_API int b200c_fold(b200c_ctx* ctx, const b200c_type* base, const void* dat
                int data_on_device, const b200c_xform* chain, int n, void* out, size_t out_cap, int out_on_device,
                size_t* out_bytes, b200c_type* out_type, int flags);
 
+/* Many constants in one call: the whole-model form of b200c_fold, standing where the reference
+ * loops over every Const::DeclareOp of a model (serializeBinaryData,
+ * src/vpux_compiler/src/dialect/VPUIP/graph-schema/export.cpp:465-479).  Items are independent;
+ * kernels of the same kind are issued as one launch over all items, so small constants do not pay
+ * one launch each.  data_on_device / out_on_device / flags apply to every item; out_bytes of each
+ * item receives the bytes written.  Side outputs of QuantizeSynth are written in place when the
+ * outputs are on the device.                                                                      */
+typedef struct b200c_fold_item {
+    const b200c_type* base;
+    const void* data;
+    size_t nbytes;
+    int32_t is_splat;
+    int32_t n; /* transformations in chain */
+    const b200c_xform* chain;
+    void* out;
+    size_t out_cap;
+    size_t out_bytes; /* result */
+} b200c_fold_item;
+B200C_API int b200c_fold_batch(b200c_ctx* ctx, b200c_fold_item* items, int count, int data_on_device, int out_on_device,
+                               int flags);
+
 /* Per-output-channel count of elements that differ from the sparsify value:
  * vpux::countNonSparseElementsPerOC (src/vpux_compiler/src/utils/sparsity.cpp:28-72)
  * applied to the folded content of (base, chain).  counts: host int64[shape[0]].  */

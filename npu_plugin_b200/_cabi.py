@@ -95,6 +95,20 @@ class b200c_xform(C.Structure):
     ]
 
 
+class b200c_fold_item(C.Structure):
+    _fields_ = [
+        ("base", C.POINTER(b200c_type)),
+        ("data", C.c_void_p),
+        ("nbytes", C.c_size_t),
+        ("is_splat", C.c_int32),
+        ("n", C.c_int32),
+        ("chain", C.POINTER(b200c_xform)),
+        ("out", C.c_void_p),
+        ("out_cap", C.c_size_t),
+        ("out_bytes", C.c_size_t),
+    ]
+
+
 # name -> (restype, argtypes) of every symbol include/b200const.h declares
 _P = C.POINTER
 SYMBOLS = {
@@ -111,6 +125,7 @@ SYMBOLS = {
     "b200c_total_alloc_size": (C.c_int64, [_P(b200c_type)]),
     "b200c_fold": (C.c_int, [C.c_void_p, _P(b200c_type), C.c_void_p, C.c_size_t, C.c_int, C.c_int, _P(b200c_xform),
                              C.c_int, C.c_void_p, C.c_size_t, C.c_int, _P(C.c_size_t), _P(b200c_type), C.c_int]),
+    "b200c_fold_batch": (C.c_int, [C.c_void_p, C.POINTER(b200c_fold_item), C.c_int, C.c_int, C.c_int, C.c_int]),
     "b200c_count_nonsparse_per_oc": (C.c_int, [C.c_void_p, _P(b200c_type), C.c_void_p, C.c_size_t, C.c_int, C.c_int,
                                                _P(b200c_xform), C.c_int, _P(C.c_int64), C.c_int64]),
     "b200c_btc_bound": (C.c_int, [C.c_size_t, _P(C.c_size_t)]),

@@ -68,12 +68,47 @@ class ShardFolder:
         self._out_size = (C.c_size_t * n)()
         self._not_smaller = (C.c_int32 * n)()
         self._nb = C.c_size_t()
+        self._items = (A.b200c_fold_item * n)()
+        for i, (bt, ch, k, ot) in enumerate(self._prepared):
+            it = self._items[i]
+            it.base = C.pointer(bt)
+            it.nbytes = decls[i].nbytes
+            it.is_splat = int(decls[i].is_splat)
+            it.n = k
+            it.chain = C.cast(ch, C.POINTER(A.b200c_xform))
+            it.out_cap = self.folded_sizes[i]
         self.comp_idx = [i for i, d in enumerate(decls) if d.compress and self.folded_sizes[i] >= MIN_COMPRESS_BYTES]
         self.blob_bound = sum((backend.btc_bound(self.folded_sizes[i]) + 31) // 32 * 32 for i in self.comp_idx) + 64
 
-    def fold(self, data_ptrs, folded_ptr, data_on_device=True, side_ptrs=None):
-        """fold() + copyTo() of every constant into folded_ptr + folded_offsets[i] (asynchronous when
-        everything is on the device; errors surface at the next synchronising call)."""
+    def fold(self, data_ptrs, folded_ptr, data_on_device=True, side_ptrs=None, max_batch_bytes=None):
+        """fold() + copyTo() of every constant into folded_ptr + folded_offsets[i] through the batched
+        entry point (asynchronous; errors surface at the next synchronising call).  With host input
+        the items are issued in groups of at most max_batch_bytes so the staging memory stays bounded."""
+        lib, ctx = self.lib, self.ctx
+        n = len(self.decls)
+        for i in range(n):
+            it = self._items[i]
+            it.data = data_ptrs[i]
+            it.out = folded_ptr + self.folded_offsets[i]
+            if side_ptrs is not None and side_ptrs[i] is not None:
+                ch = self._prepared[i][1]
+                for k in range(self._prepared[i][2]):
+                    if ch[k].kind == A.X_QUANTIZE_SYNTH:
+                        ch[k].side0, ch[k].side1 = side_ptrs[i]
+        first = 0
+        while first < n:
+            last, total = first, 0
+            while last < n and (last == first or max_batch_bytes is None or total + self.decls[last].nbytes <= max_batch_bytes):
+                total += self.decls[last].nbytes
+                last += 1
+            at = C.cast(C.addressof(self._items) + first * C.sizeof(A.b200c_fold_item), C.POINTER(A.b200c_fold_item))
+            rc = lib.b200c_fold_batch(ctx, at, last - first, int(data_on_device), 1, A.FOLD_ASYNC)
+            if rc != A.OK:
+                raise_for(rc, lib.b200c_last_error())
+            first = last
+
+    def fold_one_by_one(self, data_ptrs, folded_ptr, data_on_device=True, side_ptrs=None):
+        """Same result through one b200c_fold call per constant."""
         lib, ctx = self.lib, self.ctx
         flags = A.FOLD_ASYNC
         for i, (bt, ch, n, ot) in enumerate(self._prepared):

@@ -367,6 +367,7 @@ int b200c_fold(b200c_ctx* h, const b200c_type* base, const void* data, size_t nb
         if (!out && out_cap > 0) throw BadArg("null output pointer");
         const auto xs = chainFromC(chain, n);
         auto plan = makePlanner(ctx, base, data, nbytes, is_splat, data_on_device);
+        plan->setSideOnDevice(out_on_device != 0);
         void* devOut = out;
         if (!out_on_device) devOut = ctx->arena.alloc(out_cap ? out_cap : 1);
         const size_t wrote = plan->run(xs, devOut, out_cap);
@@ -380,6 +381,48 @@ int b200c_fold(b200c_ctx* h, const b200c_type* base, const void* data, size_t nb
         }
         if (out_bytes) *out_bytes = wrote;
         if (out_type) typeToC(plan->state().type, out_type);
+        const bool async = out_on_device && (flags & B200C_FOLD_ASYNC);
+        if (!async) {
+            syncStream(ctx);
+            checkDeviceError(ctx);
+        }
+    });
+}
+
+int b200c_fold_batch(b200c_ctx* h, b200c_fold_item* items, int count, int data_on_device, int out_on_device, int flags) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        if (count < 0 || (count > 0 && !items)) throw BadArg("bad item list");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        CallScope scope(ctx);
+        struct BatchGuard {
+            Context* c;
+            ~BatchGuard() {
+                c->batching = false;
+                c->rqBatch.clear();
+            }
+        } guard{ctx};
+        ctx->batching = out_on_device != 0 && !B2_EMU(ctx);
+        std::vector<std::pair<void*, void*>> hostOuts;  // (user pointer, device staging) when out is on the host
+        for (int i = 0; i < count; ++i) {
+            b200c_fold_item& it = items[i];
+            if (!it.out && it.out_cap > 0) throw BadArg("null output pointer");
+            const auto xs = chainFromC(it.chain, it.n);
+            auto plan = makePlanner(ctx, it.base, it.data, it.nbytes, it.is_splat, data_on_device);
+            plan->setSideOnDevice(out_on_device != 0);
+            void* devOut = it.out;
+            if (!out_on_device) devOut = ctx->arena.alloc(it.out_cap ? it.out_cap : 1);
+            it.out_bytes = plan->run(xs, devOut, it.out_cap);
+            if (!out_on_device) copyD2H(ctx, it.out, devOut, it.out_bytes);
+            for (const auto& so : plan->sideOutputs()) {
+                if (out_on_device) {
+                    copyD2D(ctx, so.user, so.dev, so.bytes);
+                } else {
+                    copyD2H(ctx, so.user, so.dev, so.bytes);
+                }
+            }
+        }
+        flushRowQuantBatch(ctx);
         const bool async = out_on_device && (flags & B200C_FOLD_ASYNC);
         if (!async) {
             syncStream(ctx);

@@ -527,8 +527,11 @@ void Planner::quantizeSynth(const Transformation& x, const TensorType& outType) 
     if (static_cast<int>(v.ops.size()) >= kMaxOps) materialize();
     const int64_t rows = _s.type.shape[0];
     const int rowDim = _s.type.memPosOf(0);
-    float* scales = static_cast<float*>(_ctx->arena.alloc(std::max<int64_t>(rows, 1) * sizeof(float)));
-    int* zps = static_cast<int*>(_ctx->arena.alloc(std::max<int64_t>(rows, 1) * sizeof(int)));
+    const bool s0Direct = _sideOnDevice && x.side0 != nullptr, s1Direct = _sideOnDevice && x.side1 != nullptr;
+    float* scales = s0Direct ? static_cast<float*>(x.side0)
+                             : static_cast<float*>(_ctx->arena.alloc(std::max<int64_t>(rows, 1) * sizeof(float)));
+    int* zps = s1Direct ? static_cast<int*>(x.side1)
+                        : static_cast<int*>(_ctx->arena.alloc(std::max<int64_t>(rows, 1) * sizeof(int)));
     flushPendingStats();
     if (rows > 0 && _s.type.count() > 0) {
         RowStatsParams rp;
@@ -566,11 +569,11 @@ void Planner::quantizeSynth(const Transformation& x, const TensorType& outType) 
     so.dev = scales;
     so.user = x.side0;
     so.bytes = static_cast<size_t>(rows) * sizeof(float);
-    if (so.user) _sides.push_back(so);
+    if (so.user && !s0Direct) _sides.push_back(so);
     so.dev = zps;
     so.user = x.side1;
     so.bytes = static_cast<size_t>(rows) * sizeof(int);
-    if (so.user) _sides.push_back(so);
+    if (so.user && !s1Direct) _sides.push_back(so);
 }
 
 // ---------------------------------------------------------------------------- sparsity

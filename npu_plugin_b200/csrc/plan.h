@@ -46,6 +46,10 @@ public:
     void runNoCopy(const std::vector<Transformation>& chain);
     std::vector<int64_t> countNonSparse();
 
+    // QuantizeSynth side outputs that live on the device are written by the kernels directly
+    void setSideOnDevice(bool v) {
+        _sideOnDevice = v;
+    }
     const ContentState& state() const {
         return _s;
     }
@@ -86,6 +90,7 @@ private:
     std::vector<std::vector<char>> _staging;
     std::vector<SideOutput> _sides;
     bool _afterBitPack = false;
+    bool _sideOnDevice = false;
     void* _finalDst = nullptr;
     size_t _finalCap = 0;
     bool _isLast = false;

@@ -305,78 +305,116 @@ __device__ __forceinline__ void zeroTail(const RowQuantParams& p) {
 }
 
 // ---- register-resident rows: identity map, 16-element units, 128-bit loads and stores -------------
-// TPR threads per row, each holding up to MAXU units.
+// TPR threads per row, each holding up to MAXU units; `g` is the index of the CTA's row group.
 template <typename T, int TPR, int MAXU, int SCHEME>
-__global__ void __launch_bounds__(256) rowQuantRegKernel(const __grid_constant__ RowQuantParams p) {
-    __shared__ float redMx[8], redMn[8], redAm[8], redOdd[8];
+__device__ __forceinline__ void rowQuantRegBody(const RowQuantParams& p, long long g, float* redMx, float* redMn,
+                                                float* redAm, float* redOdd) {
     constexpr int ROWS_PER_CTA = 256 / TPR;
     constexpr int VPU = 16 * sizeof(T) / 16;  // 128-bit vectors per unit
     const int sub = threadIdx.x / TPR, t = threadIdx.x % TPR;
     const int units = static_cast<int>(p.rowElems / 16);
-    const long long rowGroups = (p.rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
-
-    for (long long g = blockIdx.x; g < rowGroups; g += gridDim.x) {
-        const long long row = g * ROWS_PER_CTA + sub;
-        const bool live = row < p.rows;
-        const uint4* src4 = reinterpret_cast<const uint4*>(static_cast<const T*>(p.src) + row * p.rowElems);
-        uint4 x[MAXU][VPU];
+    const long long row = g * ROWS_PER_CTA + sub;
+    const bool live = row < p.rows;
+    const uint4* src4 = reinterpret_cast<const uint4*>(static_cast<const T*>(p.src) + row * p.rowElems);
+    uint4 x[MAXU][VPU];
+#pragma unroll
+    for (int i = 0; i < MAXU; ++i) {
+        const int u = t + i * TPR;
+        if (live && u < units) {
+#pragma unroll
+            for (int v = 0; v < VPU; ++v) x[i][v] = __ldg(src4 + u * VPU + v);
+        }
+    }
+    Stats s;
+    s.mx = -INFINITY;
+    s.mn = INFINITY;
+    s.amax = 0.0f;
+    s.odd = 0.0f;
+    if (sizeof(T) == 2) {
+        __half2 mx2 = __float2half2_rn(-INFINITY), mn2 = __float2half2_rn(INFINITY), am2 = __float2half2_rn(0.0f);
+        __half2 nan2 = am2;
 #pragma unroll
         for (int i = 0; i < MAXU; ++i) {
             const int u = t + i * TPR;
             if (live && u < units) {
 #pragma unroll
-                for (int v = 0; v < VPU; ++v) x[i][v] = __ldg(src4 + u * VPU + v);
+                for (int v = 0; v < VPU; ++v) accumHalf8<SCHEME>(mx2, mn2, am2, nan2, x[i][v]);
             }
         }
-        Stats s;
-        s.mx = -INFINITY;
-        s.mn = INFINITY;
-        s.amax = 0.0f;
-        s.odd = 0.0f;
-        if (sizeof(T) == 2) {
-            __half2 mx2 = __float2half2_rn(-INFINITY), mn2 = __float2half2_rn(INFINITY), am2 = __float2half2_rn(0.0f);
-            __half2 nan2 = am2;
-#pragma unroll
-            for (int i = 0; i < MAXU; ++i) {
-                const int u = t + i * TPR;
-                if (live && u < units) {
-#pragma unroll
-                    for (int v = 0; v < VPU; ++v) accumHalf8<SCHEME>(mx2, mn2, am2, nan2, x[i][v]);
-                }
-            }
-            s.mx = fmaxf(__low2float(mx2), __high2float(mx2));
-            s.mn = fminf(__low2float(mn2), __high2float(mn2));
-            s.amax = fmaxf(__low2float(am2), __high2float(am2));
-            const float nl = __low2float(nan2), nh = __high2float(nan2);
-            s.odd = (nl == nl && nh == nh) ? 0.0f : 1.0f;  // halves have no magnitude below 1e-30 other than 0
-        } else {
-#pragma unroll
-            for (int i = 0; i < MAXU; ++i) {
-                const int u = t + i * TPR;
-                if (live && u < units) {
-                    const float* f = reinterpret_cast<const float*>(&x[i][0]);
-#pragma unroll
-                    for (int k = 0; k < 16; ++k) accum(s, f[k]);
-                }
-            }
-        }
-        s = rowReduce<TPR>(s, redMx, redMn, redAm, redOdd);
-        float scale;
-        int zp;
-        scaleOf(SCHEME, s, scale, zp);
-        const RowQ rq = makeRowQ(scale, zp, s);
-        if (live && t == 0) {
-            p.scales[row] = scale;
-            p.zps[row] = zp;
-        }
+        s.mx = fmaxf(__low2float(mx2), __high2float(mx2));
+        s.mn = fminf(__low2float(mn2), __high2float(mn2));
+        s.amax = fmaxf(__low2float(am2), __high2float(am2));
+        const float nl = __low2float(nan2), nh = __high2float(nan2);
+        s.odd = (nl == nl && nh == nh) ? 0.0f : 1.0f;  // halves have no magnitude below 1e-30 other than 0
+    } else {
 #pragma unroll
         for (int i = 0; i < MAXU; ++i) {
             const int u = t + i * TPR;
-            if (live && u < units) emitUnit<T, SCHEME>(p, reinterpret_cast<const T*>(&x[i][0]), rq, row, u);
+            if (live && u < units) {
+                const float* f = reinterpret_cast<const float*>(&x[i][0]);
+#pragma unroll
+                for (int k = 0; k < 16; ++k) accum(s, f[k]);
+            }
         }
-        if (TPR > 32) __syncthreads();  // reduction slots are reused by the next row
     }
-    zeroTail(p);
+    s = rowReduce<TPR>(s, redMx, redMn, redAm, redOdd);
+    float scale;
+    int zp;
+    scaleOf(SCHEME, s, scale, zp);
+    const RowQ rq = makeRowQ(scale, zp, s);
+    if (live && t == 0) {
+        p.scales[row] = scale;
+        p.zps[row] = zp;
+    }
+#pragma unroll
+    for (int i = 0; i < MAXU; ++i) {
+        const int u = t + i * TPR;
+        if (live && u < units) emitUnit<T, SCHEME>(p, reinterpret_cast<const T*>(&x[i][0]), rq, row, u);
+    }
+    if (g == 0) {  // zero tail of the swizzle size alignment
+        for (long long a = p.dataBytes + threadIdx.x; a < p.totalBytes; a += blockDim.x) {
+            static_cast<unsigned char*>(p.dst)[swizzleAddr(a, p.swizzleKey)] = 0;
+        }
+    }
+}
+
+template <typename T, int TPR, int MAXU, int SCHEME>
+__global__ void __launch_bounds__(256) rowQuantRegKernel(const __grid_constant__ RowQuantParams p) {
+    __shared__ float redMx[8], redMn[8], redAm[8], redOdd[8];
+    constexpr int ROWS_PER_CTA = 256 / TPR;
+    const long long rowGroups = (p.rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
+    for (long long g = blockIdx.x; g < rowGroups; g += gridDim.x) {
+        rowQuantRegBody<T, TPR, MAXU, SCHEME>(p, g, redMx, redMn, redAm, redOdd);
+        if (TPR > 32) __syncthreads();  // reduction slots are reused by the next row group
+    }
+}
+
+// Many tensors in one launch: CTA b works on row group (b - groupStart[i]) of tensor i, found by a
+// binary search over the prefix sums.  Removes the launch gaps and tail effects of per-tensor launches.
+template <typename T, int TPR, int MAXU, int SCHEME>
+__global__ void __launch_bounds__(256) rowQuantRegBatchKernel(const RowQuantParams* __restrict__ items,
+                                                              const long long* __restrict__ groupStart, int nitems) {
+    __shared__ float redMx[8], redMn[8], redAm[8], redOdd[8];
+    __shared__ RowQuantParams p;
+    int lo = 0, hi = nitems - 1;
+    const long long b = blockIdx.x;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (groupStart[mid] <= b) {
+            lo = mid;
+        } else {
+            hi = mid - 1;
+        }
+    }
+    // stage the tensor's parameters in shared memory (one copy per CTA)
+    {
+        const int words = sizeof(RowQuantParams) / 4;
+        const unsigned int* srcw = reinterpret_cast<const unsigned int*>(items + lo);
+        unsigned int* dstw = reinterpret_cast<unsigned int*>(&p);
+        for (int i = threadIdx.x; i < words; i += blockDim.x) dstw[i] = srcw[i];
+    }
+    __syncthreads();
+    rowQuantRegBody<T, TPR, MAXU, SCHEME>(p, b - groupStart[lo], redMx, redMn, redAm, redOdd);
 }
 
 // ---- shared-memory staged rows: any length up to the shared-memory budget, optional permutation ---
@@ -472,16 +510,92 @@ __global__ void __launch_bounds__(256) rowQuantSmemKernel(const __grid_constant_
     zeroTail(p);
 }
 
+// ---- launch configuration -----------------------------------------------------------------------
+// A register-path configuration is (element type, threads per row, units per thread, scheme).
+struct RegConfig {
+    int srcTag, tpr, maxu, scheme;
+    bool operator==(const RegConfig& o) const {
+        return srcTag == o.srcTag && tpr == o.tpr && maxu == o.maxu && scheme == o.scheme;
+    }
+};
+
+// threads per row: the smallest group that holds the row with at most MAXU units per thread, so
+// every thread keeps several 128-bit loads in flight.  Returns false when the row needs staging.
+bool pickRegConfig(const RowQuantParams& p, RegConfig* c) {
+    const long long units = p.rowElems / 16;
+    const bool regOk = p.irank == 0 && p.vecIn && p.vecOut && p.rowElems % 16 == 0;
+    const int maxu = p.srcTag == T_F16 ? 4 : 2;
+    if (!regOk || units > 256LL * maxu) return false;
+    c->srcTag = p.srcTag;
+    c->scheme = p.scheme;
+    if (units <= 32LL * maxu) {
+        c->tpr = 32;
+        c->maxu = units <= 32 ? 1 : (units <= 64 ? 2 : maxu);
+    } else if (units <= 64LL * maxu) {
+        c->tpr = 64;
+        c->maxu = maxu;
+    } else if (units <= 128LL * maxu) {
+        c->tpr = 128;
+        c->maxu = maxu;
+    } else {
+        c->tpr = 256;
+        c->maxu = units <= 512 ? 2 : ((p.srcTag == T_F16 && units <= 768) ? 3 : maxu);
+    }
+    return true;
+}
+
 template <typename T, int TPR, int MAXU, int SCHEME>
-void launchReg(Context* ctx, const RowQuantParams& p) {
-    constexpr int ROWS_PER_CTA = 256 / TPR;
-    const long long groups = (p.rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
-    // one row group per CTA: the block scheduler staggers the load / reduce / store phases of the
-    // CTAs resident on an SM, which keeps more loads in flight than a persistent lock-step loop
-    const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>(groups, 1LL << 30)));
-    rowQuantRegKernel<T, TPR, MAXU, SCHEME><<<grid, 256, 0, ctx->stream>>>(p);
+void launchRegT(Context* ctx, const RowQuantParams* one, const RowQuantParams* itemsDev, const long long* startDev,
+                int nitems, long long totalGroups) {
+    if (one) {
+        constexpr int ROWS_PER_CTA = 256 / TPR;
+        const long long groups = (one->rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
+        // one row group per CTA: the block scheduler staggers the load / reduce / store phases of the
+        // CTAs resident on an SM, which keeps more loads in flight than a persistent lock-step loop
+        const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>(groups, 1LL << 30)));
+        rowQuantRegKernel<T, TPR, MAXU, SCHEME><<<grid, 256, 0, ctx->stream>>>(*one);
+    } else {
+        rowQuantRegBatchKernel<T, TPR, MAXU, SCHEME>
+                <<<static_cast<unsigned int>(totalGroups), 256, 0, ctx->stream>>>(itemsDev, startDev, nitems);
+    }
     B2_CUDA(cudaGetLastError());
     ++ctx->launches;
+}
+
+template <typename T, int SCHEME>
+void launchRegTS(Context* ctx, const RegConfig& c, const RowQuantParams* one, const RowQuantParams* itemsDev,
+                 const long long* startDev, int nitems, long long totalGroups) {
+#define B2_RQ_CASE(TPR_, MAXU_)                                                                                   \
+    if (c.tpr == TPR_ && c.maxu == MAXU_) {                                                                       \
+        launchRegT<T, TPR_, MAXU_, SCHEME>(ctx, one, itemsDev, startDev, nitems, totalGroups);                    \
+        return;                                                                                                   \
+    }
+    B2_RQ_CASE(32, 1)
+    B2_RQ_CASE(32, 2)
+    B2_RQ_CASE(64, 2)
+    B2_RQ_CASE(128, 2)
+    B2_RQ_CASE(256, 2)
+    if (sizeof(T) == 2) {
+        B2_RQ_CASE(32, 4)
+        B2_RQ_CASE(64, 4)
+        B2_RQ_CASE(128, 4)
+        B2_RQ_CASE(256, 3)
+        B2_RQ_CASE(256, 4)
+    }
+#undef B2_RQ_CASE
+    throw BadArg("row quantiser: no kernel for this configuration");
+}
+
+void launchRegConfig(Context* ctx, const RegConfig& c, const RowQuantParams* one, const RowQuantParams* itemsDev,
+                     const long long* startDev, int nitems, long long totalGroups) {
+    const bool sym = c.scheme == B200C_QSYNTH_SYM_I8;
+    if (c.srcTag == T_F16) {
+        sym ? launchRegTS<__half, B200C_QSYNTH_SYM_I8>(ctx, c, one, itemsDev, startDev, nitems, totalGroups)
+            : launchRegTS<__half, B200C_QSYNTH_ASYM_U4>(ctx, c, one, itemsDev, startDev, nitems, totalGroups);
+    } else {
+        sym ? launchRegTS<float, B200C_QSYNTH_SYM_I8>(ctx, c, one, itemsDev, startDev, nitems, totalGroups)
+            : launchRegTS<float, B200C_QSYNTH_ASYM_U4>(ctx, c, one, itemsDev, startDev, nitems, totalGroups);
+    }
 }
 
 template <typename T, int TPR, int SCHEME>
@@ -501,28 +615,8 @@ void launchSmem(Context* ctx, const RowQuantParams& p) {
 }
 
 template <typename T, int SCHEME>
-void dispatch(Context* ctx, const RowQuantParams& p) {
-    const long long units = p.rowElems / 16;
-    const bool regOk = p.irank == 0 && p.vecIn && p.vecOut && p.rowElems % 16 == 0;
-    constexpr int MAXU = sizeof(T) == 2 ? 4 : 2;
-    if (regOk && units <= 256LL * MAXU) {
-        // threads per row: the smallest group that holds the row with at most MAXU units per thread,
-        // so every thread keeps several 128-bit loads in flight
-        if (units <= 32LL * MAXU) {
-            units <= 32 ? launchReg<T, 32, 1, SCHEME>(ctx, p)
-                        : (units <= 64 ? launchReg<T, 32, 2, SCHEME>(ctx, p) : launchReg<T, 32, MAXU, SCHEME>(ctx, p));
-        } else if (units <= 64LL * MAXU) {
-            launchReg<T, 64, MAXU, SCHEME>(ctx, p);
-        } else if (units <= 128LL * MAXU) {
-            launchReg<T, 128, MAXU, SCHEME>(ctx, p);
-        } else if (units <= 512) {
-            launchReg<T, 256, 2, SCHEME>(ctx, p);
-        } else if (sizeof(T) == 2 && units <= 768) {
-            launchReg<T, 256, 3, SCHEME>(ctx, p);
-        } else {
-            launchReg<T, 256, MAXU, SCHEME>(ctx, p);
-        }
-    } else if (p.rowElems <= 1024) {
+void dispatchSmem(Context* ctx, const RowQuantParams& p) {
+    if (p.rowElems <= 1024) {
         launchSmem<T, 32, SCHEME>(ctx, p);
     } else {
         launchSmem<T, 256, SCHEME>(ctx, p);
@@ -542,11 +636,55 @@ void launchRowQuantFused(Context* ctx, RowQuantParams p) {
     p.vecOut = ((reinterpret_cast<uintptr_t>(p.dst) & 15) == 0 && p.rowElems % 16 == 0) ? 1 : 0;
     // rows padded to 16 bytes in shared memory so every row slot stays 128-bit aligned
     p.smemRowElems = (p.rowElems * es + 15) / 16 * 16 / es;
+    RegConfig c;
+    if (pickRegConfig(p, &c)) {
+        if (ctx->batching) {
+            ctx->rqBatch.push_back(p);  // launched by flushRowQuantBatch with its peers
+            return;
+        }
+        launchRegConfig(ctx, c, &p, nullptr, nullptr, 0, 0);
+        return;
+    }
     const bool sym = p.scheme == B200C_QSYNTH_SYM_I8;
     if (p.srcTag == T_F16) {
-        sym ? dispatch<__half, B200C_QSYNTH_SYM_I8>(ctx, p) : dispatch<__half, B200C_QSYNTH_ASYM_U4>(ctx, p);
+        sym ? dispatchSmem<__half, B200C_QSYNTH_SYM_I8>(ctx, p) : dispatchSmem<__half, B200C_QSYNTH_ASYM_U4>(ctx, p);
     } else {
-        sym ? dispatch<float, B200C_QSYNTH_SYM_I8>(ctx, p) : dispatch<float, B200C_QSYNTH_ASYM_U4>(ctx, p);
+        sym ? dispatchSmem<float, B200C_QSYNTH_SYM_I8>(ctx, p) : dispatchSmem<float, B200C_QSYNTH_ASYM_U4>(ctx, p);
+    }
+}
+
+// Launch everything queued during a batched fold: one launch per kernel configuration.
+void flushRowQuantBatch(Context* ctx) {
+    std::vector<RowQuantParams> pending;
+    pending.swap(ctx->rqBatch);
+    std::vector<bool> done(pending.size(), false);
+    for (size_t i = 0; i < pending.size(); ++i) {
+        if (done[i]) continue;
+        RegConfig c;
+        pickRegConfig(pending[i], &c);
+        std::vector<RowQuantParams> group;
+        std::vector<long long> start;
+        long long total = 0;
+        for (size_t j = i; j < pending.size(); ++j) {
+            RegConfig cj;
+            if (done[j] || !pickRegConfig(pending[j], &cj) || !(cj == c)) continue;
+            const int rowsPerCta = 256 / c.tpr;
+            const long long groups = (pending[j].rows + rowsPerCta - 1) / rowsPerCta;
+            if (total + groups > 0x7FFFFFFFLL) continue;  // next flush round
+            done[j] = true;
+            group.push_back(pending[j]);
+            start.push_back(total);
+            total += groups;
+        }
+        if (group.size() == 1) {
+            launchRegConfig(ctx, c, &group[0], nullptr, nullptr, 0, 0);
+            continue;
+        }
+        RowQuantParams* itemsDev = static_cast<RowQuantParams*>(ctx->arena.alloc(sizeof(RowQuantParams) * group.size()));
+        long long* startDev = static_cast<long long*>(ctx->arena.alloc(sizeof(long long) * start.size()));
+        copyH2D(ctx, itemsDev, group.data(), sizeof(RowQuantParams) * group.size());
+        copyH2D(ctx, startDev, start.data(), sizeof(long long) * start.size());
+        launchRegConfig(ctx, c, nullptr, itemsDev, startDev, static_cast<int>(group.size()), total);
     }
 }
 

@@ -32,6 +32,26 @@ namespace b200c {
 
 struct Context;
 
+// Fused single-pass quantiser (rowquant_kernels.cu): rows are contiguous in the source; the output
+// keeps the row order and may permute elements inside a row.
+struct RowQuantParams {
+    const void* src;
+    int srcTag;  // T_F16 or T_F32
+    long long rows, rowElems;
+    int scheme;
+    float* scales;
+    int* zps;
+    int irank;  // within-row output map: 0 = identity, else mixed radix ishape/istride (outermost first)
+    long long ishape[3], istride[3];
+    void* dst;
+    int outMode;  // 0: one byte per element, 1: BitPack nibbles
+    int swizzleKey;
+    long long dataBytes, totalBytes;
+    int vecIn, vecOut;  // filled by the launcher
+    long long smemRowElems;
+};
+
+
 // Bump allocator over device memory.  Blocks are kept for the life of the context and reused by
 // every call; reset() rewinds to the start.
 class Arena {
@@ -65,6 +85,8 @@ struct Context {
     int smCount = 148;
     size_t l2Bytes = 0;
     bool emulated = false;
+    bool batching = false;                 // inside b200c_fold_batch: fused quantiser launches are queued
+    std::vector<RowQuantParams> rqBatch;
 };
 
 // device memory through the context (host malloc under emulation)
@@ -92,25 +114,9 @@ struct RowStatsParams {
 };
 void launchRowStats(Context* ctx, const RowStatsParams& p);
 
-// Fused single-pass quantiser (rowquant_kernels.cu): rows are contiguous in the source; the output
-// keeps the row order and may permute elements inside a row.
-struct RowQuantParams {
-    const void* src;
-    int srcTag;  // T_F16 or T_F32
-    long long rows, rowElems;
-    int scheme;
-    float* scales;
-    int* zps;
-    int irank;  // within-row output map: 0 = identity, else mixed radix ishape/istride (outermost first)
-    long long ishape[3], istride[3];
-    void* dst;
-    int outMode;  // 0: one byte per element, 1: BitPack nibbles
-    int swizzleKey;
-    long long dataBytes, totalBytes;
-    int vecIn, vecOut;  // filled by the launcher
-    long long smemRowElems;
-};
+// Fused single-pass quantiser (rowquant_kernels.cu)
 void launchRowQuantFused(Context* ctx, RowQuantParams p);
+void flushRowQuantBatch(Context* ctx);
 size_t rowQuantMaxRowBytes();
 
 // sparsity (GetSparsityMap / Sparsify) on a dense buffer of `tag` elements laid out [OC][work]

@@ -1,0 +1,99 @@
+"""The batched whole-model entry point (b200c_fold_batch) against per-constant folds and the oracle."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from npu_plugin_b200 import _cabi as A
+from npu_plugin_b200.blob import ConstantDecl, ShardFolder, partition
+from npu_plugin_b200.const import DimsOrder, NDType, Transform, UniformQuantizedPerAxisType, raise_for
+
+gpu_only = pytest.mark.gpu
+
+
+def linear_decl(name, o, i):
+    q = UniformQuantizedPerAxisType(A.SI8, A.F16, [1.0] * o, [0] * o, 0, -127, 127)
+    chain = [Transform(A.X_QUANTIZE_SYNTH, i0=A.QSYNTH_SYM_I8), Transform(A.X_CONVERT_ELEM_TYPE, elem=A.SI8),
+             Transform(A.X_QUANT_CAST, elem=q), Transform(A.X_REORDER, a=DimsOrder.NHWC),
+             Transform(A.X_SWIZZLE_CONSTANT, i0=5, i1=3)]
+    return ConstantDecl(name, NDType((o, i, 1, 1), A.F16), chain, o * i * 2)
+
+
+class DevBuf:
+    def __init__(self, gpu, nbytes):
+        self.gpu, self.n = gpu, nbytes
+        p = C.c_void_p()
+        raise_for(gpu.lib.b200c_dev_alloc(gpu.ctx, max(1, nbytes), C.byref(p)), gpu.lib.b200c_last_error())
+        self.ptr = p.value
+
+    def upload(self, arr):
+        a = np.ascontiguousarray(arr).view(np.uint8).reshape(-1)
+        raise_for(self.gpu.lib.b200c_memcpy_h2d(self.gpu.ctx, self.ptr, a.ctypes.data, a.size), self.gpu.lib.b200c_last_error())
+
+    def download(self, n=None):
+        out = np.zeros(self.n if n is None else n, np.uint8)
+        raise_for(self.gpu.lib.b200c_memcpy_d2h(self.gpu.ctx, out.ctypes.data, self.ptr, out.size), self.gpu.lib.b200c_last_error())
+        return out
+
+    def free(self):
+        self.gpu.lib.b200c_dev_free(self.gpu.ctx, self.ptr)
+
+
+@gpu_only
+def test_batched_fold_matches_single_folds_and_oracle(gpu, oracle):
+    rng = np.random.default_rng(11)
+    shapes = [(64, 256), (48, 1024), (16, 4096), (40, 11008), (128, 64), (7, 20000), (33, 100)]
+    decls = [linear_decl(f"w{k}", o, i) for k, (o, i) in enumerate(shapes)]
+    decls.append(ConstantDecl("gain", NDType((512,), A.F16), [], 1024, compress=False))
+    data = [rng.normal(0, 0.02, d.nbytes // 2).astype(np.float16) for d in decls]
+    folder = ShardFolder(gpu, decls)
+    ins = [DevBuf(gpu, d.nbytes) for d in decls]
+    for b, x in zip(ins, data):
+        b.upload(x)
+    scales = [DevBuf(gpu, 4 * d.base_type.shape[0]) if d.transforms else None for d in decls]
+    zps = [DevBuf(gpu, 4 * d.base_type.shape[0]) if d.transforms else None for d in decls]
+    side = [(s.ptr, z.ptr) if s else None for s, z in zip(scales, zps)]
+    out_a, out_b = DevBuf(gpu, folder.folded_bytes), DevBuf(gpu, folder.folded_bytes)
+    folder.fold([b.ptr for b in ins], out_a.ptr, True, side)
+    raise_for(gpu.lib.b200c_synchronize(gpu.ctx), gpu.lib.b200c_last_error())
+    batched_scales = [s.download() if s else None for s in scales]
+    folder.fold_one_by_one([b.ptr for b in ins], out_b.ptr, True, side)
+    raise_for(gpu.lib.b200c_synchronize(gpu.ctx), gpu.lib.b200c_last_error())
+    a, b = out_a.download(), out_b.download()
+    for i, d in enumerate(decls):
+        off, size = folder.folded_offsets[i], folder.folded_sizes[i]
+        ref = oracle.fold(d.base_type, data[i], False, d.transforms).copyTo()
+        assert np.array_equal(a[off:off + size], ref), d.name
+        assert np.array_equal(b[off:off + size], ref), d.name
+        if d.transforms:
+            assert np.array_equal(batched_scales[i], scales[i].download()), d.name
+    # host input through the same entry point, issued in bounded groups
+    host = [np.ascontiguousarray(x) for x in data]
+    out_c = DevBuf(gpu, folder.folded_bytes)
+    folder.fold([h.ctypes.data for h in host], out_c.ptr, False, side, max_batch_bytes=200_000)
+    raise_for(gpu.lib.b200c_synchronize(gpu.ctx), gpu.lib.b200c_last_error())
+    c = out_c.download()
+    for i in range(len(decls)):
+        off, size = folder.folded_offsets[i], folder.folded_sizes[i]
+        assert np.array_equal(c[off:off + size], a[off:off + size])
+    # batched compression keeps incompressible segments as they are and reports it
+    blob = DevBuf(gpu, folder.blob_bound)
+    segs = folder.compress(out_a.ptr, blob.ptr, folder.blob_bound)
+    raw = blob.download()
+    for i, off, size, compressed in segs:
+        folded = a[folder.folded_offsets[i]:folder.folded_offsets[i] + folder.folded_sizes[i]]
+        stream, not_smaller = oracle.btc_compress(folded)
+        assert compressed == (not not_smaller)
+        expect = stream if compressed else folded
+        assert size == expect.size and np.array_equal(raw[off:off + size], expect), decls[i].name
+    for x in ins + [out_a, out_b, out_c, blob] + [s for s in scales + zps if s]:
+        x.free()
+
+
+def test_partition_is_deterministic_and_balanced():
+    decls = [linear_decl(f"t{k}", o, i) for k, (o, i) in enumerate([(4096, 4096)] * 8 + [(11008, 4096)] * 4 + [(32000, 4096)])]
+    for world in (1, 2, 4, 8):
+        owner = partition(decls, world)
+        assert owner == partition(decls, world)
+        load = [sum(d.nbytes for d, o in zip(decls, owner) if o == r) for r in range(world)]
+        assert max(load) - min(load) <= max(d.nbytes for d in decls)
