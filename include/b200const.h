@@ -263,6 +263,29 @@ B200C_API int b200c_btc_compress(b200c_ctx* ctx, const void* in, size_t n, int i
 B200C_API int b200c_btc_decompress(b200c_ctx* ctx, const void* in, size_t n, int in_on_device, void* out, size_t cap,
                          int out_on_device, size_t* out_n);
 
+/* Allocation-free form of b200c_btc_compress (no counterpart in the reference).
+ *
+ * For callers that cannot let this library allocate GPU memory: a process whose device memory is
+ * claimed in full by its own pool, so that one more cudaMalloc fails or eats into that pool, or one
+ * that cannot afford the device-wide synchronisation an allocation brings while other streams run.
+ * This call allocates nothing, on the device or through any library: `in` and `out` are the
+ * caller's device buffers and the working arrays come from a fixed buffer inside the library
+ * image (about 0.8 MiB, held by every GPU that loads the library until the process exits).
+ *
+ *  - n may be at most B200C_NOALLOC_MAX_INPUT bytes (16 MiB); larger inputs are refused with
+ *    B200C_ERR_CAPACITY and a message saying so.  cap must be at least b200c_btc_bound(n).
+ *  - `device` is the CUDA device of in/out, `stream` a cudaStream_t on it (NULL: the default
+ *    stream).  The call returns after the stream has finished the work.
+ *  - The first call on a device looks up the address of the fixed buffer; make that first call
+ *    outside any stream capture.
+ *  - All calls on one device share the fixed buffer.  Each call rewrites what it reads, so calls
+ *    may follow one another freely, but two calls whose GPU work overlaps (two threads, two
+ *    streams) race on it: serialise them.
+ * Output and return codes are those of b200c_btc_compress (B200C_NOT_SMALLER included).          */
+#define B200C_NOALLOC_MAX_INPUT ((size_t)16 << 20)
+B200C_API int b200c_btc_compress_noalloc(int device, const void* in_dev, size_t n, void* out_dev, size_t cap,
+                                         void* stream, size_t* out_n);
+
 /* Batched form used for whole-model folding: `count` independent buffers that
  * already reside on the device are compressed with one analysis launch, one
  * device prefix sum and one emit launch.  sizes/offsets are host arrays;

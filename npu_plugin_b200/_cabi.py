@@ -58,6 +58,7 @@ OK, NOT_SMALLER = 0, 1
 ERR_INVALID, ERR_THROW, ERR_CUDA, ERR_NOMEM, ERR_CAPACITY, ERR_UNSUPPORTED = -1, -2, -3, -4, -5, -6
 
 FOLD_ASYNC = 1
+NOALLOC_MAX_INPUT = 16 << 20
 
 
 class b200c_type(C.Structure):
@@ -131,6 +132,8 @@ SYMBOLS = {
     "b200c_btc_bound": (C.c_int, [C.c_size_t, _P(C.c_size_t)]),
     "b200c_btc_compress": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p, C.c_size_t, C.c_int,
                                      _P(C.c_size_t)]),
+    "b200c_btc_compress_noalloc": (C.c_int, [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p,
+                                             _P(C.c_size_t)]),
     "b200c_btc_decompress": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p, C.c_size_t, C.c_int,
                                        _P(C.c_size_t)]),
     "b200c_btc_compress_batch": (C.c_int, [C.c_void_p, C.c_int, _P(C.c_void_p), _P(C.c_size_t), C.c_void_p,

@@ -485,6 +485,17 @@ int b200c_btc_compress(b200c_ctx* h, const void* in, size_t n, int in_on_device,
     return rc != B200C_OK ? rc : (notSmaller ? B200C_NOT_SMALLER : B200C_OK);
 }
 
+int b200c_btc_compress_noalloc(int device, const void* in_dev, size_t n, void* out_dev, size_t cap, void* stream,
+                               size_t* out_n) {
+    bool notSmaller = false;
+    const int rc = guarded([&] {
+        if (!in_dev || !out_dev || !out_n) throw BadArg("null pointer");
+        codecCompressNoAlloc(device, static_cast<const unsigned char*>(in_dev), n, static_cast<unsigned char*>(out_dev), cap,
+                             static_cast<cudaStream_t>(stream), out_n, &notSmaller);
+    });
+    return rc != B200C_OK ? rc : (notSmaller ? B200C_NOT_SMALLER : B200C_OK);
+}
+
 int b200c_btc_decompress(b200c_ctx* h, const void* in, size_t n, int in_on_device, void* out, size_t cap,
                          int out_on_device, size_t* out_n) {
     return guarded([&] {

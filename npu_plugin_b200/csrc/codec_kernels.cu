@@ -6,6 +6,8 @@
 
 #include <algorithm>
 #include <cstring>
+#include <mutex>
+#include <string>
 
 namespace b200c {
 
@@ -532,6 +534,105 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
         results[j].size = jobs[j].outBytes;
         results[j].notSmaller = jobs[j].notSmaller != 0;
     }
+}
+
+// ---------------------------------------------------------------------------- allocation-free compress
+// Some hosts cannot let a library allocate device memory: a process whose whole GPU is claimed up
+// front by its own memory pool (a further cudaMalloc fails or fragments the pool), or one that must
+// not take the device-wide synchronisation an allocation implies while its other streams are busy.
+// For them the same analyse -> scan -> emit sequence runs with its working arrays carved out of a
+// fixed buffer that is part of the loaded library image.
+//
+// The buffer is a file-scope device array.  In host code its name is only a handle of the host-side
+// shadow symbol, never a device address, so the real address is fetched once per device with
+// cudaGetSymbolAddress (that device being current) and kept; kernels only ever receive that address.
+constexpr size_t kNoAllocMaxInput = 16u << 20;                                // bytes per call
+constexpr size_t kNoAllocMaxTiles = kNoAllocMaxInput / kCodecBlock / kTileBlocks;  // 64
+constexpr size_t kNoAllocPadded = kNoAllocMaxTiles * kTileBlocks;             // block slots
+constexpr size_t kNoAllocSmall = 4096;                                        // job, tile tables, error word
+constexpr size_t kNoAllocScratchBytes = kNoAllocSmall + 3 * kNoAllocPadded;
+static __device__ __align__(256) unsigned char g_noAllocScratch[kNoAllocScratchBytes];
+
+constexpr int kNoAllocMaxDevices = 64;
+static std::mutex g_noAllocMutex;
+static unsigned char* g_noAllocPtr[kNoAllocMaxDevices] = {nullptr};
+
+size_t codecNoAllocMaxInput() {
+    return kNoAllocMaxInput;
+}
+
+// Returns the stream length through *outN; notSmaller as in codecCompressBatch.  Nothing here calls
+// cudaMalloc/cudaFree or any allocating routine; host-side temporaries live on the stack.
+void codecCompressNoAlloc(int device, const unsigned char* inDev, size_t n, unsigned char* outDev, size_t cap,
+                          cudaStream_t stream, size_t* outN, bool* notSmaller) {
+    if (n == 0) refThrow("BitCompactorCodec::compress: Empty input data vector");
+    if (n > kNoAllocMaxInput) {
+        throw Capacity("b200c_btc_compress_noalloc handles at most " + std::to_string(kNoAllocMaxInput) +
+                       " input bytes per call (got " + std::to_string(n) + ")");
+    }
+    if (cap < codecBound(n)) throw Capacity("output capacity below b200c_btc_bound(n)");
+    if (device < 0 || device >= kNoAllocMaxDevices) throw BadArg("device index out of range");
+    B2_CUDA(cudaSetDevice(device));
+
+    unsigned char* scratch = nullptr;
+    {
+        // one-time set-up per device: resolve the device address of the static array
+        std::lock_guard<std::mutex> lock(g_noAllocMutex);
+        if (g_noAllocPtr[device] == nullptr) {
+            void* p = nullptr;
+            B2_CUDA(cudaGetSymbolAddress(&p, g_noAllocScratch));
+            g_noAllocPtr[device] = static_cast<unsigned char*>(p);
+        }
+        scratch = g_noAllocPtr[device];
+    }
+
+    // carve the working arrays out of the fixed buffer
+    CodecJobDev* jobDev = reinterpret_cast<CodecJobDev*>(scratch);
+    unsigned int* tileJobDev = reinterpret_cast<unsigned int*>(scratch + 256);
+    unsigned int* tileSums = reinterpret_cast<unsigned int*>(scratch + 1024);
+    unsigned long long* tileOffsets = reinterpret_cast<unsigned long long*>(scratch + 2048);
+    int* errDev = reinterpret_cast<int*>(scratch + 3072);
+    unsigned char* headers = scratch + kNoAllocSmall;
+    unsigned char* bases = headers + kNoAllocPadded;
+    unsigned char* sizes = bases + kNoAllocPadded;
+    static_assert(sizeof(CodecJobDev) <= 256 && kNoAllocMaxTiles * 4 <= 768 && (kNoAllocMaxTiles + 1) * 8 <= 1024, "layout");
+
+    CodecJobDev job;
+    std::memset(&job, 0, sizeof(job));
+    job.in = inDev;
+    job.n = n;
+    job.nblocks = (n + kCodecBlock - 1) / kCodecBlock;
+    job.nsuper = (job.nblocks + kCodecSuper - 1) / kCodecSuper;
+    job.firstBlock = 0;
+    const unsigned long long ntiles = (job.nblocks + kTileBlocks - 1) / kTileBlocks;
+    unsigned int tileJob[kNoAllocMaxTiles] = {0};  // one buffer: every tile belongs to job 0
+    unsigned int emitTiles[kNoAllocMaxTiles];
+    for (unsigned long long t = 0; t < ntiles; ++t) emitTiles[t] = static_cast<unsigned int>(t);
+
+    // The array keeps whatever the previous call left: everything read below is rewritten first --
+    // the job record and tile table here, the error word by the memset, the per-block arrays and
+    // tile sums by the analysis kernel (including the zero sizes of the padding slots).
+    B2_CUDA(cudaMemcpyAsync(jobDev, &job, sizeof(job), cudaMemcpyHostToDevice, stream));
+    B2_CUDA(cudaMemcpyAsync(tileJobDev, tileJob, sizeof(unsigned int) * ntiles, cudaMemcpyHostToDevice, stream));
+    B2_CUDA(cudaMemsetAsync(errDev, 0, sizeof(int), stream));
+    const int grid = static_cast<int>(ntiles);
+    codecAnalyzeKernel<<<grid, 256, 0, stream>>>(jobDev, tileJobDev, ntiles, headers, bases, sizes, tileSums);
+    B2_CUDA(cudaGetLastError());
+    codecScanKernel<<<1, 1024, 0, stream>>>(tileSums, ntiles, tileOffsets, jobDev, 1, cap, /*rawFallback=*/0, errDev);
+    B2_CUDA(cudaGetLastError());
+    // the emit kernel reads its tile list from the table slot, which the analysis no longer needs
+    B2_CUDA(cudaMemcpyAsync(tileJobDev + kNoAllocMaxTiles, emitTiles, sizeof(unsigned int) * ntiles, cudaMemcpyHostToDevice,
+                            stream));
+    codecEmitKernel<<<grid, 256, 0, stream>>>(jobDev, tileJobDev, tileJobDev + kNoAllocMaxTiles, ntiles, headers, bases, sizes,
+                                              tileOffsets, outDev);
+    B2_CUDA(cudaGetLastError());
+    int err = 0;
+    B2_CUDA(cudaMemcpyAsync(&job, jobDev, sizeof(job), cudaMemcpyDeviceToHost, stream));
+    B2_CUDA(cudaMemcpyAsync(&err, errDev, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    B2_CUDA(cudaStreamSynchronize(stream));
+    if (err != E_NONE || job.outBytes == 0) throw Capacity("codec: output capacity exceeded");
+    *outN = static_cast<size_t>(job.streamBytes);
+    *notSmaller = job.notSmaller != 0;
 }
 
 // ---------------------------------------------------------------------------- decode

@@ -158,6 +158,10 @@ struct CodecResult {
 // aligned).  With rawFallback a buffer whose stream would not be smaller is stored unchanged.
 void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned char* outDev, size_t outCap,
                         bool rawFallback, CodecResult* results);
+// allocation-free single-buffer variant (fixed scratch inside the library image)
+size_t codecNoAllocMaxInput();
+void codecCompressNoAlloc(int device, const unsigned char* inDev, size_t n, unsigned char* outDev, size_t cap,
+                          cudaStream_t stream, size_t* outN, bool* notSmaller);
 size_t codecDecompress(Context* ctx, const unsigned char* inDev, size_t n, unsigned char* outDev, size_t cap);
 
 // synthetic weights
