@@ -270,7 +270,7 @@ B200C_API int b200c_btc_decompress(b200c_ctx* ctx, const void* in, size_t n, int
  * that cannot afford the device-wide synchronisation an allocation brings while other streams run.
  * This call allocates nothing, on the device or through any library: `in` and `out` are the
  * caller's device buffers and the working arrays come from a fixed buffer inside the library
- * image (about 0.8 MiB, held by every GPU that loads the library until the process exits).
+ * image (about 1 MiB, held by every GPU that loads the library until the process exits).
  *
  *  - n may be at most B200C_NOALLOC_MAX_INPUT bytes (16 MiB); larger inputs are refused with
  *    B200C_ERR_CAPACITY and a message saying so.  cap must be at least b200c_btc_bound(n).

@@ -137,3 +137,33 @@ class ShardFolder:
                                                self._out_off, self._out_size, self._not_smaller)
         raise_for(rc, self.lib.b200c_last_error())
         return [(i, self._out_off[j], self._out_size[j], not self._not_smaller[j]) for j, i in enumerate(self.comp_idx)]
+
+
+def gather_segments(dist, blob, used, rank, world, gathered=None):
+    """The one exchange of the multi-GPU fold: every rank's blob prefix (`used` bytes of the 1-D uint8
+    tensor `blob`) is appended on rank 0 in rank order.  Sizes travel with an all_gather, the bytes with
+    point-to-point send/recv (NCCL over NVLink on GPUs, gloo on CPU).  Returns (per-rank sizes,
+    the assembled tensor on rank 0 or None elsewhere); `gathered` is reused when large enough."""
+    import torch
+    mine = torch.tensor([int(used)], dtype=torch.int64, device=blob.device)
+    sizes = [torch.zeros(1, dtype=torch.int64, device=blob.device) for _ in range(world)]
+    dist.all_gather(sizes, mine)
+    sizes = [int(s.item()) for s in sizes]
+    if rank != 0:
+        if used:
+            dist.send(blob[:used], dst=0)
+        return sizes, None
+    total = sum(sizes)
+    if gathered is None or gathered.numel() < total:
+        gathered = torch.empty(int(total * 1.05) + 1024, dtype=torch.uint8, device=blob.device)
+    at = sizes[0]
+    if at:
+        gathered[:at].copy_(blob[:at])
+    reqs = []
+    for r in range(1, world):
+        if sizes[r]:
+            reqs.append(dist.irecv(gathered[at:at + sizes[r]], src=r))
+        at += sizes[r]
+    for q in reqs:
+        q.wait()
+    return sizes, gathered

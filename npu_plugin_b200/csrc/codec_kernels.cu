@@ -29,134 +29,148 @@ B2_HD void loadBlock(const CodecJobDev& job, unsigned long long blk, unsigned ch
 }
 
 // ---------------------------------------------------------------------------- analyze
-// Four lanes share a 64-byte block: each loads 16 bytes (one coalesced 512-byte request per warp),
-// reduces min / max / zigzag-or / non-zero count with byte-SIMD instructions, and the four partial
-// results are combined with two shuffle steps.
+// One thread per 64-byte block: four 128-bit loads, min / max / zigzag-or / non-zero count with
+// byte-SIMD instructions, mode choice, and one packed 32-bit summary per block
+// (header | base << 8 | record size << 16), so consecutive threads store consecutive words.
 __device__ __forceinline__ unsigned int zigzag4(unsigned int x) {
     return ((x << 1) & 0xFEFEFEFEu) ^ (((x >> 7) & 0x01010101u) * 0xFFu);
 }
 
-struct LaneStats {
-    unsigned int mn, mx, zor, nnz;
+// Per-block statistics.  Byte min/max run on 16-bit lanes (bytes widened with one byte-permute per
+// half, then the native three-input u16x2 min/max); the packed-byte min/max intrinsics are emulated
+// with long instruction sequences on this architecture and made the kernel ALU-bound.
+struct BlockStats {
+    unsigned int mn, mx;  // u16x2 lanes holding byte values
+    unsigned int mag;     // OR of (b ^ signmask(b)) over the bytes: magnitude bits of the zigzag code
+    unsigned int any;     // OR of the bytes (a set bit 7 anywhere: some byte is negative)
+    unsigned int nz128;   // 128 x number of non-zero bytes
 };
 
-__device__ __forceinline__ LaneStats statsOf(uint4 v) {
-    LaneStats s;
-    unsigned int m = __vminu4(__vminu4(v.x, v.y), __vminu4(v.z, v.w));
-    m = __vminu4(m, m >> 16);
-    s.mn = __vminu4(m, m >> 8) & 0xFFu;
-    unsigned int M = __vmaxu4(__vmaxu4(v.x, v.y), __vmaxu4(v.z, v.w));
-    M = __vmaxu4(M, M >> 16);
-    s.mx = __vmaxu4(M, M >> 8) & 0xFFu;
-    unsigned int o = zigzag4(v.x) | zigzag4(v.y) | zigzag4(v.z) | zigzag4(v.w);
-    o |= o >> 16;
-    s.zor = (o | (o >> 8)) & 0xFFu;
-    s.nnz = (__popc(__vcmpne4(v.x, 0)) + __popc(__vcmpne4(v.y, 0)) + __popc(__vcmpne4(v.z, 0)) +
-             __popc(__vcmpne4(v.w, 0))) >> 3;
-    return s;
+// 0xFF in every byte whose top bit is set: prmt's selector nibbles 8..11 replicate the sign of
+// bytes 0..3 (the generic prmt form; written as PTX because the C intrinsic documents 3-bit selectors)
+__device__ __forceinline__ unsigned int signMask4(unsigned int x) {
+    unsigned int m;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(m) : "r"(x), "r"(0u), "r"(0xBA98u));
+    return m;
 }
 
-__device__ __forceinline__ LaneStats groupReduce(LaneStats s) {
-#pragma unroll
-    for (int o = 1; o <= 2; o <<= 1) {
-        s.mn = min(s.mn, __shfl_xor_sync(0xFFFFFFFFu, s.mn, o));
-        s.mx = max(s.mx, __shfl_xor_sync(0xFFFFFFFFu, s.mx, o));
-        s.zor |= __shfl_xor_sync(0xFFFFFFFFu, s.zor, o);
-        s.nnz += __shfl_xor_sync(0xFFFFFFFFu, s.nnz, o);
-    }
-    return s;
+__device__ __forceinline__ void statsAddPair(BlockStats& s, unsigned int a, unsigned int b) {
+    const unsigned int a0 = __byte_perm(a, 0, 0x4240), a1 = __byte_perm(a, 0, 0x4341);
+    const unsigned int b0 = __byte_perm(b, 0, 0x4240), b1 = __byte_perm(b, 0, 0x4341);
+    s.mn = __vimin3_u16x2(s.mn, a0, a1);
+    s.mn = __vimin3_u16x2(s.mn, b0, b1);
+    s.mx = __vimax3_u16x2(s.mx, a0, a1);
+    s.mx = __vimax3_u16x2(s.mx, b0, b1);
+    // byte-permute with the sign-replicate selector gives 0xFF for negative bytes, 0x00 otherwise
+    s.mag |= (a ^ signMask4(a)) | (b ^ signMask4(b));
+    s.any |= a | b;
+    // bit 7 of every non-zero byte: (((x & 0x7F..) + 0x7F..) | x) & 0x80..; summed by a byte dot product
+    const unsigned int na = (((a & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | a) & 0x80808080u;
+    const unsigned int nb = (((b & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | b) & 0x80808080u;
+    s.nz128 = __dp4a(na, 0x01010101u, s.nz128);
+    s.nz128 = __dp4a(nb, 0x01010101u, s.nz128);
 }
 
-// same decision as codecChoose(), from the reduced statistics
-__device__ __forceinline__ int chooseFromStats(LaneStats s, unsigned int* header) {
+__device__ __forceinline__ void statsAdd(BlockStats& s, uint4 v) {
+    statsAddPair(s, v.x, v.y);
+    statsAddPair(s, v.z, v.w);
+}
+
+// same decision as codecChoose(), from the folded statistics
+__device__ __forceinline__ unsigned int summaryOf(BlockStats s) {
+    const unsigned int mn = min(s.mn & 0xFFFFu, s.mn >> 16);
+    const unsigned int mx = max(s.mx & 0xFFFFu, s.mx >> 16);
+    // OR of zigzag(b) = (OR of (b ^ sign)) << 1 | (any negative), folded over the four byte lanes
+    unsigned int o = s.mag | (s.mag >> 16);
+    o = (o | (o >> 8)) & 0x7Fu;
+    const unsigned int zor = (o << 1) | ((s.any & 0x80808080u) ? 1u : 0u);
+    const int nnz = static_cast<int>(s.nz128 >> 7);
     int mode = 0, w = 0, size = 65;
-    if (s.mn == s.mx) {
+    if (mn == mx) {
         mode = 1;
         size = 2;
     }
-    const int wu = 32 - __clz(s.mx - s.mn);
+    const int wu = 32 - __clz(mx - mn);
     if (wu >= 1 && wu <= 7 && 2 + 8 * wu < size) {
         mode = 2;
         w = wu;
         size = 2 + 8 * wu;
     }
-    const int ws = 32 - __clz(s.zor);
+    const int ws = 32 - __clz(zor);
     if (ws >= 1 && ws <= 7 && 1 + 8 * ws < size) {
         mode = 3;
         w = ws;
         size = 1 + 8 * ws;
     }
-    if (9 + static_cast<int>(s.nnz) < size) {
+    if (9 + nnz < size) {
         mode = 4;
         w = 0;
-        size = 9 + static_cast<int>(s.nnz);
+        size = 9 + nnz;
     }
-    *header = static_cast<unsigned int>((mode << 5) | w);
-    return size;
+    return static_cast<unsigned int>((mode << 5) | w) | (mn << 8) | (static_cast<unsigned int>(size) << 16);
 }
 
-__device__ __forceinline__ uint4 loadLane16(const CodecJobDev& job, unsigned long long blk, int lane4, bool vec) {
+__device__ __forceinline__ uint4 loadLane16(const unsigned char* in, unsigned long long n, unsigned long long blk,
+                                            int lane4, bool vec) {
     const unsigned long long first = blk * kCodecBlock + static_cast<unsigned long long>(lane4) * 16;
-    if (vec && first + 16 <= job.n) return __ldg(reinterpret_cast<const uint4*>(job.in + first));
+    if (vec && first + 16 <= n) return __ldg(reinterpret_cast<const uint4*>(in + first));
     unsigned int w[4] = {0, 0, 0, 0};
     for (int i = 0; i < 16; ++i) {
-        if (first + i < job.n) w[i >> 2] |= static_cast<unsigned int>(job.in[first + i]) << (8 * (i & 3));
+        if (first + i < n) w[i >> 2] |= static_cast<unsigned int>(in[first + i]) << (8 * (i & 3));
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 __global__ void __launch_bounds__(256) codecAnalyzeKernel(const CodecJobDev* __restrict__ jobs,
                                                           const unsigned int* __restrict__ tileJob,
-                                                          unsigned long long ntiles, unsigned char* __restrict__ headers,
-                                                          unsigned char* __restrict__ bases,
-                                                          unsigned char* __restrict__ sizes,
+                                                          unsigned long long ntiles, unsigned int* __restrict__ summary,
                                                           unsigned int* __restrict__ tileSums) {
     __shared__ unsigned int red[8];
-    const int grp = threadIdx.x >> 2, lane4 = threadIdx.x & 3;
     for (unsigned long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        const CodecJobDev& job = jobs[tileJob[tile]];
-        const bool vec = (reinterpret_cast<uintptr_t>(job.in) & 15) == 0;
-        const unsigned long long tileFirst = (tile - job.firstBlock / kTileBlocks) * kTileBlocks;
+        const CodecJobDev* job = jobs + tileJob[tile];
+        const unsigned char* in = job->in;
+        const unsigned long long n = job->n, nblocks = job->nblocks;
+        const bool vec = (reinterpret_cast<uintptr_t>(in) & 15) == 0;
+        const unsigned long long tileFirst = (tile - job->firstBlock / kTileBlocks) * kTileBlocks;
+        const unsigned long long gBase = tile * kTileBlocks;
         unsigned int sum = 0;
-        const unsigned long long left = job.nblocks - tileFirst;  // blocks of the buffer from this tile on
-        const int iters = left >= kTileBlocks ? kTileBlocks / kIterBlocks
-                                              : static_cast<int>((left + kIterBlocks - 1) / kIterBlocks);
-        constexpr int UNROLL = 4;  // independent 128-bit loads in flight per thread
-        for (int it0 = 0; it0 < iters; it0 += UNROLL) {
-            uint4 v[UNROLL];
+        constexpr int UNROLL = 2;  // blocks per thread in flight (8 independent 128-bit loads)
+#pragma unroll 1
+        for (int it0 = 0; it0 < kTileBlocks / 256; it0 += UNROLL) {
+            uint4 v[UNROLL][4];
             bool valid[UNROLL];
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
-                const unsigned long long blk = tileFirst + static_cast<unsigned long long>(it0 + u) * kIterBlocks + grp;
-                valid[u] = (it0 + u) < iters && blk < job.nblocks;
-                v[u] = valid[u] ? loadLane16(job, blk, lane4, vec) : make_uint4(0, 0, 0, 0);
+                const unsigned long long blk = tileFirst + static_cast<unsigned long long>(it0 + u) * 256 + threadIdx.x;
+                valid[u] = blk < nblocks;
+                if (valid[u]) {
+                    if (vec && (blk + 1) * kCodecBlock <= n) {
+                        const uint4* p4 = reinterpret_cast<const uint4*>(in + blk * kCodecBlock);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) v[u][k] = __ldg(p4 + k);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) v[u][k] = loadLane16(in, n, blk, k, false);
+                    }
+                }
             }
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
-                if (it0 + u >= iters) break;
-                LaneStats st;
-                st.mn = 255;
-                st.mx = 0;
-                st.zor = 0;
-                st.nnz = 0;
-                if (valid[u]) st = statsOf(v[u]);
-                st = groupReduce(st);
-                if (lane4 == 0) {
-                    const unsigned long long g =
-                            tile * kTileBlocks + static_cast<unsigned long long>(it0 + u) * kIterBlocks + grp;
-                    unsigned int header = 0;
-                    const int size = valid[u] ? chooseFromStats(st, &header) : 0;
-                    headers[g] = static_cast<unsigned char>(header);
-                    bases[g] = static_cast<unsigned char>(st.mn);
-                    sizes[g] = static_cast<unsigned char>(size);
-                    sum += size;
+                unsigned int word = 0;  // padding slot: size 0
+                if (valid[u]) {
+                    BlockStats st;
+                    st.mn = 0x00FF00FFu;
+                    st.mx = 0;
+                    st.mag = 0;
+                    st.any = 0;
+                    st.nz128 = 0;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) statsAdd(st, v[u][k]);
+                    word = summaryOf(st);
                 }
+                summary[gBase + static_cast<unsigned long long>(it0 + u) * 256 + threadIdx.x] = word;
+                sum += word >> 16;
             }
-        }
-        // the rest of the tile is padding: its sizes must read as zero
-        for (unsigned long long r = static_cast<unsigned long long>(iters) * kIterBlocks + threadIdx.x; r < kTileBlocks;
-             r += blockDim.x) {
-            sizes[tile * kTileBlocks + r] = 0;
         }
         for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
         if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
@@ -269,9 +283,7 @@ __global__ void __launch_bounds__(256) codecEmitKernel(const CodecJobDev* __rest
                                                        const unsigned int* __restrict__ tileJob,
                                                        const unsigned int* __restrict__ emitTiles,
                                                        unsigned long long nEmitTiles,
-                                                       const unsigned char* __restrict__ headers,
-                                                       const unsigned char* __restrict__ bases,
-                                                       const unsigned char* __restrict__ sizes,
+                                                       const unsigned int* __restrict__ summary,
                                                        const unsigned long long* __restrict__ tileOffsets,
                                                        unsigned char* __restrict__ out) {
     __shared__ unsigned int relOff[kTileBlocks + 1];                        // record offsets inside the tile
@@ -292,14 +304,17 @@ __global__ void __launch_bounds__(256) codecEmitKernel(const CodecJobDev* __rest
 
         // exclusive scan of the 4096 record sizes: 16 per thread
         {
-            const unsigned char* sz = sizes + tile * kTileBlocks + threadIdx.x * 16;
-            const uint4 v = *reinterpret_cast<const uint4*>(sz);
-            const unsigned int w[4] = {v.x, v.y, v.z, v.w};
+            const uint4* sm4 = reinterpret_cast<const uint4*>(summary + tile * kTileBlocks + threadIdx.x * 16);
             unsigned int local[16], s = 0;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                local[i] = s;
-                s += (w[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+            for (int q = 0; q < 4; ++q) {
+                const uint4 v = sm4[q];
+                const unsigned int w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    local[q * 4 + i] = s;
+                    s += w[i] >> 16;
+                }
             }
             unsigned int incl = s;
             for (int o = 1; o < 32; o <<= 1) {
@@ -328,10 +343,11 @@ __global__ void __launch_bounds__(256) codecEmitKernel(const CodecJobDev* __rest
             const unsigned long long blk = blk0 + grp;
             if (blk < job.nblocks) {
                 const unsigned long long g = tile * kTileBlocks + static_cast<unsigned long long>(it) * kIterBlocks + grp;
-                const unsigned int header = headers[g], base = bases[g];
+                const unsigned int word = summary[g];
+                const unsigned int header = word & 0xFFu, base = (word >> 8) & 0xFFu;
                 const int mode = header >> 5, w = header & 31;
                 unsigned char* rec = window + phase + (relOff[it * kIterBlocks + grp] - winStart);
-                const uint4 v = loadLane16(job, blk, lane4, vec);
+                const uint4 v = loadLane16(job.in, job.n, blk, lane4, vec);
                 const unsigned int words[4] = {v.x, v.y, v.z, v.w};
                 if (lane4 == 0) rec[0] = static_cast<unsigned char>(header);
                 if (mode == 0) {
@@ -429,9 +445,7 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
     const unsigned long long padded = ntiles * kTileBlocks;
     CodecJobDev* jobsDev = static_cast<CodecJobDev*>(ctx->arena.alloc(sizeof(CodecJobDev) * count));
     unsigned int* tileJobDev = static_cast<unsigned int*>(ctx->arena.alloc(sizeof(unsigned int) * ntiles));
-    unsigned char* headers = static_cast<unsigned char*>(ctx->arena.alloc(padded));
-    unsigned char* bases = static_cast<unsigned char*>(ctx->arena.alloc(padded));
-    unsigned char* sizes = static_cast<unsigned char*>(ctx->arena.alloc(padded));
+    unsigned int* summary = static_cast<unsigned int*>(ctx->arena.alloc(padded * sizeof(unsigned int)));
     unsigned int* tileSums = static_cast<unsigned int*>(ctx->arena.alloc(sizeof(unsigned int) * (ntiles + 1)));
     unsigned long long* tileOffsets =
             static_cast<unsigned long long*>(ctx->arena.alloc(sizeof(unsigned long long) * (ntiles + 1)));
@@ -447,13 +461,14 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
             unsigned int sum = 0;
             for (int i = 0; i < kTileBlocks; ++i) {
                 const unsigned long long g = tile * kTileBlocks + i, blk = tileFirst + i;
-                sizes[g] = headers[g] = bases[g] = 0;
+                summary[g] = 0;
                 if (blk < job.nblocks) {
-                    unsigned char b[kCodecBlock];
+                    unsigned char b[kCodecBlock], hd, bs;
                     loadBlock(job, blk, b);
-                    sizes[g] = static_cast<unsigned char>(codecChoose(b, &headers[g], &bases[g]));
+                    const int sz = codecChoose(b, &hd, &bs);
+                    summary[g] = hd | (static_cast<unsigned int>(bs) << 8) | (static_cast<unsigned int>(sz) << 16);
                 }
-                sum += sizes[g];
+                sum += summary[g] >> 16;
             }
             tileSums[tile] = sum;
         }
@@ -483,8 +498,8 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
                 unsigned char b[kCodecBlock];
                 loadBlock(job, blk, b);
                 if (blk % kCodecSuper == 0) putU32(dst + kCodecHeaderBytes + 4 * (blk / kCodecSuper), static_cast<unsigned int>(at));
-                codecWriteRecord(b, headers[g], bases[g], records + at);
-                at += sizes[g];
+                codecWriteRecord(b, static_cast<unsigned char>(summary[g]), static_cast<unsigned char>(summary[g] >> 8), records + at);
+                at += summary[g] >> 16;
             }
             if (tileFirst + kTileBlocks >= job.nblocks) {
                 for (unsigned long long a = kCodecHeaderBytes + 4 * job.nsuper + job.recordsBytes; a < job.streamBytes; ++a) dst[a] = 0;
@@ -496,7 +511,7 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
 #endif
     {
         const int grid = static_cast<int>(std::max<unsigned long long>(1, std::min<unsigned long long>(ntiles, ctx->smCount * 8ULL)));
-        codecAnalyzeKernel<<<grid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, ntiles, headers, bases, sizes, tileSums);
+        codecAnalyzeKernel<<<grid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, ntiles, summary, tileSums);
         B2_CUDA(cudaGetLastError());
         codecScanKernel<<<1, 1024, 0, ctx->stream>>>(tileSums, ntiles, tileOffsets, jobsDev, count, outCap,
                                                      rawFallback ? 1 : 0, ctx->errWord);
@@ -522,8 +537,8 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
             unsigned int* emitDev = static_cast<unsigned int*>(ctx->arena.alloc(sizeof(unsigned int) * emitTiles.size()));
             copyH2D(ctx, emitDev, emitTiles.data(), sizeof(unsigned int) * emitTiles.size());
             const int egrid = static_cast<int>(std::min<unsigned long long>(emitTiles.size(), ctx->smCount * 4ULL));
-            codecEmitKernel<<<egrid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, emitDev, emitTiles.size(), headers, bases,
-                                                            sizes, tileOffsets, outDev);
+            codecEmitKernel<<<egrid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, emitDev, emitTiles.size(), summary,
+                                                            tileOffsets, outDev);
             B2_CUDA(cudaGetLastError());
             ++ctx->launches;
             syncStream(ctx);  // emitTiles (pageable) must stay alive until the copy is done
@@ -550,7 +565,7 @@ constexpr size_t kNoAllocMaxInput = 16u << 20;                                //
 constexpr size_t kNoAllocMaxTiles = kNoAllocMaxInput / kCodecBlock / kTileBlocks;  // 64
 constexpr size_t kNoAllocPadded = kNoAllocMaxTiles * kTileBlocks;             // block slots
 constexpr size_t kNoAllocSmall = 4096;                                        // job, tile tables, error word
-constexpr size_t kNoAllocScratchBytes = kNoAllocSmall + 3 * kNoAllocPadded;
+constexpr size_t kNoAllocScratchBytes = kNoAllocSmall + 4 * kNoAllocPadded;  // one 32-bit summary per block slot
 static __device__ __align__(256) unsigned char g_noAllocScratch[kNoAllocScratchBytes];
 
 constexpr int kNoAllocMaxDevices = 64;
@@ -592,9 +607,7 @@ void codecCompressNoAlloc(int device, const unsigned char* inDev, size_t n, unsi
     unsigned int* tileSums = reinterpret_cast<unsigned int*>(scratch + 1024);
     unsigned long long* tileOffsets = reinterpret_cast<unsigned long long*>(scratch + 2048);
     int* errDev = reinterpret_cast<int*>(scratch + 3072);
-    unsigned char* headers = scratch + kNoAllocSmall;
-    unsigned char* bases = headers + kNoAllocPadded;
-    unsigned char* sizes = bases + kNoAllocPadded;
+    unsigned int* summary = reinterpret_cast<unsigned int*>(scratch + kNoAllocSmall);
     static_assert(sizeof(CodecJobDev) <= 256 && kNoAllocMaxTiles * 4 <= 768 && (kNoAllocMaxTiles + 1) * 8 <= 1024, "layout");
 
     CodecJobDev job;
@@ -610,21 +623,21 @@ void codecCompressNoAlloc(int device, const unsigned char* inDev, size_t n, unsi
     for (unsigned long long t = 0; t < ntiles; ++t) emitTiles[t] = static_cast<unsigned int>(t);
 
     // The array keeps whatever the previous call left: everything read below is rewritten first --
-    // the job record and tile table here, the error word by the memset, the per-block arrays and
+    // the job record and tile table here, the error word by the memset, the per-block summaries and
     // tile sums by the analysis kernel (including the zero sizes of the padding slots).
     B2_CUDA(cudaMemcpyAsync(jobDev, &job, sizeof(job), cudaMemcpyHostToDevice, stream));
     B2_CUDA(cudaMemcpyAsync(tileJobDev, tileJob, sizeof(unsigned int) * ntiles, cudaMemcpyHostToDevice, stream));
     B2_CUDA(cudaMemsetAsync(errDev, 0, sizeof(int), stream));
     const int grid = static_cast<int>(ntiles);
-    codecAnalyzeKernel<<<grid, 256, 0, stream>>>(jobDev, tileJobDev, ntiles, headers, bases, sizes, tileSums);
+    codecAnalyzeKernel<<<grid, 256, 0, stream>>>(jobDev, tileJobDev, ntiles, summary, tileSums);
     B2_CUDA(cudaGetLastError());
     codecScanKernel<<<1, 1024, 0, stream>>>(tileSums, ntiles, tileOffsets, jobDev, 1, cap, /*rawFallback=*/0, errDev);
     B2_CUDA(cudaGetLastError());
     // the emit kernel reads its tile list from the table slot, which the analysis no longer needs
     B2_CUDA(cudaMemcpyAsync(tileJobDev + kNoAllocMaxTiles, emitTiles, sizeof(unsigned int) * ntiles, cudaMemcpyHostToDevice,
                             stream));
-    codecEmitKernel<<<grid, 256, 0, stream>>>(jobDev, tileJobDev, tileJobDev + kNoAllocMaxTiles, ntiles, headers, bases, sizes,
-                                              tileOffsets, outDev);
+    codecEmitKernel<<<grid, 256, 0, stream>>>(jobDev, tileJobDev, tileJobDev + kNoAllocMaxTiles, ntiles, summary, tileOffsets,
+                                              outDev);
     B2_CUDA(cudaGetLastError());
     int err = 0;
     B2_CUDA(cudaMemcpyAsync(&job, jobDev, sizeof(job), cudaMemcpyDeviceToHost, stream));
