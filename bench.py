@@ -58,15 +58,16 @@ def llama7b_decls(layers=32, hidden=4096, ffn=11008, vocab=32000):
     return decls
 
 
-def algorithmic_bytes(decls, folded_sizes, blob_sizes):
-    """Read-once + write-once bytes of one step: fold (input + folded output + scale tables) and, for
-    compressed constants, codec (folded input + stream output)."""
+def algorithmic_bytes(decls, folded_sizes, stream_sizes):
+    """Read-once + write-once bytes of one step.  Fold: input + folded output (written straight into
+    the blob slot) + scale tables.  Codec: every constant offered to it is read once; only a stream
+    that is smaller than its constant is written (stream_sizes[i] is its length, else None)."""
     fold = sum(d.nbytes for d in decls) + sum(folded_sizes)
     fold += sum(4 * d.base_type.shape[0] for d in decls if d.transforms)
     codec = 0
-    for d, fs, bs in zip(decls, folded_sizes, blob_sizes):
-        if bs is not None:
-            codec += fs + bs
+    for d, fs, ss in zip(decls, folded_sizes, stream_sizes):
+        if d.compress and fs >= 4096:
+            codec += fs + (ss or 0)
     return fold, codec
 
 
@@ -235,7 +236,7 @@ def main():
 
     owner = partition(decls, world)
     mine = [d for d, o in zip(decls, owner) if o == rank]
-    folder = ShardFolder(backend, mine)
+    folder = ShardFolder(backend, mine)  # whole-shard layout (sizes, bounds); also the N=1 path
 
     # device buffers (torch owns the memory; the library only sees pointers)
     inputs = [torch.empty(d.nbytes, dtype=torch.uint8, device="cuda") for d in mine]
@@ -244,35 +245,84 @@ def main():
                                   5, decls.index(d))
         assert rc == 0, lib.b200c_last_error()
     in_ptrs = [t.data_ptr() for t in inputs]
-    folded = torch.empty(folder.folded_bytes, dtype=torch.uint8, device="cuda")
-    blob = torch.empty(folder.blob_bound, dtype=torch.uint8, device="cuda")
     scales = [torch.empty(d.base_type.shape[0], dtype=torch.float32, device="cuda") if d.transforms else None for d in mine]
     zps = [torch.empty(d.base_type.shape[0], dtype=torch.int32, device="cuda") if d.transforms else None for d in mine]
     side = [(s.data_ptr(), z.data_ptr()) if s is not None else None for s, z in zip(scales, zps)]
-    # rank 0 assembles the model blob: its own segments plus every other rank's
-    gathered = None
+
+    # With several ranks the shard is cut into chunks: while chunk c+1 is folded and compressed, chunk
+    # c's segments already travel to rank 0 (NCCL send/recv over NVLink), so the gather hides behind
+    # the compute as far as rank 0's ingress bandwidth allows.
+    nchunks = 1 if world == 1 else 4
+    per_chunk = (sum(d.nbytes for d in mine) + nchunks - 1) // nchunks if mine else 1
+    chunks, cur, cur_bytes = [], [], 0
+    for i, d in enumerate(mine):
+        if cur and cur_bytes + d.nbytes > per_chunk and len(chunks) < nchunks - 1:
+            chunks.append(cur)
+            cur, cur_bytes = [], 0
+        cur.append(i)
+        cur_bytes += d.nbytes
+    chunks.append(cur)
+    while len(chunks) < nchunks:
+        chunks.append([])
+    cf = [ShardFolder(backend, [mine[i] for i in c]) if c else None for c in chunks]
+    fold_off, blob_off, fo, bo = [], [], 0, 0
+    for f in cf:
+        fold_off.append(fo)
+        blob_off.append(bo)
+        if f is not None:
+            fo += f.folded_bytes
+            bo += f.blob_bound
+    # every constant is folded straight into its slot of the blob; compression then works in place
+    folded = torch.empty(max(fo, 1), dtype=torch.uint8, device="cuda")
+    gathered, pg_sizes = None, None
+    if world > 1:
+        pg_sizes = dist.new_group(backend="gloo")  # chunk sizes travel on the host, off the NCCL stream
+        bounds = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(bounds, torch.tensor([fo], dtype=torch.int64), group=pg_sizes)
+        if rank == 0:
+            gathered = torch.empty(int(sum(int(b.item()) for b in bounds)) + 1024, dtype=torch.uint8, device="cuda")
 
     seg_info = {}
 
     def step(timers=None):
+        """One pass over the shard; timers = (begin, end, [per-chunk (fold0, fold1, codec1)]) CUDA events."""
         if timers:
             timers[0].record(stream)
-        folder.fold(in_ptrs, folded.data_ptr(), True, side)
+        segs_all, used_total, pending, at = [], 0, [], 0
+        for k, f in enumerate(cf):
+            used = 0
+            if f is not None:
+                c = chunks[k]
+                if timers:
+                    timers[2][k][0].record(stream)
+                f.fold([in_ptrs[i] for i in c], folded.data_ptr() + fold_off[k], True, [side[i] for i in c])
+                if timers:
+                    timers[2][k][1].record(stream)
+                segs = f.compress_inplace(folded.data_ptr() + fold_off[k])
+                if timers:
+                    timers[2][k][2].record(stream)
+                used = f.folded_bytes  # the chunk's slots, streams and untouched constants alike
+                segs_all += [(c[i], fold_off[k] + o, sz, comp) for i, o, sz, comp in segs]
+            used_total += used
+            if world > 1:
+                sizes = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+                dist.all_gather(sizes, torch.tensor([used], dtype=torch.int64), group=pg_sizes)
+                sizes = [int(x.item()) for x in sizes]
+                if rank == 0:
+                    if sizes[0]:
+                        gathered[at:at + sizes[0]].copy_(folded[fold_off[k]:fold_off[k] + sizes[0]], non_blocking=True)
+                    at += sizes[0]
+                    for r in range(1, world):
+                        if sizes[r]:
+                            pending.append(dist.irecv(gathered[at:at + sizes[r]], src=r))
+                        at += sizes[r]
+                elif used:
+                    pending.append(dist.isend(folded[fold_off[k]:fold_off[k] + used], dst=0))
+        for q in pending:
+            q.wait()
+        seg_info["segs"], seg_info["used"], seg_info["gathered"] = segs_all, used_total, at
         if timers:
             timers[1].record(stream)
-        segs = folder.compress(folded.data_ptr(), blob.data_ptr(), blob.numel())
-        if timers:
-            timers[2].record(stream)
-        used = max([o + s for _, o, s, _ in segs], default=0)
-        seg_info["segs"], seg_info["used"] = segs, used
-        if world > 1:
-            nonlocal gathered
-            sizes, g = gather_segments(dist, blob, used, rank, world, gathered)
-            if g is not None:
-                gathered = g
-            seg_info["gathered"] = sum(sizes)
-        if timers:
-            timers[3].record(stream)
 
     def sync_all():
         torch.cuda.synchronize()
@@ -286,8 +336,11 @@ def main():
         step()
     sync_all()
     launches0 = backend.launch_count()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
-    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    def mk():
+        return torch.cuda.Event(enable_timing=True)
+
+    ev = [(mk(), mk(), [(mk(), mk(), mk()) for _ in cf]) for _ in range(args.steps)]
+    t_begin, t_end = mk(), mk()
     t_begin.record(stream)
     for k in range(args.steps):
         step(ev[k])
@@ -304,14 +357,17 @@ def main():
         dist.all_reduce(ln)
         launches = int(ln.item())
     ms_per_step = elapsed_ms / args.steps
-    fold_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in ev]))
-    codec_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in ev]))
-    gather_ms = float(np.mean([e[2].elapsed_time(e[3]) for e in ev]))
+    live = [k for k, f in enumerate(cf) if f is not None]
+    fold_ms = float(np.mean([sum(e[2][k][0].elapsed_time(e[2][k][1]) for k in live) for e in ev]))
+    codec_ms = float(np.mean([sum(e[2][k][1].elapsed_time(e[2][k][2]) for k in live) for e in ev]))
+    step_ms_local = float(np.mean([e[0].elapsed_time(e[1]) for e in ev]))
+    gather_ms = max(0.0, step_ms_local - fold_ms - codec_ms)  # exposed (not hidden) part of the exchange
 
     # algorithmic bytes of the whole job (all ranks)
-    blob_sizes_local = {i: s for i, _, s, _ in seg_info["segs"]}
-    fold_b, codec_b = algorithmic_bytes(mine, folder.folded_sizes, [blob_sizes_local.get(i) for i in range(len(mine))])
-    tot = torch.tensor([fold_b, codec_b, sum(1 for _, _, _, c in seg_info["segs"] if c), seg_info["used"]],
+    stream_sizes = {i: sz for i, _, sz, comp in seg_info["segs"] if comp}
+    fold_b, codec_b = algorithmic_bytes(mine, folder.folded_sizes, [stream_sizes.get(i) for i in range(len(mine))])
+    blob_local = sum(sz for _, _, sz, _ in seg_info["segs"])
+    tot = torch.tensor([fold_b, codec_b, sum(1 for _, _, _, c in seg_info["segs"] if c), blob_local],
                        dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(tot)
@@ -320,12 +376,21 @@ def main():
 
     # roofline of the dominant kernel: the fused fold pass, one launch per linear weight
     peak, peak_kind = measured_peak()
-    n_fold_launch = len([d for d in mine if d.transforms])
+    # kernel launches of the fold phase (the batched entry point issues one launch per kernel
+    # configuration and chunk, not one per tensor)
+    l0 = backend.launch_count()
+    for k, f in enumerate(cf):
+        if f is not None:
+            f.fold([in_ptrs[i] for i in chunks[k]], folded.data_ptr() + fold_off[k], True, [side[i] for i in chunks[k]])
+    torch.cuda.synchronize()
+    n_fold_launch = int(backend.launch_count() - l0)
     fold_local_b, _ = algorithmic_bytes(mine, folder.folded_sizes, [None] * len(mine))
     achieved = fold_local_b / (fold_ms * 1e-3) / 1e9 if fold_ms > 0 else 0.0
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "peak_kind": peak_kind, "kernel": "fold pass (per-tensor quantise+reorder+swizzle)",
+                "traffic": None, "peak_kind": peak_kind, "kernel": "rowQuantRegBatchKernel (fused quantise + reorder + swizzle, all tensors of a configuration per launch)",
                 "launches_per_step": n_fold_launch, "avg_launch_ms": fold_ms / max(1, n_fold_launch),
+                "tensors_per_step": len([d for d in mine if d.transforms]),
+                "algorithmic_bytes_per_launch": fold_local_b / max(1, n_fold_launch),
                 "phase_ms": {"fold": fold_ms, "codec": codec_ms, "gather": gather_ms}}
     try:
         with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
@@ -343,47 +408,38 @@ def main():
         for h, t in zip(host_in, inputs):
             h.copy_(t)
         torch.cuda.synchronize()
-        chunks, cur, cur_bytes = [], [], 0
+        e_chunks, cur, cur_bytes = [], [], 0
         for i, d in enumerate(mine):
             if cur and cur_bytes + d.nbytes > 1_500_000_000:
-                chunks.append(cur)
+                e_chunks.append(cur)
                 cur, cur_bytes = [], 0
             cur.append(i)
             cur_bytes += d.nbytes
         if cur:
-            chunks.append(cur)
-        cf = [ShardFolder(backend, [mine[i] for i in c]) for c in chunks]
-        fold_off, blob_off, fo, bo = [], [], 0, 0
-        for f in cf:
-            fold_off.append(fo)
-            blob_off.append(bo)
+            e_chunks.append(cur)
+        e_cf = [ShardFolder(backend, [mine[i] for i in c]) for c in e_chunks]
+        e_fold_off, fo = [], 0
+        for f in e_cf:
+            e_fold_off.append(fo)
             fo += f.folded_bytes
-            bo += f.blob_bound
         e_folded = torch.empty(fo, dtype=torch.uint8, device="cuda")
-        e_blob = torch.empty(bo, dtype=torch.uint8, device="cuda")
-        host_blob = torch.empty(bo, dtype=torch.uint8, pin_memory=True)
-        host_pass = torch.empty(fo, dtype=torch.uint8, pin_memory=True)
+        host_blob = torch.empty(fo, dtype=torch.uint8, pin_memory=True)
         copy_stream = torch.cuda.Stream()
 
         def e2e_step():
             d2h = 0
-            for k, (c, f) in enumerate(zip(chunks, cf)):
-                f.fold([host_in[i].data_ptr() for i in c], e_folded.data_ptr() + fold_off[k], False,
+            for k, (c, f) in enumerate(zip(e_chunks, e_cf)):
+                f.fold([host_in[i].data_ptr() for i in c], e_folded.data_ptr() + e_fold_off[k], False,
                        [side[i] for i in c], max_batch_bytes=1 << 30)
-                segs = f.compress(e_folded.data_ptr() + fold_off[k], e_blob.data_ptr() + blob_off[k], f.blob_bound)
-                used = max([o + sz for _, o, sz, _ in segs], default=0)
+                segs = f.compress_inplace(e_folded.data_ptr() + e_fold_off[k])
                 done = torch.cuda.Event()
                 done.record(stream)
                 copy_stream.wait_event(done)
                 with torch.cuda.stream(copy_stream):
-                    if used:
-                        host_blob[blob_off[k]:blob_off[k] + used].copy_(e_blob[blob_off[k]:blob_off[k] + used], non_blocking=True)
-                        d2h += used
-                    for j in range(len(c)):
-                        if j not in f.comp_idx:  # constants that bypass the codec travel as folded
-                            a = fold_off[k] + f.folded_offsets[j]
-                            host_pass[a:a + f.folded_sizes[j]].copy_(e_folded[a:a + f.folded_sizes[j]], non_blocking=True)
-                            d2h += f.folded_sizes[j]
+                    for j, off, sz, _ in segs:  # each constant's bytes (stream or folded) go home
+                        a = e_fold_off[k] + off
+                        host_blob[a:a + sz].copy_(e_folded[a:a + sz], non_blocking=True)
+                        d2h += sz
             stream.wait_stream(copy_stream)
             return d2h
 
@@ -406,8 +462,8 @@ def main():
             dist.all_reduce(h2d)
         e2e = {"value": (fold_all + codec_all) / (ems * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ems,
                "h2d_bytes_per_step": int(h2d[0].item()), "d2h_bytes_per_step": int(h2d[1].item()),
-               "chunks": len(chunks)}
-        del host_in, host_blob, host_pass, e_folded, e_blob
+               "chunks": len(e_chunks)}
+        del host_in, host_blob, e_folded
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:

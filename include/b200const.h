@@ -295,6 +295,16 @@ B200C_API int b200c_btc_compress_batch(b200c_ctx* ctx, int count, const void* co
                              void* out_dev, size_t out_cap, size_t* out_offsets, size_t* out_sizes,
                              int32_t* not_smaller);
 
+/* In-place form of the batched compression, for blob writers that fold every constant straight
+ * into its slot of the blob: a buffer whose stream is smaller than the buffer gets the stream
+ * written over its own first bytes (out_sizes[i] = stream length, compressed[i] = 1); a buffer that
+ * would not shrink is left untouched (out_sizes[i] = sizes[i], compressed[i] = 0) and costs one read
+ * of its bytes and no write at all.  This is the outcome of the reference's compression pass --
+ * replace the constant only "if smaller" (compress_weights_btc.cpp:130-136) -- without moving
+ * incompressible constants.  Buffers are device memory; the call synchronises.                    */
+B200C_API int b200c_btc_compress_inplace_batch(b200c_ctx* ctx, int count, void* const* bufs_dev, const size_t* sizes,
+                                               size_t* out_sizes, int32_t* compressed);
+
 /* ---- synthetic weights ----------------------------------------------------------
  * Counter-based seeded generator (Philox-4x32-10 keyed by seed and stream)
  * used by the benchmark so that inputs never cross PCIe.  dist: 0 = normal

@@ -138,6 +138,26 @@ class ShardFolder:
         raise_for(rc, self.lib.b200c_last_error())
         return [(i, self._out_off[j], self._out_size[j], not self._not_smaller[j]) for j, i in enumerate(self.comp_idx)]
 
+    def compress_inplace(self, folded_ptr):
+        """Compresses every eligible folded segment where it lies: a segment that shrinks is replaced
+        by its stream (at the same offset), the others stay as they are.  The folded buffer then IS
+        the blob.  Returns (decl index, offset, size, compressed flag) for every constant; synchronises."""
+        k = len(self.comp_idx)
+        size = list(self.folded_sizes)
+        flag = [False] * len(self.decls)
+        if k:
+            for j, i in enumerate(self.comp_idx):
+                self._in_ptrs[j] = folded_ptr + self.folded_offsets[i]
+                self._sizes[j] = self.folded_sizes[i]
+            rc = self.lib.b200c_btc_compress_inplace_batch(self.ctx, k, self._in_ptrs, self._sizes, self._out_size,
+                                                           self._not_smaller)
+            raise_for(rc, self.lib.b200c_last_error())
+            for j, i in enumerate(self.comp_idx):
+                size[i], flag[i] = self._out_size[j], bool(self._not_smaller[j])
+        else:
+            raise_for(self.lib.b200c_synchronize(self.ctx), self.lib.b200c_last_error())
+        return [(i, self.folded_offsets[i], size[i], flag[i]) for i in range(len(self.decls))]
+
 
 def gather_segments(dist, blob, used, rank, world, gathered=None):
     """The one exchange of the multi-GPU fold: every rank's blob prefix (`used` bytes of the 1-D uint8

@@ -474,7 +474,7 @@ int b200c_btc_compress(b200c_ctx* h, const void* in, size_t n, int in_on_device,
         if (!out_on_device) devOut = static_cast<unsigned char*>(ctx->arena.alloc(cap));
         CodecBuf buf{devIn, n};
         CodecResult res{};
-        codecCompressBatch(ctx, 1, &buf, devOut, cap, /*rawFallback=*/false, &res);
+        codecCompressBatch(ctx, 1, &buf, devOut, cap, /*rawFallback=*/0, &res);
         if (!out_on_device) {
             copyD2H(ctx, out, devOut + res.offset, res.size);
             syncStream(ctx);
@@ -532,12 +532,30 @@ int b200c_btc_compress_batch(b200c_ctx* h, int count, const void* const* in_dev,
         std::vector<CodecBuf> bufs(count);
         for (int i = 0; i < count; ++i) bufs[i] = CodecBuf{static_cast<const unsigned char*>(in_dev[i]), sizes[i]};
         std::vector<CodecResult> res(count);
-        codecCompressBatch(ctx, count, bufs.data(), static_cast<unsigned char*>(out_dev), out_cap, /*rawFallback=*/true,
+        codecCompressBatch(ctx, count, bufs.data(), static_cast<unsigned char*>(out_dev), out_cap, /*rawFallback=*/1,
                            res.data());
         for (int i = 0; i < count; ++i) {
             out_offsets[i] = res[i].offset;
             out_sizes[i] = res[i].size;
             if (not_smaller) not_smaller[i] = res[i].notSmaller ? 1 : 0;
+        }
+    });
+}
+
+int b200c_btc_compress_inplace_batch(b200c_ctx* h, int count, void* const* bufs_dev, const size_t* sizes, size_t* out_sizes,
+                                     int32_t* compressed) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        CallScope scope(ctx);
+        if (count < 0 || (count > 0 && (!bufs_dev || !sizes || !out_sizes))) throw BadArg("bad batch arguments");
+        std::vector<CodecBuf> bufs(count);
+        for (int i = 0; i < count; ++i) bufs[i] = CodecBuf{static_cast<const unsigned char*>(bufs_dev[i]), sizes[i]};
+        std::vector<CodecResult> res(count);
+        codecCompressBatch(ctx, count, bufs.data(), nullptr, 0, /*rawFallback=*/2, res.data());
+        for (int i = 0; i < count; ++i) {
+            out_sizes[i] = res[i].size;
+            if (compressed) compressed[i] = res[i].notSmaller ? 0 : 1;
         }
     });
 }

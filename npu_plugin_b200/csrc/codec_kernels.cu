@@ -198,12 +198,21 @@ B2_HD void layoutJobs(CodecJobDev* jobs, int njobs, const unsigned long long* ti
         const unsigned long long raw = kCodecHeaderBytes + 4 * job.nsuper + job.recordsBytes;
         job.streamBytes = (raw + 31) & ~31ull;
         job.notSmaller = job.n <= job.streamBytes;  // bit_compactor_codec.cpp:36-39
-        job.outBytes = (rawFallback && job.notSmaller) ? job.n : job.streamBytes;
+        job.failed = 0;
+        // rawFallback 0: always the stream; 1: buffers that do not shrink are stored unchanged;
+        // 2: buffers that do not shrink take no output at all (the caller keeps them where they are)
+        if (rawFallback == 2 && job.notSmaller) {
+            job.outBytes = 0;
+            job.outBase = run;
+            continue;
+        }
+        job.outBytes = (rawFallback == 1 && job.notSmaller) ? job.n : job.streamBytes;
         job.outBase = run;
         run = (run + job.outBytes + 31) & ~31ull;
         if (job.outBase + job.outBytes > outCap) {
             if (*err == E_NONE) *err = E_CODEC;
             job.outBytes = 0;
+            job.failed = 1;
         }
     }
 }
@@ -424,7 +433,9 @@ __global__ void __launch_bounds__(256) codecEmitKernel(const CodecJobDev* __rest
 }
 
 void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned char* outDev, size_t outCap,
-                        bool rawFallback, CodecResult* results) {
+                        int rawFallback, CodecResult* results) {
+    const bool inPlace = rawFallback == 2;  // streams replace the head of their own input buffer
+    if (inPlace) outCap = ~static_cast<size_t>(0) >> 1;
     if (count <= 0) return;
     std::vector<CodecJobDev> jobs(count);
     std::vector<unsigned int> tileJob;
@@ -479,13 +490,20 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
         }
         tileOffsets[ntiles] = run;
         layoutJobs(jobsDev, count, tileOffsets, outCap, rawFallback, ctx->errWord);
+        std::vector<unsigned char> tempOut;
+        if (inPlace) {
+            size_t need = 64;
+            for (int j = 0; j < count; ++j) need = std::max<size_t>(need, jobsDev[j].outBase + jobsDev[j].outBytes + 64);
+            tempOut.resize(need);
+            outDev = tempOut.data();
+        }
         for (unsigned long long tile = 0; tile < ntiles; ++tile) {
             const CodecJobDev& job = jobsDev[tileJobDev[tile]];
             if (job.outBytes == 0) continue;
             unsigned char* dst = outDev + job.outBase;
             const unsigned long long jobFirstTile = job.firstBlock / kTileBlocks;
             const unsigned long long tileFirst = (tile - jobFirstTile) * kTileBlocks;
-            if (rawFallback && job.notSmaller) {
+            if (rawFallback == 1 && job.notSmaller) {
                 if (tileFirst == 0) std::memcpy(dst, job.in, job.n);
                 continue;
             }
@@ -507,6 +525,11 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
         }
         ctx->launches += 3;
         std::memcpy(jobs.data(), jobsDev, sizeof(CodecJobDev) * count);
+        if (inPlace) {
+            for (int j = 0; j < count; ++j) {
+                if (jobs[j].outBytes) std::memcpy(const_cast<unsigned char*>(jobs[j].in), outDev + jobs[j].outBase, jobs[j].outBytes);
+            }
+        }
     } else
 #endif
     {
@@ -514,7 +537,7 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
         codecAnalyzeKernel<<<grid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, ntiles, summary, tileSums);
         B2_CUDA(cudaGetLastError());
         codecScanKernel<<<1, 1024, 0, ctx->stream>>>(tileSums, ntiles, tileOffsets, jobsDev, count, outCap,
-                                                     rawFallback ? 1 : 0, ctx->errWord);
+                                                     rawFallback, ctx->errWord);
         B2_CUDA(cudaGetLastError());
         ctx->launches += 2;
         copyD2H(ctx, jobs.data(), jobsDev, sizeof(CodecJobDev) * count);
@@ -523,9 +546,16 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
         // buffers that do not shrink are stored as they are (a device-to-device copy); the others
         // go through the emit kernel
         std::vector<unsigned int> emitTiles;
+        if (inPlace) {
+            // the streams are built in scratch memory and then copied over the head of their inputs
+            size_t need = 64;
+            for (int j = 0; j < count; ++j) need = std::max<size_t>(need, jobs[j].outBase + jobs[j].outBytes + 64);
+            outDev = static_cast<unsigned char*>(ctx->arena.alloc(need));
+        }
         for (int j = 0; j < count; ++j) {
+            if (jobs[j].failed) throw Capacity("codec: output capacity exceeded");
             if (jobs[j].outBytes == 0) continue;
-            if (rawFallback && jobs[j].notSmaller) {
+            if (rawFallback == 1 && jobs[j].notSmaller) {
                 copyD2D(ctx, outDev + jobs[j].outBase, jobs[j].in, jobs[j].n);
                 continue;
             }
@@ -541,12 +571,19 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
                                                             tileOffsets, outDev);
             B2_CUDA(cudaGetLastError());
             ++ctx->launches;
+            if (inPlace) {
+                for (int j = 0; j < count; ++j) {
+                    if (jobs[j].outBytes) {
+                        copyD2D(ctx, const_cast<unsigned char*>(jobs[j].in), outDev + jobs[j].outBase, jobs[j].outBytes);
+                    }
+                }
+            }
             syncStream(ctx);  // emitTiles (pageable) must stay alive until the copy is done
         }
     }
     for (int j = 0; j < count; ++j) {
-        results[j].offset = jobs[j].outBase;
-        results[j].size = jobs[j].outBytes;
+        results[j].offset = inPlace ? 0 : jobs[j].outBase;
+        results[j].size = (inPlace && jobs[j].notSmaller) ? jobs[j].n : jobs[j].outBytes;
         results[j].notSmaller = jobs[j].notSmaller != 0;
     }
 }

@@ -144,7 +144,7 @@ struct CodecJobDev {
     unsigned long long n, nblocks, nsuper, firstBlock;
     unsigned long long recordsBytes, streamBytes, outBase, outBytes;
     int notSmaller;
-    int _pad;
+    int failed;
 };
 struct CodecBuf {
     const unsigned char* in;  // device
@@ -156,8 +156,10 @@ struct CodecResult {
 };
 // Compresses `count` device buffers into outDev; segment i starts at results[i].offset (32-byte
 // aligned).  With rawFallback a buffer whose stream would not be smaller is stored unchanged.
+// rawFallback 2: in place -- a buffer whose stream is smaller gets the stream written over its own
+// head (results[i].size = stream length), every other buffer is left untouched; outDev is unused.
 void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned char* outDev, size_t outCap,
-                        bool rawFallback, CodecResult* results);
+                        int rawFallback, CodecResult* results);
 // allocation-free single-buffer variant (fixed scratch inside the library image)
 size_t codecNoAllocMaxInput();
 void codecCompressNoAlloc(int device, const unsigned char* inDev, size_t n, unsigned char* outDev, size_t cap,

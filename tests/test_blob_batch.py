@@ -46,6 +46,12 @@ def test_batched_fold_matches_single_folds_and_oracle(gpu, oracle):
     decls = [linear_decl(f"w{k}", o, i) for k, (o, i) in enumerate(shapes)]
     decls.append(ConstantDecl("gain", NDType((512,), A.F16), [], 1024, compress=False))
     data = [rng.normal(0, 0.02, d.nbytes // 2).astype(np.float16) for d in decls]
+    # an int8 constant with small values: this one does compress
+    small = np.clip(np.rint(rng.laplace(0, 3, (64, 1024, 1, 1))), -127, 127).astype(np.int8)
+    qs = UniformQuantizedPerAxisType(A.SI8, A.F16, [1.0] * 64, [0] * 64, 0, -127, 127)
+    decls.append(ConstantDecl("small", NDType((64, 1024, 1, 1), A.SI8),
+                              [Transform(A.X_QUANT_CAST, elem=qs), Transform(A.X_REORDER, a=DimsOrder.NHWC)], small.size))
+    data.append(small)
     folder = ShardFolder(gpu, decls)
     ins = [DevBuf(gpu, d.nbytes) for d in decls]
     for b, x in zip(ins, data):
@@ -86,6 +92,23 @@ def test_batched_fold_matches_single_folds_and_oracle(gpu, oracle):
         assert compressed == (not not_smaller)
         expect = stream if compressed else folded
         assert size == expect.size and np.array_equal(raw[off:off + size], expect), decls[i].name
+    assert any(c for _, _, _, c in segs) and not all(c for _, _, _, c in segs)
+    # in-place form: streams replace the head of their own segment, the rest is not touched
+    inplace = folder.compress_inplace(out_b.ptr)
+    after = out_b.download()
+    assert len(inplace) == len(decls)
+    for i, off, size, compressed in inplace:
+        folded = a[off:off + folder.folded_sizes[i]]
+        if i in folder.comp_idx:
+            stream, not_smaller = oracle.btc_compress(folded)
+            assert compressed == (not not_smaller), decls[i].name
+        else:
+            assert not compressed
+        if compressed:
+            assert size == stream.size and np.array_equal(after[off:off + size], stream), decls[i].name
+            assert np.array_equal(gpu.btc_decompress(after[off:off + size], folded.size), folded)
+        else:
+            assert size == folded.size and np.array_equal(after[off:off + size], folded), decls[i].name
     for x in ins + [out_a, out_b, out_c, blob] + [s for s in scales + zps if s]:
         x.free()
 
