@@ -28,7 +28,8 @@ import numpy as np  # noqa: E402
 
 from npu_plugin_b200 import _cabi as A  # noqa: E402
 from npu_plugin_b200.blob import ConstantDecl, ShardFolder, gather_segments, partition  # noqa: E402
-from npu_plugin_b200.const import (DimsOrder, NDType, Transform, UniformQuantizedPerAxisType)  # noqa: E402
+from npu_plugin_b200.const import (DimsOrder, NDType, Transform, UniformQuantizedPerAxisType,  # noqa: E402
+                                   UniformQuantizedType)
 
 HBM_FALLBACK_GBS = 6650.0
 
@@ -58,12 +59,87 @@ def llama7b_decls(layers=32, hidden=4096, ffn=11008, vocab=32000):
     return decls
 
 
+def conv_weight_decls(instances):
+    """configs[0]: f32 [256,256,3,3] -> sym int8 per-channel -> OIYX->OYXI -> pad I to x16 -> Swizzle(5)."""
+    decls = []
+    for k in range(instances):
+        q = UniformQuantizedPerAxisType(A.SI8, A.F32, [1.0] * 256, [0] * 256, 0, -127, 127)
+        chain = [Transform(A.X_QUANTIZE_SYNTH, i0=A.QSYNTH_SYM_I8), Transform(A.X_CONVERT_ELEM_TYPE, elem=A.SI8),
+                 Transform(A.X_QUANT_CAST, elem=q), Transform(A.X_REORDER, a=DimsOrder.OYXI),
+                 Transform(A.X_PAD_WITH_ZERO, a=(0, 0, 0, 0), b=(0, 0, 0, 0)), Transform(A.X_SWIZZLE_CONSTANT, i0=5, i1=3)]
+        d = ConstantDecl(f"conv{k}", NDType((256, 256, 3, 3), A.F32), chain, 256 * 256 * 9 * 4, compress=False)
+        d.synth = (A.F32, 0, 0.05, 0.0)
+        decls.append(d)
+    return decls
+
+
+def int4_linear_decls(instances):
+    """configs[1]: f16 [11008,4096] -> asym u4 per-channel -> BitPack (-> NHWC); and a Dequantize leg
+    u8 [11008,4096] -> per-axis QuantCast -> Dequantize -> f16."""
+    decls = []
+    O, I = 11008, 4096
+    for k in range(instances):
+        q = UniformQuantizedPerAxisType(A.UI8, A.F16, [1.0] * O, [0] * O, 0, 0, 15)
+        chain = [Transform(A.X_QUANTIZE_SYNTH, i0=A.QSYNTH_ASYM_U4), Transform(A.X_CONVERT_ELEM_TYPE, elem=A.UI8),
+                 Transform(A.X_QUANT_CAST, elem=q), Transform(A.X_REORDER, a=DimsOrder.NHWC), Transform(A.X_BIT_PACK, i0=4)]
+        d = ConstantDecl(f"pack{k}", NDType((O, I, 1, 1), A.F16), chain, O * I * 2, compress=False)
+        d.synth = (A.F16, 0, 0.02, 0.0)
+        decls.append(d)
+        qd = UniformQuantizedPerAxisType(A.UI8, A.F16, [0.001 + 1e-6 * (j % 97) for j in range(O)], [j % 16 for j in range(O)], 0, 0, 15)
+        chain = [Transform(A.X_QUANT_CAST, elem=qd), Transform(A.X_REORDER, a=DimsOrder.NHWC), Transform(A.X_DEQUANTIZE)]
+        d = ConstantDecl(f"dequant{k}", NDType((O, I, 1, 1), A.UI8), chain, O * I, compress=False)
+        d.synth = (A.SI8, 1, 0.0, 0.0)
+        decls.append(d)
+    return decls
+
+
+def sparse_conv_decls(instances):
+    """configs[2]: int8 [1024,1024,1,1], 50 % zeros -> GetSparsityMap -> Swizzle and Sparsify -> Swizzle."""
+    decls = []
+    for k in range(instances):
+        for name, chain in (("map", [Transform(A.X_GET_SPARSITY_MAP), Transform(A.X_SWIZZLE_CONSTANT, i0=5, i1=3)]),
+                            ("vals", [Transform(A.X_SPARSIFY, i0=0), Transform(A.X_SWIZZLE_CONSTANT, i0=5, i1=3)])):
+            d = ConstantDecl(f"{name}{k}", NDType((1024, 1024, 1, 1), A.SI8), chain, 1024 * 1024, compress=False)
+            d.synth = (A.SI8, 1, 0.5, 0.0)
+            d.stream = k  # both chains of an instance see the same weights
+            decls.append(d)
+    return decls
+
+
+def resnet50_shapes():
+    shapes = [(64, 3, 7, 7)]
+    inplanes = 64
+    for width, blocks in ((64, 3), (128, 4), (256, 6), (512, 3)):
+        for b in range(blocks):
+            shapes += [(width, inplanes, 1, 1), (width, width, 3, 3), (width * 4, width, 1, 1)]
+            if b == 0:
+                shapes.append((width * 4, inplanes, 1, 1))
+            inplanes = width * 4
+    shapes.append((1000, 2048, 1, 1))
+    return shapes
+
+
+def resnet_decls(instances):
+    """configs[3]: 53 conv + fc int8 weights -> QuantCast -> OIYX->OYXI (-> pad I to x16) -> block codec."""
+    decls = []
+    for k in range(instances):
+        for j, (o, i, y, x) in enumerate(resnet50_shapes()):
+            q = UniformQuantizedType(A.SI8, A.F16, 0.01, 0, -127, 127)
+            chain = [Transform(A.X_QUANT_CAST, elem=q), Transform(A.X_REORDER, a=DimsOrder.OYXI)]
+            if i % 16 and i < 16:
+                chain.append(Transform(A.X_PAD_WITH_ZERO, a=(0, 0, 0, 0), b=(0, 16 - i % 16, 0, 0)))
+            d = ConstantDecl(f"r{k}.{j}", NDType((o, i, y, x), A.SI8), chain, o * i * y * x, compress=True)
+            d.synth = (A.SI8, 2, 12.0, 0.1)
+            decls.append(d)
+    return decls
+
+
 def algorithmic_bytes(decls, folded_sizes, stream_sizes):
     """Read-once + write-once bytes of one step.  Fold: input + folded output (written straight into
     the blob slot) + scale tables.  Codec: every constant offered to it is read once; only a stream
     that is smaller than its constant is written (stream_sizes[i] is its length, else None)."""
     fold = sum(d.nbytes for d in decls) + sum(folded_sizes)
-    fold += sum(4 * d.base_type.shape[0] for d in decls if d.transforms)
+    fold += sum(4 * d.base_type.shape[0] for d in decls if any(t.kind == A.X_QUANTIZE_SYNTH for t in d.transforms))
     codec = 0
     for d, fs, ss in zip(decls, folded_sizes, stream_sizes):
         if d.compress and fs >= 4096:
@@ -131,13 +207,28 @@ def measured_peak():
 
 
 # ----------------------------------------------------------------------------- CPU (reference arm / cpu_baseline)
+def host_data(d, rng):
+    """Host copy of a constant's synthetic values (same distributions as the device generator)."""
+    dt, kind, p0, p1 = getattr(d, "synth", (A.F16, 0, 0.02, 0.0))
+    n = d.base_type.getNumElements()
+    if kind == 0:
+        return rng.normal(0, p0, n).astype(np.float32 if dt == A.F32 else np.float16)
+    if kind == 1:
+        x = rng.integers(-127, 128, n).astype(np.int8)
+        x[rng.random(n) < p0] = 0
+        return x
+    x = np.clip(np.rint(rng.laplace(0, p0, n)), -127, 127).astype(np.int8)
+    x[rng.random(n) < p1] = 0
+    return x
+
+
 def cpu_sample_decls(decls, budget_elems):
     """A bounded sample of the workload for the host: whole tensors, in model order, up to the budget."""
     out, total = [], 0
     for d in decls:
         if not d.transforms:
             continue
-        n = d.nbytes // 2
+        n = d.base_type.getNumElements()
         if out and total + n > budget_elems:
             break
         out.append(d)
@@ -154,7 +245,7 @@ def run_cpu(decls, steps, warmup, budget_elems, threads=None):
     cores = orc.set_threads(threads or (os.cpu_count() or 1))
     sample = cpu_sample_decls(decls, budget_elems)
     rng = np.random.default_rng(5)
-    data = [rng.normal(0, 0.02, d.base_type.getNumElements()).astype(np.float16) for d in sample]
+    data = [host_data(d, rng) for d in sample]
     side = [(np.zeros(d.base_type.shape[0], np.float32), np.zeros(d.base_type.shape[0], np.int32)) for d in sample]
     for d, s in zip(sample, side):
         for t in d.transforms:
@@ -167,8 +258,12 @@ def run_cpu(decls, steps, warmup, budget_elems, threads=None):
         for d, x in zip(sample, data):
             c = orc.fold(d.base_type, x, False, d.transforms)
             folded = c.copyTo()
-            stream, _ = orc.btc_compress(folded)
-            b += d.nbytes + folded.size + 4 * d.base_type.shape[0] + folded.size + stream.size
+            b += d.nbytes + folded.size
+            if any(t.kind == A.X_QUANTIZE_SYNTH for t in d.transforms):
+                b += 4 * d.base_type.shape[0]
+            if d.compress and folded.size >= 4096:
+                stream, not_smaller = orc.btc_compress(folded)
+                b += folded.size + (0 if not_smaller else stream.size)
         dt = time.perf_counter() - t0
         if it >= warmup:
             times.append(dt)
@@ -177,7 +272,7 @@ def run_cpu(decls, steps, warmup, budget_elems, threads=None):
         for t in d.transforms:
             t.side0 = t.side1 = None
     sec = float(np.mean(times))
-    desc = f"{len(sample)} linear tensors ({sum(d.nbytes for d in sample) // 2} elements) of the 7B-shape model, fold + codec"
+    desc = f"the first {len(sample)} constants of the workload ({sum(d.base_type.getNumElements() for d in sample)} elements), fold + codec"
     return bytes_step / sec / 1e9, sec * 1e3, cores, desc
 
 
@@ -189,6 +284,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of the 7B-shape workload (32 = the named config)")
+    ap.add_argument("--workload", default="llama7b", choices=["llama7b", "cfg1", "cfg2", "cfg3", "cfg4"],
+                    help="llama7b = BASELINE configs[4] (the default bench line); cfgK = configs[K-1], batched")
+    ap.add_argument("--instances", type=int, default=None, help="independent instances per step for cfg1..cfg4")
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -198,11 +296,25 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    decls = llama7b_decls(layers=args.layers)
-    workload = f"llama7b-shape fold: {len([d for d in decls if d.transforms])} linear f16 weights -> sym int8 per-channel " \
-               f"-> Reorder -> Swizzle(5) -> block codec; {len(decls)} constants, layers={args.layers}"
-    config = {"workload": workload, "sharding": "by tensor (LPT)", "l2": "per-step working set (>26 GB at N=1) exceeds L2",
-              "layers": args.layers}
+    if args.workload == "llama7b":
+        decls = llama7b_decls(layers=args.layers)
+        workload = f"llama7b-shape fold: {len([d for d in decls if d.transforms])} linear f16 weights -> sym int8 per-channel " \
+                   f"-> Reorder -> Swizzle(5) -> block codec; {len(decls)} constants, layers={args.layers}"
+        config = {"workload": workload, "sharding": "by tensor (LPT)", "l2": "per-step working set (>26 GB at N=1) exceeds L2",
+                  "layers": args.layers}
+        dtype_name = "f16->i8"
+    else:
+        builder, default_n, text = {
+            "cfg1": (conv_weight_decls, 128, "conv weight f32 [256,256,3,3] -> sym int8 -> OYXI -> pad -> Swizzle(5)"),
+            "cfg2": (int4_linear_decls, 2, "f16 [11008,4096] -> asym u4 -> BitPack; and u8 -> per-axis Dequantize -> f16"),
+            "cfg3": (sparse_conv_decls, 128, "int8 [1024,1024,1,1] 50% sparse -> sparsity map + sparsify, both Swizzle(5)"),
+            "cfg4": (resnet_decls, 16, "ResNet-50-shaped int8 set (54 tensors) -> QuantCast -> OYXI (-> pad) -> block codec"),
+        }[args.workload]
+        n_inst = args.instances or default_n
+        decls = builder(n_inst)
+        config = {"workload": f"{args.workload}: {text}; {n_inst} independent instances per step",
+                  "sharding": "by tensor (LPT)", "l2": "instances rotate through buffers larger than L2", "instances": n_inst}
+        dtype_name = {"cfg1": "f32->i8", "cfg2": "f16->u4", "cfg3": "i8", "cfg4": "i8"}[args.workload]
 
     if args.impl == "reference":
         if rank != 0:
@@ -210,7 +322,7 @@ def main():
         gbs, ms, cores, desc = run_cpu(decls, max(1, args.steps), max(0, args.warmup), args.cpu_budget)
         line = {"impl": "reference", "metric": "folded_weight_GBps", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-                "scaling": "strong", "vs_baseline": None, "dtype": "f16->i8", "data": "synthetic", "config": config,
+                "scaling": "strong", "vs_baseline": None, "dtype": dtype_name, "data": "synthetic", "config": config,
                 "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": desc},
                 "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
@@ -241,12 +353,14 @@ def main():
     # device buffers (torch owns the memory; the library only sees pointers)
     inputs = [torch.empty(d.nbytes, dtype=torch.uint8, device="cuda") for d in mine]
     for i, d in enumerate(mine):
-        rc = lib.b200c_synth_fill(ctx, inputs[i].data_ptr(), d.nbytes // 2, A.F16, 0, 0.02 if d.transforms else 1.0, 0.0,
-                                  5, decls.index(d))
+        dt, dist_kind, p0, p1 = getattr(d, "synth", (A.F16, 0, 0.02 if d.transforms else 1.0, 0.0))
+        rc = lib.b200c_synth_fill(ctx, inputs[i].data_ptr(), d.nbytes * 8 // A.dtype_bits(dt), dt, dist_kind, p0, p1, 5,
+                                  getattr(d, "stream", decls.index(d)))
         assert rc == 0, lib.b200c_last_error()
     in_ptrs = [t.data_ptr() for t in inputs]
-    scales = [torch.empty(d.base_type.shape[0], dtype=torch.float32, device="cuda") if d.transforms else None for d in mine]
-    zps = [torch.empty(d.base_type.shape[0], dtype=torch.int32, device="cuda") if d.transforms else None for d in mine]
+    has_q = [any(t.kind == A.X_QUANTIZE_SYNTH for t in d.transforms) for d in mine]
+    scales = [torch.empty(d.base_type.shape[0], dtype=torch.float32, device="cuda") if q else None for d, q in zip(mine, has_q)]
+    zps = [torch.empty(d.base_type.shape[0], dtype=torch.int32, device="cuda") if q else None for d, q in zip(mine, has_q)]
     side = [(s.data_ptr(), z.data_ptr()) if s is not None else None for s, z in zip(scales, zps)]
 
     # With several ranks the shard is cut into chunks: while chunk c+1 is folded and compressed, chunk
@@ -473,7 +587,7 @@ def main():
     if rank == 0:
         line = {"metric": "folded_weight_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-                "vs_baseline": None, "dtype": "f16->i8", "data": "synthetic", "config": config, "clocks": clocks,
+                "vs_baseline": None, "dtype": dtype_name, "data": "synthetic", "config": config, "clocks": clocks,
                 "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu,
                 "bytes": {"fold": fold_all, "codec": codec_all, "blob": blob_bytes, "compressed_tensors": n_compressed},
                 "per_gpu_GBps": value / world}

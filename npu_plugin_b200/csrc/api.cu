@@ -400,6 +400,7 @@ int b200c_fold_batch(b200c_ctx* h, b200c_fold_item* items, int count, int data_o
             ~BatchGuard() {
                 c->batching = false;
                 c->rqBatch.clear();
+                c->tileBatch.clear();
             }
         } guard{ctx};
         ctx->batching = out_on_device != 0 && !B2_EMU(ctx);
@@ -423,6 +424,7 @@ int b200c_fold_batch(b200c_ctx* h, b200c_fold_item* items, int count, int data_o
             }
         }
         flushRowQuantBatch(ctx);
+        flushTileBatch(ctx);
         const bool async = out_on_device && (flags & B200C_FOLD_ASYNC);
         if (!async) {
             syncStream(ctx);

@@ -208,9 +208,28 @@ void Planner::flushPendingStats() {
     launchRowStats(_ctx, _pending.stats);
 }
 
+// Queued (batched) launches are only safe for the kernel that writes an item's final output:
+// anything an item's later kernels read must have been launched in stream order.
+struct ImmediateLaunches {
+    Context* ctx;
+    bool saved;
+    ImmediateLaunches(Context* c, bool immediate): ctx(c), saved(c->batching) {
+        if (immediate) ctx->batching = false;
+    }
+    ~ImmediateLaunches() {
+        ctx->batching = saved;
+    }
+};
+
 void Planner::runGeneric(const GenParams& p) {
     flushPendingStats();
-    launchGeneric(_ctx, p);
+    ImmediateLaunches scope(_ctx, !_emittingFinal);
+    TileItem item;
+    if (!B2_EMU(_ctx) && makeTileItem(p, &item)) {
+        launchTile(_ctx, item);
+    } else {
+        launchGeneric(_ctx, p);
+    }
 }
 
 // The whole remaining chain is "quantise every row, permute inside rows, store bytes/nibbles
@@ -281,6 +300,7 @@ bool Planner::tryFusedRowQuant(void* dst, int outMode, int outTag, int swizzleKe
     rq.dataBytes = dataBytes;
     rq.totalBytes = totalBytes;
     _pending.active = false;
+    ImmediateLaunches scope(_ctx, !_emittingFinal);
     launchRowQuantFused(_ctx, rq);
     return true;
 }
@@ -907,7 +927,9 @@ void Planner::swizzle(const Transformation& x, const TensorType& outType) {  // 
             if (total) launchSwizzleCopy(_ctx, _s.view.src, packed, dst, total, key, 0);
         }
     } else {
+        _emittingFinal = direct;
         emitCopyTo(dst, static_cast<size_t>(total), key, total);
+        _emittingFinal = false;
     }
     const int keepStorage = _s.type.bits() == 1 ? _s.storage : outType.dtype;
     View nv;
@@ -936,7 +958,10 @@ size_t Planner::run(const std::vector<Transformation>& chain, void* dst, size_t 
     if (_wroteFinal) return _finalBytes;
     const size_t need = static_cast<size_t>(_s.type.allocBytes());
     if (need > cap) throw Capacity("output buffer too small: need " + std::to_string(need) + " bytes");
-    return emitCopyTo(dst, cap, -1, 0);
+    _emittingFinal = true;
+    const size_t wrote = emitCopyTo(dst, cap, -1, 0);
+    _emittingFinal = false;
+    return wrote;
 }
 
 void Planner::runNoCopy(const std::vector<Transformation>& chain) {

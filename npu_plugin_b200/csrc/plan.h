@@ -91,6 +91,7 @@ private:
     std::vector<SideOutput> _sides;
     bool _afterBitPack = false;
     bool _sideOnDevice = false;
+    bool _emittingFinal = false;  // the kernel being issued writes the caller's output and nothing reads it later
     void* _finalDst = nullptr;
     size_t _finalCap = 0;
     bool _isLast = false;

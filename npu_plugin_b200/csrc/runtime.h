@@ -73,6 +73,18 @@ private:
     std::vector<Block> _blocks;
 };
 
+// One tile-kernel work item (tile_kernels.cu): a view in canonical form plus its tiling.
+struct TileItem {
+    GenParams g;
+    int py;          // output dim whose source stride is 1 (the transposed direction), or -1
+    int tx, ty;      // tile extents along the innermost output dim and along py
+    int esIn;        // bytes per source element
+    int needCoords;  // a per-axis operation needs the full coordinates of every element
+    long long tilesX, tilesY, tiles;
+    long long outStride[kMaxDims];
+};
+bool makeTileItem(const GenParams& p, TileItem* out);
+
 struct Context {
     int device = 0;
     cudaStream_t ownStream = nullptr;
@@ -87,6 +99,7 @@ struct Context {
     bool emulated = false;
     bool batching = false;                 // inside b200c_fold_batch: fused quantiser launches are queued
     std::vector<RowQuantParams> rqBatch;
+    std::vector<TileItem> tileBatch;
 };
 
 // device memory through the context (host malloc under emulation)
@@ -102,6 +115,9 @@ void checkDeviceError(Context* ctx);
 
 // ---- kernel entry points (defined in the .cu files) ----------------------------------------
 void launchGeneric(Context* ctx, const GenParams& p);
+// queued while ctx->batching is set, launched by flushTileBatch
+void launchTile(Context* ctx, const TileItem& it);
+void flushTileBatch(Context* ctx);
 
 struct RowStatsParams {
     GenParams view;       // evaluates the Content before quantisation (outMode unused)
