@@ -409,7 +409,9 @@ def main():
                 c = chunks[k]
                 if timers:
                     timers[2][k][0].record(stream)
+                h0 = time.perf_counter()
                 f.fold([in_ptrs[i] for i in c], folded.data_ptr() + fold_off[k], True, [side[i] for i in c])
+                seg_info["issue_s"] = seg_info.get("issue_s", 0.0) + (time.perf_counter() - h0)
                 if timers:
                     timers[2][k][1].record(stream)
                 segs = f.compress_inplace(folded.data_ptr() + fold_off[k])
@@ -456,8 +458,10 @@ def main():
     ev = [(mk(), mk(), [(mk(), mk(), mk()) for _ in cf]) for _ in range(args.steps)]
     t_begin, t_end = mk(), mk()
     t_begin.record(stream)
+    seg_info["issue_s"] = 0.0
     for k in range(args.steps):
         step(ev[k])
+    fold_issue_ms = seg_info["issue_s"] * 1e3 / max(1, args.steps)
     t_end.record(stream)
     sync_all()
     clocks = sampler.stop()
@@ -505,7 +509,7 @@ def main():
                 "launches_per_step": n_fold_launch, "avg_launch_ms": fold_ms / max(1, n_fold_launch),
                 "tensors_per_step": len([d for d in mine if d.transforms]),
                 "algorithmic_bytes_per_launch": fold_local_b / max(1, n_fold_launch),
-                "phase_ms": {"fold": fold_ms, "codec": codec_ms, "gather": gather_ms}}
+                "phase_ms": {"fold": fold_ms, "codec": codec_ms, "gather": gather_ms, "fold_host_issue": fold_issue_ms}}
     try:
         with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
             roofline["traffic"] = json.load(f).get("fold_dram_bytes_per_launch")

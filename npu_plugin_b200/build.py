@@ -5,7 +5,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["api.cu", "plan.cu", "fold_kernels.cu", "rowquant_kernels.cu", "tile_kernels.cu", "sparsity_kernels.cu", "codec_kernels.cu", "synth_kernels.cu",
+SOURCES = ["api.cu", "plan.cu", "fold_kernels.cu", "rowquant_kernels.cu", "tile_kernels.cu", "dequant_kernels.cu", "sparsity_kernels.cu", "codec_kernels.cu", "synth_kernels.cu",
            "infer.cpp"]
 HEADERS = ["ctype.h", "view.h", "runtime.h", "plan.h", "codec.h", os.path.join("..", "..", "include", "b200const.h")]
 LIB = os.path.join(CSRC, "libb200const.so")

@@ -225,6 +225,7 @@ void Planner::runGeneric(const GenParams& p) {
     flushPendingStats();
     ImmediateLaunches scope(_ctx, !_emittingFinal);
     TileItem item;
+    if (!B2_EMU(_ctx) && tryLaunchDequantRows(_ctx, p)) return;
     if (!B2_EMU(_ctx) && makeTileItem(p, &item)) {
         launchTile(_ctx, item);
     } else {

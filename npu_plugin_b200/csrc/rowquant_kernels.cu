@@ -419,95 +419,134 @@ __global__ void __launch_bounds__(256) rowQuantRegBatchKernel(const RowQuantPara
 
 // ---- shared-memory staged rows: any length up to the shared-memory budget, optional permutation ---
 template <typename T, int TPR, int SCHEME>
+__device__ __forceinline__ void rowQuantSmemBody(const RowQuantParams& p, long long g, unsigned char* smemRaw, float* redMx,
+                                                 float* redMn, float* redAm, float* redOdd) {
+    constexpr int ROWS_PER_CTA = 256 / TPR;
+    const int sub = threadIdx.x / TPR, t = threadIdx.x % TPR;
+    const int L = static_cast<int>(p.rowElems);
+    T* rowSm = reinterpret_cast<T*>(smemRaw) + static_cast<long long>(sub) * p.smemRowElems;
+    const long long row = g * ROWS_PER_CTA + sub;
+    const bool live = row < p.rows;
+    const T* src = static_cast<const T*>(p.src) + row * p.rowElems;
+    Stats s;
+    s.mx = -INFINITY;
+    s.mn = INFINITY;
+    s.amax = 0.0f;
+    s.odd = 0.0f;
+    if (live) {
+        if (p.vecIn) {
+            constexpr int PER = 16 / sizeof(T);
+            const int nvec = L / PER;
+            const uint4* src4 = reinterpret_cast<const uint4*>(src);
+            uint4* sm4 = reinterpret_cast<uint4*>(rowSm);
+            for (int v = t; v < nvec; v += TPR) {
+                const uint4 xv = __ldg(src4 + v);
+                sm4[v] = xv;
+                const T* e = reinterpret_cast<const T*>(&xv);
+#pragma unroll
+                for (int i = 0; i < PER; ++i) accum(s, elemToFloat<T>(e[i]));
+            }
+        } else {
+            for (int j = t; j < L; j += TPR) {
+                const T xv = src[j];
+                rowSm[j] = xv;
+                accum(s, elemToFloat<T>(xv));
+            }
+        }
+    }
+    s = rowReduce<TPR>(s, redMx, redMn, redAm, redOdd);  // its barrier also publishes the staged row
+    if (TPR == 32) __syncwarp();
+    float scale;
+    int zp;
+    scaleOf(SCHEME, s, scale, zp);
+    const RowQ rq = makeRowQ(scale, zp, s);
+    if (live && t == 0) {
+        p.scales[row] = scale;
+        p.zps[row] = zp;
+    }
+    if (live) {
+        unsigned char* dst = static_cast<unsigned char*>(p.dst);
+        if (p.vecOut) {
+            // two-level permutation whose inner extent is a multiple of 16 (e.g. [I][Y*X] -> [Y*X][I]
+            // with I % 16 == 0): the 16 outputs of a unit share the outer index, one division per unit
+            const bool twoLevel = p.irank == 2 && (p.ishape[1] % 16) == 0;
+            const int inner = static_cast<int>(p.ishape[1]), st0 = static_cast<int>(p.istride[0]),
+                      st1 = static_cast<int>(p.istride[1]);
+            for (int u = t; u < L / 16; u += TPR) {
+                T e[16];
+                if (p.irank == 0) {
+                    const uint4* sm4 = reinterpret_cast<const uint4*>(rowSm + u * 16);
+                    uint4* e4 = reinterpret_cast<uint4*>(e);
+#pragma unroll
+                    for (int v = 0; v < static_cast<int>(16 * sizeof(T) / 16); ++v) e4[v] = sm4[v];
+                } else if (twoLevel) {
+                    const int j = u * 16;
+                    const int outer = j / inner, in0 = j - outer * inner;
+                    const T* base = rowSm + outer * st0 + in0 * st1;
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) e[k] = base[k * st1];
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) e[k] = rowSm[rowMap(p, u * 16 + k)];
+                }
+                emitUnit<T, SCHEME>(p, e, rq, row, u);
+            }
+        } else if (p.outMode == 0) {
+            for (int j = t; j < L; j += TPR) {
+                const int q = quantOne<SCHEME>(elemToFloat<T>(rowSm[rowMap(p, j)]), rq);
+                dst[swizzleAddr(row * p.rowElems + j, p.swizzleKey)] = static_cast<unsigned char>(q);
+            }
+        } else {
+            for (int j = t; j < L / 2; j += TPR) {
+                const unsigned int lo = static_cast<unsigned int>(quantOne<SCHEME>(elemToFloat<T>(rowSm[rowMap(p, 2 * j)]), rq)) & 0xFu;
+                const unsigned int hi = static_cast<unsigned int>(quantOne<SCHEME>(elemToFloat<T>(rowSm[rowMap(p, 2 * j + 1)]), rq)) & 0xFu;
+                dst[row * (p.rowElems / 2) + j] = static_cast<unsigned char>(lo | (hi << 4));
+            }
+        }
+    }
+    if (g == 0) {  // zero tail of the swizzle size alignment
+        for (long long a = p.dataBytes + threadIdx.x; a < p.totalBytes; a += blockDim.x) {
+            static_cast<unsigned char*>(p.dst)[swizzleAddr(a, p.swizzleKey)] = 0;
+        }
+    }
+}
+
+template <typename T, int TPR, int SCHEME>
 __global__ void __launch_bounds__(256) rowQuantSmemKernel(const __grid_constant__ RowQuantParams p) {
     extern __shared__ __align__(16) unsigned char smemRaw[];
     __shared__ float redMx[8], redMn[8], redAm[8], redOdd[8];
     constexpr int ROWS_PER_CTA = 256 / TPR;
-    const int sub = threadIdx.x / TPR, t = threadIdx.x % TPR;
-    const long long L = p.rowElems;
-    T* rowSm = reinterpret_cast<T*>(smemRaw) + static_cast<long long>(sub) * p.smemRowElems;
     const long long rowGroups = (p.rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
-
     for (long long g = blockIdx.x; g < rowGroups; g += gridDim.x) {
-        const long long row = g * ROWS_PER_CTA + sub;
-        const bool live = row < p.rows;
-        const T* src = static_cast<const T*>(p.src) + row * L;
-        Stats s;
-        s.mx = -INFINITY;
-        s.mn = INFINITY;
-        s.amax = 0.0f;
-        s.odd = 0.0f;
-        if (live) {
-            if (p.vecIn) {
-                constexpr int PER = 16 / sizeof(T);
-                const long long nvec = L / PER;
-                const uint4* src4 = reinterpret_cast<const uint4*>(src);
-                uint4* sm4 = reinterpret_cast<uint4*>(rowSm);
-                for (long long v = t; v < nvec; v += TPR) {
-                    const uint4 xv = __ldg(src4 + v);
-                    sm4[v] = xv;
-                    const T* e = reinterpret_cast<const T*>(&xv);
-#pragma unroll
-                    for (int i = 0; i < PER; ++i) accum(s, elemToFloat<T>(e[i]));
-                }
-            } else {
-                for (long long j = t; j < L; j += TPR) {
-                    const T xv = src[j];
-                    rowSm[j] = xv;
-                    accum(s, elemToFloat<T>(xv));
-                }
-            }
-        }
-        if (TPR > 32) {
-            s = blockReduce256(s, redMx, redMn, redAm, redOdd);  // its barrier also publishes the staged row
+        rowQuantSmemBody<T, TPR, SCHEME>(p, g, smemRaw, redMx, redMn, redAm, redOdd);
+        __syncthreads();  // the row buffer and the reduction slots are reused by the next row group
+    }
+}
+
+template <typename T, int TPR, int SCHEME>
+__global__ void __launch_bounds__(256) rowQuantSmemBatchKernel(const RowQuantParams* __restrict__ items,
+                                                               const long long* __restrict__ groupStart, int nitems) {
+    extern __shared__ __align__(16) unsigned char smemRaw[];
+    __shared__ float redMx[8], redMn[8], redAm[8], redOdd[8];
+    __shared__ RowQuantParams p;
+    int lo = 0, hi = nitems - 1;
+    const long long b = blockIdx.x;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (groupStart[mid] <= b) {
+            lo = mid;
         } else {
-            s = warpReduce(s);
-            __syncwarp();
-        }
-        float scale;
-        int zp;
-        scaleOf(SCHEME, s, scale, zp);
-        const RowQ rq = makeRowQ(scale, zp, s);
-        if (live && t == 0) {
-            p.scales[row] = scale;
-            p.zps[row] = zp;
-        }
-        if (live) {
-            unsigned char* dst = static_cast<unsigned char*>(p.dst);
-            if (p.vecOut) {
-                for (long long u = t; u < L / 16; u += TPR) {
-                    T e[16];
-                    if (p.irank == 0) {
-                        const uint4* sm4 = reinterpret_cast<const uint4*>(rowSm + u * 16);
-                        uint4* e4 = reinterpret_cast<uint4*>(e);
-#pragma unroll
-                        for (int v = 0; v < static_cast<int>(16 * sizeof(T) / 16); ++v) e4[v] = sm4[v];
-                    } else {
-#pragma unroll
-                        for (int k = 0; k < 16; ++k) e[k] = rowSm[rowMap(p, u * 16 + k)];
-                    }
-                    emitUnit<T, SCHEME>(p, e, rq, row, u);
-                }
-            } else if (p.outMode == 0) {
-                for (long long j = t; j < L; j += TPR) {
-                    const int q = quantOne<SCHEME>(elemToFloat<T>(rowSm[rowMap(p, j)]), rq);
-                    dst[swizzleAddr(row * L + j, p.swizzleKey)] = static_cast<unsigned char>(q);
-                }
-            } else {
-                for (long long j = t; j < L / 2; j += TPR) {
-                    const unsigned int lo = static_cast<unsigned int>(quantOne<SCHEME>(elemToFloat<T>(rowSm[rowMap(p, 2 * j)]), rq)) & 0xFu;
-                    const unsigned int hi = static_cast<unsigned int>(quantOne<SCHEME>(elemToFloat<T>(rowSm[rowMap(p, 2 * j + 1)]), rq)) & 0xFu;
-                    dst[row * (L / 2) + j] = static_cast<unsigned char>(lo | (hi << 4));
-                }
-            }
-        }
-        if (TPR > 32) {
-            __syncthreads();  // the row buffer and the reduction slots are reused by the next row
-        } else {
-            __syncwarp();
+            hi = mid - 1;
         }
     }
-    zeroTail(p);
+    {
+        const int words = sizeof(RowQuantParams) / 4;
+        const unsigned int* srcw = reinterpret_cast<const unsigned int*>(items + lo);
+        unsigned int* dstw = reinterpret_cast<unsigned int*>(&p);
+        for (int i = threadIdx.x; i < words; i += blockDim.x) dstw[i] = srcw[i];
+    }
+    __syncthreads();
+    rowQuantSmemBody<T, TPR, SCHEME>(p, b - groupStart[lo], smemRaw, redMx, redMn, redAm, redOdd);
 }
 
 // ---- launch configuration -----------------------------------------------------------------------
@@ -599,28 +638,64 @@ void launchRegConfig(Context* ctx, const RegConfig& c, const RowQuantParams* one
 }
 
 template <typename T, int TPR, int SCHEME>
-void launchSmem(Context* ctx, const RowQuantParams& p) {
+void launchSmemT(Context* ctx, const RowQuantParams* one, const RowQuantParams* itemsDev, const long long* startDev,
+                 int nitems, long long totalGroups, size_t smem) {
     constexpr int ROWS_PER_CTA = 256 / TPR;
-    const size_t smem = static_cast<size_t>(ROWS_PER_CTA) * p.smemRowElems * sizeof(T);
     if (smem > 48 * 1024) {
         B2_CUDA(cudaFuncSetAttribute(rowQuantSmemKernel<T, TPR, SCHEME>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(smem)));
+        B2_CUDA(cudaFuncSetAttribute(rowQuantSmemBatchKernel<T, TPR, SCHEME>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(smem)));
     }
-    const long long groups = (p.rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
-    const long long perSm = std::max<long long>(1, std::min<long long>(8, (200 * 1024) / std::max<size_t>(smem, 1024)));
-    const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>(groups, ctx->smCount * perSm)));
-    rowQuantSmemKernel<T, TPR, SCHEME><<<grid, 256, smem, ctx->stream>>>(p);
+    if (one) {
+        const long long groups = (one->rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
+        const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>(groups, 1LL << 30)));
+        rowQuantSmemKernel<T, TPR, SCHEME><<<grid, 256, smem, ctx->stream>>>(*one);
+    } else {
+        rowQuantSmemBatchKernel<T, TPR, SCHEME>
+                <<<static_cast<unsigned int>(totalGroups), 256, smem, ctx->stream>>>(itemsDev, startDev, nitems);
+    }
     B2_CUDA(cudaGetLastError());
     ++ctx->launches;
 }
 
-template <typename T, int SCHEME>
-void dispatchSmem(Context* ctx, const RowQuantParams& p) {
-    if (p.rowElems <= 1024) {
-        launchSmem<T, 32, SCHEME>(ctx, p);
-    } else {
-        launchSmem<T, 256, SCHEME>(ctx, p);
+// staged configuration: (element type, threads per row, scheme); maxu is 0
+void launchSmemConfig(Context* ctx, const RegConfig& c, const RowQuantParams* one, const RowQuantParams* itemsDev,
+                      const long long* startDev, int nitems, long long totalGroups, size_t smem) {
+    const bool sym = c.scheme == B200C_QSYNTH_SYM_I8;
+#define B2_SM_CASE(T_, TPR_)                                                                                              \
+    if (sym) {                                                                                                            \
+        launchSmemT<T_, TPR_, B200C_QSYNTH_SYM_I8>(ctx, one, itemsDev, startDev, nitems, totalGroups, smem);              \
+    } else {                                                                                                              \
+        launchSmemT<T_, TPR_, B200C_QSYNTH_ASYM_U4>(ctx, one, itemsDev, startDev, nitems, totalGroups, smem);             \
     }
+    if (c.srcTag == T_F16) {
+        if (c.tpr == 32) {
+            B2_SM_CASE(__half, 32)
+        } else {
+            B2_SM_CASE(__half, 256)
+        }
+    } else {
+        if (c.tpr == 32) {
+            B2_SM_CASE(float, 32)
+        } else {
+            B2_SM_CASE(float, 256)
+        }
+    }
+#undef B2_SM_CASE
+}
+
+size_t smemBytesOf(const RowQuantParams& p, int tpr) {
+    return static_cast<size_t>(256 / tpr) * p.smemRowElems * (p.srcTag == T_F16 ? 2 : 4);
+}
+
+// configuration of any item: register path when it fits, staged path otherwise (maxu == 0)
+void pickConfig(const RowQuantParams& p, RegConfig* c) {
+    if (pickRegConfig(p, c)) return;
+    c->srcTag = p.srcTag;
+    c->scheme = p.scheme;
+    c->maxu = 0;
+    c->tpr = p.rowElems <= 1024 ? 32 : 256;
 }
 
 }  // namespace
@@ -636,20 +711,16 @@ void launchRowQuantFused(Context* ctx, RowQuantParams p) {
     p.vecOut = ((reinterpret_cast<uintptr_t>(p.dst) & 15) == 0 && p.rowElems % 16 == 0) ? 1 : 0;
     // rows padded to 16 bytes in shared memory so every row slot stays 128-bit aligned
     p.smemRowElems = (p.rowElems * es + 15) / 16 * 16 / es;
-    RegConfig c;
-    if (pickRegConfig(p, &c)) {
-        if (ctx->batching) {
-            ctx->rqBatch.push_back(p);  // launched by flushRowQuantBatch with its peers
-            return;
-        }
-        launchRegConfig(ctx, c, &p, nullptr, nullptr, 0, 0);
+    if (ctx->batching) {
+        ctx->rqBatch.push_back(p);  // launched by flushRowQuantBatch with its peers
         return;
     }
-    const bool sym = p.scheme == B200C_QSYNTH_SYM_I8;
-    if (p.srcTag == T_F16) {
-        sym ? dispatchSmem<__half, B200C_QSYNTH_SYM_I8>(ctx, p) : dispatchSmem<__half, B200C_QSYNTH_ASYM_U4>(ctx, p);
+    RegConfig c;
+    pickConfig(p, &c);
+    if (c.maxu > 0) {
+        launchRegConfig(ctx, c, &p, nullptr, nullptr, 0, 0);
     } else {
-        sym ? dispatchSmem<float, B200C_QSYNTH_SYM_I8>(ctx, p) : dispatchSmem<float, B200C_QSYNTH_ASYM_U4>(ctx, p);
+        launchSmemConfig(ctx, c, &p, nullptr, nullptr, 0, 0, smemBytesOf(p, c.tpr));
     }
 }
 
@@ -661,13 +732,16 @@ void flushRowQuantBatch(Context* ctx) {
     for (size_t i = 0; i < pending.size(); ++i) {
         if (done[i]) continue;
         RegConfig c;
-        pickRegConfig(pending[i], &c);
+        pickConfig(pending[i], &c);
         std::vector<RowQuantParams> group;
         std::vector<long long> start;
         long long total = 0;
+        size_t smem = 0;
         for (size_t j = i; j < pending.size(); ++j) {
             RegConfig cj;
-            if (done[j] || !pickRegConfig(pending[j], &cj) || !(cj == c)) continue;
+            if (done[j]) continue;
+            pickConfig(pending[j], &cj);
+            if (!(cj == c)) continue;
             const int rowsPerCta = 256 / c.tpr;
             const long long groups = (pending[j].rows + rowsPerCta - 1) / rowsPerCta;
             if (total + groups > 0x7FFFFFFFLL) continue;  // next flush round
@@ -675,16 +749,23 @@ void flushRowQuantBatch(Context* ctx) {
             group.push_back(pending[j]);
             start.push_back(total);
             total += groups;
+            if (c.maxu == 0) smem = std::max(smem, smemBytesOf(pending[j], c.tpr));
         }
-        if (group.size() == 1) {
-            launchRegConfig(ctx, c, &group[0], nullptr, nullptr, 0, 0);
-            continue;
+        const bool one = group.size() == 1;
+        RowQuantParams* itemsDev = nullptr;
+        long long* startDev = nullptr;
+        if (!one) {
+            itemsDev = static_cast<RowQuantParams*>(ctx->arena.alloc(sizeof(RowQuantParams) * group.size()));
+            startDev = static_cast<long long*>(ctx->arena.alloc(sizeof(long long) * start.size()));
+            copyH2D(ctx, itemsDev, group.data(), sizeof(RowQuantParams) * group.size());
+            copyH2D(ctx, startDev, start.data(), sizeof(long long) * start.size());
         }
-        RowQuantParams* itemsDev = static_cast<RowQuantParams*>(ctx->arena.alloc(sizeof(RowQuantParams) * group.size()));
-        long long* startDev = static_cast<long long*>(ctx->arena.alloc(sizeof(long long) * start.size()));
-        copyH2D(ctx, itemsDev, group.data(), sizeof(RowQuantParams) * group.size());
-        copyH2D(ctx, startDev, start.data(), sizeof(long long) * start.size());
-        launchRegConfig(ctx, c, nullptr, itemsDev, startDev, static_cast<int>(group.size()), total);
+        if (c.maxu > 0) {
+            launchRegConfig(ctx, c, one ? &group[0] : nullptr, itemsDev, startDev, static_cast<int>(group.size()), total);
+        } else {
+            launchSmemConfig(ctx, c, one ? &group[0] : nullptr, itemsDev, startDev, static_cast<int>(group.size()), total,
+                             smem);
+        }
     }
 }
 

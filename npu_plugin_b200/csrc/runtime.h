@@ -118,6 +118,8 @@ void launchGeneric(Context* ctx, const GenParams& p);
 // queued while ctx->batching is set, launched by flushTileBatch
 void launchTile(Context* ctx, const TileItem& it);
 void flushTileBatch(Context* ctx);
+// contiguous rows of 8-bit storage with one Dequantize and f16/f32 output (dequant_kernels.cu)
+bool tryLaunchDequantRows(Context* ctx, const GenParams& p);
 
 struct RowStatsParams {
     GenParams view;       // evaluates the Content before quantisation (outMode unused)
