@@ -48,6 +48,7 @@ class ShardFolder:
         self.decls = decls
         self._keep = []
         self._prepared = []
+        self._marshalled = None
         self.folded_offsets, self.folded_sizes = [], []
         at = 0
         for d in decls:
@@ -86,15 +87,18 @@ class ShardFolder:
         the items are issued in groups of at most max_batch_bytes so the staging memory stays bounded."""
         lib, ctx = self.lib, self.ctx
         n = len(self.decls)
-        for i in range(n):
-            it = self._items[i]
-            it.data = data_ptrs[i]
-            it.out = folded_ptr + self.folded_offsets[i]
-            if side_ptrs is not None and side_ptrs[i] is not None:
-                ch = self._prepared[i][1]
-                for k in range(self._prepared[i][2]):
-                    if ch[k].kind == A.X_QUANTIZE_SYNTH:
-                        ch[k].side0, ch[k].side1 = side_ptrs[i]
+        key = (tuple(data_ptrs), folded_ptr, tuple(side_ptrs) if side_ptrs is not None else None)
+        if key != self._marshalled:  # the same buffers as last time: the item array is already filled in
+            for i in range(n):
+                it = self._items[i]
+                it.data = data_ptrs[i]
+                it.out = folded_ptr + self.folded_offsets[i]
+                if side_ptrs is not None and side_ptrs[i] is not None:
+                    ch = self._prepared[i][1]
+                    for k in range(self._prepared[i][2]):
+                        if ch[k].kind == A.X_QUANTIZE_SYNTH:
+                            ch[k].side0, ch[k].side1 = side_ptrs[i]
+            self._marshalled = key
         first = 0
         while first < n:
             last, total = first, 0
@@ -113,6 +117,7 @@ class ShardFolder:
         flags = A.FOLD_ASYNC
         for i, (bt, ch, n, ot) in enumerate(self._prepared):
             d = self.decls[i]
+            self._marshalled = None
             if side_ptrs is not None and side_ptrs[i] is not None:
                 for k in range(n):
                     if ch[k].kind == A.X_QUANTIZE_SYNTH:

@@ -401,10 +401,18 @@ int b200c_fold_batch(b200c_ctx* h, b200c_fold_item* items, int count, int data_o
                 c->batching = false;
                 c->rqBatch.clear();
                 c->tileBatch.clear();
+                c->mapBatch.clear();
+                c->sparseBatch.clear();
+                c->queuedBytes = 0;
             }
         } guard{ctx};
+        // Queued launches go out in growing slices (32 MB of input, then twice as much each time), so
+        // the device starts early and works while the host plans the remaining items.
+        long long flushAt = 32LL << 20;
+        ctx->queuedBytes = 0;
         ctx->batching = out_on_device != 0 && !B2_EMU(ctx);
         std::vector<std::pair<void*, void*>> hostOuts;  // (user pointer, device staging) when out is on the host
+        std::vector<std::pair<int, const long long*>> deferred;  // items whose size is read back at the end
         for (int i = 0; i < count; ++i) {
             b200c_fold_item& it = items[i];
             if (!it.out && it.out_cap > 0) throw BadArg("null output pointer");
@@ -422,13 +430,30 @@ int b200c_fold_batch(b200c_ctx* h, b200c_fold_item* items, int count, int data_o
                     copyD2H(ctx, so.user, so.dev, so.bytes);
                 }
             }
+            if (plan->deferredBytes()) deferred.push_back({i, plan->deferredBytes()});
+            if (ctx->queuedBytes >= flushAt) {
+                flushRowQuantBatch(ctx);
+                flushTileBatch(ctx);
+                flushSparsityBatch(ctx);
+                ctx->queuedBytes = 0;
+                flushAt = std::min(flushAt * 2, 4LL << 30);
+            }
         }
         flushRowQuantBatch(ctx);
         flushTileBatch(ctx);
-        const bool async = out_on_device && (flags & B200C_FOLD_ASYNC);
+        flushSparsityBatch(ctx);
+        const bool async = out_on_device && (flags & B200C_FOLD_ASYNC) && deferred.empty();
         if (!async) {
+            // results whose size only the data decides: one read-back for all of them
+            std::vector<long long> sizes(deferred.size(), 0);
+            for (size_t k = 0; k < deferred.size(); ++k) copyD2H(ctx, &sizes[k], deferred[k].second, sizeof(long long));
             syncStream(ctx);
             checkDeviceError(ctx);
+            for (size_t k = 0; k < deferred.size(); ++k) {
+                b200c_fold_item& it = items[deferred[k].first];
+                if (static_cast<size_t>(sizes[k]) > it.out_cap) throw Capacity("output buffer too small");
+                it.out_bytes = static_cast<size_t>(sizes[k]);
+            }
         }
     });
 }

@@ -20,7 +20,7 @@ size_t codecBound(size_t n) {
 // Blocks are indexed in a padded space in which every buffer starts on a tile boundary
 // (kTileBlocks blocks), so one tile never straddles two buffers.
 constexpr int kTileBlocks = 4096;
-constexpr int kIterBlocks = 64;  // blocks handled per CTA iteration: 256 threads, 4 lanes per block
+constexpr int kIterBlocks = 256;  // blocks per CTA iteration: 256 threads, 4 lanes per block, 4 rounds between barriers
 
 B2_HD void loadBlock(const CodecJobDev& job, unsigned long long blk, unsigned char* b) {
     const unsigned long long first = blk * kCodecBlock;
@@ -253,10 +253,88 @@ __global__ void __launch_bounds__(1024) codecScanKernel(const unsigned int* __re
         if (threadIdx.x == blockDim.x - 1) carry = before + mine;
         __syncthreads();
     }
-    if (threadIdx.x == 0) {
-        tileOffsets[ntiles] = carry;
-        __threadfence_block();
-        layoutJobs(jobs, njobs, tileOffsets, outCap, rawFallback, err);
+    if (threadIdx.x == 0) tileOffsets[ntiles] = carry;
+    __syncthreads();  // tileOffsets (written by this CTA) is read back below
+    // per-buffer layout, the parallel form of layoutJobs: sizes per buffer, then an exclusive scan of
+    // the 32-byte aligned output sizes for the placement
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (int base = 0; base < njobs; base += blockDim.x) {
+        const int j = base + threadIdx.x;
+        unsigned long long mine = 0, outBytes = 0;
+        bool skip = false;
+        if (j < njobs) {
+            CodecJobDev& job = jobs[j];
+            const unsigned long long t0 = job.firstBlock / kTileBlocks;
+            const unsigned long long t1 = t0 + (job.nblocks + kTileBlocks - 1) / kTileBlocks;
+            job.recordsBytes = tileOffsets[t1] - tileOffsets[t0];
+            const unsigned long long raw = kCodecHeaderBytes + 4 * job.nsuper + job.recordsBytes;
+            job.streamBytes = (raw + 31) & ~31ull;
+            job.notSmaller = job.n <= job.streamBytes;
+            job.failed = 0;
+            skip = rawFallback == 2 && job.notSmaller;
+            outBytes = skip ? 0 : ((rawFallback == 1 && job.notSmaller) ? job.n : job.streamBytes);
+            mine = (outBytes + 31) & ~31ull;
+        }
+        unsigned long long incl = mine;
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) warpSum[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            unsigned long long w = warpSum[lane];
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long t = __shfl_up_sync(0xFFFFFFFFu, w, o);
+                if (lane >= o) w += t;
+            }
+            warpSum[lane] = w;
+        }
+        __syncthreads();
+        const unsigned long long before = carry + (warp ? warpSum[warp - 1] : 0) + incl - mine;
+        if (j < njobs) {
+            CodecJobDev& job = jobs[j];
+            job.outBase = before;
+            job.outBytes = outBytes;
+            if (!skip && before + outBytes > outCap) {
+                atomicCAS(err, E_NONE, E_CODEC);
+                job.outBytes = 0;
+                job.failed = 1;
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) carry = before + mine;
+        __syncthreads();
+    }
+}
+
+// In-place mode: every stream built in scratch memory goes over the head of its own input buffer.
+// One CTA per tile of a compressed buffer copies the tile's share (256 KB) of the stream.
+__global__ void __launch_bounds__(256) codecCopyBackKernel(const CodecJobDev* __restrict__ jobs,
+                                                           const unsigned int* __restrict__ tileJob,
+                                                           const unsigned int* __restrict__ emitTiles,
+                                                           unsigned long long nEmitTiles,
+                                                           const unsigned char* __restrict__ scratch) {
+    for (unsigned long long e = blockIdx.x; e < nEmitTiles; e += gridDim.x) {
+        const unsigned long long tile = emitTiles[e];
+        const CodecJobDev& job = jobs[tileJob[tile]];
+        const unsigned long long rel = tile - job.firstBlock / kTileBlocks;
+        const unsigned long long span = static_cast<unsigned long long>(kTileBlocks) * kCodecBlock;
+        const unsigned long long lo = rel * span;
+        if (lo >= job.outBytes) continue;
+        const unsigned long long len = min(span, job.outBytes - lo);
+        const unsigned char* src = scratch + job.outBase + lo;
+        unsigned char* dst = const_cast<unsigned char*>(job.in) + lo;
+        if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+            const unsigned long long nvec = len / 16;
+            for (unsigned long long v = threadIdx.x; v < nvec; v += blockDim.x) {
+                reinterpret_cast<uint4*>(dst)[v] = reinterpret_cast<const uint4*>(src)[v];
+            }
+            for (unsigned long long b = nvec * 16 + threadIdx.x; b < len; b += blockDim.x) dst[b] = src[b];
+        } else {
+            for (unsigned long long b = threadIdx.x; b < len; b += blockDim.x) dst[b] = src[b];
+        }
     }
 }
 
@@ -349,13 +427,15 @@ __global__ void __launch_bounds__(256) codecEmitKernel(const CodecJobDev* __rest
             const unsigned int winEnd = relOff[(it + 1) * kIterBlocks];
             const unsigned long long outStart = tileRel + winStart;  // offset inside the records area
             const unsigned int phase = static_cast<unsigned int>(reinterpret_cast<uintptr_t>(records + outStart) & 15);
-            const unsigned long long blk = blk0 + grp;
+            for (int sub = 0; sub < kIterBlocks / 64; ++sub) {
+            const int bi = sub * 64 + grp;  // block of this iteration handled by the 4-lane group
+            const unsigned long long blk = blk0 + bi;
             if (blk < job.nblocks) {
-                const unsigned long long g = tile * kTileBlocks + static_cast<unsigned long long>(it) * kIterBlocks + grp;
+                const unsigned long long g = tile * kTileBlocks + static_cast<unsigned long long>(it) * kIterBlocks + bi;
                 const unsigned int word = summary[g];
                 const unsigned int header = word & 0xFFu, base = (word >> 8) & 0xFFu;
                 const int mode = header >> 5, w = header & 31;
-                unsigned char* rec = window + phase + (relOff[it * kIterBlocks + grp] - winStart);
+                unsigned char* rec = window + phase + (relOff[it * kIterBlocks + bi] - winStart);
                 const uint4 v = loadLane16(job.in, job.n, blk, lane4, vec);
                 const unsigned int words[4] = {v.x, v.y, v.z, v.w};
                 if (lane4 == 0) rec[0] = static_cast<unsigned char>(header);
@@ -400,9 +480,11 @@ __global__ void __launch_bounds__(256) codecEmitKernel(const CodecJobDev* __rest
                         if (b != 0) *nz++ = static_cast<unsigned char>(b);
                     }
                 }
-                if (grp == 0 && lane4 == 0) {
-                    putU32(dst + kCodecHeaderBytes + 4 * (blk0 / kCodecSuper), static_cast<unsigned int>(outStart));
+                if (grp == 0 && lane4 == 0) {  // blk is the first block of an index group of 64
+                    putU32(dst + kCodecHeaderBytes + 4 * (blk / kCodecSuper),
+                           static_cast<unsigned int>(tileRel + relOff[it * kIterBlocks + bi]));
                 }
+            }
             }
             __syncthreads();
             // copy the window out: [outStart, outStart + len) of the records area
@@ -572,11 +654,9 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
             B2_CUDA(cudaGetLastError());
             ++ctx->launches;
             if (inPlace) {
-                for (int j = 0; j < count; ++j) {
-                    if (jobs[j].outBytes) {
-                        copyD2D(ctx, const_cast<unsigned char*>(jobs[j].in), outDev + jobs[j].outBase, jobs[j].outBytes);
-                    }
-                }
+                codecCopyBackKernel<<<egrid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, emitDev, emitTiles.size(), outDev);
+                B2_CUDA(cudaGetLastError());
+                ++ctx->launches;
             }
             syncStream(ctx);  // emitTiles (pageable) must stay alive until the copy is done
         }

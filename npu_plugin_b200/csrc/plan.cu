@@ -633,6 +633,12 @@ static unsigned long long sparseBitsFor(int64_t value, int tag, bool checked) {
     }
 }
 
+// the transformation being applied is followed by exactly one more, a SwizzleConstant that writes
+// the caller's buffer
+bool Planner::finalSwizzleFollows() const {
+    return _next != nullptr && _nextIsLast && _next->kind == B200C_X_SWIZZLE_CONSTANT && _finalDst != nullptr;
+}
+
 void Planner::getSparsityMap(const TensorType& outType, int swizzleKey) {
     const int64_t sv = sparsifyValue(_s.type);
     const int tag = sparsityTag(_s.type);
@@ -647,9 +653,36 @@ void Planner::getSparsityMap(const TensorType& outType, int swizzleKey) {
     }
     const void* dense = denseAs(tag);
     const size_t bytes = static_cast<size_t>(oc * outBits / 8);
-    void* dst = _ctx->arena.alloc(bytes ? bytes : 1);
-    if (bytes) {
-        launchSparsityMap(_ctx, dense, tag, oc, work, outBits, sparseBitsFor(sv, tag, false), dst, swizzleKey);
+    void* dst = nullptr;
+    const bool swzNext = finalSwizzleFollows();
+    if (!B2_EMU(_ctx) && bytes > 0 && tagBytes(tag) == 1 && work % 16 == 0 && _finalDst && (_isLast || swzNext) &&
+        ((reinterpret_cast<uintptr_t>(dense) | reinterpret_cast<uintptr_t>(_finalDst)) & 15) == 0) {
+        // 8-bit elements and the result is the caller's output: one (batched) launch writes the map
+        // where it belongs, through the swizzle rotation when the chain ends in SwizzleConstant
+        MapItem it;
+        it.src = static_cast<const unsigned char*>(dense);
+        it.dst = static_cast<unsigned char*>(_finalDst);
+        it.oc = oc;
+        it.work = work;
+        it.outBytesPerOC = outBits / 8;
+        it.sparseByte = static_cast<unsigned int>(sparseBitsFor(sv, tag, false) & 0xFF);
+        it.swizzleKey = swzNext ? static_cast<int>(static_cast<uint32_t>(_next->i0) % 6u) : -1;
+        it.totalBytes = swzNext ? roundUp(static_cast<int64_t>(bytes), kSwizzleSizeAlign) : static_cast<int64_t>(bytes);
+        if (static_cast<size_t>(it.totalBytes) > _finalCap) throw Capacity("output buffer too small");
+        launchMapItem(_ctx, it);
+        dst = _finalDst;
+        if (swzNext) {
+            _fusedSwizzle = true;
+            _fusedTotal = it.totalBytes;
+        } else {
+            _wroteFinal = true;
+            _finalBytes = bytes;
+        }
+    } else {
+        dst = _ctx->arena.alloc(bytes ? bytes : 1);
+        if (bytes) {
+            launchSparsityMap(_ctx, dense, tag, oc, work, outBits, sparseBitsFor(sv, tag, false), dst, swizzleKey);
+        }
     }
     View nv;
     nv.src = dst;
@@ -691,6 +724,59 @@ void Planner::sparsify(const Transformation& x) {  // sparsify.cpp:115-186
     const int eb = tagBytes(tag);
     const unsigned long long sbits = sparseBitsFor(sv, tag, true);
     const void* dense = denseAs(tag);
+
+    const bool swzNext = finalSwizzleFollows();
+    if (!B2_EMU(_ctx) && eb == 1 && oc > 0 && work > 0 && work % 16 == 0 && _finalDst && (_isLast || swzNext) &&
+        ((reinterpret_cast<uintptr_t>(dense) | reinterpret_cast<uintptr_t>(_finalDst)) & 15) == 0 &&
+        (x.hasAux || _ctx->batching)) {
+        // 8-bit elements and the result is the caller's output: count, channel offsets and the
+        // compaction run as three (batched) launches that write the values where they belong.  Without
+        // numActualElements the size of the result is only known on the device; the batched entry
+        // point reads it back once for all items.
+        SparseItem it;
+        it.src = static_cast<const unsigned char*>(dense);
+        it.dst = static_cast<unsigned char*>(_finalDst);
+        it.oc = oc;
+        it.work = work;
+        it.counts = static_cast<long long*>(_ctx->arena.alloc(static_cast<size_t>(oc) * sizeof(long long)));
+        it.offsets = static_cast<long long*>(_ctx->arena.alloc(static_cast<size_t>(oc + 1) * sizeof(long long)));
+        it.bytesOut = static_cast<long long*>(_ctx->arena.alloc(sizeof(long long)));
+        it.dstCap = static_cast<long long>(_finalCap);
+        it.fixedBytes = -1;
+        it.sparseByte = static_cast<unsigned int>(sbits & 0xFF);
+        it.swizzleKey = swzNext ? static_cast<int>(static_cast<uint32_t>(_next->i0) % 6u) : -1;
+        it.err = _ctx->errWord;
+        int64_t total = 0;
+        if (x.hasAux) {
+            for (int64_t n : x.aux) total += roundUp(n * eb, kWeightSetAlign);
+            it.fixedBytes = total;
+            const int64_t written = swzNext ? roundUp(total, kSwizzleSizeAlign) : total;
+            if (static_cast<size_t>(written) > _finalCap) throw Capacity("output buffer too small");
+            _finalBytes = static_cast<size_t>(written);
+        } else {
+            _deferredBytes = it.bytesOut;
+            _finalBytes = 0;
+        }
+        launchSparseItem(_ctx, it);
+        const TensorType outType = withShapeAndElem(_s.type, {total, 1, 1, 1}, B200C_UI8, QuantInfo());
+        View nv;
+        nv.src = _finalDst;
+        nv.srcBytes = static_cast<size_t>(total);
+        nv.srcTag = T_U8;
+        setShape(nv, outType.memShape());
+        contiguousStrides(nv);
+        _s.view = nv;
+        _s.type = outType;
+        _s.storage = B200C_UI8;
+        _s.splat = false;
+        if (swzNext) {
+            _fusedSwizzle = true;
+            _fusedTotal = static_cast<int64_t>(_finalBytes);
+        } else {
+            _wroteFinal = true;
+        }
+        return;
+    }
 
     // actual per-channel counts always drive the layout (the running index of sparsify.cpp:137-154);
     // numActualElements only sizes the buffer
@@ -903,6 +989,23 @@ size_t Planner::emitCopyTo(void* dst, size_t cap, int swizzleKey, int64_t totalB
 // ---------------------------------------------------------------------------- SwizzleConstant
 void Planner::swizzle(const Transformation& x, const TensorType& outType) {  // swizzle_transform.cpp:202-239
     const int key = static_cast<int>(static_cast<uint32_t>(x.i0) % 6u);  // setStaggerBits: bits % (MAX_SWIZZLE_KEY + 1)
+    if (_fusedSwizzle) {  // the producing kernel already wrote the rotated bytes into the caller's buffer
+        _fusedSwizzle = false;
+        const int keep = _s.type.bits() == 1 ? _s.storage : outType.dtype;
+        View nv;
+        nv.src = _finalDst;
+        nv.srcBytes = static_cast<size_t>(_fusedTotal);
+        nv.srcTag = dtBits(keep) >= 8 ? tagOfStorage(keep) : static_cast<int>(T_NONE);
+        setShape(nv, outType.memShape());
+        contiguousStrides(nv);
+        _s.view = nv;
+        _s.type = outType;
+        _s.storage = keep;
+        _s.splat = false;
+        _wroteFinal = true;
+        _finalBytes = static_cast<size_t>(_fusedTotal);
+        return;
+    }
     const int64_t total = roundUp(_s.type.allocBytes(), kSwizzleSizeAlign);
     void* dst = nullptr;
     const bool direct = _finalDst != nullptr && _isLast;
@@ -953,9 +1056,12 @@ size_t Planner::run(const std::vector<Transformation>& chain, void* dst, size_t 
     _finalCap = cap;
     for (size_t i = 0; i < chain.size(); ++i) {
         _isLast = (i + 1 == chain.size());
+        _next = _isLast ? nullptr : &chain[i + 1];
+        _nextIsLast = (i + 2 == chain.size());
         _wroteFinal = false;
         apply(chain[i]);
     }
+    _next = nullptr;
     if (_wroteFinal) return _finalBytes;
     const size_t need = static_cast<size_t>(_s.type.allocBytes());
     if (need > cap) throw Capacity("output buffer too small: need " + std::to_string(need) + " bytes");

@@ -56,6 +56,11 @@ public:
     const std::vector<SideOutput>& sideOutputs() const {
         return _sides;
     }
+    // device word holding the size of the final result when only the data decides it (Sparsify
+    // without numActualElements written straight to the output); nullptr otherwise
+    const long long* deferredBytes() const {
+        return _deferredBytes;
+    }
 
 private:
     void apply(const Transformation& x);
@@ -97,6 +102,12 @@ private:
     bool _isLast = false;
     bool _wroteFinal = false;
     size_t _finalBytes = 0;
+    const Transformation* _next = nullptr;  // the transformation after the one being applied
+    bool _nextIsLast = false;
+    bool _fusedSwizzle = false;  // the producer already wrote the swizzled bytes of the final SwizzleConstant
+    int64_t _fusedTotal = 0;
+    const long long* _deferredBytes = nullptr;
+    bool finalSwizzleFollows() const;
 };
 
 }  // namespace b200c

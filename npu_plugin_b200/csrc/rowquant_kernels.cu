@@ -713,6 +713,7 @@ void launchRowQuantFused(Context* ctx, RowQuantParams p) {
     p.smemRowElems = (p.rowElems * es + 15) / 16 * 16 / es;
     if (ctx->batching) {
         ctx->rqBatch.push_back(p);  // launched by flushRowQuantBatch with its peers
+        ctx->queuedBytes += p.rows * p.rowElems * es;
         return;
     }
     RegConfig c;

@@ -80,10 +80,38 @@ struct TileItem {
     int tx, ty;      // tile extents along the innermost output dim and along py
     int esIn;        // bytes per source element
     int needCoords;  // a per-axis operation needs the full coordinates of every element
-    long long tilesX, tilesY, tiles;
+    int fast;        // 0: element-wise body; 1: raw contiguous copy; 2: raw transpose of source-contiguous blocks
+    int tz;          // fast == 2: consecutive outer blocks (dim rank-3) per tile
+    long long tilesX, tilesY, tilesZ, tiles;
     long long outStride[kMaxDims];
 };
 bool makeTileItem(const GenParams& p, TileItem* out);
+
+// One GetSparsityMap of 8-bit elements written straight to its final place (sparsity_kernels.cu).
+struct MapItem {
+    const unsigned char* src;
+    unsigned char* dst;
+    long long oc, work;        // channels, elements per channel (a multiple of 16)
+    long long outBytesPerOC;   // map bytes per channel (rows padded to 128 bits)
+    long long totalBytes;      // bytes to write: the map, then zeros up to the swizzle size alignment
+    unsigned int sparseByte;
+    int swizzleKey;
+};
+
+// One Sparsify of 8-bit elements written straight to its final place.
+struct SparseItem {
+    const unsigned char* src;
+    unsigned char* dst;
+    long long oc, work;
+    long long* counts;     // [oc] non-sparse elements per channel (device scratch)
+    long long* offsets;    // [oc + 1] byte offset of every channel, total at [oc] (device scratch)
+    long long* bytesOut;   // device word: size of the result in bytes
+    long long dstCap;      // bytes available at dst
+    long long fixedBytes;  // buffer size given by numActualElements, or -1 when the data decides
+    unsigned int sparseByte;
+    int swizzleKey;        // -1: not swizzled
+    int* err;
+};
 
 struct Context {
     int device = 0;
@@ -100,6 +128,9 @@ struct Context {
     bool batching = false;                 // inside b200c_fold_batch: fused quantiser launches are queued
     std::vector<RowQuantParams> rqBatch;
     std::vector<TileItem> tileBatch;
+    std::vector<MapItem> mapBatch;
+    std::vector<SparseItem> sparseBatch;
+    long long queuedBytes = 0;             // input bytes of the queued launches (drives early flushes)
 };
 
 // device memory through the context (host malloc under emulation)
@@ -137,6 +168,11 @@ void launchRowQuantFused(Context* ctx, RowQuantParams p);
 void flushRowQuantBatch(Context* ctx);
 size_t rowQuantMaxRowBytes();
 
+// 8-bit sparsity transforms whose result goes straight to the caller's buffer: queued while
+// ctx->batching is set and launched by flushSparsityBatch (one launch per stage for all items)
+void launchMapItem(Context* ctx, const MapItem& it);
+void launchSparseItem(Context* ctx, const SparseItem& it);
+void flushSparsityBatch(Context* ctx);
 // sparsity (GetSparsityMap / Sparsify) on a dense buffer of `tag` elements laid out [OC][work]
 void launchSparsityMap(Context* ctx, const void* src, int tag, long long oc, long long work, long long outBitsPerOC,
                        unsigned long long sparseBits, void* dstBits, int swizzleKey);

@@ -6,6 +6,7 @@
 #include "runtime.h"
 
 #include <algorithm>
+#include <vector>
 
 namespace b200c {
 
@@ -296,6 +297,285 @@ void launchSparsifyScatter(Context* ctx, const void* src, int tag, long long oc,
                                                          static_cast<unsigned char*>(dst), dstBytes, swizzleKey, err);
     B2_CUDA(cudaGetLastError());
     ++ctx->launches;
+}
+
+// ---------------------------------------------------------------------------- batched 8-bit paths
+// Many tensors per launch; a CTA (or warp) finds its item with a binary search over prefix sums.
+namespace {
+
+__device__ __forceinline__ int findItem(const long long* __restrict__ start, int nitems, long long b) {
+    int lo = 0, hi = nitems - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (start[mid] <= b) {
+            lo = mid;
+        } else {
+            hi = mid - 1;
+        }
+    }
+    return lo;
+}
+
+// 0x80 in every byte of w that differs from the matching byte of sv4
+__device__ __forceinline__ unsigned int neBytes(unsigned int w, unsigned int sv4) {
+    const unsigned int y = w ^ sv4;
+    return (((y & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | y) & 0x80808080u;
+}
+
+// bit k set when byte k of the 16-byte vector differs from the sparse value
+__device__ __forceinline__ unsigned int neMask16(const uint4& v, unsigned int sv4) {
+    const unsigned int w[4] = {v.x, v.y, v.z, v.w};
+    unsigned int m = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const unsigned int ne = neBytes(w[i], sv4) >> 7;  // 0x01 per differing byte
+        m |= (((ne * 0x01020408u) >> 24) & 0xFu) << (4 * i);
+    }
+    return m;
+}
+
+constexpr int kMapUnitsPerCta = 1024;  // 16 input bytes -> 2 map bytes per unit, 4 units per thread
+
+__global__ void __launch_bounds__(256) sparsityMapBatchKernel(const MapItem* __restrict__ items,
+                                                              const long long* __restrict__ ctaStart, int nitems) {
+    const int k = findItem(ctaStart, nitems, blockIdx.x);
+    const MapItem it = items[k];
+    const unsigned int sv4 = it.sparseByte * 0x01010101u;
+    const long long unitsPerOC = it.outBytesPerOC / 2, dataUnitsPerOC = it.work / 16;
+    const long long units = (it.totalBytes + 1) / 2, mapUnits = it.oc * unitsPerOC;
+    const long long first = (blockIdx.x - ctaStart[k]) * kMapUnitsPerCta;
+#pragma unroll
+    for (int r = 0; r < kMapUnitsPerCta / 256; ++r) {
+        const long long u = first + r * 256 + threadIdx.x;
+        if (u >= units) break;
+        unsigned int mask16 = 0;
+        if (u < mapUnits) {
+            const long long oc = u / unitsPerOC, j = u - oc * unitsPerOC;
+            if (j < dataUnitsPerOC) mask16 = neMask16(__ldg(reinterpret_cast<const uint4*>(it.src + oc * it.work) + j), sv4);
+        }
+        // two output bytes; a 16-byte swizzle chunk is never split
+        *reinterpret_cast<unsigned short*>(it.dst + swizzleAddr(u * 2, it.swizzleKey)) = static_cast<unsigned short>(mask16);
+    }
+}
+
+// one warp per channel
+__global__ void __launch_bounds__(256) sparseCountBatchKernel(const SparseItem* __restrict__ items,
+                                                              const long long* __restrict__ chanStart, int nitems,
+                                                              long long nchan) {
+    const long long ch = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (ch >= nchan) return;
+    const int lane = threadIdx.x & 31;
+    const int k = findItem(chanStart, nitems, ch);
+    const SparseItem& it = items[k];
+    const long long c = ch - chanStart[k];
+    const unsigned int sv4 = it.sparseByte * 0x01010101u;
+    const uint4* row = reinterpret_cast<const uint4*>(it.src + c * it.work);
+    const long long nvec = it.work / 16;
+    int n = 0;
+    for (long long v = lane; v < nvec; v += 32) {
+        const uint4 x = __ldg(row + v);
+        n += __popc(neBytes(x.x, sv4)) + __popc(neBytes(x.y, sv4)) + __popc(neBytes(x.z, sv4)) + __popc(neBytes(x.w, sv4));
+    }
+    for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xFFFFFFFFu, n, o);
+    if (lane == 0) it.counts[c] = n;
+}
+
+// one CTA per item: channel offsets (16-byte aligned channel starts) and the size of the result
+__global__ void __launch_bounds__(1024) sparseOffsetsBatchKernel(const SparseItem* __restrict__ items) {
+    __shared__ long long warpSum[32];
+    __shared__ long long carry;
+    const SparseItem& it = items[blockIdx.x];
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (long long tile = 0; tile < it.oc; tile += blockDim.x) {
+        const long long c = tile + threadIdx.x;
+        const long long mine = c < it.oc ? ((it.counts[c] + 15) & ~15ll) : 0;
+        long long incl = mine;
+        for (int o = 1; o < 32; o <<= 1) {
+            const long long t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) warpSum[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            long long w = warpSum[lane];
+            for (int o = 1; o < 32; o <<= 1) {
+                const long long t = __shfl_up_sync(0xFFFFFFFFu, w, o);
+                if (lane >= o) w += t;
+            }
+            warpSum[lane] = w;
+        }
+        __syncthreads();
+        const long long before = carry + (warp ? warpSum[warp - 1] : 0) + incl - mine;
+        if (c < it.oc) it.offsets[c] = before;
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) carry = before + mine;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        it.offsets[it.oc] = carry;
+        const long long buffer = it.fixedBytes >= 0 ? it.fixedBytes : carry;
+        *it.bytesOut = it.swizzleKey >= 0 ? ((buffer + 511) & ~511ll) : buffer;
+    }
+}
+
+// One warp per channel keeps the element order: every round takes 32 x 16 elements, ranks the
+// survivors with popc and a warp scan, compacts them into a shared-memory staging line and writes
+// whole 16-byte chunks (channel starts are 16-byte aligned, so chunks never straddle channels and
+// the swizzle rotation applies to them directly).  The last chunk of a channel is padded with
+// zeros; the warp of the last channel also zeroes the rest of the buffer.
+__global__ void __launch_bounds__(256) sparseScatterBatchKernel(const SparseItem* __restrict__ items,
+                                                                const long long* __restrict__ chanStart, int nitems,
+                                                                long long nchan) {
+    __shared__ __align__(16) unsigned char stage[8][544];
+    const long long ch = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (ch >= nchan) return;
+    const int lane = threadIdx.x & 31;
+    unsigned char* st = stage[threadIdx.x >> 5];
+    const int k = findItem(chanStart, nitems, ch);
+    const SparseItem& it = items[k];
+    const long long c = ch - chanStart[k];
+    const unsigned int sv4 = it.sparseByte * 0x01010101u;
+    const uint4* row = reinterpret_cast<const uint4*>(it.src + c * it.work);
+    const long long nvec = it.work / 16;
+    const long long written = *it.bytesOut;                                    // size of the result
+    const long long dataEnd = it.fixedBytes >= 0 ? it.fixedBytes : written;   // values must end here
+    const long long cap = min(written, it.dstCap);
+    long long outPos = it.offsets[c];
+    int fill = 0;
+    bool overflow = false;
+    for (long long base = 0; base < nvec; base += 32) {
+        const long long v = base + lane;
+        uint4 x = make_uint4(0, 0, 0, 0);
+        unsigned int m = 0;
+        if (v < nvec) {
+            x = __ldg(row + v);
+            m = neMask16(x, sv4);
+        }
+        const int cnt = __popc(m);
+        int incl = cnt;
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        int pos = fill + incl - cnt;
+        const unsigned int w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if ((m >> i) & 1u) st[pos++] = static_cast<unsigned char>(w[i >> 2] >> (8 * (i & 3)));
+        }
+        fill += __shfl_sync(0xFFFFFFFFu, incl, 31);
+        __syncwarp();
+        const int nch = fill >> 4, rem = fill & 15;
+        if (lane < nch) {
+            const long long a = outPos + lane * 16;
+            if (a + 16 > dataEnd) {
+                overflow = true;
+            } else if (a + 16 <= cap) {
+                *reinterpret_cast<uint4*>(it.dst + swizzleAddr(a, it.swizzleKey)) = *reinterpret_cast<const uint4*>(st + lane * 16);
+            }
+        }
+        const unsigned char keep = lane < rem ? st[nch * 16 + lane] : 0;
+        __syncwarp();
+        if (lane < rem) st[lane] = keep;
+        __syncwarp();
+        outPos += static_cast<long long>(nch) * 16;
+        fill = rem;
+    }
+    if (fill > 0) {
+        if (lane >= fill && lane < 16) st[lane] = 0;
+        __syncwarp();
+        if (lane == 0) {
+            if (outPos + 16 > dataEnd) {
+                overflow = true;
+            } else if (outPos + 16 <= cap) {
+                *reinterpret_cast<uint4*>(it.dst + swizzleAddr(outPos, it.swizzleKey)) = *reinterpret_cast<const uint4*>(st);
+            }
+        }
+        outPos += 16;
+    }
+    if (overflow) atomicCAS(it.err, E_NONE, E_SPARSE_OVERFLOW);
+    if (c == it.oc - 1) {  // zero fill behind the last channel (16-byte chunks, then bytes)
+        long long a = outPos + lane * 16ll;
+        for (; a + 16 <= cap; a += 512) *reinterpret_cast<uint4*>(it.dst + swizzleAddr(a, it.swizzleKey)) = make_uint4(0, 0, 0, 0);
+        const long long tailAt = outPos + ((cap > outPos ? cap - outPos : 0) / 16) * 16;
+        for (long long b = tailAt + lane; b < cap; b += 32) it.dst[swizzleAddr(b, it.swizzleKey)] = 0;
+    }
+}
+
+template <typename T>
+T* uploadItems(Context* ctx, const std::vector<T>& v) {
+    T* d = static_cast<T*>(ctx->arena.alloc(sizeof(T) * v.size()));
+    copyH2D(ctx, d, v.data(), sizeof(T) * v.size());
+    return d;
+}
+
+void runMapItems(Context* ctx, const std::vector<MapItem>& items) {
+    if (items.empty()) return;
+    std::vector<long long> start;
+    long long ctas = 0;
+    for (const MapItem& it : items) {
+        start.push_back(ctas);
+        ctas += ((it.totalBytes + 1) / 2 + kMapUnitsPerCta - 1) / kMapUnitsPerCta;
+    }
+    if (ctas <= 0 || ctas > 0x7FFFFFFFLL) throw NotBuilt("sparsity map batch too large for one launch");
+    sparsityMapBatchKernel<<<static_cast<unsigned int>(ctas), 256, 0, ctx->stream>>>(uploadItems(ctx, items), uploadItems(ctx, start),
+                                                                                      static_cast<int>(items.size()));
+    B2_CUDA(cudaGetLastError());
+    ++ctx->launches;
+}
+
+void runSparseItems(Context* ctx, const std::vector<SparseItem>& items) {
+    if (items.empty()) return;
+    std::vector<long long> start;
+    long long nchan = 0;
+    for (const SparseItem& it : items) {
+        start.push_back(nchan);
+        nchan += it.oc;
+    }
+    const long long ctas = (nchan + 7) / 8;
+    if (ctas <= 0 || ctas > 0x7FFFFFFFLL) throw NotBuilt("sparsify batch too large for one launch");
+    const SparseItem* d = uploadItems(ctx, items);
+    const long long* ds = uploadItems(ctx, start);
+    const int n = static_cast<int>(items.size());
+    sparseCountBatchKernel<<<static_cast<unsigned int>(ctas), 256, 0, ctx->stream>>>(d, ds, n, nchan);
+    B2_CUDA(cudaGetLastError());
+    sparseOffsetsBatchKernel<<<n, 1024, 0, ctx->stream>>>(d);
+    B2_CUDA(cudaGetLastError());
+    sparseScatterBatchKernel<<<static_cast<unsigned int>(ctas), 256, 0, ctx->stream>>>(d, ds, n, nchan);
+    B2_CUDA(cudaGetLastError());
+    ctx->launches += 3;
+}
+
+}  // namespace
+
+void launchMapItem(Context* ctx, const MapItem& it) {
+    if (it.totalBytes <= 0) return;
+    if (ctx->batching) {
+        ctx->mapBatch.push_back(it);
+        ctx->queuedBytes += it.oc * it.work;
+        return;
+    }
+    runMapItems(ctx, std::vector<MapItem>(1, it));
+}
+
+void launchSparseItem(Context* ctx, const SparseItem& it) {
+    if (ctx->batching) {
+        ctx->sparseBatch.push_back(it);
+        ctx->queuedBytes += it.oc * it.work;
+        return;
+    }
+    runSparseItems(ctx, std::vector<SparseItem>(1, it));
+}
+
+void flushSparsityBatch(Context* ctx) {
+    std::vector<MapItem> maps;
+    std::vector<SparseItem> sparse;
+    maps.swap(ctx->mapBatch);
+    sparse.swap(ctx->sparseBatch);
+    runMapItems(ctx, maps);
+    runSparseItems(ctx, sparse);
 }
 
 }  // namespace b200c

@@ -31,6 +31,132 @@ B2_HD bool insideBoxes(const GenParams& g, const long long* coord, int* hit) {
     return true;
 }
 
+
+// swizzled position of byte address a (16-byte chunks move inside 512-byte blocks, the low 4 bits stay)
+__device__ __forceinline__ long long swz(long long a, int key) {
+    return swizzleAddr(a, key);
+}
+
+// fast == 1: the tile is a run of nx elements contiguous in source and output; bytes are copied as they are
+__device__ __forceinline__ void copyTile(const GenParams& g, long long srcElem, long long outElem, int nx, int es) {
+    const unsigned char* src = static_cast<const unsigned char*>(g.src) + srcElem * es;
+    unsigned char* dst = static_cast<unsigned char*>(g.dst);
+    const long long outByte = outElem * es;
+    const long long bytes = static_cast<long long>(nx) * es;
+    const bool vec = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) | static_cast<uintptr_t>(outByte)) & 15) == 0;
+    const long long nvec = vec ? bytes / 16 : 0;
+    for (long long v = threadIdx.x; v < nvec; v += kTileThreads) {
+        const uint4 x = __ldg(reinterpret_cast<const uint4*>(src) + v);
+        *reinterpret_cast<uint4*>(dst + swz(outByte + v * 16, g.swizzleKey)) = x;
+    }
+    for (long long b = nvec * 16 + threadIdx.x; b < bytes; b += kTileThreads) dst[swz(outByte + b, g.swizzleKey)] = src[b];
+}
+
+// byte i of a register array of 32-bit words, i known at compile time
+#define B2_SEL(i_) ((i_) & 3)
+template <int YI>
+__device__ __forceinline__ uint4 gather9(const unsigned int (&w)[36]) {
+    // output bytes k = 0..15 are source bytes k * 9 + YI of the thread's 144-byte span
+    unsigned int o[4];
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        const int i0 = (4 * m + 0) * 9 + YI, i1 = (4 * m + 1) * 9 + YI, i2 = (4 * m + 2) * 9 + YI, i3 = (4 * m + 3) * 9 + YI;
+        const unsigned int lo = __byte_perm(w[i0 >> 2], w[i1 >> 2], B2_SEL(i0) | ((4 + B2_SEL(i1)) << 4));
+        const unsigned int hi = __byte_perm(w[i2 >> 2], w[i3 >> 2], B2_SEL(i2) | ((4 + B2_SEL(i3)) << 4));
+        o[m] = __byte_perm(lo, hi, 0x5410);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+#undef B2_SEL
+
+// fast == 2: nz blocks of [nx][ny] elements, contiguous in the source, become nz blocks of [ny][nx].
+// The source span is staged linearly (128-bit loads where aligned), the output is written in 32-bit
+// or 128-bit pieces along x.
+__device__ __forceinline__ void transposeTile(const GenParams& g, long long srcElem, long long outElem, int nz, int ny, int nx,
+                                              long long outStrideY, int es, unsigned char* smem) {
+    const unsigned char* src = static_cast<const unsigned char*>(g.src) + srcElem * es;
+    unsigned char* dst = static_cast<unsigned char*>(g.dst);
+    const int block = nx * ny;  // elements of one block; also the output stride between blocks
+    const int bytes = nz * block * es;
+    const int phase = static_cast<int>(reinterpret_cast<uintptr_t>(src) & 15);
+    {
+        const int head = min(bytes, (16 - phase) & 15);
+        const int nvec = (bytes - head) / 16;
+        const int tailAt = head + nvec * 16;
+        if (threadIdx.x < head) smem[phase + threadIdx.x] = src[threadIdx.x];
+        const uint4* s4 = reinterpret_cast<const uint4*>(src + head);
+        uint4* d4 = reinterpret_cast<uint4*>(smem + phase + head);
+        for (int v = threadIdx.x; v < nvec; v += kTileThreads) d4[v] = __ldg(s4 + v);
+        if (threadIdx.x < bytes - tailAt) smem[phase + tailAt + threadIdx.x] = src[tailAt + threadIdx.x];
+    }
+    __syncthreads();
+    const unsigned char* sm = smem + phase;
+    const long long outByte0 = outElem * es;
+    const bool dst16 = ((reinterpret_cast<uintptr_t>(dst) | static_cast<uintptr_t>(outByte0)) & 15) == 0;
+    if (es == 1 && ny == 9 && phase == 0 && (nx & 15) == 0 && dst16 && (outStrideY & 15) == 0) {
+        const int unitsX = nx >> 4;
+        const int units = nz * unitsX;
+        for (int u = threadIdx.x; u < units; u += kTileThreads) {
+            const int zi = u / unitsX, xu = u - zi * unitsX;
+            unsigned int w[36];
+            const uint4* s4 = reinterpret_cast<const uint4*>(sm + (zi * block + xu * 16 * 9));
+#pragma unroll
+            for (int i = 0; i < 9; ++i) {
+                const uint4 v = s4[i];
+                w[4 * i] = v.x;
+                w[4 * i + 1] = v.y;
+                w[4 * i + 2] = v.z;
+                w[4 * i + 3] = v.w;
+            }
+            const long long o = outByte0 + static_cast<long long>(zi) * block + xu * 16;
+            *reinterpret_cast<uint4*>(dst + swz(o + 0 * outStrideY, g.swizzleKey)) = gather9<0>(w);
+            *reinterpret_cast<uint4*>(dst + swz(o + 1 * outStrideY, g.swizzleKey)) = gather9<1>(w);
+            *reinterpret_cast<uint4*>(dst + swz(o + 2 * outStrideY, g.swizzleKey)) = gather9<2>(w);
+            *reinterpret_cast<uint4*>(dst + swz(o + 3 * outStrideY, g.swizzleKey)) = gather9<3>(w);
+            *reinterpret_cast<uint4*>(dst + swz(o + 4 * outStrideY, g.swizzleKey)) = gather9<4>(w);
+            *reinterpret_cast<uint4*>(dst + swz(o + 5 * outStrideY, g.swizzleKey)) = gather9<5>(w);
+            *reinterpret_cast<uint4*>(dst + swz(o + 6 * outStrideY, g.swizzleKey)) = gather9<6>(w);
+            *reinterpret_cast<uint4*>(dst + swz(o + 7 * outStrideY, g.swizzleKey)) = gather9<7>(w);
+            *reinterpret_cast<uint4*>(dst + swz(o + 8 * outStrideY, g.swizzleKey)) = gather9<8>(w);
+        }
+        return;
+    }
+    const int perWord = 4 / es;  // es is 1, 2 or 4 here
+    const bool words = ((reinterpret_cast<uintptr_t>(dst) | static_cast<uintptr_t>(outByte0)) & 3) == 0 &&
+                       ((outStrideY * es) & 3) == 0 && (nx % perWord) == 0 && ((static_cast<long long>(block) * es) & 3) == 0;
+    if (words) {
+        const int wordsX = nx / perWord;
+        const int perBlock = ny * wordsX;
+        const int total = nz * perBlock;
+        for (int t = threadIdx.x; t < total; t += kTileThreads) {
+            const int zi = t / perBlock, r = t - zi * perBlock;
+            const int yi = r / wordsX, xw = r - yi * wordsX;
+            const unsigned char* b = sm + (zi * block + xw * perWord * ny + yi) * es;
+            unsigned int word;
+            if (es == 1) {
+                word = b[0] | (static_cast<unsigned int>(b[ny]) << 8) | (static_cast<unsigned int>(b[2 * ny]) << 16) |
+                       (static_cast<unsigned int>(b[3 * ny]) << 24);
+            } else if (es == 2) {
+                word = *reinterpret_cast<const unsigned short*>(b) |
+                       (static_cast<unsigned int>(*reinterpret_cast<const unsigned short*>(b + 2 * ny)) << 16);
+            } else {
+                word = *reinterpret_cast<const unsigned int*>(b);
+            }
+            const long long o = outByte0 + (static_cast<long long>(zi) * block + yi * outStrideY + xw * perWord) * es;
+            *reinterpret_cast<unsigned int*>(dst + swz(o, g.swizzleKey)) = word;
+        }
+        return;
+    }
+    const int total = nz * block;
+    for (int t = threadIdx.x; t < total; t += kTileThreads) {
+        const int zi = t / block, r = t - zi * block;
+        const int yi = r / nx, xi = r - yi * nx;
+        const unsigned char* b = sm + (zi * block + xi * ny + yi) * es;
+        const long long o = outByte0 + (static_cast<long long>(zi) * block + yi * outStrideY + xi) * es;
+        for (int k = 0; k < es; ++k) dst[swz(o + k, g.swizzleKey)] = b[k];
+    }
+}
+
 __device__ __forceinline__ void tileBody(const TileItem& it, long long tile, unsigned char* smem) {
     const GenParams& g = it.g;
     const int px = g.rank - 1, py = it.py;
@@ -43,12 +169,18 @@ __device__ __forceinline__ void tileBody(const TileItem& it, long long tile, uns
     // outer coordinates (all dims but x and y), source and output offsets of the tile origin
     long long coord[kMaxDims];
     long long srcBase = g.base, outBase = 0;
+    int nz = 1;
     for (int k = g.rank - 2; k >= 0; --k) {
         if (k == py) continue;
-        const long long s = g.shape[k];
+        const bool blocked = it.fast == 2 && it.tz > 1 && k == g.rank - 3;
+        const long long s = blocked ? it.tilesZ : g.shape[k];
         const long long q = rest / s;
-        const long long c = rest - q * s;
+        long long c = rest - q * s;
         rest = q;
+        if (blocked) {
+            c *= it.tz;
+            nz = static_cast<int>(min(static_cast<long long>(it.tz), g.shape[k] - c));
+        }
         coord[k] = c;
         srcBase += c * g.stride[k];
         outBase += c * it.outStride[k];
@@ -57,6 +189,19 @@ __device__ __forceinline__ void tileBody(const TileItem& it, long long tile, uns
     const int nx = static_cast<int>(min(static_cast<long long>(it.tx), shapeX - x0));
     const int ny = static_cast<int>(min(static_cast<long long>(it.ty), shapeY - y0));
     const int es = it.esIn;
+    if (it.fast) {
+        if (it.fast == 1) {
+            copyTile(g, srcBase + x0, outBase + x0, nx, es);
+        } else {
+            transposeTile(g, srcBase + x0 * sx, outBase + x0, nz, ny, nx, it.outStride[py], es, smem);
+        }
+        if (tile == 0) {
+            for (long long a = g.dataBytes + threadIdx.x; a < g.totalBytes; a += kTileThreads) {
+                static_cast<unsigned char*>(g.dst)[swizzleAddr(a, g.swizzleKey)] = 0;
+            }
+        }
+        return;
+    }
     const int pitch = it.ty * es + 4;
     const bool simple = g.nBoxes == 0 && !it.needCoords;
     int err = E_NONE;
@@ -273,11 +418,32 @@ bool makeTileItem(const GenParams& p, TileItem* out) {
         it.ty = 1;
         it.tx = static_cast<int>(std::min<long long>(g.shape[px], 2048));
     }
+    // views that only move bytes take the vectorised bodies
+    const bool raw = g.nOps == 0 && g.nBoxes == 0 && (g.outMode == OUT_RAW || g.outTag == g.srcTag) &&
+                     tagBytes(g.outTag) == it.esIn;
+    it.fast = 0;
+    it.tz = 1;
+    it.tilesZ = 1;
+    if (raw && it.py < 0 && g.stride[px] == 1) {
+        it.fast = 1;
+        it.tx = static_cast<int>(std::min<long long>(g.shape[px], 16384 / it.esIn));
+    } else if (raw && it.py >= 0 && it.esIn <= 4 && g.stride[px] == g.shape[it.py] &&
+               g.shape[it.py] * it.esIn * 16 <= kTileSmemBytes - 16) {
+        it.fast = 2;
+        const long long ny = g.shape[it.py];
+        it.ty = static_cast<int>(ny);
+        const long long room = (kTileSmemBytes - 16) / (ny * it.esIn);  // x extent that fits the staging buffer
+        it.tx = static_cast<int>(std::min<long long>(g.shape[px], std::max<long long>(16, room / 16 * 16)));
+        if (it.tx == g.shape[px] && it.py == g.rank - 2 && g.rank >= 3 && g.stride[g.rank - 3] == g.shape[px] * ny) {
+            it.tz = static_cast<int>(std::max<long long>(1, std::min<long long>(g.shape[g.rank - 3], room / g.shape[px])));
+            it.tilesZ = (g.shape[g.rank - 3] + it.tz - 1) / it.tz;
+        }
+    }
     it.tilesX = (g.shape[px] + it.tx - 1) / it.tx;
     it.tilesY = it.py >= 0 ? (g.shape[it.py] + it.ty - 1) / it.ty : 1;
     long long outer = 1;
     for (int k = 0; k < g.rank - 1; ++k)
-        if (k != it.py) outer *= g.shape[k];
+        if (k != it.py) outer *= (it.tz > 1 && k == g.rank - 3) ? it.tilesZ : g.shape[k];
     it.tiles = it.tilesX * it.tilesY * outer;
     if (it.tiles <= 0 || it.tiles > 0x7FFFFFFFLL) return false;
     *out = it;
@@ -287,6 +453,7 @@ bool makeTileItem(const GenParams& p, TileItem* out) {
 void launchTile(Context* ctx, const TileItem& it) {
     if (ctx->batching) {
         ctx->tileBatch.push_back(it);
+        ctx->queuedBytes += it.g.outElems * it.esIn;
         return;
     }
     const int grid = static_cast<int>(std::min<long long>(it.tiles, ctx->smCount * 64LL));

@@ -404,3 +404,46 @@ def test_fused_quantiser_ties_and_extremes(gpu, oracle, npdt, dt, scheme, rowlen
         ag, ao = chain(gpu, swz, pack), chain(oracle, swz, pack)
         assert_same(ag.fold(), ao.fold())
         assert np.array_equal(ag.sideScales, ao.sideScales) and np.array_equal(ag.sideZeroPoints, ao.sideZeroPoints)
+
+
+# ------------------------------------------------------------------ byte-moving views (tile kernel bodies)
+# Reorders and copies that change no value take vectorised bodies in the tile kernel: block transposes
+# with 3x3 kernels (register byte permutes), other kernel sizes and element widths (32-bit pieces),
+# unaligned extents (scalar pieces), with and without the swizzle rotation and a leading SubView that
+# breaks the 16-byte alignment of the source.
+@pytest.mark.parametrize("shape", [(64, 64, 3, 3), (40, 512, 3, 3), (7, 48, 3, 3), (16, 20, 3, 3), (8, 32, 7, 7),
+                                   (12, 6, 5, 5), (5, 3, 2, 2), (300, 16, 1, 1), (3, 1000, 1, 1)])
+@pytest.mark.parametrize("dt,npdt", [(A.SI8, np.int8), (A.F16, np.float16), (A.F32, np.float32), (A.F64, np.float64)])
+@pytest.mark.parametrize("swizzle", [False, True])
+def test_reorder_moves_bytes(gpu, oracle, shape, dt, npdt, swizzle):
+    rng = np.random.default_rng(11)
+    w = rng.integers(-100, 100, shape).astype(npdt)
+
+    def build(backend):
+        a = ContentAttr.get(w, NDType(shape, dt), backend=backend).reorder(DimsOrder.OYXI)
+        return a.swizzleConstant(5, 3) if swizzle else a
+
+    cg, co = both(build, gpu, oracle)
+    assert_same(cg, co)
+    if not swizzle:
+        want = np.ascontiguousarray(w.transpose(0, 2, 3, 1)).view(np.uint8).ravel()
+        assert np.array_equal(cg.copyTo().ravel()[:want.size], want)
+
+
+@pytest.mark.parametrize("off", [1, 3, 16])
+@pytest.mark.parametrize("chan", [64, 20])
+@pytest.mark.parametrize("inner", [False, True])
+def test_reorder_after_subview(gpu, oracle, off, chan, inner):
+    rng = np.random.default_rng(12)
+    shape = (40 + off, chan + (off if inner else 0), 3, 3)
+    w = rng.integers(-100, 100, shape).astype(np.int8)
+    lo = (off, off if inner else 0, 0, 0)
+
+    def build(backend):
+        a = ContentAttr.get(w, NDType(shape, A.SI8), backend=backend).subview(lo, (40, chan, 3, 3))
+        return a.reorder(DimsOrder.OYXI)
+
+    cg, co = both(build, gpu, oracle)
+    assert_same(cg, co)
+    want = np.ascontiguousarray(w[lo[0]:, lo[1]:].transpose(0, 2, 3, 1)).view(np.uint8).ravel()
+    assert np.array_equal(cg.copyTo().ravel(), want)
