@@ -3,7 +3,15 @@
 #include "../../include/b200const.h"
 #include "plan.h"
 
+#include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <cstdio>
+#include <condition_variable>
 #include <cstdlib>
+#include <exception>
+#include <functional>
+#include <thread>
 #include <cstring>
 #include <memory>
 #include <string>
@@ -133,7 +141,7 @@ void* Arena::alloc(size_t bytes, size_t align) {
             return b.ptr + at;
         }
     }
-    const size_t minBlock = 64ull << 20;
+    const size_t minBlock = _minBlock;
     const size_t size = std::max(minBlock, (bytes + align + 4095) / 4096 * 4096);
     Block nb;
     nb.ptr = static_cast<char*>(devMalloc(_ctx, size));
@@ -207,6 +215,95 @@ static std::vector<Transformation> chainFromC(const b200c_xform* chain, int n) {
 }
 
 // After an asynchronous failure the arena and the error word must be left clean for the next call.
+// ---------------------------------------------------------------------------- planning threads
+// The reference folds constants in a parallel loop (export.cpp:465); here the host part of a fold --
+// type inference, view composition, launch parameters -- is what runs in parallel, while every
+// launch still goes to the context's one stream.
+class PlanPool {
+public:
+    explicit PlanPool(int n) {
+        for (int i = 0; i < n; ++i) _threads.emplace_back([this, i] { loop(i); });
+    }
+    ~PlanPool() {
+        {
+            std::lock_guard<std::mutex> lk(_m);
+            _stop = true;
+            ++_gen;
+        }
+        _cv.notify_all();
+        for (auto& t : _threads) t.join();
+    }
+    int size() const {
+        return static_cast<int>(_threads.size());
+    }
+    // runs fn(worker index) once on every thread and waits for all of them
+    void run(const std::function<void(int)>& fn) {
+        std::unique_lock<std::mutex> lk(_m);
+        _job = &fn;
+        _pending = size();
+        ++_gen;
+        _cv.notify_all();
+        _done.wait(lk, [&] { return _pending == 0; });
+        _job = nullptr;
+    }
+
+private:
+    void loop(int id) {
+        unsigned long long seen = 0;
+        for (;;) {
+            std::unique_lock<std::mutex> lk(_m);
+            _cv.wait(lk, [&] { return _gen != seen; });
+            seen = _gen;
+            if (_stop) return;
+            const std::function<void(int)>* fn = _job;
+            lk.unlock();
+            (*fn)(id);
+            lk.lock();
+            if (--_pending == 0) _done.notify_one();
+        }
+    }
+    std::vector<std::thread> _threads;
+    std::mutex _m;
+    std::condition_variable _cv, _done;
+    const std::function<void(int)>* _job = nullptr;
+    unsigned long long _gen = 0;
+    int _pending = 0;
+    bool _stop = false;
+};
+
+static int planThreads() {
+    if (const char* e = std::getenv("B200C_PLAN_THREADS")) return std::max(0, std::min(64, std::atoi(e)));
+    const unsigned hw = std::thread::hardware_concurrency();
+    return static_cast<int>(std::max(1u, std::min(8u, hw / 2)));
+}
+
+static void ensurePool(Context* ctx) {
+    if (ctx->pool || B2_EMU(ctx)) return;
+    const int n = planThreads();
+    if (n < 2) return;
+    for (int i = 0; i < n; ++i) {
+        Context* w = new Context();
+        w->device = ctx->device;
+        w->errWord = ctx->errWord;
+        w->errHost = ctx->errHost;
+        w->smCount = ctx->smCount;
+        w->l2Bytes = ctx->l2Bytes;
+        w->arena.setMinBlock(4ull << 20);
+        ctx->workers.push_back(w);
+    }
+    ctx->pool = new PlanPool(n);
+}
+
+static void destroyPool(Context* ctx) {
+    delete ctx->pool;
+    ctx->pool = nullptr;
+    for (Context* w : ctx->workers) {
+        w->arena.releaseAll();
+        delete w;
+    }
+    ctx->workers.clear();
+}
+
 struct CallScope {
     Context* ctx;
     std::unique_lock<std::mutex> lock;
@@ -284,6 +381,7 @@ void b200c_destroy(b200c_ctx* h) {
         if (ctx->errWord) cudaFree(ctx->errWord);
         if (ctx->errHost) cudaFreeHost(ctx->errHost);
     }
+    destroyPool(ctx);
     ctx->arena.releaseAll();  // frees the blocks while the device is still current
     if (!B2_EMU(ctx) && ctx->ownStream) cudaStreamDestroy(ctx->ownStream);
     delete ctx;
@@ -398,55 +496,137 @@ int b200c_fold_batch(b200c_ctx* h, b200c_fold_item* items, int count, int data_o
         struct BatchGuard {
             Context* c;
             ~BatchGuard() {
-                c->batching = false;
-                c->rqBatch.clear();
-                c->tileBatch.clear();
-                c->mapBatch.clear();
-                c->sparseBatch.clear();
-                c->queuedBytes = 0;
+                for (Context* q : c->workers) clear(q);
+                clear(c);
+            }
+            static void clear(Context* q) {
+                q->batching = false;
+                q->rqBatch.clear();
+                q->tileBatch.clear();
+                q->mapBatch.clear();
+                q->sparseBatch.clear();
+                q->queuedBytes = 0;
             }
         } guard{ctx};
-        // Queued launches go out in growing slices (32 MB of input, then twice as much each time), so
-        // the device starts early and works while the host plans the remaining items.
-        long long flushAt = 32LL << 20;
-        ctx->queuedBytes = 0;
         ctx->batching = out_on_device != 0 && !B2_EMU(ctx);
-        std::vector<std::pair<void*, void*>> hostOuts;  // (user pointer, device staging) when out is on the host
-        std::vector<std::pair<int, const long long*>> deferred;  // items whose size is read back at the end
-        for (int i = 0; i < count; ++i) {
+        ctx->queuedBytes = 0;
+        typedef std::vector<std::pair<int, const long long*>> Deferred;  // items whose size is read back at the end
+        Deferred deferred;
+
+        // one item: plan it, launch or queue its kernels on `c`, note a size that is still on the device
+        auto foldItem = [&](Context* c, int i, Deferred& later) {
             b200c_fold_item& it = items[i];
             if (!it.out && it.out_cap > 0) throw BadArg("null output pointer");
             const auto xs = chainFromC(it.chain, it.n);
-            auto plan = makePlanner(ctx, it.base, it.data, it.nbytes, it.is_splat, data_on_device);
+            auto plan = makePlanner(c, it.base, it.data, it.nbytes, it.is_splat, data_on_device);
             plan->setSideOnDevice(out_on_device != 0);
             void* devOut = it.out;
-            if (!out_on_device) devOut = ctx->arena.alloc(it.out_cap ? it.out_cap : 1);
+            if (!out_on_device) devOut = c->arena.alloc(it.out_cap ? it.out_cap : 1);
             it.out_bytes = plan->run(xs, devOut, it.out_cap);
-            if (!out_on_device) copyD2H(ctx, it.out, devOut, it.out_bytes);
+            if (!out_on_device) copyD2H(c, it.out, devOut, it.out_bytes);
             for (const auto& so : plan->sideOutputs()) {
                 if (out_on_device) {
-                    copyD2D(ctx, so.user, so.dev, so.bytes);
+                    copyD2D(c, so.user, so.dev, so.bytes);
                 } else {
-                    copyD2H(ctx, so.user, so.dev, so.bytes);
+                    copyD2H(c, so.user, so.dev, so.bytes);
                 }
             }
-            if (plan->deferredBytes()) deferred.push_back({i, plan->deferredBytes()});
-            if (ctx->queuedBytes >= flushAt) {
-                flushRowQuantBatch(ctx);
-                flushTileBatch(ctx);
-                flushSparsityBatch(ctx);
-                ctx->queuedBytes = 0;
-                flushAt = std::min(flushAt * 2, 4LL << 30);
+            if (plan->deferredBytes()) later.push_back({i, plan->deferredBytes()});
+        };
+        auto flushAll = [&] {
+            flushRowQuantBatch(ctx);
+            flushTileBatch(ctx);
+            flushSparsityBatch(ctx);
+            ctx->queuedBytes = 0;
+        };
+
+        // Items are taken in waves of growing input size (32 MB, then twice as much each time): the
+        // queued launches of a wave go out when it has been planned, so the device starts early and
+        // works while the host plans the rest.  A wave with enough items is planned by the pool.
+        const bool parallelOk = ctx->batching && data_on_device;
+        if (parallelOk) ensurePool(ctx);
+        long long waveBytes = 32LL << 20;
+        int first = 0;
+        // B200C_TRACE=1: host time of planning, flushing and the final wait, on stderr
+        static const bool trace = std::getenv("B200C_TRACE") != nullptr;
+        double tPlan = 0, tFlush = 0, tSync = 0;
+        int waves = 0, parallelWaves = 0;
+        auto now = [] { return std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now().time_since_epoch()).count(); };
+        while (first < count) {
+            const double t0 = now();
+            ++waves;
+            int last = first;
+            long long bytes = 0;
+            while (last < count && (last == first || bytes < waveBytes)) bytes += static_cast<long long>(items[last++].nbytes);
+            const int n = last - first;
+            if (parallelOk && ctx->pool && n >= 4 * ctx->pool->size()) {
+                ++parallelWaves;
+                const int nw = ctx->pool->size();
+                std::atomic<int> next(first);
+                std::vector<std::exception_ptr> failure(nw);
+                std::vector<int> failedAt(nw, count);
+                std::vector<Deferred> later(nw);
+                for (Context* w : ctx->workers) {
+                    w->stream = ctx->stream;
+                    w->batching = true;
+                    w->launches = 0;
+                    if (first == 0) w->arena.reset();
+                }
+                ctx->pool->run([&](int id) {
+                    Context* w = ctx->workers[id];
+                    if (cudaSetDevice(w->device) != cudaSuccess) {
+                        failure[id] = std::make_exception_ptr(CudaFail("cudaSetDevice failed on a planning thread"));
+                        failedAt[id] = first;
+                        return;
+                    }
+                    for (;;) {
+                        const int i = next.fetch_add(1);
+                        if (i >= last) break;
+                        try {
+                            foldItem(w, i, later[id]);
+                        } catch (...) {
+                            failure[id] = std::current_exception();
+                            failedAt[id] = i;
+                            break;
+                        }
+                    }
+                });
+                int bad = -1;
+                for (int k = 0; k < nw; ++k)
+                    if (failure[k] && (bad < 0 || failedAt[k] < failedAt[bad])) bad = k;
+                if (bad >= 0) std::rethrow_exception(failure[bad]);  // the error of the earliest failing item
+                for (int k = 0; k < nw; ++k) {
+                    Context* w = ctx->workers[k];
+                    ctx->rqBatch.insert(ctx->rqBatch.end(), w->rqBatch.begin(), w->rqBatch.end());
+                    ctx->tileBatch.insert(ctx->tileBatch.end(), w->tileBatch.begin(), w->tileBatch.end());
+                    ctx->mapBatch.insert(ctx->mapBatch.end(), w->mapBatch.begin(), w->mapBatch.end());
+                    ctx->sparseBatch.insert(ctx->sparseBatch.end(), w->sparseBatch.begin(), w->sparseBatch.end());
+                    w->rqBatch.clear();
+                    w->tileBatch.clear();
+                    w->mapBatch.clear();
+                    w->sparseBatch.clear();
+                    ctx->launches += w->launches;
+                    w->launches = 0;
+                    deferred.insert(deferred.end(), later[k].begin(), later[k].end());
+                }
+            } else {
+                for (int i = first; i < last; ++i) foldItem(ctx, i, deferred);
             }
+            const double t1 = now();
+            flushAll();
+            tPlan += t1 - t0;
+            tFlush += now() - t1;
+            waveBytes = std::min(waveBytes * 2, 4LL << 30);
+            first = last;
         }
-        flushRowQuantBatch(ctx);
-        flushTileBatch(ctx);
-        flushSparsityBatch(ctx);
+        const double tEnd = now();
         const bool async = out_on_device && (flags & B200C_FOLD_ASYNC) && deferred.empty();
         if (!async) {
             // results whose size only the data decides: one read-back for all of them
             std::vector<long long> sizes(deferred.size(), 0);
-            for (size_t k = 0; k < deferred.size(); ++k) copyD2H(ctx, &sizes[k], deferred[k].second, sizeof(long long));
+            std::vector<const long long*> words;
+            for (const auto& d : deferred) words.push_back(d.second);
+            gatherDeviceWords(ctx, words, sizes.data());
             syncStream(ctx);
             checkDeviceError(ctx);
             for (size_t k = 0; k < deferred.size(); ++k) {
@@ -454,6 +634,11 @@ int b200c_fold_batch(b200c_ctx* h, b200c_fold_item* items, int count, int data_o
                 if (static_cast<size_t>(sizes[k]) > it.out_cap) throw Capacity("output buffer too small");
                 it.out_bytes = static_cast<size_t>(sizes[k]);
             }
+        }
+        tSync = now() - tEnd;
+        if (trace) {
+            std::fprintf(stderr, "[b200c] fold_batch: %d items, %d waves (%d parallel), plan %.0f us, flush %.0f us, wait %.0f us\n", count,
+                         waves, parallelWaves, tPlan, tFlush, tSync);
         }
     });
 }

@@ -404,9 +404,16 @@ void Planner::apply(const Transformation& x) {
         std::memset(&fb, 0, sizeof(fb));
         fb.tag = tag;
         fb.pos = static_cast<int>(v.ops.size());
+        bool widens = false;
+        for (int k = 0; k < v.rank; ++k) widens = widens || shape[k] != inShape[k];
         if (outType.q.kind == B200C_Q_PER_AXIS) {
             if (outType.rank() != 4) refThrow("Unsupported shape size %d", outType.rank());
             if (outType.q.axis != 0) refThrow("Only per-channel quantization is supported");
+        }
+        if (outType.q.kind == B200C_Q_PER_AXIS && (!widens || outType.q.zpsAllEqual())) {
+            // nothing to fill, or one value for every channel: no table
+            fb.bits = outType.q.n ? castIntToTag(outType.q.zps[0], tag) : 0;
+        } else if (outType.q.kind == B200C_Q_PER_AXIS) {
             const size_t es = tagBytes(tag);
             std::vector<char> table(outType.q.n * es);
             for (size_t i = 0; i < outType.q.n; ++i) {
@@ -435,8 +442,6 @@ void Planner::apply(const Transformation& x) {
             if (op.dim >= 0) op.off -= before[op.dim];
         for (auto& b : v.boxes)
             if (b.table) b.tableOff -= before[b.tableDim];
-        bool widens = false;
-        for (int k = 0; k < v.rank; ++k) widens = widens || shape[k] != inShape[k];
         if (widens) v.boxes.push_back(fb);  // a zero-width pad fills nothing
         _s.type = outType;
         _s.splat = false;

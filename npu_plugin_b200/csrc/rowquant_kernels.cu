@@ -396,16 +396,8 @@ __global__ void __launch_bounds__(256) rowQuantRegBatchKernel(const RowQuantPara
                                                               const long long* __restrict__ groupStart, int nitems) {
     __shared__ float redMx[8], redMn[8], redAm[8], redOdd[8];
     __shared__ RowQuantParams p;
-    int lo = 0, hi = nitems - 1;
     const long long b = blockIdx.x;
-    while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (groupStart[mid] <= b) {
-            lo = mid;
-        } else {
-            hi = mid - 1;
-        }
-    }
+    const int lo = findBatchItem(groupStart, nitems, b);
     // stage the tensor's parameters in shared memory (one copy per CTA)
     {
         const int words = sizeof(RowQuantParams) / 4;
@@ -441,7 +433,7 @@ __device__ __forceinline__ void rowQuantSmemBody(const RowQuantParams& p, long l
             uint4* sm4 = reinterpret_cast<uint4*>(rowSm);
             for (int v = t; v < nvec; v += TPR) {
                 const uint4 xv = __ldg(src4 + v);
-                sm4[v] = xv;
+                sm4[v + ((v * PER) >> p.padLog2)] = xv;  // padLog2 is 31 when the row is not padded
                 const T* e = reinterpret_cast<const T*>(&xv);
 #pragma unroll
                 for (int i = 0; i < PER; ++i) accum(s, elemToFloat<T>(e[i]));
@@ -480,11 +472,17 @@ __device__ __forceinline__ void rowQuantSmemBody(const RowQuantParams& p, long l
 #pragma unroll
                     for (int v = 0; v < static_cast<int>(16 * sizeof(T) / 16); ++v) e4[v] = sm4[v];
                 } else if (twoLevel) {
+                    // the staged row carries 16 bytes of padding per 2^padLog2 elements, chosen so that
+                    // the lanes of a warp (16 * st1 elements apart) fall into different banks
+                    constexpr int PADSH = sizeof(T) == 4 ? 2 : 3;
                     const int j = u * 16;
                     const int outer = j / inner, in0 = j - outer * inner;
-                    const T* base = rowSm + outer * st0 + in0 * st1;
+                    const int s0 = outer * st0 + in0 * st1;
 #pragma unroll
-                    for (int k = 0; k < 16; ++k) e[k] = base[k * st1];
+                    for (int k = 0; k < 16; ++k) {
+                        const int si = s0 + k * st1;
+                        e[k] = rowSm[si + ((si >> p.padLog2) << PADSH)];
+                    }
                 } else {
 #pragma unroll
                     for (int k = 0; k < 16; ++k) e[k] = rowSm[rowMap(p, u * 16 + k)];
@@ -529,16 +527,8 @@ __global__ void __launch_bounds__(256) rowQuantSmemBatchKernel(const RowQuantPar
     extern __shared__ __align__(16) unsigned char smemRaw[];
     __shared__ float redMx[8], redMn[8], redAm[8], redOdd[8];
     __shared__ RowQuantParams p;
-    int lo = 0, hi = nitems - 1;
     const long long b = blockIdx.x;
-    while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (groupStart[mid] <= b) {
-            lo = mid;
-        } else {
-            hi = mid - 1;
-        }
-    }
+    const int lo = findBatchItem(groupStart, nitems, b);
     {
         const int words = sizeof(RowQuantParams) / 4;
         const unsigned int* srcw = reinterpret_cast<const unsigned int*>(items + lo);
@@ -711,6 +701,14 @@ void launchRowQuantFused(Context* ctx, RowQuantParams p) {
     p.vecOut = ((reinterpret_cast<uintptr_t>(p.dst) & 15) == 0 && p.rowElems % 16 == 0) ? 1 : 0;
     // rows padded to 16 bytes in shared memory so every row slot stays 128-bit aligned
     p.smemRowElems = (p.rowElems * es + 15) / 16 * 16 / es;
+    p.padLog2 = 31;  // no padding
+    if (p.vecIn && p.vecOut && p.irank == 2 && p.ishape[1] % 16 == 0 && p.istride[1] > 1) {
+        // two-level permutation read back with a stride: pad the staged row (see rowQuantSmemBody)
+        int tz = 0;
+        while (((p.istride[1] >> tz) & 1) == 0) ++tz;
+        p.padLog2 = 6 + tz;
+        p.smemRowElems += ((p.rowElems >> p.padLog2) + 1) * (16 / es);
+    }
     if (ctx->batching) {
         ctx->rqBatch.push_back(p);  // launched by flushRowQuantBatch with its peers
         ctx->queuedBytes += p.rows * p.rowElems * es;
@@ -757,6 +755,7 @@ void flushRowQuantBatch(Context* ctx) {
         long long* startDev = nullptr;
         if (!one) {
             itemsDev = static_cast<RowQuantParams*>(ctx->arena.alloc(sizeof(RowQuantParams) * group.size()));
+            appendCoarseIndex(start, total);
             startDev = static_cast<long long*>(ctx->arena.alloc(sizeof(long long) * start.size()));
             copyH2D(ctx, itemsDev, group.data(), sizeof(RowQuantParams) * group.size());
             copyH2D(ctx, startDev, start.data(), sizeof(long long) * start.size());

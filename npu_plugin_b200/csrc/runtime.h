@@ -49,6 +49,7 @@ struct RowQuantParams {
     long long dataBytes, totalBytes;
     int vecIn, vecOut;  // filled by the launcher
     long long smemRowElems;
+    int padLog2;  // staged rows: 16 bytes of padding after every 2^padLog2 elements (31: none), filled by the launcher
 };
 
 
@@ -57,6 +58,9 @@ struct RowQuantParams {
 class Arena {
 public:
     explicit Arena(Context* ctx): _ctx(ctx) {
+    }
+    void setMinBlock(size_t bytes) {
+        _minBlock = bytes;
     }
     ~Arena();
     void* alloc(size_t bytes, size_t align = 256);
@@ -71,6 +75,7 @@ private:
     };
     Context* _ctx;
     std::vector<Block> _blocks;
+    size_t _minBlock = 64ull << 20;
 };
 
 // One tile-kernel work item (tile_kernels.cu): a view in canonical form plus its tiling.
@@ -113,6 +118,8 @@ struct SparseItem {
     int* err;
 };
 
+class PlanPool;
+
 struct Context {
     int device = 0;
     cudaStream_t ownStream = nullptr;
@@ -131,7 +138,42 @@ struct Context {
     std::vector<MapItem> mapBatch;
     std::vector<SparseItem> sparseBatch;
     long long queuedBytes = 0;             // input bytes of the queued launches (drives early flushes)
+    // planning threads of the batched entry point: each plans items into a context of its own
+    // (same stream and error word, own scratch arena and launch queues)
+    PlanPool* pool = nullptr;
+    std::vector<Context*> workers;
 };
+
+
+// ---- batched launches: which item does unit b belong to? ------------------------------------
+// `start` holds the exclusive prefix sums of the items' unit counts (nitems entries) followed by a
+// coarse index: entry g is the item that contains unit 64 * g, plus one closing entry.  A lookup
+// reads two neighbouring coarse entries and then searches only between them (usually nothing).
+inline void appendCoarseIndex(std::vector<long long>& start, long long total) {
+    const size_t n = start.size();
+    const long long groups = (total + 63) / 64;
+    size_t k = 0;
+    for (long long g = 0; g < groups; ++g) {
+        while (k + 1 < n && start[k + 1] <= g * 64) ++k;
+        start.push_back(static_cast<long long>(k));
+    }
+    start.push_back(static_cast<long long>(n ? n - 1 : 0));
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ int findBatchItem(const long long* __restrict__ start, int nitems, long long b) {
+    const long long* coarse = start + nitems;
+    int lo = static_cast<int>(coarse[b >> 6]), hi = static_cast<int>(coarse[(b >> 6) + 1]);
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (start[mid] <= b) {
+            lo = mid;
+        } else {
+            hi = mid - 1;
+        }
+    }
+    return lo;
+}
+#endif
 
 // device memory through the context (host malloc under emulation)
 void* devMalloc(Context* ctx, size_t bytes);
@@ -173,6 +215,8 @@ size_t rowQuantMaxRowBytes();
 void launchMapItem(Context* ctx, const MapItem& it);
 void launchSparseItem(Context* ctx, const SparseItem& it);
 void flushSparsityBatch(Context* ctx);
+// hostOut[i] = *ptrs[i] (device words), valid after the stream has been synchronised
+void gatherDeviceWords(Context* ctx, const std::vector<const long long*>& ptrs, long long* hostOut);
 // sparsity (GetSparsityMap / Sparsify) on a dense buffer of `tag` elements laid out [OC][work]
 void launchSparsityMap(Context* ctx, const void* src, int tag, long long oc, long long work, long long outBitsPerOC,
                        unsigned long long sparseBits, void* dstBits, int swizzleKey);

@@ -303,19 +303,6 @@ void launchSparsifyScatter(Context* ctx, const void* src, int tag, long long oc,
 // Many tensors per launch; a CTA (or warp) finds its item with a binary search over prefix sums.
 namespace {
 
-__device__ __forceinline__ int findItem(const long long* __restrict__ start, int nitems, long long b) {
-    int lo = 0, hi = nitems - 1;
-    while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (start[mid] <= b) {
-            lo = mid;
-        } else {
-            hi = mid - 1;
-        }
-    }
-    return lo;
-}
-
 // 0x80 in every byte of w that differs from the matching byte of sv4
 __device__ __forceinline__ unsigned int neBytes(unsigned int w, unsigned int sv4) {
     const unsigned int y = w ^ sv4;
@@ -338,7 +325,7 @@ constexpr int kMapUnitsPerCta = 1024;  // 16 input bytes -> 2 map bytes per unit
 
 __global__ void __launch_bounds__(256) sparsityMapBatchKernel(const MapItem* __restrict__ items,
                                                               const long long* __restrict__ ctaStart, int nitems) {
-    const int k = findItem(ctaStart, nitems, blockIdx.x);
+    const int k = findBatchItem(ctaStart, nitems, blockIdx.x);
     const MapItem it = items[k];
     const unsigned int sv4 = it.sparseByte * 0x01010101u;
     const long long unitsPerOC = it.outBytesPerOC / 2, dataUnitsPerOC = it.work / 16;
@@ -365,7 +352,7 @@ __global__ void __launch_bounds__(256) sparseCountBatchKernel(const SparseItem* 
     const long long ch = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
     if (ch >= nchan) return;
     const int lane = threadIdx.x & 31;
-    const int k = findItem(chanStart, nitems, ch);
+    const int k = findBatchItem(chanStart, nitems, ch);
     const SparseItem& it = items[k];
     const long long c = ch - chanStart[k];
     const unsigned int sv4 = it.sparseByte * 0x01010101u;
@@ -433,7 +420,7 @@ __global__ void __launch_bounds__(256) sparseScatterBatchKernel(const SparseItem
     if (ch >= nchan) return;
     const int lane = threadIdx.x & 31;
     unsigned char* st = stage[threadIdx.x >> 5];
-    const int k = findItem(chanStart, nitems, ch);
+    const int k = findBatchItem(chanStart, nitems, ch);
     const SparseItem& it = items[k];
     const long long c = ch - chanStart[k];
     const unsigned int sv4 = it.sparseByte * 0x01010101u;
@@ -504,6 +491,11 @@ __global__ void __launch_bounds__(256) sparseScatterBatchKernel(const SparseItem
     }
 }
 
+__global__ void gatherWordsKernel(const long long* const* __restrict__ ptrs, long long* __restrict__ out, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = *ptrs[i];
+}
+
 template <typename T>
 T* uploadItems(Context* ctx, const std::vector<T>& v) {
     T* d = static_cast<T*>(ctx->arena.alloc(sizeof(T) * v.size()));
@@ -520,6 +512,7 @@ void runMapItems(Context* ctx, const std::vector<MapItem>& items) {
         ctas += ((it.totalBytes + 1) / 2 + kMapUnitsPerCta - 1) / kMapUnitsPerCta;
     }
     if (ctas <= 0 || ctas > 0x7FFFFFFFLL) throw NotBuilt("sparsity map batch too large for one launch");
+    appendCoarseIndex(start, ctas);
     sparsityMapBatchKernel<<<static_cast<unsigned int>(ctas), 256, 0, ctx->stream>>>(uploadItems(ctx, items), uploadItems(ctx, start),
                                                                                       static_cast<int>(items.size()));
     B2_CUDA(cudaGetLastError());
@@ -536,6 +529,7 @@ void runSparseItems(Context* ctx, const std::vector<SparseItem>& items) {
     }
     const long long ctas = (nchan + 7) / 8;
     if (ctas <= 0 || ctas > 0x7FFFFFFFLL) throw NotBuilt("sparsify batch too large for one launch");
+    appendCoarseIndex(start, nchan);
     const SparseItem* d = uploadItems(ctx, items);
     const long long* ds = uploadItems(ctx, start);
     const int n = static_cast<int>(items.size());
@@ -567,6 +561,19 @@ void launchSparseItem(Context* ctx, const SparseItem& it) {
         return;
     }
     runSparseItems(ctx, std::vector<SparseItem>(1, it));
+}
+
+// out[i] = *ptrs[i] for n device words scattered over scratch memory: one launch and one copy
+// instead of n small copies
+void gatherDeviceWords(Context* ctx, const std::vector<const long long*>& ptrs, long long* hostOut) {
+    if (ptrs.empty()) return;
+    const int n = static_cast<int>(ptrs.size());
+    const long long* const* d = uploadItems(ctx, ptrs);
+    long long* out = static_cast<long long*>(ctx->arena.alloc(sizeof(long long) * ptrs.size()));
+    gatherWordsKernel<<<(n + 255) / 256, 256, 0, ctx->stream>>>(d, out, n);
+    B2_CUDA(cudaGetLastError());
+    ++ctx->launches;
+    copyD2H(ctx, hostOut, out, sizeof(long long) * ptrs.size());
 }
 
 void flushSparsityBatch(Context* ctx) {

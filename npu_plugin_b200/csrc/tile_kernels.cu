@@ -310,16 +310,8 @@ __global__ void __launch_bounds__(kTileThreads) foldTileBatchKernel(const TileIt
                                                                     const long long* __restrict__ tileStart, int nitems) {
     __shared__ __align__(16) unsigned char smem[kTileSmemBytes];
     __shared__ TileItem it;
-    int lo = 0, hi = nitems - 1;
     const long long b = blockIdx.x;
-    while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (tileStart[mid] <= b) {
-            lo = mid;
-        } else {
-            hi = mid - 1;
-        }
-    }
+    const int lo = findBatchItem(tileStart, nitems, b);
     {
         const int words = sizeof(TileItem) / 4;
         const unsigned int* s = reinterpret_cast<const unsigned int*>(items + lo);
@@ -483,9 +475,10 @@ void flushTileBatch(Context* ctx) {
             ctx->batching = was;
         } else {
             TileItem* itemsDev = static_cast<TileItem*>(ctx->arena.alloc(sizeof(TileItem) * n));
-            long long* startDev = static_cast<long long*>(ctx->arena.alloc(sizeof(long long) * n));
+            appendCoarseIndex(start, total);
+            long long* startDev = static_cast<long long*>(ctx->arena.alloc(sizeof(long long) * start.size()));
             copyH2D(ctx, itemsDev, pending.data() + first, sizeof(TileItem) * n);
-            copyH2D(ctx, startDev, start.data(), sizeof(long long) * n);
+            copyH2D(ctx, startDev, start.data(), sizeof(long long) * start.size());
             foldTileBatchKernel<<<static_cast<unsigned int>(total), kTileThreads, 0, ctx->stream>>>(itemsDev, startDev, n);
             B2_CUDA(cudaGetLastError());
             ++ctx->launches;

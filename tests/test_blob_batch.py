@@ -120,3 +120,64 @@ def test_partition_is_deterministic_and_balanced():
         assert owner == partition(decls, world)
         load = [sum(d.nbytes for d, o in zip(decls, owner) if o == r) for r in range(world)]
         assert max(load) - min(load) <= max(d.nbytes for d in decls)
+
+
+@gpu_only
+def test_many_small_constants_in_one_batch(gpu, oracle):
+    """Enough items for the planning threads, mixing every batched kernel family: fused quantiser
+    (register and staged), tile transposes, sparsity map and sparsify (size known only on the
+    device), dequantize rows.  Every output and every reported size must equal the oracle's."""
+    rng = np.random.default_rng(21)
+    decls, data = [], []
+    q8 = lambda o: UniformQuantizedPerAxisType(A.SI8, A.F16, [1.0] * o, [0] * o, 0, -127, 127)
+    for k in range(96):
+        kind = k % 6
+        if kind == 0:
+            o, i = int(rng.integers(4, 40)), int(rng.choice([64, 256, 1040, 4096]))
+            decls.append(linear_decl(f"lin{k}", o, i))
+            data.append(rng.normal(0, 0.02, o * i).astype(np.float16))
+        elif kind == 1:
+            o, i = int(rng.integers(2, 24)), int(rng.choice([16, 32, 64]))
+            x = rng.integers(-127, 128, (o, i, 3, 3)).astype(np.int8)
+            decls.append(ConstantDecl(f"conv{k}", NDType(x.shape, A.SI8),
+                                      [Transform(A.X_QUANT_CAST, elem=q8(o)), Transform(A.X_REORDER, a=DimsOrder.NHWC)], x.size))
+            data.append(x)
+        elif kind in (2, 3):
+            o, i = int(rng.integers(3, 50)), int(rng.choice([16, 128, 1024]))
+            x = rng.integers(-127, 128, (o, i, 1, 1)).astype(np.int8)
+            x[rng.random(x.shape) < 0.5] = 0
+            first = Transform(A.X_GET_SPARSITY_MAP) if kind == 2 else Transform(A.X_SPARSIFY, i0=0)
+            chain = [first] + ([Transform(A.X_SWIZZLE_CONSTANT, i0=5, i1=3)] if k % 4 < 2 else [])
+            decls.append(ConstantDecl(f"sp{k}", NDType(x.shape, A.SI8), chain, x.size, compress=False))
+            data.append(x)
+        elif kind == 4:
+            o, i = int(rng.integers(2, 30)), int(rng.choice([48, 4096]))
+            x = rng.integers(0, 256, (o, i)).astype(np.uint8)
+            qt = UniformQuantizedPerAxisType(A.UI8, A.F16, list(rng.uniform(0.001, 0.1, o)), list(map(int, rng.integers(0, 255, o))), 0, 0, 255)
+            decls.append(ConstantDecl(f"dq{k}", NDType(x.shape, A.UI8),
+                                      [Transform(A.X_QUANT_CAST, elem=qt), Transform(A.X_DEQUANTIZE)], x.size, compress=False))
+            data.append(x)
+        else:
+            x = rng.normal(0, 1, (int(rng.integers(1, 9)), 33)).astype(np.float16)
+            decls.append(ConstantDecl(f"gain{k}", NDType(x.shape, A.F16), [], x.nbytes, compress=False))
+            data.append(x)
+    folder = ShardFolder(gpu, decls)
+    ins = [DevBuf(gpu, d.nbytes) for d in decls]
+    for b, x in zip(ins, data):
+        b.upload(x)
+    has_q = [any(t.kind == A.X_QUANTIZE_SYNTH for t in d.transforms) for d in decls]
+    scales = [DevBuf(gpu, 4 * d.base_type.shape[0]) if q else None for d, q in zip(decls, has_q)]
+    zps = [DevBuf(gpu, 4 * d.base_type.shape[0]) if q else None for d, q in zip(decls, has_q)]
+    side = [(s.ptr, z.ptr) if s else None for s, z in zip(scales, zps)]
+    out = DevBuf(gpu, folder.folded_bytes)
+    for _ in range(2):  # the second pass reuses the marshalled items and the warmed-up pool
+        folder.fold([b.ptr for b in ins], out.ptr, True, side)
+        raise_for(gpu.lib.b200c_synchronize(gpu.ctx), gpu.lib.b200c_last_error())
+        a = out.download()
+        for i, d in enumerate(decls):
+            ref = oracle.fold(d.base_type, data[i], False, d.transforms).copyTo().view(np.uint8).ravel()
+            off = folder.folded_offsets[i]
+            assert folder._items[i].out_bytes == ref.size, (d.name, folder._items[i].out_bytes, ref.size)
+            assert np.array_equal(a[off:off + ref.size], ref), d.name
+    for b in ins + [out] + [s for s in scales + zps if s]:
+        b.free()
