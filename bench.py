@@ -27,7 +27,7 @@ sys.path.insert(0, ROOT)
 import numpy as np  # noqa: E402
 
 from npu_plugin_b200 import _cabi as A  # noqa: E402
-from npu_plugin_b200.blob import ConstantDecl, ShardFolder, gather_segments, partition  # noqa: E402
+from npu_plugin_b200.blob import ConstantDecl, ShardFolder, gather_aware_weights, partition  # noqa: E402
 from npu_plugin_b200.const import (DimsOrder, NDType, Transform, UniformQuantizedPerAxisType,  # noqa: E402
                                    UniformQuantizedType)
 
@@ -280,7 +280,7 @@ def run_cpu(decls, steps, warmup, budget_elems, threads=None):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of the 7B-shape workload (32 = the named config)")
@@ -300,7 +300,7 @@ def main():
         decls = llama7b_decls(layers=args.layers)
         workload = f"llama7b-shape fold: {len([d for d in decls if d.transforms])} linear f16 weights -> sym int8 per-channel " \
                    f"-> Reorder -> Swizzle(5) -> block codec; {len(decls)} constants, layers={args.layers}"
-        config = {"workload": workload, "sharding": "by tensor (LPT)", "l2": "per-step working set (>26 GB at N=1) exceeds L2",
+        config = {"workload": workload, "sharding": "by tensor (LPT; rank 0's share balances its compute against its ingress)", "l2": "per-step working set (>26 GB at N=1) exceeds L2",
                   "layers": args.layers}
         dtype_name = "f16->i8"
     else:
@@ -335,7 +335,15 @@ def main():
 
     torch.cuda.set_device(local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # the segment transfers run on NCCL's own high-priority stream, so their kernels get SMs while
+        # the fold kernels of the next chunk fill the machine
+        # point-to-point transfers get the full set of channels whatever the number of ranks
+        os.environ.setdefault("NCCL_MIN_P2P_NCHANNELS", "32")
+        os.environ.setdefault("NCCL_MAX_P2P_NCHANNELS", "32")
+        opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), pg_options=opts)
+    # the planning threads of all ranks share the host's cores
+    os.environ.setdefault("B200C_PLAN_THREADS", str(max(1, min(8, (os.cpu_count() or 8) // (2 * world)))))
     backend = CudaBackend(local_rank)
     lib, ctx = backend.lib, backend.ctx
     # a real (non-default) stream shared by torch and the library, so that torch's CUDA events are
@@ -346,7 +354,13 @@ def main():
     assert stream.cuda_stream != 0
     lib.b200c_set_stream(ctx, C.c_void_p(stream.cuda_stream))
 
-    owner = partition(decls, world)
+    # Every other rank's slots must enter rank 0 through its NVLink ingress, so rank 0 takes the larger
+    # share of the constants: its compute time for that share balances the ingress time of the rest
+    # (rates: 4 TB/s of algorithmic bytes for rank 0's kernels while it receives, 750 GB/s for the link; input bytes x 2 and
+    # x 0.5 approximate algorithmic and blob bytes of a constant before anything has run).
+    total_in = sum(d.nbytes for d in decls)
+    weights = gather_aware_weights(world, compute_seconds=2.0 * total_in / 4.0e12, transfer_seconds=0.5 * total_in / 0.75e12)
+    owner = partition(decls, world, weights)
     mine = [d for d, o in zip(decls, owner) if o == rank]
     folder = ShardFolder(backend, mine)  # whole-shard layout (sizes, bounds); also the N=1 path
 
@@ -386,15 +400,33 @@ def main():
         if f is not None:
             fo += f.folded_bytes
             bo += f.blob_bound
-    # every constant is folded straight into its slot of the blob; compression then works in place
-    folded = torch.empty(max(fo, 1), dtype=torch.uint8, device="cuda")
-    gathered, pg_sizes = None, None
+    # Every constant is folded straight into its slot of the blob; compression then works in place, so
+    # the slot layout is known before any data is seen.  With several ranks the blob on rank 0 holds,
+    # chunk after chunk, every rank's slots; rank 0 folds its own chunks directly into their final
+    # place and receives the others' next to them.
+    gathered, place = None, None
     if world > 1:
-        pg_sizes = dist.new_group(backend="gloo")  # chunk sizes travel on the host, off the NCCL stream
-        bounds = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
-        dist.all_gather(bounds, torch.tensor([fo], dtype=torch.int64), group=pg_sizes)
+        pg_sizes = dist.new_group(backend="gloo")  # set-up only: the chunk sizes of every rank
+        mine_sizes = torch.tensor([f.folded_bytes if f is not None else 0 for f in cf], dtype=torch.int64)
+        all_sizes = [torch.zeros(nchunks, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(all_sizes, mine_sizes, group=pg_sizes)
+        place, at = [[0] * world for _ in range(nchunks)], 0
+        for k in range(nchunks):
+            for r in range(world):
+                place[k][r] = at
+                at += int(all_sizes[r][k])
         if rank == 0:
-            gathered = torch.empty(int(sum(int(b.item()) for b in bounds)) + 1024, dtype=torch.uint8, device="cuda")
+            gathered = torch.empty(at + 1024, dtype=torch.uint8, device="cuda")
+            folded = gathered
+            fold_off = [place[k][0] for k in range(nchunks)]
+        # the segment table (constant, offset, size, compressed) of every rank follows its last chunk
+        counts = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(counts, torch.tensor([len(mine)], dtype=torch.int64), group=pg_sizes)
+        tables = [torch.zeros((int(c.item()), 4), dtype=torch.int64, device="cuda") for c in counts] if rank == 0 else None
+        my_table_host = torch.zeros((len(mine), 4), dtype=torch.int64, pin_memory=True)
+        my_table = torch.zeros((len(mine), 4), dtype=torch.int64, device="cuda")
+    if gathered is None:
+        folded = torch.empty(max(fo, 1), dtype=torch.uint8, device="cuda")
 
     seg_info = {}
 
@@ -403,6 +435,15 @@ def main():
         if timers:
             timers[0].record(stream)
         segs_all, used_total, pending, at = [], 0, [], 0
+        if world > 1 and rank == 0:
+            # every receive is posted before rank 0 starts its own work, chunk by chunk and peer by peer
+            # (the order in which the peers send)
+            for k in range(nchunks):
+                for r in range(1, world):
+                    n = int(all_sizes[r][k])
+                    if n:
+                        pending.append(dist.irecv(gathered[place[k][r]:place[k][r] + n], src=r))
+            at = place[nchunks - 1][world - 1] + int(all_sizes[world - 1][nchunks - 1])
         for k, f in enumerate(cf):
             used = 0
             if f is not None:
@@ -420,20 +461,15 @@ def main():
                 used = f.folded_bytes  # the chunk's slots, streams and untouched constants alike
                 segs_all += [(c[i], fold_off[k] + o, sz, comp) for i, o, sz, comp in segs]
             used_total += used
-            if world > 1:
-                sizes = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
-                dist.all_gather(sizes, torch.tensor([used], dtype=torch.int64), group=pg_sizes)
-                sizes = [int(x.item()) for x in sizes]
-                if rank == 0:
-                    if sizes[0]:
-                        gathered[at:at + sizes[0]].copy_(folded[fold_off[k]:fold_off[k] + sizes[0]], non_blocking=True)
-                    at += sizes[0]
-                    for r in range(1, world):
-                        if sizes[r]:
-                            pending.append(dist.irecv(gathered[at:at + sizes[r]], src=r))
-                        at += sizes[r]
-                elif used:
-                    pending.append(dist.isend(folded[fold_off[k]:fold_off[k] + used], dst=0))
+            if world > 1 and rank != 0 and used:
+                pending.append(dist.isend(folded[fold_off[k]:fold_off[k] + used], dst=0))
+        if world > 1 and len(mine):
+            if rank == 0:
+                pending += [dist.irecv(tables[r], src=r) for r in range(1, world) if tables[r].numel()]
+            else:
+                my_table_host.numpy()[:] = np.asarray(segs_all, dtype=np.int64).reshape(-1, 4)
+                my_table.copy_(my_table_host, non_blocking=True)
+                pending.append(dist.isend(my_table, dst=0))
         for q in pending:
             q.wait()
         seg_info["segs"], seg_info["used"], seg_info["gathered"] = segs_all, used_total, at
@@ -480,6 +516,12 @@ def main():
     codec_ms = float(np.mean([sum(e[2][k][1].elapsed_time(e[2][k][2]) for k in live) for e in ev]))
     step_ms_local = float(np.mean([e[0].elapsed_time(e[1]) for e in ev]))
     gather_ms = max(0.0, step_ms_local - fold_ms - codec_ms)  # exposed (not hidden) part of the exchange
+    per_rank = None
+    if world > 1:  # every rank's own view of the timed region: [ms per step, fold, codec] on its stream
+        mine_t = torch.tensor([t_begin.elapsed_time(t_end) / args.steps, fold_ms, codec_ms], dtype=torch.float64, device="cuda")
+        all_t = [torch.zeros_like(mine_t) for _ in range(world)]
+        dist.all_gather(all_t, mine_t)
+        per_rank = [[round(float(x), 3) for x in t.tolist()] for t in all_t]
 
     # algorithmic bytes of the whole job (all ranks)
     stream_sizes = {i: sz for i, _, sz, comp in seg_info["segs"] if comp}
@@ -509,7 +551,8 @@ def main():
                 "launches_per_step": n_fold_launch, "avg_launch_ms": fold_ms / max(1, n_fold_launch),
                 "tensors_per_step": len([d for d in mine if d.transforms]),
                 "algorithmic_bytes_per_launch": fold_local_b / max(1, n_fold_launch),
-                "phase_ms": {"fold": fold_ms, "codec": codec_ms, "gather": gather_ms, "fold_host_issue": fold_issue_ms}}
+                "phase_ms": {"fold": fold_ms, "codec": codec_ms, "gather": gather_ms, "fold_host_issue": fold_issue_ms},
+                "per_rank_ms": per_rank}
     try:
         with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
             roofline["traffic"] = json.load(f).get("fold_dram_bytes_per_launch")

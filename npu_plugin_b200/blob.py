@@ -27,16 +27,33 @@ class ConstantDecl:
         self.nbytes, self.compress, self.is_splat = int(nbytes), bool(compress), bool(is_splat)
 
 
-def partition(decls, world_size):
-    """Deterministic longest-processing-time assignment of constants to ranks by input bytes."""
+def partition(decls, world_size, weights=None):
+    """Deterministic longest-processing-time assignment of constants to ranks by input bytes.
+    `weights` (one positive number per rank, default all equal) are the shares of the work the ranks
+    should get: a rank with twice the weight ends up with about twice the bytes."""
+    w = [1.0] * world_size if weights is None else [float(x) for x in weights]
+    if len(w) != world_size or min(w) <= 0:
+        raise ValueError("weights: one positive number per rank")
     order = sorted(range(len(decls)), key=lambda i: (-decls[i].nbytes, i))
     load = [0] * world_size
     owner = [0] * len(decls)
     for i in order:
-        r = min(range(world_size), key=lambda k: (load[k], k))
+        r = min(range(world_size), key=lambda k: ((load[k] + decls[i].nbytes) / w[k], k))
         owner[i] = r
         load[r] += decls[i].nbytes
     return owner
+
+
+def gather_aware_weights(world_size, compute_seconds, transfer_seconds):
+    """Shares for partition() when every other rank's output must travel to rank 0: rank 0's share f
+    balances its own compute time f * compute against the ingress time (1 - f) * transfer of what the
+    others produce, and never drops below an equal split.  compute_seconds: one GPU doing the whole
+    job; transfer_seconds: the whole output crossing one link."""
+    if world_size == 1:
+        return [1.0]
+    f = max(1.0 / world_size, transfer_seconds / (compute_seconds + transfer_seconds))
+    f = min(f, 0.95)
+    return [f] + [(1.0 - f) / (world_size - 1)] * (world_size - 1)
 
 
 class ShardFolder:

@@ -178,7 +178,12 @@ __device__ __forceinline__ Stats rowReduce(Stats s, float* redMx, float* redMn, 
             redAm[warp] = s.amax;
             redOdd[warp] = s.odd;
         }
-        __syncthreads();
+        // only the TPR threads of a row wait for one another: rows of a CTA proceed independently
+        if (TPR == 256) {
+            __syncthreads();
+        } else {
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + static_cast<int>(threadIdx.x) / TPR), "n"(TPR) : "memory");
+        }
         constexpr int WPR = TPR / 32;
         const int first = (warp / WPR) * WPR;
 #pragma unroll

@@ -181,3 +181,19 @@ def test_many_small_constants_in_one_batch(gpu, oracle):
             assert np.array_equal(a[off:off + ref.size], ref), d.name
     for b in ins + [out] + [s for s in scales + zps if s]:
         b.free()
+
+
+def test_weighted_partition_follows_the_shares():
+    from npu_plugin_b200.blob import gather_aware_weights
+    decls = [ConstantDecl(f"c{k}", NDType((4,), A.F16), [], 1000 + 37 * (k % 11)) for k in range(400)]
+    total = sum(d.nbytes for d in decls)
+    for world in (2, 4, 8):
+        w = gather_aware_weights(world, compute_seconds=5.0, transfer_seconds=9.0)
+        assert abs(sum(w) - 1.0) < 1e-9 and abs(w[0] - 9.0 / 14.0) < 1e-9
+        owner = partition(decls, world, w)
+        for r in range(world):
+            share = sum(d.nbytes for d, o in zip(decls, owner) if o == r) / total
+            assert abs(share - w[r]) < 0.02, (world, r, share, w[r])
+    # cheap transfers: an equal split
+    assert gather_aware_weights(4, 5.0, 0.1) == [0.25] * 4
+    assert gather_aware_weights(1, 5.0, 9.0) == [1.0]
