@@ -227,7 +227,11 @@ B200C_API int b200c_fold(b200c_ctx* ctx, const b200c_type* base, const void* dat
  * kernels of the same kind are issued as one launch over all items, so small constants do not pay
  * one launch each.  data_on_device / out_on_device / flags apply to every item; out_bytes of each
  * item receives the bytes written.  Side outputs of QuantizeSynth are written in place when the
- * outputs are on the device.                                                                      */
+ * outputs are on the device.  Planning (type inference, view composition, launch parameters) of
+ * large batches runs on a small pool of host threads (B200C_PLAN_THREADS overrides their number,
+ * 0 or 1 = none), as the reference folds constants in a parallel loop; all launches still go to the
+ * context's one stream.  When an item's size depends on its data (Sparsify without
+ * numActualElements) the call waits for the device once, at its end, even with B200C_FOLD_ASYNC. */
 typedef struct b200c_fold_item {
     const b200c_type* base;
     const void* data;

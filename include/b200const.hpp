@@ -1,0 +1,466 @@
+/*
+ * b200const.hpp -- header-only C++17 host layer over the C ABI of b200const.h.
+ *
+ * It mirrors the part of the reference's C++ interface that constant folding goes through --
+ * vpux::Const::ContentAttr with its builder methods and fold(), and vpux::Const::Content with
+ * getType(), getValues<T>() and copyTo()
+ * (src/vpux_compiler/include/vpux/compiler/dialect/const/attributes/content.hpp,
+ *  src/vpux_compiler/include/vpux/compiler/dialect/const/utils/content.hpp) -- with the same method
+ * names, argument meaning and error behaviour (a failing call throws b200::Const::Error carrying the
+ * text the reference would have put into VPUX_THROW).  MLIR types are replaced by small value types
+ * (NDType, DimsOrder, QuantParams).  Everything here only marshals descriptors: all arithmetic runs
+ * in the library's CUDA kernels, and there is no CPU path.
+ */
+#ifndef B200CONST_HPP_
+#define B200CONST_HPP_
+
+#include "b200const.h"
+
+#include <algorithm>
+#include <cstdint>
+#include <cstring>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+namespace b200 {
+namespace Const {
+
+class Error : public std::runtime_error {
+public:
+    Error(int code, const std::string& what): std::runtime_error(what), _code(code) {
+    }
+    int code() const {  // one of B200C_ERR_*
+        return _code;
+    }
+
+private:
+    int _code;
+};
+
+inline void check(int rc) {
+    if (rc < 0) throw Error(rc, b200c_last_error());
+}
+
+// vpux::DimsOrder: perm[k] = logical dimension stored at memory position k (outermost first)
+struct DimsOrder {
+    std::vector<uint8_t> perm;
+    static DimsOrder identity(int rank) {
+        DimsOrder o;
+        for (int k = 0; k < rank; ++k) o.perm.push_back(static_cast<uint8_t>(k));
+        return o;
+    }
+    static DimsOrder fromPermutation(std::initializer_list<int> p) {
+        DimsOrder o;
+        for (int d : p) o.perm.push_back(static_cast<uint8_t>(d));
+        return o;
+    }
+    static DimsOrder NCHW() {
+        return identity(4);
+    }
+    static DimsOrder NHWC() {
+        return fromPermutation({0, 2, 3, 1});
+    }
+    static DimsOrder OIYX() {
+        return identity(4);
+    }
+    static DimsOrder OYXI() {
+        return fromPermutation({0, 2, 3, 1});
+    }
+    bool operator==(const DimsOrder& o) const {
+        return perm == o.perm;
+    }
+};
+
+// mlir::quant::UniformQuantizedType / UniformQuantizedPerAxisType
+struct QuantParams {
+    int kind = B200C_Q_NONE;
+    int axis = 0;
+    int expressed = B200C_F32;
+    int64_t qmin = 0, qmax = 0;
+    std::vector<double> scales;
+    std::vector<int64_t> zps;
+    static QuantParams perTensor(int expressed, double scale, int64_t zp, int64_t qmin, int64_t qmax) {
+        QuantParams q;
+        q.kind = B200C_Q_PER_TENSOR;
+        q.expressed = expressed;
+        q.scales = {scale};
+        q.zps = {zp};
+        q.qmin = qmin;
+        q.qmax = qmax;
+        return q;
+    }
+    static QuantParams perAxis(int expressed, std::vector<double> scales, std::vector<int64_t> zps, int axis, int64_t qmin,
+                               int64_t qmax) {
+        QuantParams q;
+        q.kind = B200C_Q_PER_AXIS;
+        q.expressed = expressed;
+        q.scales = std::move(scales);
+        q.zps = std::move(zps);
+        q.axis = axis;
+        q.qmin = qmin;
+        q.qmax = qmax;
+        return q;
+    }
+};
+
+// vpux::NDTypeInterface of a constant: shape, element type (storage integer for quantised types), order
+struct NDType {
+    int dtype = 0;
+    std::vector<int64_t> shape;
+    DimsOrder order;
+    QuantParams quant;
+
+    NDType() = default;
+    NDType(std::vector<int64_t> s, int dt): dtype(dt), shape(std::move(s)), order(DimsOrder::identity(static_cast<int>(shape.size()))) {
+    }
+    NDType(std::vector<int64_t> s, int dt, DimsOrder o): dtype(dt), shape(std::move(s)), order(std::move(o)) {
+    }
+    NDType(std::vector<int64_t> s, int storage, QuantParams q): dtype(storage), shape(std::move(s)),
+            order(DimsOrder::identity(static_cast<int>(shape.size()))), quant(std::move(q)) {
+    }
+    int getRank() const {
+        return static_cast<int>(shape.size());
+    }
+    int64_t getNumElements() const {
+        int64_t n = 1;
+        for (auto d : shape) n *= d;
+        return n;
+    }
+    // the POD form; borrows the scale / zero-point storage of *this
+    b200c_type toC() const {
+        if (shape.size() > B200C_MAX_RANK) throw Error(B200C_ERR_INVALID, "rank above B200C_MAX_RANK");
+        b200c_type t;
+        std::memset(&t, 0, sizeof(t));
+        t.dtype = dtype;
+        t.rank = getRank();
+        for (int k = 0; k < t.rank; ++k) {
+            t.shape[k] = shape[k];
+            t.order[k] = order.perm[k];
+        }
+        t.qkind = quant.kind;
+        t.qaxis = quant.axis;
+        t.qexpressed = quant.expressed;
+        t.qmin = quant.qmin;
+        t.qmax = quant.qmax;
+        t.nq = static_cast<int64_t>(quant.scales.size());
+        t.scales = quant.scales.data();
+        t.zps = quant.zps.data();
+        return t;
+    }
+    static NDType fromC(const b200c_type& t) {
+        NDType r;
+        r.dtype = t.dtype;
+        r.shape.assign(t.shape, t.shape + t.rank);
+        r.order.perm.assign(t.order, t.order + t.rank);
+        r.quant.kind = t.qkind;
+        r.quant.axis = t.qaxis;
+        r.quant.expressed = t.qexpressed;
+        r.quant.qmin = t.qmin;
+        r.quant.qmax = t.qmax;
+        if (t.qkind != B200C_Q_NONE) {
+            r.quant.scales.assign(t.scales, t.scales + t.nq);
+            r.quant.zps.assign(t.zps, t.zps + t.nq);
+        }
+        return r;
+    }
+    int64_t getTotalAllocSize() const {  // NDTypeInterface::getTotalAllocSize
+        const b200c_type t = toC();
+        return b200c_total_alloc_size(&t);
+    }
+};
+
+// One device context (stream + scratch memory); calls on one context are serialised.
+class Backend {
+public:
+    explicit Backend(int device = 0) {
+        check(b200c_create(device, &_ctx));
+    }
+    ~Backend() {
+        b200c_destroy(_ctx);
+    }
+    Backend(const Backend&) = delete;
+    Backend& operator=(const Backend&) = delete;
+    b200c_ctx* ctx() const {
+        return _ctx;
+    }
+
+private:
+    b200c_ctx* _ctx = nullptr;
+};
+
+// vpux::Const::Content after fold(): the folded bytes in the layout copyTo() produces, on the host
+class Content {
+public:
+    Content(NDType type, std::vector<uint8_t> bytes): _type(std::move(type)), _bytes(std::move(bytes)) {
+    }
+    const NDType& getType() const {
+        return _type;
+    }
+    // Const::Content::copyTo(MutableArrayRef<char>)
+    void copyTo(void* dst, size_t cap) const {
+        if (cap < _bytes.size()) throw Error(B200C_ERR_CAPACITY, "Const::Content::copyTo: buffer too small");
+        std::memcpy(dst, _bytes.data(), _bytes.size());
+    }
+    const std::vector<uint8_t>& getRawBytes() const {
+        return _bytes;
+    }
+    // values of byte-sized, non-quantised element types
+    template <typename T>
+    std::vector<T> getValues() const {
+        if (_bytes.size() % sizeof(T) != 0) throw Error(B200C_ERR_INVALID, "getValues: element size does not divide the buffer");
+        std::vector<T> v(_bytes.size() / sizeof(T));
+        std::memcpy(v.data(), _bytes.data(), _bytes.size());
+        return v;
+    }
+
+private:
+    NDType _type;
+    std::vector<uint8_t> _bytes;
+};
+
+// vpux::Const::ContentAttr: a base content plus an ordered transformation list.  The builder methods
+// return a new attribute, as the reference's do; a transformation is inserted at the position
+// getInsertionPosition gives it (content.cpp:268-299).
+class ContentAttr {
+public:
+    // ContentAttr::get(baseContent): `data` is copied
+    static ContentAttr get(const void* data, size_t nbytes, NDType baseType, bool isSplat = false) {
+        ContentAttr a;
+        a._base = std::move(baseType);
+        a._data = std::make_shared<std::vector<uint8_t>>(static_cast<const uint8_t*>(data),
+                                                         static_cast<const uint8_t*>(data) + nbytes);
+        a._splat = isSplat;
+        return a;
+    }
+    template <typename T>
+    static ContentAttr get(const std::vector<T>& values, NDType baseType, bool isSplat = false) {
+        return get(values.data(), values.size() * sizeof(T), std::move(baseType), isSplat);
+    }
+
+    ContentAttr convertElemType(int dtype) const {
+        Step s(B200C_X_CONVERT_ELEM_TYPE);
+        s.type.dtype = dtype;
+        return add(std::move(s));
+    }
+    ContentAttr quantCast(const QuantParams& q, int storage) const {  // quantCast(nullptr) = quantCast()
+        Step s(B200C_X_QUANT_CAST);
+        s.type.dtype = storage;
+        s.type.quant = q;
+        return add(std::move(s));
+    }
+    ContentAttr quantCast() const {
+        return add(Step(B200C_X_QUANT_CAST));
+    }
+    ContentAttr dequantize() const {
+        return add(Step(B200C_X_DEQUANTIZE));
+    }
+    ContentAttr rescale(double scale) const {
+        Step s(B200C_X_RESCALE);
+        s.x.f = scale;
+        return add(std::move(s));
+    }
+    ContentAttr add(double bias) const {
+        Step s(B200C_X_ADD);
+        s.x.f = bias;
+        return add(std::move(s));
+    }
+    ContentAttr reorder(const DimsOrder& order) const {
+        Step s(B200C_X_REORDER);
+        s.x.n = static_cast<int32_t>(order.perm.size());
+        for (size_t k = 0; k < order.perm.size(); ++k) s.x.a[k] = order.perm[k];
+        return add(std::move(s));
+    }
+    ContentAttr transpose(const DimsOrder& order) const {
+        Step s(B200C_X_TRANSPOSE);
+        s.x.n = static_cast<int32_t>(order.perm.size());
+        for (size_t k = 0; k < order.perm.size(); ++k) s.x.a[k] = order.perm[k];
+        return add(std::move(s));
+    }
+    ContentAttr reshape(const std::vector<int64_t>& shape) const {
+        Step s(B200C_X_RESHAPE);
+        fill(s.x.b, shape, &s.x.n);
+        return add(std::move(s));
+    }
+    ContentAttr subview(const std::vector<int64_t>& offset, const std::vector<int64_t>& shape) const {
+        Step s(B200C_X_SUBVIEW);
+        fill(s.x.a, offset, &s.x.n);
+        fill(s.x.b, shape, &s.x.n);
+        return add(std::move(s));
+    }
+    ContentAttr padWithZero(const std::vector<int64_t>& padBefore, const std::vector<int64_t>& padAfter) const {
+        Step s(B200C_X_PAD_WITH_ZERO);
+        fill(s.x.a, padBefore, &s.x.n);
+        fill(s.x.b, padAfter, &s.x.n);
+        return add(std::move(s));
+    }
+    ContentAttr broadcast(int64_t axis, int64_t value) const {
+        Step s(B200C_X_BROADCAST);
+        s.x.i0 = axis;
+        s.x.i1 = value;
+        return add(std::move(s));
+    }
+    ContentAttr bitPack(int64_t width) const {
+        Step s(B200C_X_BIT_PACK);
+        s.x.i0 = width;
+        return add(std::move(s));
+    }
+    ContentAttr getSparsityMap() const {
+        return add(Step(B200C_X_GET_SPARSITY_MAP));
+    }
+    // sparsify(compressOutputType, numActualElements): numActualElements may be empty
+    ContentAttr sparsify(bool compressOutputType, const std::vector<int64_t>& numActualElements = {}) const {
+        Step s(B200C_X_SPARSIFY);
+        s.x.i0 = compressOutputType ? 1 : 0;
+        s.aux = numActualElements;
+        return add(std::move(s));
+    }
+    ContentAttr swizzleConstant(uint64_t swizzleKey, uint64_t arch) const {
+        Step s(B200C_X_SWIZZLE_CONSTANT);
+        s.x.i0 = static_cast<int64_t>(swizzleKey);
+        s.x.i1 = static_cast<int64_t>(arch);
+        return add(std::move(s));
+    }
+
+    const NDType& getBaseType() const {
+        return _base;
+    }
+    bool isSplat() const {
+        return _splat;
+    }
+    size_t getNumTransformations() const {
+        return _steps.size();
+    }
+    int getTransformationKind(size_t i) const {
+        return _steps[i].x.kind;
+    }
+
+    // ContentAttr::getType(): inferFinalType over the list (pure host code in the library)
+    NDType getType() const {
+        Marshalled m(*this);
+        b200c_type out;
+        std::memset(&out, 0, sizeof(out));
+        std::vector<double> scales(maxQuantEntries());
+        std::vector<int64_t> zps(scales.size());
+        out.scales = scales.data();
+        out.zps = zps.data();
+        out.nq = static_cast<int64_t>(scales.size());
+        check(b200c_infer_type(&m.base, m.chain.data(), static_cast<int>(m.chain.size()), &out));
+        return NDType::fromC(out);
+    }
+
+    // ContentAttr::fold() + Content::copyTo() on the device behind `be`
+    Content fold(const Backend& be) const {
+        Marshalled m(*this);
+        const NDType finalType = getType();
+        size_t cap = static_cast<size_t>(finalType.getTotalAllocSize());
+        std::vector<uint8_t> out(cap ? cap : 1);
+        size_t written = 0;
+        check(b200c_fold(be.ctx(), &m.base, _data->data(), _data->size(), _splat ? 1 : 0, /*data_on_device=*/0,
+                         m.chain.data(), static_cast<int>(m.chain.size()), out.data(), cap, /*out_on_device=*/0, &written,
+                         nullptr, 0));
+        out.resize(written);
+        return Content(finalType, std::move(out));
+    }
+
+    // vpux::countNonSparseElementsPerOC on the folded content
+    std::vector<int64_t> countNonSparseElementsPerOC(const Backend& be) const {
+        Marshalled m(*this);
+        const NDType t = getType();
+        std::vector<int64_t> counts(t.shape.empty() ? 0 : static_cast<size_t>(t.shape[0]));
+        check(b200c_count_nonsparse_per_oc(be.ctx(), &m.base, _data->data(), _data->size(), _splat ? 1 : 0, 0, m.chain.data(),
+                                           static_cast<int>(m.chain.size()), counts.data(), static_cast<int64_t>(counts.size())));
+        return counts;
+    }
+
+private:
+    struct Step {
+        b200c_xform x;
+        NDType type;               // owns the quantisation arrays x.type points to
+        std::vector<int64_t> aux;  // owns x.aux
+        explicit Step(int kind) {
+            std::memset(&x, 0, sizeof(x));
+            x.kind = kind;
+        }
+    };
+    // the C descriptors of an attribute; pointers refer to storage owned by the attribute
+    struct Marshalled {
+        b200c_type base;
+        std::vector<b200c_xform> chain;
+        explicit Marshalled(const ContentAttr& a): base(a._base.toC()) {
+            for (const Step& s : a._steps) {
+                b200c_xform x = s.x;
+                if (s.type.dtype != 0 || s.type.quant.kind != B200C_Q_NONE) x.type = s.type.toC();  // element type only
+                x.aux = s.aux.empty() ? nullptr : s.aux.data();
+                x.naux = static_cast<int64_t>(s.aux.size());
+                chain.push_back(x);
+            }
+        }
+    };
+
+    static void fill(int64_t* dst, const std::vector<int64_t>& v, int32_t* n) {
+        if (v.size() > B200C_MAX_RANK) throw Error(B200C_ERR_INVALID, "rank above B200C_MAX_RANK");
+        for (size_t k = 0; k < v.size(); ++k) dst[k] = v[k];
+        *n = static_cast<int32_t>(v.size());
+    }
+    // room for the per-axis parameters of any type the list can produce (the quantised axis can grow
+    // through PadWithZero and Broadcast)
+    size_t maxQuantEntries() const {
+        int64_t n = 1;
+        for (auto d : _base.shape) n = std::max<int64_t>(n, d);
+        for (const Step& s : _steps) {
+            n = std::max<int64_t>(n, static_cast<int64_t>(s.type.quant.scales.size()));
+            int64_t grow = std::max<int64_t>(0, s.x.i1);
+            for (int k = 0; k < B200C_MAX_RANK; ++k) grow = std::max(grow, std::max(s.x.a[k], s.x.b[k]));
+            n += grow;
+        }
+        return static_cast<size_t>(std::min<int64_t>(n, int64_t(1) << 24) + 64);
+    }
+    // ContentAttr::addTransformation: insert at getInsertionPosition, then re-check the final type
+    ContentAttr add(Step s) const {
+        std::vector<int32_t> kinds;
+        for (const Step& t : _steps) kinds.push_back(t.x.kind);
+        int pos = 0;
+        check(b200c_insert_position(kinds.data(), static_cast<int>(kinds.size()), s.x.kind, &pos));
+        ContentAttr r = *this;
+        r._steps.insert(r._steps.begin() + pos, std::move(s));
+        (void)r.getType();  // throws what inferOutputType would
+        return r;
+    }
+
+    NDType _base;
+    std::shared_ptr<std::vector<uint8_t>> _data;
+    bool _splat = false;
+    std::vector<Step> _steps;
+};
+
+// vpux::BitCompactorCodec::compress (src/vpux_compiler/src/utils/bit_compactor_codec.cpp:15-42):
+// returns false (mlir::failure) when the stream would not be smaller than the input
+inline bool compress(const Backend& be, const std::vector<uint8_t>& data, std::vector<uint8_t>* stream) {
+    size_t bound = 0, n = 0;
+    check(b200c_btc_bound(data.size(), &bound));
+    stream->resize(bound);
+    const int rc = b200c_btc_compress(be.ctx(), data.data(), data.size(), 0, stream->data(), bound, 0, &n);
+    check(rc);
+    if (rc == B200C_NOT_SMALLER) {
+        stream->clear();
+        return false;
+    }
+    stream->resize(n);
+    return true;
+}
+
+inline std::vector<uint8_t> decompress(const Backend& be, const std::vector<uint8_t>& stream, size_t originalSize) {
+    std::vector<uint8_t> out(originalSize ? originalSize : 1);
+    size_t n = 0;
+    check(b200c_btc_decompress(be.ctx(), stream.data(), stream.size(), 0, out.data(), originalSize, 0, &n));
+    out.resize(n);
+    return out;
+}
+
+}  // namespace Const
+}  // namespace b200
+
+#endif /* B200CONST_HPP_ */

@@ -20,7 +20,7 @@ size_t codecBound(size_t n) {
 // Blocks are indexed in a padded space in which every buffer starts on a tile boundary
 // (kTileBlocks blocks), so one tile never straddles two buffers.
 constexpr int kTileBlocks = 4096;
-constexpr int kIterBlocks = 256;  // blocks per CTA iteration: 256 threads, 4 lanes per block, 4 rounds between barriers
+constexpr int kIterBlocks = 256;  // blocks per CTA iteration: 256 threads, one 64-byte block each
 
 B2_HD void loadBlock(const CodecJobDev& job, unsigned long long blk, unsigned char* b) {
     const unsigned long long first = blk * kCodecBlock;
@@ -420,6 +420,23 @@ __global__ void __launch_bounds__(256) codecEmitKernel(const CodecJobDev* __rest
 
         if (tileFirst == 0 && threadIdx.x == 0) writeStreamHeader(job, dst);
 
+        // one 64-byte block per thread and iteration; the next iteration's block is loaded while the
+        // current one is encoded
+        auto loadMine = [&](int it, uint4 (&v)[4]) {
+            const unsigned long long blk = tileFirst + static_cast<unsigned long long>(it) * kIterBlocks + threadIdx.x;
+            if (it < kTileBlocks / kIterBlocks && blk < job.nblocks) {
+                if (vec && (blk + 1) * kCodecBlock <= job.n) {
+                    const uint4* p4 = reinterpret_cast<const uint4*>(job.in + blk * kCodecBlock);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) v[k] = __ldg(p4 + k);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) v[k] = loadLane16(job.in, job.n, blk, k, false);
+                }
+            }
+        };
+        uint4 nxt[4] = {};
+        loadMine(0, nxt);
         for (int it = 0; it < kTileBlocks / kIterBlocks; ++it) {
             const unsigned long long blk0 = tileFirst + static_cast<unsigned long long>(it) * kIterBlocks;
             if (blk0 >= job.nblocks) break;
@@ -427,64 +444,57 @@ __global__ void __launch_bounds__(256) codecEmitKernel(const CodecJobDev* __rest
             const unsigned int winEnd = relOff[(it + 1) * kIterBlocks];
             const unsigned long long outStart = tileRel + winStart;  // offset inside the records area
             const unsigned int phase = static_cast<unsigned int>(reinterpret_cast<uintptr_t>(records + outStart) & 15);
-            for (int sub = 0; sub < kIterBlocks / 64; ++sub) {
-            const int bi = sub * 64 + grp;  // block of this iteration handled by the 4-lane group
+            const int bi = threadIdx.x;
             const unsigned long long blk = blk0 + bi;
+            uint4 cur[4] = {nxt[0], nxt[1], nxt[2], nxt[3]};
+            loadMine(it + 1, nxt);
             if (blk < job.nblocks) {
                 const unsigned long long g = tile * kTileBlocks + static_cast<unsigned long long>(it) * kIterBlocks + bi;
                 const unsigned int word = summary[g];
                 const unsigned int header = word & 0xFFu, base = (word >> 8) & 0xFFu;
                 const int mode = header >> 5, w = header & 31;
                 unsigned char* rec = window + phase + (relOff[it * kIterBlocks + bi] - winStart);
-                const uint4 v = loadLane16(job.in, job.n, blk, lane4, vec);
-                const unsigned int words[4] = {v.x, v.y, v.z, v.w};
-                if (lane4 == 0) rec[0] = static_cast<unsigned char>(header);
+                const unsigned int words[16] = {cur[0].x, cur[0].y, cur[0].z, cur[0].w, cur[1].x, cur[1].y, cur[1].z, cur[1].w,
+                                                cur[2].x, cur[2].y, cur[2].z, cur[2].w, cur[3].x, cur[3].y, cur[3].z, cur[3].w};
+                rec[0] = static_cast<unsigned char>(header);
                 if (mode == 0) {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) rec[1 + lane4 * 16 + i] = static_cast<unsigned char>(words[i >> 2] >> (8 * (i & 3)));
+                    for (int i = 0; i < 64; ++i) rec[1 + i] = static_cast<unsigned char>(words[i >> 2] >> (8 * (i & 3)));
                 } else if (mode == 1) {
-                    if (lane4 == 0) rec[1] = static_cast<unsigned char>(base);
+                    rec[1] = static_cast<unsigned char>(base);
                 } else if (mode == 2 || mode == 3) {
                     const int skip = mode == 2 ? 2 : 1;
-                    if (mode == 2 && lane4 == 0) rec[1] = static_cast<unsigned char>(base);
+                    if (mode == 2) rec[1] = static_cast<unsigned char>(base);
 #pragma unroll
-                    for (int gq = 0; gq < 2; ++gq) {  // two 8-element groups per lane
-                        unsigned long long word = 0;
+                    for (int gq = 0; gq < 8; ++gq) {  // eight 8-element groups, w bytes each
+                        unsigned long long packed = 0;
 #pragma unroll
                         for (int k = 0; k < 8; ++k) {
                             const unsigned int b = (words[gq * 2 + (k >> 2)] >> (8 * (k & 3))) & 0xFFu;
                             const unsigned long long f = mode == 2 ? ((b - base) & 0xFFu) : zigzag8(b);
-                            word |= f << (k * w);
+                            packed |= f << (k * w);
                         }
-                        unsigned char* g8 = rec + skip + (lane4 * 2 + gq) * w;
-                        for (int j = 0; j < w; ++j) g8[j] = static_cast<unsigned char>(word >> (8 * j));
+                        unsigned char* g8 = rec + skip + gq * w;
+                        for (int j = 0; j < w; ++j) g8[j] = static_cast<unsigned char>(packed >> (8 * j));
                     }
-                } else {  // sparse: mask bytes then the non-zero bytes in order
-                    unsigned int m16 = 0;
+                } else {  // sparse: 8 mask bytes, then the non-zero bytes in order
+                    unsigned char* nz = rec + 9;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) m16 |= static_cast<unsigned int>(((words[i >> 2] >> (8 * (i & 3))) & 0xFFu) != 0) << i;
-                    rec[1 + lane4 * 2] = static_cast<unsigned char>(m16);
-                    rec[2 + lane4 * 2] = static_cast<unsigned char>(m16 >> 8);
-                    const unsigned int mine = __popc(m16);
-                    // exclusive prefix of the non-zero counts over the four lanes of the group
-                    const unsigned int mask4 = 0xFu << (lane & ~3);
-                    unsigned int incl = mine;
-                    const unsigned int a = __shfl_up_sync(mask4, incl, 1, 4);
-                    if (lane4 >= 1) incl += a;
-                    const unsigned int b2 = __shfl_up_sync(mask4, incl, 2, 4);
-                    if (lane4 >= 2) incl += b2;
-                    unsigned char* nz = rec + 9 + (incl - mine);
+                    for (int q = 0; q < 8; ++q) {
+                        unsigned int m8 = 0;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const unsigned int b = (words[i >> 2] >> (8 * (i & 3))) & 0xFFu;
-                        if (b != 0) *nz++ = static_cast<unsigned char>(b);
+                        for (int i = 0; i < 8; ++i) {
+                            const unsigned int b = (words[q * 2 + (i >> 2)] >> (8 * (i & 3))) & 0xFFu;
+                            m8 |= static_cast<unsigned int>(b != 0) << i;
+                            if (b != 0) *nz++ = static_cast<unsigned char>(b);
+                        }
+                        rec[1 + q] = static_cast<unsigned char>(m8);
                     }
                 }
-                if (grp == 0 && lane4 == 0) {  // blk is the first block of an index group of 64
+                if ((bi & (kCodecSuper - 1)) == 0) {  // first block of an index group of 64
                     putU32(dst + kCodecHeaderBytes + 4 * (blk / kCodecSuper),
                            static_cast<unsigned int>(tileRel + relOff[it * kIterBlocks + bi]));
                 }
-            }
             }
             __syncthreads();
             // copy the window out: [outStart, outStart + len) of the records area

@@ -664,19 +664,23 @@ void launchSmemConfig(Context* ctx, const RegConfig& c, const RowQuantParams* on
     } else {                                                                                                              \
         launchSmemT<T_, TPR_, B200C_QSYNTH_ASYM_U4>(ctx, one, itemsDev, startDev, nitems, totalGroups, smem);             \
     }
-    if (c.srcTag == T_F16) {
-        if (c.tpr == 32) {
-            B2_SM_CASE(__half, 32)
-        } else {
-            B2_SM_CASE(__half, 256)
-        }
-    } else {
-        if (c.tpr == 32) {
-            B2_SM_CASE(float, 32)
-        } else {
-            B2_SM_CASE(float, 256)
-        }
+#define B2_SM_TPR(T_)               \
+    switch (c.tpr) {                \
+    case 32:                        \
+        B2_SM_CASE(T_, 32) break;   \
+    case 64:                        \
+        B2_SM_CASE(T_, 64) break;   \
+    case 128:                       \
+        B2_SM_CASE(T_, 128) break;  \
+    default:                        \
+        B2_SM_CASE(T_, 256) break;  \
     }
+    if (c.srcTag == T_F16) {
+        B2_SM_TPR(__half)
+    } else {
+        B2_SM_TPR(float)
+    }
+#undef B2_SM_TPR
 #undef B2_SM_CASE
 }
 
@@ -690,7 +694,10 @@ void pickConfig(const RowQuantParams& p, RegConfig* c) {
     c->srcTag = p.srcTag;
     c->scheme = p.scheme;
     c->maxu = 0;
-    c->tpr = p.rowElems <= 1024 ? 32 : 256;
+    // threads per row by the staged row's size: several short rows share a CTA, so the per-CTA start-up
+    // (item lookup, parameter copy) is spread over more bytes and more loads are in flight per SM
+    const long long rowBytes = p.rowElems * (p.srcTag == T_F16 ? 2 : 4);
+    c->tpr = rowBytes <= 4096 ? 32 : rowBytes <= 16384 ? 64 : rowBytes <= 49152 ? 128 : 256;
 }
 
 }  // namespace

@@ -1,0 +1,132 @@
+// Exercises the C++ host layer (include/b200const.hpp) the way the reference's unit tests exercise
+// vpux::Const::ContentAttr (tests/unit/vpux_compiler/dialect/const/content_tests.cpp): build an
+// attribute, add transformations, fold, compare with a plain-loop expectation written here.
+// Exit code 0 = all checks passed; each failure prints one line.
+#include "b200const.hpp"
+
+#include <cmath>
+#include <cstdio>
+#include <numeric>
+#include <random>
+
+using namespace b200::Const;
+
+static int failures = 0;
+#define EXPECT(cond, what)                                  \
+    do {                                                    \
+        if (!(cond)) {                                      \
+            std::printf("FAILED: %s (%s)\n", what, #cond);  \
+            ++failures;                                     \
+        }                                                   \
+    } while (0)
+
+int main() {
+    // ---- host-only part: insertion order and type inference (content_tests.cpp:1342-1393) ----
+    {
+        std::vector<float> vals(2 * 16 * 3 * 3);
+        std::iota(vals.begin(), vals.end(), 0.0f);
+        auto a = ContentAttr::get(vals, NDType({2, 16, 3, 3}, B200C_F32));
+        auto b = a.swizzleConstant(5, 3).getSparsityMap().rescale(2.0);  // added out of order on purpose
+        EXPECT(b.getNumTransformations() == 3, "three transformations");
+        EXPECT(b.getTransformationKind(0) == B200C_X_RESCALE, "NONE first");
+        EXPECT(b.getTransformationKind(1) == B200C_X_GET_SPARSITY_MAP, "PREFERRED_LAST second");
+        EXPECT(b.getTransformationKind(2) == B200C_X_SWIZZLE_CONSTANT, "LAST last");
+        bool threw = false;
+        try {
+            b.bitPack(4);
+        } catch (const Error& e) {
+            threw = e.code() == B200C_ERR_THROW;
+        }
+        EXPECT(threw, "a second LAST transformation throws");
+        const NDType t = a.reorder(DimsOrder::NHWC()).padWithZero({0, 0, 0, 0}, {0, 16, 0, 0}).getType();
+        EXPECT((t.shape == std::vector<int64_t>{2, 32, 3, 3}) && t.order == DimsOrder::NHWC(), "inferred type of reorder + pad");
+    }
+    if (std::getenv("B200C_MIRROR_HOST_ONLY")) {
+        std::printf("%s (host-only part)\n", failures ? "FAILED" : "OK");
+        return failures ? 1 : 0;
+    }
+
+    Backend be(0);
+    // ---- ConvertElemType + Reorder + PadWithZero + Add, f32 -> checked casts (content_tests.cpp style) ----
+    {
+        const std::vector<int64_t> shape{2, 3, 2, 2};
+        std::vector<float> vals(24);
+        std::iota(vals.begin(), vals.end(), 0.0f);
+        auto c = ContentAttr::get(vals, NDType(shape, B200C_F32))
+                         .add(1.0)
+                         .reorder(DimsOrder::NHWC())
+                         .padWithZero({0, 0, 0, 0}, {0, 1, 0, 0})
+                         .convertElemType(B200C_SI8)
+                         .fold(be);
+        EXPECT((c.getType().shape == std::vector<int64_t>{2, 4, 2, 2}), "padded shape");
+        const auto got = c.getValues<int8_t>();
+        std::vector<int8_t> want;
+        for (int n = 0; n < 2; ++n)
+            for (int h = 0; h < 2; ++h)
+                for (int w = 0; w < 2; ++w)
+                    for (int ch = 0; ch < 4; ++ch)
+                        want.push_back(ch < 3 ? static_cast<int8_t>(vals[((n * 3 + ch) * 2 + h) * 2 + w] + 1) : 0);
+        EXPECT(got == want, "add + NHWC reorder + pad + convert");
+    }
+    // ---- per-axis Dequantize to f16-expressed type: float((q - zp) * double scale) ----
+    {
+        std::vector<uint8_t> q(4 * 8);
+        for (size_t i = 0; i < q.size(); ++i) q[i] = static_cast<uint8_t>(i * 7);
+        const std::vector<double> scales{0.5, 0.25, 2.0, 0.125};
+        const std::vector<int64_t> zps{0, 3, 128, 255};
+        auto c = ContentAttr::get(q, NDType({4, 8}, B200C_UI8))
+                         .quantCast(QuantParams::perAxis(B200C_F32, scales, zps, 0, 0, 255), B200C_UI8)
+                         .dequantize()
+                         .fold(be);
+        const auto got = c.getValues<float>();
+        bool same = got.size() == q.size();
+        for (size_t i = 0; same && i < q.size(); ++i)
+            same = got[i] == static_cast<float>((static_cast<int64_t>(q[i]) - zps[i / 8]) * scales[i / 8]);
+        EXPECT(same, "per-axis dequantize");
+    }
+    // ---- GetSparsityMap + Sparsify + countNonSparseElementsPerOC on a 50 % sparse int8 weight ----
+    {
+        std::mt19937 rng(7);
+        std::vector<int8_t> w(8 * 32);
+        for (auto& v : w) v = (rng() & 1) ? static_cast<int8_t>(static_cast<int>(rng() % 255) - 127) : 0;
+        auto base = ContentAttr::get(w, NDType({8, 32, 1, 1}, B200C_SI8));
+        const auto counts = base.countNonSparseElementsPerOC(be);
+        const auto map = base.getSparsityMap().fold(be).getRawBytes();
+        const auto vals = base.sparsify(false).fold(be).getRawBytes();
+        bool ok = map.size() == 8 * 16 && counts.size() == 8;
+        size_t at = 0;
+        for (int oc = 0; ok && oc < 8; ++oc) {
+            int64_t n = 0;
+            for (int j = 0; j < 32; ++j) {
+                const bool nz = w[oc * 32 + j] != 0;
+                ok = ok && (((map[oc * 16 + j / 8] >> (j % 8)) & 1) == (nz ? 1 : 0));
+                if (nz) {
+                    ok = ok && at + n < vals.size() && static_cast<int8_t>(vals[at + n]) == w[oc * 32 + j];
+                    ++n;
+                }
+            }
+            ok = ok && counts[oc] == n;
+            at += static_cast<size_t>((n + 15) / 16 * 16);
+        }
+        EXPECT(ok, "sparsity map (LSB first, rows padded to 128 bits), compacted values (16-byte channel starts), counts");
+    }
+    // ---- SwizzleConstant address rule (swizzle key 5) and the codec round trip ----
+    {
+        std::vector<uint8_t> x(4096);
+        for (size_t i = 0; i < x.size(); ++i) x[i] = static_cast<uint8_t>((i / 16) & 0xFF);
+        const auto sw = ContentAttr::get(x, NDType({4096, 1, 1, 1}, B200C_UI8)).swizzleConstant(5, 3).fold(be).getRawBytes();
+        bool ok = sw.size() == 4096;
+        for (size_t a = 0; ok && a < x.size(); a += 16) {
+            const size_t block = (a >> 9) & 63, stagger = (block & 31) << 4;
+            const size_t to = (a & ~size_t(511)) + ((a + stagger) & 511);
+            ok = std::memcmp(&sw[to], &x[a], 16) == 0;
+        }
+        EXPECT(ok, "swizzle address rule");
+        std::vector<uint8_t> stream;
+        const bool smaller = compress(be, x, &stream);
+        EXPECT(smaller && stream.size() < x.size(), "codec shrinks a ramp of 16-byte runs");
+        EXPECT(decompress(be, stream, x.size()) == x, "codec round trip");
+    }
+    std::printf("%s\n", failures ? "FAILED" : "OK");
+    return failures ? 1 : 0;
+}
