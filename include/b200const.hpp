@@ -302,6 +302,16 @@ public:
         s.x.i1 = value;
         return add(std::move(s));
     }
+    ContentAttr reverse(int64_t axis) const {
+        Step s(B200C_X_REVERSE);
+        s.x.i0 = axis;
+        return add(std::move(s));
+    }
+    ContentAttr expandDilated(const std::vector<int64_t>& dilations) const {
+        Step s(B200C_X_EXPAND_DILATED);
+        fill(s.x.a, dilations, &s.x.n);
+        return add(std::move(s));
+    }
     ContentAttr bitPack(int64_t width) const {
         Step s(B200C_X_BIT_PACK);
         s.x.i0 = width;

@@ -507,6 +507,9 @@ class ContentAttr:
     def reverse(self, axis):
         return self.addTransformation(Transform(A.X_REVERSE, i0=axis))
 
+    def expandDilated(self, dilations):
+        return self.addTransformation(Transform(A.X_EXPAND_DILATED, a=tuple(dilations)))
+
     def bitPack(self, width):
         return self.addTransformation(Transform(A.X_BIT_PACK, i0=width))
 

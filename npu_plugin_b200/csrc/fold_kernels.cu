@@ -37,6 +37,50 @@ void launchGeneric(Context* ctx, const GenParams& p) {
     ++ctx->launches;
 }
 
+// ---------------------------------------------------------------------------- ExpandDilated
+// One output element per thread: positions whose kernel coordinates are multiples of the dilations
+// take the source element, all others the fill value (expand_dilated.cpp:88-122).
+B2_HD void expandDilatedUnit(const unsigned char* src, unsigned char* dst, int es, long long ky, long long kx, long long dky,
+                             long long dkx, long long d0, long long d1, unsigned long long fill, long long o) {
+    const long long x = o % dkx;
+    const long long y = (o / dkx) % dky;
+    const long long plane = o / (dkx * dky);
+    unsigned long long bits = fill;
+    if (y % d0 == 0 && x % d1 == 0) {
+        const unsigned char* s = src + ((plane * ky + y / d0) * kx + x / d1) * es;
+        bits = 0;
+        for (int b = 0; b < es; ++b) bits |= static_cast<unsigned long long>(s[b]) << (8 * b);
+    }
+    for (int b = 0; b < es; ++b) dst[o * es + b] = static_cast<unsigned char>(bits >> (8 * b));
+}
+
+__global__ void __launch_bounds__(256) expandDilatedKernel(const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
+                                                           int es, long long ky, long long kx, long long dky, long long dkx,
+                                                           long long d0, long long d1, unsigned long long fill, long long n) {
+    const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long o = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; o < n; o += step) {
+        expandDilatedUnit(src, dst, es, ky, kx, dky, dkx, d0, d1, fill, o);
+    }
+}
+
+void launchExpandDilated(Context* ctx, const void* src, void* dst, int es, long long planes, long long ky, long long kx,
+                         long long dky, long long dkx, long long d0, long long d1, unsigned long long fill) {
+    const long long n = planes * dky * dkx;
+    if (n <= 0) return;
+    const unsigned char* s = static_cast<const unsigned char*>(src);
+    unsigned char* d = static_cast<unsigned char*>(dst);
+#ifdef B200C_HOST_EMULATION
+    if (B2_EMU(ctx)) {
+        for (long long o = 0; o < n; ++o) expandDilatedUnit(s, d, es, ky, kx, dky, dkx, d0, d1, fill, o);
+        ++ctx->launches;
+        return;
+    }
+#endif
+    expandDilatedKernel<<<gridFor(ctx, n, 256, 8), 256, 0, ctx->stream>>>(s, d, es, ky, kx, dky, dkx, d0, d1, fill, n);
+    B2_CUDA(cudaGetLastError());
+    ++ctx->launches;
+}
+
 // ---------------------------------------------------------------------------- row statistics
 struct RowAcc {
     float mx, mn, amax;

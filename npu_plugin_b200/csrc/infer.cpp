@@ -353,8 +353,15 @@ TensorType inferOne(const Transformation& x, const TensorType& in) {
         if (x.i0 != B200C_QSYNTH_SYM_I8 && x.i0 != B200C_QSYNTH_ASYM_U4) throw BadArg("QuantizeSynth: unknown scheme");
         return in;
 
-    case B200C_X_EXPAND_DILATED:
-        throw NotBuilt("ExpandDilated is not built yet");
+    case B200C_X_EXPAND_DILATED: {  // expand_dilated.cpp:78-82, getDilatedType (utils/dilated_utils.cpp:11-34)
+        if (in.rank() != 4) refThrow("Got invalid tensor rank '4'");
+        if (x.a.size() < 2) throw BadArg("ExpandDilated needs two dilations");
+        if (x.a[0] < 1 || x.a[1] < 1) throw BadArg("ExpandDilated: dilations must be positive");
+        std::vector<int64_t> shape = in.shape;
+        shape[2] = in.shape[2] + (in.shape[2] - 1) * (x.a[0] - 1);
+        shape[3] = in.shape[3] + (in.shape[3] - 1) * (x.a[1] - 1);
+        return withShape(in, shape);
+    }
     default:
         throw BadArg("unknown transformation kind " + std::to_string(x.kind));
     }

@@ -536,9 +536,129 @@ void Planner::apply(const Transformation& x) {
         return;
     }
 
+    case B200C_X_BROADCAST: {  // broadcast.cpp:84-116: the memory dim of `axis` is tiled value / extent times
+        needByteStorage("Broadcast");
+        if (_s.splat) {  // the single stored element is copied
+            _s.type = outType;
+            setShape(v, outType.memShape());
+            return;
+        }
+        materialize();
+        const int r = _s.type.rank();
+        const int pos = _s.type.memPosOf(static_cast<int>(x.i0));
+        const auto mem = _s.type.memShape();
+        const int64_t extent = mem[pos];
+        if (extent == 0 || x.i1 % extent) {
+            refThrow("Can't broadcast from %lld to %lld", static_cast<long long>(extent), static_cast<long long>(x.i1));
+        }
+        if (r + 1 > kMaxDims) throw NotBuilt("Broadcast of a rank-8 tensor");
+        // dense source read through a view with one more dim: [.., factor (stride 0), extent, ..]
+        GenParams p = paramsFor(v);
+        p.rank = r + 1;
+        long long st = 1;
+        std::vector<long long> dense(r);
+        for (int k = r - 1; k >= 0; --k) {
+            dense[k] = st;
+            st *= mem[k];
+        }
+        for (int k = 0, j = 0; k < r; ++k) {
+            if (k == pos) {
+                p.shape[j] = x.i1 / extent;
+                p.stride[j++] = 0;
+            }
+            p.shape[j] = mem[k];
+            p.stride[j++] = dense[k];
+        }
+        p.base = 0;
+        remapDense(p, curTag(), outType, _s.storage);
+        return;
+    }
+
+    case B200C_X_REVERSE: {  // reverse.cpp:55-117: runs of `spatialDims` consecutive values are reversed
+        needByteStorage("Reverse");
+        const int dt = _s.type.dtype;
+        if (!(dt == B200C_SI8 || dt == B200C_UI8 || dt == B200C_F16 || dt == B200C_BF16 || dt == B200C_F32)) {
+            refThrow("Unexpected data type");
+        }
+        const int r = _s.type.rank();
+        if (!(x.i0 >= 0 && x.i0 < r - 1)) {
+            refThrow("Const::Content::reverse: got unexpected content dimension %lld", static_cast<long long>(x.i0));
+        }
+        int64_t spatial = 1;
+        for (int k = r - 1; k > x.i0; --k) spatial *= _s.type.shape[k];
+        const int tag = tagOfLogical(_s.type);
+        const int64_t n = _s.type.count();
+        const void* dense = denseAs(tag);  // getValues<StorageType>() of every element, splat included
+        GenParams p;
+        std::memset(&p, 0, sizeof(p));
+        p.src = dense;
+        p.srcTag = tag;
+        p.err = _ctx->errWord;
+        p.swizzleKey = -1;
+        p.rank = 2;
+        p.shape[0] = spatial ? n / spatial : 0;
+        p.shape[1] = spatial;
+        p.stride[0] = spatial;
+        p.stride[1] = -1;
+        p.base = spatial - 1;
+        remapDense(p, tag, outType, dt);
+        return;
+    }
+
+    case B200C_X_EXPAND_DILATED: {  // expand_dilated.cpp:88-122: raw storage elements scattered into a zero-filled buffer
+        needByteStorage("ExpandDilated");
+        if (_s.splat) throw NotBuilt("ExpandDilated of a splat (the reference reads past its single stored element)");
+        if (outType.q.kind == B200C_Q_PER_AXIS) throw NotBuilt("ExpandDilated of a per-axis quantised constant");
+        materialize();
+        const int tag = curTag();
+        const int es = tagBytes(tag);
+        const int64_t n = outType.count();
+        void* dst = _ctx->arena.alloc(n ? static_cast<size_t>(n) * es : 1);
+        const unsigned long long fill = outType.q.kind == B200C_Q_PER_TENSOR ? castIntToTag(outType.q.zps[0], tag) : 0ull;
+        if (n > 0) {
+            launchExpandDilated(_ctx, v.src, dst, es, _s.type.shape[0] * _s.type.shape[1], _s.type.shape[2], _s.type.shape[3],
+                                outType.shape[2], outType.shape[3], x.a[0], x.a[1], fill);
+        }
+        View nv;
+        nv.src = dst;
+        nv.srcBytes = static_cast<size_t>(n) * es;
+        nv.srcTag = tag;
+        setShape(nv, outType.memShape());
+        contiguousStrides(nv);
+        v = nv;
+        _s.type = outType;
+        return;
+    }
+
     default:
         throw NotBuilt("transformation kind " + std::to_string(x.kind) + " is not built");
     }
+}
+
+// Runs the element kernel over a hand-built view of a dense buffer and makes the result the new
+// (dense) content: what a materialising transformation of the reference leaves behind.
+void Planner::remapDense(GenParams p, int tag, const TensorType& outType, int storage) {
+    const int64_t n = outType.count();
+    const size_t bytes = static_cast<size_t>(n) * tagBytes(tag);
+    void* dst = _ctx->arena.alloc(bytes ? bytes : 1);
+    if (n > 0) {
+        p.dst = dst;
+        p.outMode = OUT_RAW;
+        p.outTag = tag;
+        p.outElems = p.outUnits = n;
+        p.dataBytes = p.totalBytes = static_cast<long long>(bytes);
+        runGeneric(p);
+    }
+    View nv;
+    nv.src = dst;
+    nv.srcBytes = bytes;
+    nv.srcTag = tag;
+    setShape(nv, outType.memShape());
+    contiguousStrides(nv);
+    _s.view = nv;
+    _s.type = outType;
+    _s.storage = storage;
+    _s.splat = false;
 }
 
 // ---------------------------------------------------------------------------- QuantizeSynth

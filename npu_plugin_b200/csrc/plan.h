@@ -77,6 +77,7 @@ private:
     void swizzle(const Transformation& x, const TensorType& outType);
     size_t emitCopyTo(void* dst, size_t cap, int swizzleKey, int64_t totalBytes);
     void runGeneric(const GenParams& p);
+    void remapDense(GenParams p, int tag, const TensorType& outType, int storage);
     void flushPendingStats();
     bool tryFusedRowQuant(void* dst, int outMode, int outTag, int swizzleKey, int64_t dataBytes, int64_t totalBytes);
 

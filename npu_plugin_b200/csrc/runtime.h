@@ -188,6 +188,9 @@ void checkDeviceError(Context* ctx);
 
 // ---- kernel entry points (defined in the .cu files) ----------------------------------------
 void launchGeneric(Context* ctx, const GenParams& p);
+// ExpandDilated: element (plane, ky, kx) of the dense source goes to (plane, ky * d0, kx * d1); the rest is `fill`
+void launchExpandDilated(Context* ctx, const void* src, void* dst, int es, long long planes, long long ky, long long kx,
+                         long long dky, long long dkx, long long d0, long long d1, unsigned long long fill);
 // queued while ctx->batching is set, launched by flushTileBatch
 void launchTile(Context* ctx, const TileItem& it);
 void flushTileBatch(Context* ctx);

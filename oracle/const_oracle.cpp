@@ -992,6 +992,14 @@ static Type inferOutputType(const Xform& x, const Type& in) {
         if (!(in.q.kind == B200C_Q_NONE && isFloatDt(in.dtype))) throwf("QuantizeSynth expects a float tensor");
         return in;
     }
+    case B200C_X_EXPAND_DILATED: {  // CA/expand_dilated.cpp:78-82, getDilatedType (utils/dilated_utils.cpp:11-34)
+        if (in.rank() != 4) throwf("Got invalid tensor rank '4'");
+        if (x.a.size() < 2) throw std::invalid_argument("ExpandDilated needs two dilations");
+        Type out = in;
+        out.shape[2] = in.shape[2] + (in.shape[2] - 1) * (x.a[0] - 1);
+        out.shape[3] = in.shape[3] + (in.shape[3] - 1) * (x.a[1] - 1);
+        return out;
+    }
     default:
         throw Unsupported("transformation kind not restated in the oracle");
     }
@@ -1240,6 +1248,67 @@ static Content xBroadcast(const Xform& x, Content& in) {
         const int64_t p = t / factor, f = t % factor;
         std::memcpy(dst + single * p * factor + single * f, in.data + p * after * es, static_cast<size_t>(single));
     });
+    return out;
+}
+
+// ---- Reverse (CA/reverse.cpp:55-88, 93-117) ----
+// Every run of `spatialDims` consecutive values (in the order getValues yields them) is reversed;
+// the result is stored in the C type of the logical element type.
+template <class T>
+static Content reverseImpl(Content& in, const Type& outType, int64_t axis) {
+    Content out = allocTemp(outType, outType.dtype, false);
+    T* dst = reinterpret_cast<T*>(out.raw());
+    const int rank = in.type.rank();
+    if (!(axis >= 0 && axis < rank - 1)) {
+        throwf("Const::Content::reverse: got unexpected content dimension %lld", static_cast<long long>(axis));
+    }
+    int64_t spatial = 1;
+    for (int k = rank - 1; k > axis; --k) spatial *= in.type.shape[k];
+    const auto v = getValues<T>(in);
+    std::vector<T> vals(static_cast<size_t>(v.count));
+    for (int64_t i = 0; i < v.count; ++i) vals[static_cast<size_t>(i)] = v[i];
+    for (int64_t at = 0; at < v.count; at += spatial) {
+        const int64_t end = std::min<int64_t>(at + spatial, v.count);
+        std::reverse(vals.begin() + at, vals.begin() + end);
+    }
+    std::memcpy(dst, vals.data(), vals.size() * sizeof(T));
+    return out;
+}
+
+static Content xReverse(const Xform& x, Content& in) {
+    const Type outType = inferOutputType(x, in.type);
+    const int dt = in.type.dtype;  // the normalised storage integer for quantised types
+    if (dt == B200C_SI8) return reverseImpl<int8_t>(in, outType, x.i0);
+    if (dt == B200C_UI8) return reverseImpl<uint8_t>(in, outType, x.i0);
+    if (dt == B200C_F16) return reverseImpl<f16>(in, outType, x.i0);
+    if (dt == B200C_BF16) return reverseImpl<bf16>(in, outType, x.i0);
+    if (dt == B200C_F32) return reverseImpl<float>(in, outType, x.i0);
+    throwf("Unexpected data type");
+    return Content();
+}
+
+// ---- ExpandDilated (CA/expand_dilated.cpp:88-122) ----
+// Raw storage elements are scattered into a zero-filled buffer; indices are computed from the
+// logical shapes as if the layout were OIYX, exactly as the reference does.
+static Content xExpandDilated(const Xform& x, Content& in) {
+    const Type outType = inferOutputType(x, in.type);
+    Content out = allocTemp(outType, in.storage, false);
+    fillWithZero(out);
+    if (dbits(in.storage) < 8) throwf("Unsupported storage type of size '%d' bits.", dbits(in.storage));
+    const int64_t es = dbits(in.storage) / 8;
+    const int64_t OC = in.type.shape[0], IC = in.type.shape[1], KY = in.type.shape[2], KX = in.type.shape[3];
+    const int64_t dKY = outType.shape[2], dKX = outType.shape[3];
+    if (in.splat) throw Unsupported("ExpandDilated of a splat reads past its single stored element in the reference");
+    char* dst = out.raw();
+    for (int64_t oc = 0; oc < OC; ++oc)
+        for (int64_t ic = 0; ic < IC; ++ic)
+            for (int64_t ky = 0; ky < KY; ++ky)
+                for (int64_t kx = 0; kx < KX; ++kx) {
+                    const int64_t dky = ky + (x.a[0] - 1) * ky, dkx = kx + (x.a[1] - 1) * kx;
+                    const int64_t o = dkx + dky * dKX + ic * dKX * dKY + oc * dKX * dKY * IC;
+                    const int64_t i = kx + ky * KX + ic * KX * KY + oc * KX * KY * IC;
+                    std::memcpy(dst + o * es, in.data + i * es, static_cast<size_t>(es));
+                }
     return out;
 }
 
@@ -1544,6 +1613,10 @@ static Content applyTransform(const Xform& x, Content& in) {
         return xPad(x, in);
     case B200C_X_BROADCAST:
         return xBroadcast(x, in);
+    case B200C_X_REVERSE:
+        return xReverse(x, in);
+    case B200C_X_EXPAND_DILATED:
+        return xExpandDilated(x, in);
     case B200C_X_BIT_PACK:
         return xBitPack(x, in);
     case B200C_X_GET_SPARSITY_MAP:

@@ -447,3 +447,46 @@ def test_reorder_after_subview(gpu, oracle, off, chan, inner):
     assert_same(cg, co)
     want = np.ascontiguousarray(w[lo[0]:, lo[1]:].transpose(0, 2, 3, 1)).view(np.uint8).ravel()
     assert np.array_equal(cg.copyTo().ravel(), want)
+
+
+# ------------------------------------------------------------------ Broadcast / Reverse / ExpandDilated
+@pytest.mark.parametrize("dt,npdt", [(A.SI8, np.int8), (A.UI8, np.uint8), (A.F16, np.float16), (A.F32, np.float32)])
+@pytest.mark.parametrize("order", [None, DimsOrder.NHWC])
+def test_remaining_transforms_match_oracle(gpu, oracle, dt, npdt, order):
+    rng = np.random.default_rng(31)
+    shape = (3, 4, 5, 6)
+    w = rng.integers(0, 100, shape).astype(npdt)
+
+    def base(backend):
+        a = ContentAttr.get(w, NDType(shape, dt), backend=backend)
+        return a.reorder(order) if order is not None else a
+
+    builders = [
+        lambda b: base(b).reverse(0),
+        lambda b: base(b).reverse(2),
+        lambda b: base(b).add(1.0).reverse(1) if dt in (A.F16, A.F32) else base(b).reverse(1),
+        lambda b: base(b).expandDilated((2, 3)),
+        lambda b: base(b).subview((0, 1, 0, 0), (3, 2, 5, 6)).expandDilated((1, 2)),
+        lambda b: base(b).subview((0, 0, 0, 0), (1, 4, 5, 6)).broadcast(0, 4),
+        lambda b: base(b).subview((0, 1, 0, 0), (3, 1, 5, 6)).broadcast(1, 5).reverse(1),
+        lambda b: base(b).subview((0, 0, 2, 0), (3, 4, 1, 6)).broadcast(2, 3).padWithZero((0, 0, 1, 0), (0, 0, 0, 2)),
+    ]
+    for k, build in enumerate(builders):
+        cg, co = build(gpu).fold(), build(oracle).fold()
+        try:
+            assert_same(cg, co)
+        except AssertionError as e:
+            raise AssertionError(f"builder {k}: {e}")
+
+
+def test_expand_dilated_quantised_fill(gpu, oracle):
+    rng = np.random.default_rng(32)
+    w = rng.integers(0, 255, (2, 3, 3, 3)).astype(np.uint8)
+    q = UniformQuantizedType(A.UI8, A.F16, 0.5, 128, 0, 255)
+
+    def build(backend):
+        return ContentAttr.get(w, NDType(w.shape, A.UI8), backend=backend).quantCast(q).expandDilated((2, 2))
+
+    cg, co = both(build, gpu, oracle)
+    assert_same(cg, co)
+    assert cg.copyTo().reshape(2, 3, 5, 5)[0, 0, 1, 1] == 128  # the gaps hold the zero point

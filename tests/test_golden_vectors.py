@@ -396,3 +396,63 @@ def test_swizzle_address_rule(backend, key):
         dst = (a & ~511) + ((a + stagger) & 511)
         exp[dst:dst + 16] = x[a:a + 16]
     assert np.array_equal(raw, exp)
+
+
+# ---- the remaining transformations: Broadcast, Reverse, ExpandDilated --------------------------------
+# LIT constant_folding.mlir:108-205 broadcastNonSplat*: the broadcast axis is tiled, whatever lies inside it repeats
+@pytest.mark.parametrize("vals,shape,steps,final,want", [
+    ([1, 2, 3], (1, 3, 1, 1), [(0, 3)], (1, 9, 1, 1), [1, 2, 3, 1, 2, 3, 1, 2, 3]),          # PreChannel :110-119
+    ([1, 2, 3], (1, 3, 1, 1), [(2, 3)], (1, 9, 1, 1), [1, 1, 1, 2, 2, 2, 3, 3, 3]),          # PostChannel :124-133
+    ([1, 2, 3, 4, 5, 6], (1, 3, 1, 2), [(2, 2)], None, [1, 2, 1, 2, 3, 4, 3, 4, 5, 6, 5, 6]),  # MiddleChannel :138-149
+    (list(range(1, 13)), (1, 3, 2, 2), [(2, 4)], None,
+     [1, 2, 3, 4, 1, 2, 3, 4, 5, 6, 7, 8, 5, 6, 7, 8, 9, 10, 11, 12, 9, 10, 11, 12]),       # MiddleChannelNone1 :154-164
+])
+def test_lit_broadcast_non_splat(backend, vals, shape, steps, final, want):
+    a = attr(backend, vals, (len(vals),), A.I8, np.uint8).reshape(shape)
+    for axis, value in steps:
+        a = a.broadcast(axis, value)
+    if final is not None:
+        a = a.reshape(final)
+    assert list(a.fold().copyTo()) == want
+
+
+# LIT constant_folding.mlir:168-205 broadcastNonSplatTwoDims / MultiDims (f32 -> f16, two broadcasts)
+@pytest.mark.parametrize("shape,steps", [((1, 1, 1, 4), [(1, 4), (2, 4)]), ((1, 1, 4, 1), [(1, 4), (3, 4)])])
+def test_lit_broadcast_two_dims(backend, shape, steps):
+    base = np.array([1, 2, 3, 4], np.float32).reshape(shape)
+    a = attr(backend, base, shape, A.F32).convertElemType(A.F16).reshape(shape)
+    for axis, value in steps:
+        a = a.broadcast(axis, value)
+    c = a.fold()
+    assert c.getType().shape == (1, 4, 4, 4)
+    assert np.array_equal(c.getValues().reshape(1, 4, 4, 4), np.broadcast_to(base, (1, 4, 4, 4)).astype(np.float16))
+
+
+# UT:792-868 ReverseCWise / ReverseNWise: everything behind the axis is reversed as one run
+@pytest.mark.parametrize("axis", [0, 1])
+def test_reverse(backend, axis):
+    N, Cc, H, W = 2, 3, 4, 5
+    vals = iota(N * Cc * H * W, np.float32)
+    c = attr(backend, vals, (N, Cc, H, W), A.F32).reverse(axis).fold()
+    assert c.getType() == NDType((N, Cc, H, W), A.F32)
+    run = {0: Cc * H * W, 1: H * W}[axis]
+    assert np.array_equal(c.getValues().reshape(-1, run), vals.reshape(-1, run)[:, ::-1])
+
+
+def test_reverse_errors(backend):
+    with pytest.raises(ConstError):  # the last dim cannot be the axis (reverse.cpp:64-65)
+        attr(backend, iota(6, np.float32), (2, 3), A.F32).reverse(1).fold()
+    with pytest.raises(ConstError):  # si32 is not among the handled element types (reverse.cpp:103-116)
+        attr(backend, iota(6, np.int32), (2, 3), A.SI32).reverse(0).fold()
+
+
+# UT:1395-1442 ExpandDilated: 5x5 kernels, dilation 3 -> 13x13 with zeros between the taps
+def test_expand_dilated(backend):
+    OC, IC, KY, KX, d = 2, 2, 5, 5, 3
+    vals = iota(OC * IC * KY * KX, np.int32)
+    c = attr(backend, vals, (OC, IC, KY, KX), A.SI32).expandDilated((d, d)).fold()
+    dK = KY + (KY - 1) * (d - 1)
+    assert c.getType() == NDType((OC, IC, dK, dK), A.SI32)
+    want = np.zeros((OC, IC, dK, dK), np.int32)
+    want[:, :, ::d, ::d] = vals.reshape(OC, IC, KY, KX)
+    assert np.array_equal(c.getValues().reshape(want.shape), want)
