@@ -305,10 +305,10 @@ def main():
         dtype_name = "f16->i8"
     else:
         builder, default_n, text = {
-            "cfg1": (conv_weight_decls, 128, "conv weight f32 [256,256,3,3] -> sym int8 -> OYXI -> pad -> Swizzle(5)"),
+            "cfg1": (conv_weight_decls, 512, "conv weight f32 [256,256,3,3] -> sym int8 -> OYXI -> pad -> Swizzle(5)"),
             "cfg2": (int4_linear_decls, 8, "f16 [11008,4096] -> asym u4 -> BitPack; and u8 -> per-axis Dequantize -> f16"),
-            "cfg3": (sparse_conv_decls, 128, "int8 [1024,1024,1,1] 50% sparse -> sparsity map + sparsify, both Swizzle(5)"),
-            "cfg4": (resnet_decls, 16, "ResNet-50-shaped int8 set (54 tensors) -> QuantCast -> OYXI (-> pad) -> block codec"),
+            "cfg3": (sparse_conv_decls, 512, "int8 [1024,1024,1,1] 50% sparse -> sparsity map + sparsify, both Swizzle(5)"),
+            "cfg4": (resnet_decls, 32, "ResNet-50-shaped int8 set (54 tensors) -> QuantCast -> OYXI (-> pad) -> block codec"),
         }[args.workload]
         n_inst = args.instances or default_n
         decls = builder(n_inst)

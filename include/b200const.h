@@ -121,6 +121,11 @@ enum b200c_xform_kind {
     B200C_X_TRANSPOSE = 16,   /* a = order permutation                           */
     B200C_X_REVERSE = 17,     /* i0 = axis                                       */
     B200C_X_EXPAND_DILATED = 18, /* a[0..1] = dilations                          */
+    /* relocate_weights_table.cpp:122-203.  n = clusters, a[k] = offsets[k] (first output channel of
+     * cluster k), b[k] = weightsPtr[k], i0 = sparsityPtr, i1 = weightsElemBitSize (0 = absent),
+     * aux = numElems of the weights compression scheme (one per output channel; NULL = no
+     * compression), f = its alignment in bytes (0 = the default 16).                              */
+    B200C_X_RELOCATE_WEIGHTS_TABLE = 19,
     /* Synthetic producer step with no reference counterpart: per-channel
      * (axis 0) quantisation of a float tensor.  i0 = scheme:
      *   0: symmetric int8  scale = max|w|/127, zp = 0, round-half-even, clamp [-127,127]

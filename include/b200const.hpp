@@ -312,6 +312,20 @@ public:
         fill(s.x.a, dilations, &s.x.n);
         return add(std::move(s));
     }
+    // numElems / alignment stand for the VPUIP::CompressionSchemeAttr (empty = no weights compression)
+    ContentAttr relocateWeightsTablePointers(const std::vector<int32_t>& weightsPtr, uint64_t sparsityPtr,
+                                             const std::vector<int64_t>& offsets, uint64_t weightsElemBitSize = 0,
+                                             const std::vector<int64_t>& numElems = {}, int64_t alignment = 0) const {
+        Step s(B200C_X_RELOCATE_WEIGHTS_TABLE);
+        if (weightsPtr.size() != offsets.size()) throw Error(B200C_ERR_INVALID, "one weights pointer per cluster offset");
+        fill(s.x.a, offsets, &s.x.n);
+        fill(s.x.b, std::vector<int64_t>(weightsPtr.begin(), weightsPtr.end()), &s.x.n);
+        s.x.i0 = static_cast<int64_t>(sparsityPtr);
+        s.x.i1 = static_cast<int64_t>(weightsElemBitSize);
+        s.x.f = static_cast<double>(alignment);
+        s.aux = numElems;
+        return add(std::move(s));
+    }
     ContentAttr bitPack(int64_t width) const {
         Step s(B200C_X_BIT_PACK);
         s.x.i0 = width;

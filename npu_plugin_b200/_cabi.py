@@ -50,6 +50,7 @@ X_BROADCAST = 15
 X_TRANSPOSE = 16
 X_REVERSE = 17
 X_EXPAND_DILATED = 18
+X_RELOCATE_WEIGHTS_TABLE = 19
 X_QUANTIZE_SYNTH = 100
 
 QSYNTH_SYM_I8, QSYNTH_ASYM_U4 = 0, 1

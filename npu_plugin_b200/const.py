@@ -212,7 +212,7 @@ _NAMES = {A.X_CONVERT_ELEM_TYPE: "ConvertElemType", A.X_QUANT_CAST: "QuantCast",
           A.X_PAD_WITH_ZERO: "PadWithZero", A.X_BIT_PACK: "BitPack", A.X_GET_SPARSITY_MAP: "GetSparsityMap",
           A.X_SPARSIFY: "Sparsify", A.X_SWIZZLE_CONSTANT: "SwizzleConstant", A.X_RESHAPE: "Reshape",
           A.X_CHANGE_SHAPE_AND_ELEM_TYPE: "ChangeShapeAndElemType", A.X_BROADCAST: "Broadcast",
-          A.X_TRANSPOSE: "Transpose", A.X_REVERSE: "Reverse", A.X_EXPAND_DILATED: "ExpandDilated",
+          A.X_TRANSPOSE: "Transpose", A.X_REVERSE: "Reverse", A.X_EXPAND_DILATED: "ExpandDilated", A.X_RELOCATE_WEIGHTS_TABLE: "RelocateWeightsTable",
           A.X_QUANTIZE_SYNTH: "QuantizeSynth"}
 
 
@@ -509,6 +509,12 @@ class ContentAttr:
 
     def expandDilated(self, dilations):
         return self.addTransformation(Transform(A.X_EXPAND_DILATED, a=tuple(dilations)))
+
+    def relocateWeightsTablePointers(self, weightsPtr, sparsityPtr, offsets, weightsElemBitSize=0, numElems=None,
+                                     alignment=0):
+        """relocate_weights_table.cpp:205-213; numElems/alignment stand for the CompressionSchemeAttr."""
+        return self.addTransformation(Transform(A.X_RELOCATE_WEIGHTS_TABLE, a=tuple(offsets), b=tuple(weightsPtr),
+                                                i0=sparsityPtr, i1=weightsElemBitSize, aux=numElems, f=alignment))
 
     def bitPack(self, width):
         return self.addTransformation(Transform(A.X_BIT_PACK, i0=width))

@@ -540,12 +540,12 @@ int b200c_fold_batch(b200c_ctx* h, b200c_fold_item* items, int count, int data_o
             ctx->queuedBytes = 0;
         };
 
-        // Items are taken in waves of growing input size (32 MB, then twice as much each time): the
+        // Items are taken in waves of growing input size (256 MB, then twice as much each time): the
         // queued launches of a wave go out when it has been planned, so the device starts early and
         // works while the host plans the rest.  A wave with enough items is planned by the pool.
         const bool parallelOk = ctx->batching && data_on_device;
         if (parallelOk) ensurePool(ctx);
-        long long waveBytes = 32LL << 20;
+        long long waveBytes = 256LL << 20;
         int first = 0;
         // B200C_TRACE=1: host time of planning, flushing and the final wait, on stderr
         static const bool trace = std::getenv("B200C_TRACE") != nullptr;

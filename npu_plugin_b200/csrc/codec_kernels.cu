@@ -465,17 +465,32 @@ __global__ void __launch_bounds__(256) codecEmitKernel(const CodecJobDev* __rest
                 } else if (mode == 2 || mode == 3) {
                     const int skip = mode == 2 ? 2 : 1;
                     if (mode == 2) rec[1] = static_cast<unsigned char>(base);
+                    // field values of four bytes at a time: (b - base) & 0xFF per byte, or the zigzag code
+                    const unsigned int base4 = base * 0x01010101u;
+                    const unsigned int W1 = 1u << w, W2 = W1 << w, W4 = W2 << (2 * w);  // w <= 7: W4 <= 2^28
 #pragma unroll
                     for (int gq = 0; gq < 8; ++gq) {  // eight 8-element groups, w bytes each
-                        unsigned long long packed = 0;
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            const unsigned int b = (words[gq * 2 + (k >> 2)] >> (8 * (k & 3))) & 0xFFu;
-                            const unsigned long long f = mode == 2 ? ((b - base) & 0xFFu) : zigzag8(b);
-                            packed |= f << (k * w);
+                        unsigned int lo = words[gq * 2], hi = words[gq * 2 + 1];
+                        if (mode == 2) {
+                            // per-byte subtraction without borrows across bytes
+                            lo = ((lo | 0x80808080u) - (base4 & 0x7F7F7F7Fu)) ^ ((lo ^ ~base4) & 0x80808080u);
+                            hi = ((hi | 0x80808080u) - (base4 & 0x7F7F7F7Fu)) ^ ((hi ^ ~base4) & 0x80808080u);
+                        } else {
+                            lo = zigzag4(lo);
+                            hi = zigzag4(hi);
                         }
+                        // value k goes to bits [k*w, k*w + w): pairs, quads and the final 64-bit word by multiply-add
+                        const unsigned int f0 = lo & 0xFFu, f1 = (lo >> 8) & 0xFFu, f2 = (lo >> 16) & 0xFFu, f3 = lo >> 24;
+                        const unsigned int f4 = hi & 0xFFu, f5 = (hi >> 8) & 0xFFu, f6 = (hi >> 16) & 0xFFu, f7 = hi >> 24;
+                        const unsigned int q0 = (f3 * W1 + f2) * W2 + (f1 * W1 + f0);
+                        const unsigned int q1 = (f7 * W1 + f6) * W2 + (f5 * W1 + f4);
+                        const unsigned long long packed = static_cast<unsigned long long>(q1) * W4 + q0;
+                        const unsigned int plo = static_cast<unsigned int>(packed), phi = static_cast<unsigned int>(packed >> 32);
                         unsigned char* g8 = rec + skip + gq * w;
-                        for (int j = 0; j < w; ++j) g8[j] = static_cast<unsigned char>(packed >> (8 * j));
+#pragma unroll
+                        for (int j = 0; j < 7; ++j) {
+                            if (j < w) g8[j] = static_cast<unsigned char>((j < 4 ? plo : phi) >> (8 * (j & 3)));
+                        }
                     }
                 } else {  // sparse: 8 mask bytes, then the non-zero bytes in order
                     unsigned char* nz = rec + 9;

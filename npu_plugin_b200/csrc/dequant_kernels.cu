@@ -4,7 +4,8 @@
 //
 // A row shares one (scale, zero point), so the 256 possible results of a row are computed once --
 // with exactly the reference's double-precision expression -- into a shared-memory table in the
-// output type, and every element becomes one table lookup.  Loads and stores are 128-bit.
+// output type (one table per warp), and every element becomes one table lookup.  Loads and stores
+// are 128-bit.
 #include "runtime.h"
 
 #include <algorithm>
@@ -28,23 +29,32 @@ struct DequantRowsParams {
     long long dataBytes, totalBytes;
 };
 
+// One warp per (row, chunk of the row): the warp builds the row's table with exactly the reference's
+// double-precision expression, then streams its chunk with independent 128-bit loads.  Warps of a
+// CTA never wait for one another.
 __global__ void __launch_bounds__(256) dequantRowsKernel(const __grid_constant__ DequantRowsParams p, long long chunksPerRow,
                                                          long long chunkElems) {
-    __shared__ float lut32[256];
-    __shared__ unsigned short lut16[256];
+    __shared__ float lut32All[8][256];
+    __shared__ unsigned short lut16All[8][256];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* lut32 = lut32All[warp];
+    unsigned short* lut16 = lut16All[warp];
     const long long work = p.rows * chunksPerRow;
     long long lastRow = -1;
-    for (long long w = blockIdx.x; w < work; w += gridDim.x) {
+    for (long long w = static_cast<long long>(blockIdx.x) * 8 + warp; w < work; w += static_cast<long long>(gridDim.x) * 8) {
         const long long row = w / chunksPerRow, chunk = w - row * chunksPerRow;
         if (row != lastRow) {
-            __syncthreads();
-            const int q = p.srcSigned ? static_cast<int>(static_cast<signed char>(threadIdx.x)) : static_cast<int>(threadIdx.x);
+            __syncwarp();
             const double s = p.perAxis ? p.scales[row] : p.scale;
             const long long zp = p.perAxis ? p.zps[row] : p.zp;
-            const float r = static_cast<float>(static_cast<double>(static_cast<long long>(q) - zp) * s);
-            lut32[threadIdx.x] = r;
-            lut16[threadIdx.x] = __half_as_ushort(__float2half_rn(r));
-            __syncthreads();
+#pragma unroll
+            for (int e = lane; e < 256; e += 32) {
+                const int q = p.srcSigned ? static_cast<int>(static_cast<signed char>(e)) : e;
+                const float r = static_cast<float>(static_cast<double>(static_cast<long long>(q) - zp) * s);
+                lut32[e] = r;
+                lut16[e] = __half_as_ushort(__float2half_rn(r));
+            }
+            __syncwarp();
             lastRow = row;
         }
         const long long first = chunk * chunkElems;
@@ -54,38 +64,46 @@ __global__ void __launch_bounds__(256) dequantRowsKernel(const __grid_constant__
         const bool vec = ((reinterpret_cast<uintptr_t>(src) | (p.outHalf ? outElem * 2 : outElem * 4)) & 15) == 0 &&
                          (reinterpret_cast<uintptr_t>(p.dst) & 15) == 0;
         const long long nvec = vec ? n / 16 : 0;
-        for (long long u = threadIdx.x; u < nvec; u += blockDim.x) {
-            const uint4 v = __ldg(reinterpret_cast<const uint4*>(src) + u);
-            const unsigned int wds[4] = {v.x, v.y, v.z, v.w};
-            if (p.outHalf) {
-                unsigned int o[8];
+        unsigned char* d = static_cast<unsigned char*>(p.dst);
+        for (long long u0 = 0; u0 < nvec; u0 += 128) {  // four independent loads per lane and round
+            uint4 v[4];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const unsigned int b0 = (wds[i >> 1] >> (16 * (i & 1))) & 0xFFu;
-                    const unsigned int b1 = (wds[i >> 1] >> (16 * (i & 1) + 8)) & 0xFFu;
-                    o[i] = lut16[b0] | (static_cast<unsigned int>(lut16[b1]) << 16);
-                }
-                const long long a = (outElem + u * 16) * 2;
-                unsigned char* d = static_cast<unsigned char*>(p.dst);
-                *reinterpret_cast<uint4*>(d + swizzleAddr(a, p.swizzleKey)) = make_uint4(o[0], o[1], o[2], o[3]);
-                *reinterpret_cast<uint4*>(d + swizzleAddr(a + 16, p.swizzleKey)) = make_uint4(o[4], o[5], o[6], o[7]);
-            } else {
-                const long long a = (outElem + u * 16) * 4;
-                unsigned char* d = static_cast<unsigned char*>(p.dst);
+            for (int r = 0; r < 4; ++r) {
+                const long long u = u0 + r * 32 + lane;
+                if (u < nvec) v[r] = __ldg(reinterpret_cast<const uint4*>(src) + u);
+            }
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    float4 f;
-                    f.x = lut32[wds[i] & 0xFFu];
-                    f.y = lut32[(wds[i] >> 8) & 0xFFu];
-                    f.z = lut32[(wds[i] >> 16) & 0xFFu];
-                    f.w = lut32[wds[i] >> 24];
-                    *reinterpret_cast<float4*>(d + swizzleAddr(a + 16 * i, p.swizzleKey)) = f;
+            for (int r = 0; r < 4; ++r) {
+                const long long u = u0 + r * 32 + lane;
+                if (u >= nvec) continue;
+                const unsigned int wds[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+                if (p.outHalf) {
+                    unsigned int o[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const unsigned int b0 = (wds[i >> 1] >> (16 * (i & 1))) & 0xFFu;
+                        const unsigned int b1 = (wds[i >> 1] >> (16 * (i & 1) + 8)) & 0xFFu;
+                        o[i] = lut16[b0] | (static_cast<unsigned int>(lut16[b1]) << 16);
+                    }
+                    const long long a = (outElem + u * 16) * 2;
+                    *reinterpret_cast<uint4*>(d + swizzleAddr(a, p.swizzleKey)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4*>(d + swizzleAddr(a + 16, p.swizzleKey)) = make_uint4(o[4], o[5], o[6], o[7]);
+                } else {
+                    const long long a = (outElem + u * 16) * 4;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float4 f;
+                        f.x = lut32[wds[i] & 0xFFu];
+                        f.y = lut32[(wds[i] >> 8) & 0xFFu];
+                        f.z = lut32[(wds[i] >> 16) & 0xFFu];
+                        f.w = lut32[wds[i] >> 24];
+                        *reinterpret_cast<float4*>(d + swizzleAddr(a + 16 * i, p.swizzleKey)) = f;
+                    }
                 }
             }
         }
-        for (long long j = nvec * 16 + threadIdx.x; j < n; j += blockDim.x) {
+        for (long long j = nvec * 16 + lane; j < n; j += 32) {
             const unsigned int b = src[j];
-            unsigned char* d = static_cast<unsigned char*>(p.dst);
             if (p.outHalf) {
                 *reinterpret_cast<unsigned short*>(d + swizzleAddr((outElem + j) * 2, p.swizzleKey)) = lut16[b];
             } else {
@@ -140,8 +158,8 @@ bool tryLaunchDequantRows(Context* ctx, const GenParams& p) {
     // chunks of a row per CTA: long rows are split so the grid covers the machine
     const long long chunkElems = std::max<long long>(4096, (cols + 63) / 64 / 16 * 16);
     const long long chunksPerRow = (cols + chunkElems - 1) / chunkElems;
-    const long long work = rows * chunksPerRow;
-    const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>(work, ctx->smCount * 8LL)));
+    const long long work = rows * chunksPerRow;  // one warp each
+    const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>((work + 7) / 8, ctx->smCount * 8LL)));
     dequantRowsKernel<<<grid, 256, 0, ctx->stream>>>(q, chunksPerRow, chunkElems);
     B2_CUDA(cudaGetLastError());
     ++ctx->launches;

@@ -81,6 +81,58 @@ void launchExpandDilated(Context* ctx, const void* src, void* dst, int es, long 
     ++ctx->launches;
 }
 
+// ---------------------------------------------------------------------------- RelocateWeightsTable
+B2_HD void relocateUnit(const RelocateParams& p, long long oc) {
+    int weightStep = 0, sparsityStep = 0;
+    if (p.oc >= 2) {
+        weightStep = p.values[4] - p.values[0];
+        sparsityStep = p.values[5] - p.values[1];
+    }
+    const int c = p.clusterOf[oc];
+    const long long rel = oc - p.offsets[c];
+    const long long step = p.steps ? p.steps[oc] : static_cast<long long>(weightStep) * rel;
+    const long long at = oc * 4;
+    int err = E_NONE;
+    const long long w = p.weightsPtr[c] + step;
+    if (w < -2147483648ll || w > 2147483647ll) err = E_CAST_RANGE;
+    p.patched[at] = static_cast<int>(w);
+    int sp = p.values[at + 1];
+    if (sp != 0xFFFFFF) {  // SPARSITY_PTR_WHEN_NO_SPARSITY
+        const long long v = p.sparsityPtr + rel * static_cast<long long>(sparsityStep);
+        if (v < -2147483648ll || v > 2147483647ll) err = E_CAST_RANGE;
+        sp = static_cast<int>(v);
+    }
+    p.patched[at + 1] = sp;
+    p.patched[at + 2] = p.values[at + 2];
+    p.patched[at + 3] = p.values[at + 3];
+    if (err != E_NONE) {
+#ifdef __CUDA_ARCH__
+        atomicCAS(p.err, E_NONE, err);
+#else
+        if (*p.err == E_NONE) *p.err = err;
+#endif
+    }
+}
+
+__global__ void __launch_bounds__(256) relocateWeightsTableKernel(const __grid_constant__ RelocateParams p) {
+    const long long step = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long oc = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; oc < p.oc; oc += step) relocateUnit(p, oc);
+}
+
+void launchRelocateWeightsTable(Context* ctx, const RelocateParams& p) {
+    if (p.oc <= 0) return;
+#ifdef B200C_HOST_EMULATION
+    if (B2_EMU(ctx)) {
+        for (long long oc = 0; oc < p.oc; ++oc) relocateUnit(p, oc);
+        ++ctx->launches;
+        return;
+    }
+#endif
+    relocateWeightsTableKernel<<<gridFor(ctx, p.oc, 256, 8), 256, 0, ctx->stream>>>(p);
+    B2_CUDA(cudaGetLastError());
+    ++ctx->launches;
+}
+
 // ---------------------------------------------------------------------------- row statistics
 struct RowAcc {
     float mx, mn, amax;

@@ -241,6 +241,9 @@ TensorType inferOne(const Transformation& x, const TensorType& in) {
     case B200C_X_ADD:      // add.cpp:52-54
     case B200C_X_REVERSE:  // reverse.cpp:50-52
         return in;
+    case B200C_X_RELOCATE_WEIGHTS_TABLE:  // relocate_weights_table.cpp:114-116
+        if (x.a.empty() || x.a.size() != x.b.size()) throw BadArg("RelocateWeightsTable: one weights pointer per cluster offset");
+        return in;
 
     case B200C_X_REORDER: {  // reorder.cpp:67-73
         if (static_cast<int>(x.a.size()) != in.rank()) refThrow("DimsOrder doesn't match type");

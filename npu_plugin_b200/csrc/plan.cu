@@ -605,6 +605,63 @@ void Planner::apply(const Transformation& x) {
         return;
     }
 
+    case B200C_X_RELOCATE_WEIGHTS_TABLE: {  // relocate_weights_table.cpp:122-203
+        needByteStorage("RelocateWeightsTable");
+        const int64_t n = _s.type.count();
+        const int64_t oc = n / 4;  // WEIGHT_TABLE_NUM_ELEMENTS_PER_OC entries per output channel
+        const void* dense = denseAs(T_I32);  // getValues<int32_t>()
+        int* dst = static_cast<int*>(_ctx->arena.alloc(n ? static_cast<size_t>(n) * 4 : 1));
+        if (n > oc * 4) fillBytes(_ctx, dst + oc * 4, 0, static_cast<size_t>(n - oc * 4) * 4);
+        RelocateParams rp;
+        std::memset(&rp, 0, sizeof(rp));
+        rp.values = static_cast<const int*>(dense);
+        rp.patched = dst;
+        rp.oc = oc;
+        const int clusters = static_cast<int>(x.a.size());
+        bool segmented = false;  // all clusters at the same channel offset: the weights are not segmented
+        for (size_t k = 0; k < x.a.size(); ++k) {
+            rp.offsets[k] = x.a[k];
+            rp.weightsPtr[k] = static_cast<int32_t>(x.b[k]);
+            if (k > 0 && x.a[k] != x.a[k - 1]) segmented = true;
+        }
+        // the reference advances its cluster index by at most one per channel (:141-143, :186-189)
+        std::vector<int> clusterOf(static_cast<size_t>(std::max<int64_t>(oc, 1)), 0);
+        for (int64_t c = 0, ch = 0; ch < oc; ++ch) {
+            if (segmented && c + 1 < clusters && ch >= x.a[static_cast<size_t>(c + 1)]) ++c;
+            clusterOf[static_cast<size_t>(ch)] = static_cast<int>(c);
+        }
+        rp.clusterOf = static_cast<const int*>(uploadTable(clusterOf.data(), clusterOf.size() * sizeof(int)));
+        rp.sparsityPtr = static_cast<int32_t>(x.i0);
+        rp.err = _ctx->errWord;
+        if (x.hasAux) {
+            if (static_cast<int64_t>(x.aux.size()) != oc) {
+                refThrow("Invalid weights compression with %zu elements for %lld channels", x.aux.size(), static_cast<long long>(oc));
+            }
+            if (x.i1 == 0) refThrow("Missing weights element type attribute");
+            const int64_t alignment = x.f > 0 ? static_cast<int64_t>(x.f) : kWeightSetAlign;
+            std::vector<long long> steps(static_cast<size_t>(oc));
+            int64_t off = 0;
+            for (int64_t ch = 0; ch < oc; ++ch) {
+                if (ch > 0 && clusterOf[static_cast<size_t>(ch)] != clusterOf[static_cast<size_t>(ch - 1)]) off = 0;
+                steps[static_cast<size_t>(ch)] = off;
+                off += roundUp((x.aux[static_cast<size_t>(ch)] * x.i1 + 7) / 8, alignment);
+            }
+            rp.steps = static_cast<const long long*>(uploadTable(steps.data(), steps.size() * sizeof(long long)));
+        }
+        launchRelocateWeightsTable(_ctx, rp);
+        View nv;
+        nv.src = dst;
+        nv.srcBytes = static_cast<size_t>(n) * 4;
+        nv.srcTag = T_I32;
+        setShape(nv, outType.memShape());
+        contiguousStrides(nv);
+        v = nv;
+        _s.type = outType;
+        _s.storage = B200C_SI32;
+        _s.splat = false;
+        return;
+    }
+
     case B200C_X_EXPAND_DILATED: {  // expand_dilated.cpp:88-122: raw storage elements scattered into a zero-filled buffer
         needByteStorage("ExpandDilated");
         if (_s.splat) throw NotBuilt("ExpandDilated of a splat (the reference reads past its single stored element)");

@@ -188,6 +188,20 @@ void checkDeviceError(Context* ctx);
 
 // ---- kernel entry points (defined in the .cu files) ----------------------------------------
 void launchGeneric(Context* ctx, const GenParams& p);
+// RelocateWeightsTable (relocate_weights_table.cpp:122-203): one thread per output channel patches
+// the weights pointer and, unless it holds the "no sparsity" marker, the sparsity pointer
+struct RelocateParams {
+    const int* values;  // dense weights table, 4 entries per output channel
+    int* patched;
+    long long oc;
+    const int* clusterOf;            // cluster index of every output channel (the reference's running index)
+    long long offsets[kMaxDims];     // first output channel of every cluster
+    long long weightsPtr[kMaxDims];  // base weights pointer of every cluster
+    int sparsityPtr;
+    const long long* steps;  // per-channel weights pointer offsets of a compressed layout, or nullptr
+    int* err;
+};
+void launchRelocateWeightsTable(Context* ctx, const RelocateParams& p);
 // ExpandDilated: element (plane, ky, kx) of the dense source goes to (plane, ky * d0, kx * d1); the rest is `fill`
 void launchExpandDilated(Context* ctx, const void* src, void* dst, int es, long long planes, long long ky, long long kx,
                          long long dky, long long dkx, long long d0, long long d1, unsigned long long fill);

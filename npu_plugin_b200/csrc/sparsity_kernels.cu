@@ -321,7 +321,7 @@ __device__ __forceinline__ unsigned int neMask16(const uint4& v, unsigned int sv
     return m;
 }
 
-constexpr int kMapUnitsPerCta = 1024;  // 16 input bytes -> 2 map bytes per unit, 4 units per thread
+constexpr int kMapUnitsPerCta = 2048;  // 16 input bytes -> 2 map bytes per unit, 8 units per thread
 
 __global__ void __launch_bounds__(256) sparsityMapBatchKernel(const MapItem* __restrict__ items,
                                                               const long long* __restrict__ ctaStart, int nitems) {
@@ -345,26 +345,38 @@ __global__ void __launch_bounds__(256) sparsityMapBatchKernel(const MapItem* __r
     }
 }
 
-// one warp per channel
+// one warp per kChanPerWarp consecutive channels (the item lookup is paid once per warp)
+constexpr int kChanPerWarp = 4;
+
+__device__ __forceinline__ int nextItem(const long long* __restrict__ chanStart, int nitems, int k, long long ch) {
+    while (k + 1 < nitems && chanStart[k + 1] <= ch) ++k;
+    return k;
+}
+
 __global__ void __launch_bounds__(256) sparseCountBatchKernel(const SparseItem* __restrict__ items,
                                                               const long long* __restrict__ chanStart, int nitems,
                                                               long long nchan) {
-    const long long ch = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    if (ch >= nchan) return;
+    const long long ch0 = (static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5)) * kChanPerWarp;
+    if (ch0 >= nchan) return;
     const int lane = threadIdx.x & 31;
-    const int k = findBatchItem(chanStart, nitems, ch);
-    const SparseItem& it = items[k];
-    const long long c = ch - chanStart[k];
-    const unsigned int sv4 = it.sparseByte * 0x01010101u;
-    const uint4* row = reinterpret_cast<const uint4*>(it.src + c * it.work);
-    const long long nvec = it.work / 16;
-    int n = 0;
-    for (long long v = lane; v < nvec; v += 32) {
-        const uint4 x = __ldg(row + v);
-        n += __popc(neBytes(x.x, sv4)) + __popc(neBytes(x.y, sv4)) + __popc(neBytes(x.z, sv4)) + __popc(neBytes(x.w, sv4));
+    int k = findBatchItem(chanStart, nitems, ch0);
+    for (int q = 0; q < kChanPerWarp; ++q) {
+        const long long ch = ch0 + q;
+        if (ch >= nchan) break;
+        k = nextItem(chanStart, nitems, k, ch);
+        const SparseItem& it = items[k];
+        const long long c = ch - chanStart[k];
+        const unsigned int sv4 = it.sparseByte * 0x01010101u;
+        const uint4* row = reinterpret_cast<const uint4*>(it.src + c * it.work);
+        const long long nvec = it.work / 16;
+        int n = 0;
+        for (long long v = lane; v < nvec; v += 32) {
+            const uint4 x = __ldg(row + v);
+            n += __popc(neBytes(x.x, sv4)) + __popc(neBytes(x.y, sv4)) + __popc(neBytes(x.z, sv4)) + __popc(neBytes(x.w, sv4));
+        }
+        for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xFFFFFFFFu, n, o);
+        if (lane == 0) it.counts[c] = n;
     }
-    for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xFFFFFFFFu, n, o);
-    if (lane == 0) it.counts[c] = n;
 }
 
 // one CTA per item: channel offsets (16-byte aligned channel starts) and the size of the result
@@ -416,11 +428,15 @@ __global__ void __launch_bounds__(256) sparseScatterBatchKernel(const SparseItem
                                                                 const long long* __restrict__ chanStart, int nitems,
                                                                 long long nchan) {
     __shared__ __align__(16) unsigned char stage[8][544];
-    const long long ch = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    if (ch >= nchan) return;
+    const long long ch0 = (static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5)) * kChanPerWarp;
+    if (ch0 >= nchan) return;
     const int lane = threadIdx.x & 31;
     unsigned char* st = stage[threadIdx.x >> 5];
-    const int k = findBatchItem(chanStart, nitems, ch);
+    int k = findBatchItem(chanStart, nitems, ch0);
+    for (int q = 0; q < kChanPerWarp; ++q) {
+    const long long ch = ch0 + q;
+    if (ch >= nchan) break;
+    k = nextItem(chanStart, nitems, k, ch);
     const SparseItem& it = items[k];
     const long long c = ch - chanStart[k];
     const unsigned int sv4 = it.sparseByte * 0x01010101u;
@@ -489,6 +505,8 @@ __global__ void __launch_bounds__(256) sparseScatterBatchKernel(const SparseItem
         const long long tailAt = outPos + ((cap > outPos ? cap - outPos : 0) / 16) * 16;
         for (long long b = tailAt + lane; b < cap; b += 32) it.dst[swizzleAddr(b, it.swizzleKey)] = 0;
     }
+    __syncwarp();  // the staging line is reused by the next channel
+    }
 }
 
 __global__ void gatherWordsKernel(const long long* const* __restrict__ ptrs, long long* __restrict__ out, int n) {
@@ -527,7 +545,7 @@ void runSparseItems(Context* ctx, const std::vector<SparseItem>& items) {
         start.push_back(nchan);
         nchan += it.oc;
     }
-    const long long ctas = (nchan + 7) / 8;
+    const long long ctas = (nchan + 8 * kChanPerWarp - 1) / (8 * kChanPerWarp);
     if (ctas <= 0 || ctas > 0x7FFFFFFFLL) throw NotBuilt("sparsify batch too large for one launch");
     appendCoarseIndex(start, nchan);
     const SparseItem* d = uploadItems(ctx, items);

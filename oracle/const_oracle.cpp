@@ -915,7 +915,8 @@ static Type inferOutputType(const Xform& x, const Type& in) {
     }
     case B200C_X_RESCALE:  // CA/rescale.cpp:55-57
     case B200C_X_ADD:      // CA/add.cpp:52-54
-    case B200C_X_REVERSE:  // CA/reverse.cpp:50-52
+    case B200C_X_REVERSE:                 // CA/reverse.cpp:50-52
+    case B200C_X_RELOCATE_WEIGHTS_TABLE:  // CA/relocate_weights_table.cpp:114-116
         return in;
     case B200C_X_REORDER: {  // CA/reorder.cpp:67-73
         if (static_cast<int>(x.a.size()) != in.rank()) throwf("DimsOrder doesn't match type");
@@ -1312,6 +1313,69 @@ static Content xExpandDilated(const Xform& x, Content& in) {
     return out;
 }
 
+// ---- RelocateWeightsTable (CA/relocate_weights_table.cpp:122-203) ----
+static int32_t checkedI32(int64_t v) {
+    if (v < INT32_MIN || v > INT32_MAX) throwf("Can not safely cast");
+    return static_cast<int32_t>(v);
+}
+
+static Content xRelocateWeightsTable(const Xform& x, Content& in) {
+    const int64_t perOC = 4;  // WEIGHT_TABLE_NUM_ELEMENTS_PER_OC
+    const Type outType = inferOutputType(x, in.type);
+    Content out = allocTemp(outType, B200C_SI32, false);
+    int32_t* patched = reinterpret_cast<int32_t*>(out.raw());
+    const auto values = getValues<int32_t>(in);
+    const int32_t sparsityPtr = static_cast<int32_t>(x.i0);
+    const std::vector<int64_t>& offsets = x.a;
+    int32_t weightPtrStep = 0, sparsityPtrStep = 0;
+    if (values.count >= perOC * 2) {
+        weightPtrStep = values[perOC] - values[0];
+        sparsityPtrStep = values[perOC + 1] - values[1];
+    }
+    const int64_t OC = values.count / perOC;
+    const int64_t numClusters = static_cast<int64_t>(offsets.size());
+    bool segmented = false;
+    for (size_t k = 1; k < offsets.size(); ++k) segmented = segmented || offsets[k] != offsets[k - 1];
+    auto isNewCluster = [&](int64_t oc, int64_t cur) {
+        return segmented && (cur + 1) < numClusters && oc >= offsets[static_cast<size_t>(cur + 1)];
+    };
+    std::vector<int64_t> steps(static_cast<size_t>(OC));
+    if (x.hasAux) {
+        if (static_cast<int64_t>(x.aux.size()) != OC) {
+            throwf("Invalid weights compression with %zu elements for %lld channels", x.aux.size(), (long long)OC);
+        }
+        if (x.i1 == 0) throwf("Missing weights element type attribute");
+        const int64_t alignment = x.f > 0 ? static_cast<int64_t>(x.f) : 16;
+        int64_t off = 0;
+        for (int64_t oc = 0, c = 0; oc < OC; ++oc) {
+            if (isNewCluster(oc, c)) {
+                ++c;
+                off = 0;
+            }
+            steps[static_cast<size_t>(oc)] = off;
+            const int64_t bytes = (x.aux[static_cast<size_t>(oc)] * x.i1 + 7) / 8;
+            off += (bytes + alignment - 1) / alignment * alignment;
+        }
+    } else {
+        for (int64_t oc = 0, c = 0; oc < OC; ++oc) {
+            if (isNewCluster(oc, c)) ++c;
+            steps[static_cast<size_t>(oc)] = static_cast<int64_t>(weightPtrStep) * (oc - offsets[static_cast<size_t>(c)]);
+        }
+    }
+    for (int64_t oc = 0, c = 0; oc < OC; ++oc) {
+        if (isNewCluster(oc, c)) ++c;
+        const int64_t at = oc * perOC;
+        patched[at] = checkedI32(x.b[static_cast<size_t>(c)] + steps[static_cast<size_t>(oc)]);
+        patched[at + 1] = values[at + 1];
+        if (values[at + 1] != 0xFFFFFF) {  // SPARSITY_PTR_WHEN_NO_SPARSITY
+            patched[at + 1] = checkedI32(sparsityPtr + (oc - offsets[static_cast<size_t>(c)]) * static_cast<int64_t>(sparsityPtrStep));
+        }
+        patched[at + 2] = values[at + 2];
+        patched[at + 3] = values[at + 3];
+    }
+    return out;
+}
+
 // ---- BitPack (CA/bit_pack.cpp:108-130) ----
 static Content xBitPack(const Xform& x, Content& in) {
     if (in.splat) throwf("Bit pack does not support splat inputs.");
@@ -1617,6 +1681,8 @@ static Content applyTransform(const Xform& x, Content& in) {
         return xReverse(x, in);
     case B200C_X_EXPAND_DILATED:
         return xExpandDilated(x, in);
+    case B200C_X_RELOCATE_WEIGHTS_TABLE:
+        return xRelocateWeightsTable(x, in);
     case B200C_X_BIT_PACK:
         return xBitPack(x, in);
     case B200C_X_GET_SPARSITY_MAP:

@@ -490,3 +490,29 @@ def test_expand_dilated_quantised_fill(gpu, oracle):
     cg, co = both(build, gpu, oracle)
     assert_same(cg, co)
     assert cg.copyTo().reshape(2, 3, 5, 5)[0, 0, 1, 1] == 128  # the gaps hold the zero point
+
+
+# ------------------------------------------------------------------ RelocateWeightsTable
+@pytest.mark.parametrize("offsets,ptrs", [((0, 0), (1000, 1000)), ((0, 16, 32), (4096, 8192, 12288)), ((0, 8, 8, 40), (64, 128, 192, 256))])
+@pytest.mark.parametrize("compressed", [False, True])
+def test_relocate_weights_table(gpu, oracle, offsets, ptrs, compressed):
+    rng = np.random.default_rng(41)
+    OC = 48
+    table = np.zeros((OC, 1, 1, 4), np.int32)
+    table[:, 0, 0, 0] = 512 + 144 * np.arange(OC)      # weights pointers, constant step
+    table[:, 0, 0, 1] = 7000 + 32 * np.arange(OC)      # sparsity pointers
+    table[::5, 0, 0, 1] = 0xFFFFFF                      # channels without a sparsity map keep the marker
+    table[:, 0, 0, 2:] = rng.integers(-1000, 1000, (OC, 2))
+    table[5, 0, 0, 1] = 7000 + 32                       # keep entries 0 and 1 regular: they define the steps
+    table[0, 0, 0, 1] = 7000
+    num = [int(v) for v in rng.integers(1, 300, OC)] if compressed else None
+
+    def build(backend):
+        a = ContentAttr.get(table, NDType(table.shape, A.SI32), backend=backend)
+        return a.relocateWeightsTablePointers(ptrs, 90000, offsets, 8 if compressed else 0, num, 0)
+
+    cg, co = both(build, gpu, oracle)
+    assert_same(cg, co)
+    got = cg.getValues().reshape(OC, 4)
+    assert np.array_equal(got[:, 2:], table[:, 0, 0, 2:])
+    assert got[0, 0] == ptrs[0] and (got[10::5, 1] == 0xFFFFFF).all()
