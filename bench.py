@@ -14,11 +14,13 @@ Prints ONE JSON line (rank 0).
 """
 import argparse
 import ctypes as C
+import gc
 import json
 import os
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -27,7 +29,7 @@ sys.path.insert(0, ROOT)
 import numpy as np  # noqa: E402
 
 from npu_plugin_b200 import _cabi as A  # noqa: E402
-from npu_plugin_b200.blob import ConstantDecl, ShardFolder, gather_aware_weights, partition  # noqa: E402
+from npu_plugin_b200.blob import ConstantDecl, PeerWindow, ShardFolder, gather_aware_weights, partition  # noqa: E402
 from npu_plugin_b200.const import (DimsOrder, NDType, Transform, UniformQuantizedPerAxisType,  # noqa: E402
                                    UniformQuantizedType)
 
@@ -223,7 +225,7 @@ def host_data(d, rng):
 
 
 def cpu_sample_decls(decls, budget_elems):
-    """A bounded sample of the workload for the host: whole tensors, in model order, up to the budget."""
+    """A bounded sample of the workload for the host: whole tensors, in model order, up to the element limit."""
     out, total = [], 0
     for d in decls:
         if not d.transforms:
@@ -289,8 +291,10 @@ def main():
     ap.add_argument("--instances", type=int, default=None, help="independent instances per step for cfg1..cfg4")
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--gather", default="pull", choices=["pull", "nccl"],
+                    help="multi-rank exchange: rank 0 pulls peers' slots through CUDA IPC with device copies, or NCCL send/recv")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--cpu-budget", type=int, default=220_000_000, help="elements of the CPU sample")
+    ap.add_argument("--cpu-sample-elements", type=int, default=220_000_000, help="elements of the CPU sample")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -300,7 +304,7 @@ def main():
         decls = llama7b_decls(layers=args.layers)
         workload = f"llama7b-shape fold: {len([d for d in decls if d.transforms])} linear f16 weights -> sym int8 per-channel " \
                    f"-> Reorder -> Swizzle(5) -> block codec; {len(decls)} constants, layers={args.layers}"
-        config = {"workload": workload, "sharding": "by tensor (LPT; rank 0's share balances its compute against its ingress)", "l2": "per-step working set (>26 GB at N=1) exceeds L2",
+        config = {"workload": workload, "sharding": "by tensor (LPT; rank 0's share balances its compute against its ingress)", "gather": args.gather, "l2": "per-step working set (>26 GB at N=1) exceeds L2",
                   "layers": args.layers}
         dtype_name = "f16->i8"
     else:
@@ -319,7 +323,7 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return
-        gbs, ms, cores, desc = run_cpu(decls, max(1, args.steps), max(0, args.warmup), args.cpu_budget)
+        gbs, ms, cores, desc = run_cpu(decls, max(1, args.steps), max(0, args.warmup), args.cpu_sample_elements)
         line = {"impl": "reference", "metric": "folded_weight_GBps", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": dtype_name, "data": "synthetic", "config": config,
@@ -356,10 +360,13 @@ def main():
 
     # Every other rank's slots must enter rank 0 through its NVLink ingress, so rank 0 takes the larger
     # share of the constants: its compute time for that share balances the ingress time of the rest
-    # (rates: 4 TB/s of algorithmic bytes for rank 0's kernels while it receives, 750 GB/s for the link; input bytes x 2 and
+    # (rates: 4-5 TB/s of algorithmic bytes for rank 0's kernels while it receives, 750 GB/s for the link; input bytes x 2 and
     # x 0.5 approximate algorithmic and blob bytes of a constant before anything has run).
     total_in = sum(d.nbytes for d in decls)
-    weights = gather_aware_weights(world, compute_seconds=2.0 * total_in / 4.0e12, transfer_seconds=0.5 * total_in / 0.75e12)
+    # rank 0's kernels keep their pace while copy engines bring the peers' slots in; NCCL's receive
+    # kernels take SMs and memory bandwidth from them
+    rate = 5.0e12 if args.gather == "pull" else 4.0e12
+    weights = gather_aware_weights(world, compute_seconds=2.0 * total_in / rate, transfer_seconds=0.5 * total_in / 0.75e12)
     owner = partition(decls, world, weights)
     mine = [d for d, o in zip(decls, owner) if o == rank]
     folder = ShardFolder(backend, mine)  # whole-shard layout (sizes, bounds); also the N=1 path
@@ -380,11 +387,13 @@ def main():
     # With several ranks the shard is cut into chunks: while chunk c+1 is folded and compressed, chunk
     # c's segments already travel to rank 0 (NCCL send/recv over NVLink), so the gather hides behind
     # the compute as far as rank 0's ingress bandwidth allows.
-    nchunks = 1 if world == 1 else 4
-    per_chunk = (sum(d.nbytes for d in mine) + nchunks - 1) // nchunks if mine else 1
+    nchunks = 1 if world == 1 else 8
+    # rank 0's slots are produced where they stay, so in pull mode it has nothing to pipeline: one chunk
+    my_chunks = 1 if (rank == 0 and args.gather == "pull") else nchunks
+    per_chunk = (sum(d.nbytes for d in mine) + my_chunks - 1) // my_chunks if mine else 1
     chunks, cur, cur_bytes = [], [], 0
     for i, d in enumerate(mine):
-        if cur and cur_bytes + d.nbytes > per_chunk and len(chunks) < nchunks - 1:
+        if cur and cur_bytes + d.nbytes > per_chunk and len(chunks) < my_chunks - 1:
             chunks.append(cur)
             cur, cur_bytes = [], 0
         cur.append(i)
@@ -415,6 +424,8 @@ def main():
             for r in range(world):
                 place[k][r] = at
                 at += int(all_sizes[r][k])
+        # where chunk k starts inside rank r's own buffer (the running sum of its chunk sizes)
+        peer_off = [[int(sum(int(all_sizes[r][j]) for j in range(k))) for k in range(nchunks)] for r in range(world)]
         if rank == 0:
             gathered = torch.empty(at + 1024, dtype=torch.uint8, device="cuda")
             folded = gathered
@@ -427,7 +438,36 @@ def main():
         my_table = torch.zeros((len(mine), 4), dtype=torch.int64, device="cuda")
     if gathered is None:
         folded = torch.empty(max(fo, 1), dtype=torch.uint8, device="cuda")
-
+    peers, copy_stream, gather_mode = None, None, "none"
+    release = torch.zeros(1, dtype=torch.int64)
+    if world > 1:
+        # Pull mode: every peer exports its blob buffer; rank 0 maps them and copies ready chunks with
+        # device-to-device copies on a stream of its own.  Readiness and release travel on the host (gloo).
+        gather_mode = args.gather
+        if gather_mode == "pull":
+            ok = torch.ones(1, dtype=torch.int64)
+            desc = None
+            if rank:
+                try:
+                    desc = PeerWindow.export(folded)
+                except Exception as e:
+                    sys.stderr.write(f"[bench] rank {rank}: cannot export its buffer ({e})\n")
+            descs = [None] * world
+            dist.gather_object(desc, descs if rank == 0 else None, dst=0, group=pg_sizes)
+            if rank == 0:
+                try:
+                    peers = [None] + [PeerWindow.open(d) for d in descs[1:]]
+                    copy_stream = torch.cuda.Stream()
+                    probe = torch.empty(16, dtype=torch.uint8, device="cuda")
+                    for r in range(1, world):
+                        probe.copy_(peers[r][:16])
+                    torch.cuda.synchronize()
+                except Exception as e:  # no peer mapping on this machine: NCCL send/recv instead
+                    sys.stderr.write(f"[bench] peer windows unavailable ({e}); using NCCL send/recv\n")
+                    ok[0] = 0
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=pg_sizes)
+            if int(ok.item()) == 0:
+                gather_mode, peers = "nccl", None
     seg_info = {}
 
     def step(timers=None):
@@ -435,15 +475,35 @@ def main():
         if timers:
             timers[0].record(stream)
         segs_all, used_total, pending, at = [], 0, [], 0
+        puller = None
         if world > 1 and rank == 0:
-            # every receive is posted before rank 0 starts its own work, chunk by chunk and peer by peer
-            # (the order in which the peers send)
-            for k in range(nchunks):
-                for r in range(1, world):
-                    n = int(all_sizes[r][k])
-                    if n:
-                        pending.append(dist.irecv(gathered[place[k][r]:place[k][r] + n], src=r))
             at = place[nchunks - 1][world - 1] + int(all_sizes[world - 1][nchunks - 1])
+            if gather_mode == "pull":
+                # a host thread waits for the peers' "chunk k is ready" notes (in the order they are sent)
+                # and queues the copies on the copy stream while this thread folds rank 0's own chunks
+                notes = [(k, r, torch.zeros(1, dtype=torch.int64)) for k in range(nchunks) for r in range(1, world)
+                         if int(all_sizes[r][k])]
+                reqs = [dist.irecv(t, src=r, group=pg_sizes) for k, r, t in notes]
+
+                def pull():
+                    torch.cuda.set_device(local_rank)
+                    for (k, r, _), q in zip(notes, reqs):
+                        q.wait()
+                        n = int(all_sizes[r][k])
+                        with torch.cuda.stream(copy_stream):
+                            gathered[place[k][r]:place[k][r] + n].copy_(peers[r][peer_off[r][k]:peer_off[r][k] + n], non_blocking=True)
+
+                copy_stream.wait_stream(stream)
+                puller = threading.Thread(target=pull)
+                puller.start()
+            else:
+                # every receive is posted before rank 0 starts its own work, chunk by chunk and peer by peer
+                # (the order in which the peers send)
+                for k in range(nchunks):
+                    for r in range(1, world):
+                        n = int(all_sizes[r][k])
+                        if n:
+                            pending.append(dist.irecv(gathered[place[k][r]:place[k][r] + n], src=r))
         for k, f in enumerate(cf):
             used = 0
             if f is not None:
@@ -462,7 +522,29 @@ def main():
                 segs_all += [(c[i], fold_off[k] + o, sz, comp) for i, o, sz, comp in segs]
             used_total += used
             if world > 1 and rank != 0 and used:
-                pending.append(dist.isend(folded[fold_off[k]:fold_off[k] + used], dst=0))
+                if gather_mode == "pull":  # compress_inplace has synchronised: the chunk is complete
+                    dist.send(torch.tensor([k], dtype=torch.int64), dst=0, group=pg_sizes)
+                else:
+                    pending.append(dist.isend(folded[fold_off[k]:fold_off[k] + used], dst=0))
+        if world > 1 and gather_mode == "pull":
+            # segment tables and the release of the peers' buffers travel on the host
+            if rank == 0:
+                puller.join()
+                stream.wait_stream(copy_stream)
+                if timers:
+                    timers[1].record(stream)
+                copy_stream.synchronize()
+                tabs = [None] * world
+                dist.gather_object(None, tabs, dst=0, group=pg_sizes)
+                seg_info["tables"] = tabs
+            else:
+                if timers:
+                    timers[1].record(stream)
+                dist.gather_object(segs_all, None, dst=0, group=pg_sizes)
+            # the peers may overwrite their buffers only after rank 0 has copied them
+            dist.broadcast(release, src=0, group=pg_sizes)
+            seg_info["segs"], seg_info["used"], seg_info["gathered"] = segs_all, used_total, at
+            return
         if world > 1 and len(mine):
             if rank == 0:
                 pending += [dist.irecv(tables[r], src=r) for r in range(1, world) if tables[r].numel()]
@@ -482,6 +564,10 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
+    # The workload description holds millions of Python objects (per-channel scale lists); a cyclic
+    # garbage collection walking them would stall the host in the middle of a step.
+    gc.collect()
+    gc.freeze()
     sampler = ClockSampler(local_rank)
     sampler.start()  # sampled from the warm-up on: the timed region can be shorter than nvidia-smi's start-up
     for _ in range(max(args.warmup, 0)):
@@ -628,7 +714,7 @@ def main():
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        gbs, ms, cores, desc = run_cpu(decls, 1, 0, args.cpu_budget)
+        gbs, ms, cores, desc = run_cpu(decls, 1, 0, args.cpu_sample_elements)
         cpu = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": desc, "ms_per_sample": ms}
 
     if rank == 0:

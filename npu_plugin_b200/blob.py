@@ -181,6 +181,26 @@ class ShardFolder:
         return [(i, self.folded_offsets[i], size[i], flag[i]) for i in range(len(self.decls))]
 
 
+class PeerWindow:
+    """Another rank's blob buffer mapped into this process through CUDA IPC, so that rank 0 can pull
+    slots with plain device-to-device copies (the copy engines move them over NVLink; no kernel runs on
+    either GPU, unlike a send/recv pair whose copy loops compete with the fold kernels for SMs)."""
+
+    @staticmethod
+    def export(tensor):
+        """A picklable description of a 1-D uint8 CUDA tensor's memory (sent to the pulling rank)."""
+        return tuple(tensor.untyped_storage()._share_cuda_()) + (int(tensor.storage_offset()), int(tensor.numel()))
+
+    @staticmethod
+    def open(desc):
+        """The exporting rank's tensor as seen from this process (lives on the exporter's device)."""
+        import torch
+        *share, offset, numel = desc
+        storage = torch.UntypedStorage._new_shared_cuda(*share)
+        whole = torch.empty(0, dtype=torch.uint8, device=storage.device).set_(storage)
+        return whole[offset:offset + numel]
+
+
 def gather_segments(dist, blob, used, rank, world, gathered=None):
     """The one exchange of the multi-GPU fold: every rank's blob prefix (`used` bytes of the 1-D uint8
     tensor `blob`) is appended on rank 0 in rank order.  Sizes travel with an all_gather, the bytes with

@@ -60,6 +60,61 @@ void copyH2D(Context* ctx, void* dst, const void* src, size_t n) {
     }
     B2_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, ctx->stream));
 }
+void uploadSmall(Context* ctx, void* dst, const void* src, size_t n) {
+    if (n == 0) return;
+    if (B2_EMU(ctx)) {
+        std::memcpy(dst, src, n);
+        return;
+    }
+    const size_t need = (n + 63) / 64 * 64;
+    Context::StageChunk* c = nullptr;
+    for (auto& k : ctx->stage) {
+        if (k.used + need <= k.size) {
+            c = &k;
+            break;
+        }
+    }
+    if (!c) {
+        Context::StageChunk nk;
+        nk.size = std::max<size_t>(need, 4ull << 20);
+        nk.used = 0;
+        void* p = nullptr;
+        const cudaError_t e = cudaHostAlloc(&p, nk.size, cudaHostAllocDefault);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            throw NoMem(std::string("cudaHostAlloc of staging memory failed: ") + cudaGetErrorString(e));
+        }
+        nk.ptr = static_cast<char*>(p);
+        ctx->stage.push_back(nk);
+        c = &ctx->stage.back();
+    }
+    char* at = c->ptr + c->used;
+    c->used += need;
+    std::memcpy(at, src, n);
+    B2_CUDA(cudaMemcpyAsync(dst, at, n, cudaMemcpyHostToDevice, ctx->stream));
+    if (!ctx->stageDone) B2_CUDA(cudaEventCreateWithFlags(&ctx->stageDone, cudaEventDisableTiming));
+    B2_CUDA(cudaEventRecord(ctx->stageDone, ctx->stream));
+    ctx->stagePending = true;
+}
+
+// Start of a call: the staging chunks may be refilled once the uploads of the previous call are done.
+void resetStage(Context* ctx) {
+    if (ctx->stagePending) {
+        B2_CUDA(cudaEventSynchronize(ctx->stageDone));
+        ctx->stagePending = false;
+    }
+    for (auto& k : ctx->stage) k.used = 0;
+}
+
+void releaseStage(Context* ctx) {
+    if (ctx->stagePending) cudaEventSynchronize(ctx->stageDone);
+    ctx->stagePending = false;
+    for (auto& k : ctx->stage) cudaFreeHost(k.ptr);
+    ctx->stage.clear();
+    if (ctx->stageDone) cudaEventDestroy(ctx->stageDone);
+    ctx->stageDone = nullptr;
+}
+
 void copyD2H(Context* ctx, void* dst, const void* src, size_t n) {
     if (n == 0) return;
     if (B2_EMU(ctx)) {
@@ -299,6 +354,7 @@ static void destroyPool(Context* ctx) {
     ctx->pool = nullptr;
     for (Context* w : ctx->workers) {
         w->arena.releaseAll();
+        releaseStage(w);
         delete w;
     }
     ctx->workers.clear();
@@ -313,6 +369,7 @@ struct CallScope {
             if (e != cudaSuccess) throw CudaFail(std::string("cudaSetDevice: ") + cudaGetErrorString(e));
         }
         ctx->arena.reset();
+        resetStage(ctx);
     }
 };
 
@@ -382,6 +439,7 @@ void b200c_destroy(b200c_ctx* h) {
         if (ctx->errHost) cudaFreeHost(ctx->errHost);
     }
     destroyPool(ctx);
+    if (!B2_EMU(ctx)) releaseStage(ctx);
     ctx->arena.releaseAll();  // frees the blocks while the device is still current
     if (!B2_EMU(ctx) && ctx->ownStream) cudaStreamDestroy(ctx->ownStream);
     delete ctx;
@@ -570,7 +628,10 @@ int b200c_fold_batch(b200c_ctx* h, b200c_fold_item* items, int count, int data_o
                     w->stream = ctx->stream;
                     w->batching = true;
                     w->launches = 0;
-                    if (first == 0) w->arena.reset();
+                    if (first == 0) {
+                        w->arena.reset();
+                        resetStage(w);
+                    }
                 }
                 ctx->pool->run([&](int id) {
                     Context* w = ctx->workers[id];

@@ -567,8 +567,8 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
     unsigned int* tileSums = static_cast<unsigned int*>(ctx->arena.alloc(sizeof(unsigned int) * (ntiles + 1)));
     unsigned long long* tileOffsets =
             static_cast<unsigned long long*>(ctx->arena.alloc(sizeof(unsigned long long) * (ntiles + 1)));
-    copyH2D(ctx, jobsDev, jobs.data(), sizeof(CodecJobDev) * count);
-    copyH2D(ctx, tileJobDev, tileJob.data(), sizeof(unsigned int) * ntiles);
+    uploadSmall(ctx, jobsDev, jobs.data(), sizeof(CodecJobDev) * count);
+    uploadSmall(ctx, tileJobDev, tileJob.data(), sizeof(unsigned int) * ntiles);
 
 #ifdef B200C_HOST_EMULATION
     if (B2_EMU(ctx)) {
@@ -672,7 +672,7 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
         }
         if (!emitTiles.empty()) {
             unsigned int* emitDev = static_cast<unsigned int*>(ctx->arena.alloc(sizeof(unsigned int) * emitTiles.size()));
-            copyH2D(ctx, emitDev, emitTiles.data(), sizeof(unsigned int) * emitTiles.size());
+            uploadSmall(ctx, emitDev, emitTiles.data(), sizeof(unsigned int) * emitTiles.size());
             const int egrid = static_cast<int>(std::min<unsigned long long>(emitTiles.size(), ctx->smCount * 4ULL));
             codecEmitKernel<<<egrid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, emitDev, emitTiles.size(), summary,
                                                             tileOffsets, outDev);
@@ -683,7 +683,7 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
                 B2_CUDA(cudaGetLastError());
                 ++ctx->launches;
             }
-            syncStream(ctx);  // emitTiles (pageable) must stay alive until the copy is done
+            syncStream(ctx);  // the call hands finished buffers back
         }
     }
     for (int j = 0; j < count; ++j) {

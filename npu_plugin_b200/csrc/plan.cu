@@ -119,9 +119,7 @@ int Planner::curTag() const {
 
 void* Planner::uploadTable(const void* host, size_t bytes) {
     void* d = _ctx->arena.alloc(bytes);
-    // the staging copy must outlive the async copy: keep it until the plan dies
-    _staging.emplace_back(static_cast<const char*>(host), static_cast<const char*>(host) + bytes);
-    copyH2D(_ctx, d, _staging.back().data(), bytes);
+    uploadSmall(_ctx, d, host, bytes);
     return d;
 }
 

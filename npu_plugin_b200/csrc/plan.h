@@ -93,7 +93,6 @@ private:
 
     Context* _ctx;
     ContentState _s;
-    std::vector<std::vector<char>> _staging;
     std::vector<SideOutput> _sides;
     bool _afterBitPack = false;
     bool _sideOnDevice = false;

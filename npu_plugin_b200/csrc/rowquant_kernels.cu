@@ -414,7 +414,7 @@ __global__ void __launch_bounds__(256) rowQuantRegBatchKernel(const RowQuantPara
     rowQuantRegBody<T, TPR, MAXU, SCHEME>(p, b - groupStart[lo], redMx, redMn, redAm, redOdd);
 }
 
-// ---- shared-memory staged rows: any length up to the shared-memory budget, optional permutation ---
+// ---- shared-memory staged rows: any length up to the shared-memory capacity, optional permutation ---
 template <typename T, int TPR, int SCHEME>
 __device__ __forceinline__ void rowQuantSmemBody(const RowQuantParams& p, long long g, unsigned char* smemRaw, float* redMx,
                                                  float* redMn, float* redAm, float* redOdd) {
@@ -769,8 +769,8 @@ void flushRowQuantBatch(Context* ctx) {
             itemsDev = static_cast<RowQuantParams*>(ctx->arena.alloc(sizeof(RowQuantParams) * group.size()));
             appendCoarseIndex(start, total);
             startDev = static_cast<long long*>(ctx->arena.alloc(sizeof(long long) * start.size()));
-            copyH2D(ctx, itemsDev, group.data(), sizeof(RowQuantParams) * group.size());
-            copyH2D(ctx, startDev, start.data(), sizeof(long long) * start.size());
+            uploadSmall(ctx, itemsDev, group.data(), sizeof(RowQuantParams) * group.size());
+            uploadSmall(ctx, startDev, start.data(), sizeof(long long) * start.size());
         }
         if (c.maxu > 0) {
             launchRegConfig(ctx, c, one ? &group[0] : nullptr, itemsDev, startDev, static_cast<int>(group.size()), total);

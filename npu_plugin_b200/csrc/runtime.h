@@ -142,6 +142,15 @@ struct Context {
     // (same stream and error word, own scratch arena and launch queues)
     PlanPool* pool = nullptr;
     std::vector<Context*> workers;
+    // pinned staging for the library's own small uploads (tables, launch parameter arrays): chunks are
+    // filled front to back during a call and reused by the next call once `stageDone` has passed
+    struct StageChunk {
+        char* ptr;
+        size_t size, used;
+    };
+    std::vector<StageChunk> stage;
+    cudaEvent_t stageDone = nullptr;
+    bool stagePending = false;
 };
 
 
@@ -179,6 +188,11 @@ __device__ __forceinline__ int findBatchItem(const long long* __restrict__ start
 void* devMalloc(Context* ctx, size_t bytes);
 void devFree(Context* ctx, void* p);
 void copyH2D(Context* ctx, void* dst, const void* src, size_t n);
+// host -> device copy of internal data through pinned staging: returns at once, never waits for the
+// stream (a copy from pageable memory may); `src` can be freed on return
+void uploadSmall(Context* ctx, void* dst, const void* src, size_t n);
+void resetStage(Context* ctx);
+void releaseStage(Context* ctx);
 void copyD2H(Context* ctx, void* dst, const void* src, size_t n);
 void copyD2D(Context* ctx, void* dst, const void* src, size_t n);
 void fillBytes(Context* ctx, void* dst, int value, size_t n);

@@ -517,7 +517,7 @@ __global__ void gatherWordsKernel(const long long* const* __restrict__ ptrs, lon
 template <typename T>
 T* uploadItems(Context* ctx, const std::vector<T>& v) {
     T* d = static_cast<T*>(ctx->arena.alloc(sizeof(T) * v.size()));
-    copyH2D(ctx, d, v.data(), sizeof(T) * v.size());
+    uploadSmall(ctx, d, v.data(), sizeof(T) * v.size());
     return d;
 }
 

@@ -477,8 +477,8 @@ void flushTileBatch(Context* ctx) {
             TileItem* itemsDev = static_cast<TileItem*>(ctx->arena.alloc(sizeof(TileItem) * n));
             appendCoarseIndex(start, total);
             long long* startDev = static_cast<long long*>(ctx->arena.alloc(sizeof(long long) * start.size()));
-            copyH2D(ctx, itemsDev, pending.data() + first, sizeof(TileItem) * n);
-            copyH2D(ctx, startDev, start.data(), sizeof(long long) * start.size());
+            uploadSmall(ctx, itemsDev, pending.data() + first, sizeof(TileItem) * n);
+            uploadSmall(ctx, startDev, start.data(), sizeof(long long) * start.size());
             foldTileBatchKernel<<<static_cast<unsigned int>(total), kTileThreads, 0, ctx->stream>>>(itemsDev, startDev, n);
             B2_CUDA(cudaGetLastError());
             ++ctx->launches;
