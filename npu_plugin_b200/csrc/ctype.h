@@ -12,6 +12,8 @@
 #include <stdexcept>
 #include <string>
 #include <vector>
+#include <utility>
+#include <initializer_list>
 
 namespace b200c {
 
@@ -78,6 +80,96 @@ inline int64_t roundUp(int64_t v, int64_t a) {
     return (v + a - 1) / a * a;
 }
 
+// Fixed-capacity vector for shapes, orders and transformation arguments (at most B200C_MAX_RANK
+// entries): same interface as the part of std::vector used here, no heap allocation.
+template <class T>
+class SmallVec {
+public:
+    SmallVec() = default;
+    SmallVec(std::initializer_list<T> l) {
+        assign(l.begin(), l.end());
+    }
+    explicit SmallVec(size_t n, T val = T()) {
+        assign(n, val);
+    }
+    template <class It, class = decltype(*std::declval<It>())>
+    SmallVec(It a, It b) {
+        assign(a, b);
+    }
+    SmallVec(const std::vector<T>& v) {
+        assign(v.begin(), v.end());
+    }
+    operator std::vector<T>() const {
+        return std::vector<T>(begin(), end());
+    }
+    size_t size() const {
+        return static_cast<size_t>(_n);
+    }
+    bool empty() const {
+        return _n == 0;
+    }
+    T& operator[](size_t i) {
+        return _v[i];
+    }
+    const T& operator[](size_t i) const {
+        return _v[i];
+    }
+    T* begin() {
+        return _v;
+    }
+    T* end() {
+        return _v + _n;
+    }
+    const T* begin() const {
+        return _v;
+    }
+    const T* end() const {
+        return _v + _n;
+    }
+    const T* data() const {
+        return _v;
+    }
+    T& back() {
+        return _v[_n - 1];
+    }
+    void clear() {
+        _n = 0;
+    }
+    void push_back(const T& x) {
+        if (_n >= kCap) throw BadArg("more than B200C_MAX_RANK entries");
+        _v[_n++] = x;
+    }
+    void resize(size_t n, T val = T()) {
+        if (n > static_cast<size_t>(kCap)) throw BadArg("more than B200C_MAX_RANK entries");
+        for (size_t i = static_cast<size_t>(_n); i < n; ++i) _v[i] = val;
+        _n = static_cast<int>(n);
+    }
+    void assign(size_t n, T val) {
+        _n = 0;
+        resize(n, val);
+    }
+    template <class It, class = decltype(*std::declval<It>())>
+    void assign(It a, It b) {
+        _n = 0;
+        for (; a != b; ++a) push_back(static_cast<T>(*a));
+    }
+    bool operator==(const SmallVec& o) const {
+        if (_n != o._n) return false;
+        for (int i = 0; i < _n; ++i)
+            if (!(_v[i] == o._v[i])) return false;
+        return true;
+    }
+    bool operator!=(const SmallVec& o) const {
+        return !(*this == o);
+    }
+
+private:
+    static constexpr int kCap = B200C_MAX_RANK;
+    T _v[kCap] = {};
+    int _n = 0;
+};
+using Dims = SmallVec<int64_t>;
+
 // Quantisation parameters.  The scale / zero-point arrays are views: they either borrow the
 // caller's descriptor arrays (valid for the duration of one C ABI call) or point into storage
 // owned through the shared pointers, so copying a type never copies the tables.
@@ -108,8 +200,8 @@ struct QuantInfo {
 
 struct TensorType {
     int dtype = 0;  // for quantised types: the normalised storage integer
-    std::vector<int64_t> shape;
-    std::vector<int> order;  // order[k] = logical dim at memory position k, outermost first
+    Dims shape;
+    SmallVec<int> order;  // order[k] = logical dim at memory position k, outermost first
     QuantInfo q;
 
     int rank() const {
@@ -135,12 +227,12 @@ struct TensorType {
         order.resize(shape.size());
         for (size_t k = 0; k < shape.size(); ++k) order[k] = static_cast<int>(k);
     }
-    std::vector<int64_t> memOrder(const std::vector<int64_t>& logical) const {
-        std::vector<int64_t> m(logical.size());
+    Dims memOrder(const Dims& logical) const {
+        Dims m(logical.size());
         for (size_t k = 0; k < logical.size(); ++k) m[k] = logical[order[k]];
         return m;
     }
-    std::vector<int64_t> memShape() const {
+    Dims memShape() const {
         return memOrder(shape);
     }
     int memPosOf(int logicalDim) const {
@@ -156,7 +248,7 @@ struct TensorType {
 
 struct Transformation {
     int kind = 0;
-    std::vector<int64_t> a, b;
+    Dims a, b;
     double f = 0;
     int64_t i0 = 0, i1 = 0;
     bool hasType = false;
@@ -183,8 +275,8 @@ bool acceptsSubByteStorage(int kind);
 int insertPosition(const std::vector<int>& kinds, int newKind);
 
 // helpers the planner also needs
-TensorType withShape(const TensorType& in, const std::vector<int64_t>& shape);
-TensorType withShapeAndElem(const TensorType& in, const std::vector<int64_t>& shape, int dtype, const QuantInfo& q);
+TensorType withShape(const TensorType& in, const Dims& shape);
+TensorType withShapeAndElem(const TensorType& in, const Dims& shape, int dtype, const QuantInfo& q);
 int64_t sparsifyValue(const TensorType& t);
 
 constexpr int64_t kSwizzleSizeAlign = 512;  // SWIZZLING_SIZE_ALIGNMENT_VPUX37XX

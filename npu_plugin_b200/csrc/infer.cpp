@@ -106,7 +106,7 @@ static void checkPerAxis(const TensorType& t) {
 
 // Where a per-axis dimension lands after a reshape that only adds/removes unit dims
 // (getQuantizedAxis, src/vpux_compiler/src/utils/types.cpp:128-165).  Returns -1 when it cannot be traced.
-static int axisAfterReshape(int axis, const std::vector<int64_t>& from, const std::vector<int64_t>& to) {
+static int axisAfterReshape(int axis, const Dims& from, const Dims& to) {
     if (axis < 0 || static_cast<size_t>(axis) >= from.size()) return -1;
     size_t leadFrom = 0, leadTo = 0;
     while (leadFrom < from.size() && from[leadFrom] == 1) ++leadFrom;
@@ -122,7 +122,7 @@ static int axisAfterReshape(int axis, const std::vector<int64_t>& from, const st
 }
 
 // changeShape (type_interfaces.cpp:176-196): identity order follows the new rank, any other order must fit
-TensorType withShape(const TensorType& in, const std::vector<int64_t>& shape) {
+TensorType withShape(const TensorType& in, const Dims& shape) {
     TensorType out = in;
     out.shape = shape;
     if (in.identityOrder()) {
@@ -139,7 +139,7 @@ TensorType withShape(const TensorType& in, const std::vector<int64_t>& shape) {
 }
 
 // changeShapeElemType (type_interfaces.cpp:217-233)
-TensorType withShapeAndElem(const TensorType& in, const std::vector<int64_t>& shape, int dtype, const QuantInfo& q) {
+TensorType withShapeAndElem(const TensorType& in, const Dims& shape, int dtype, const QuantInfo& q) {
     TensorType out = in;
     out.shape = shape;
     if (in.identityOrder()) {
@@ -162,7 +162,7 @@ static TensorType withElem(const TensorType& in, int dtype, const QuantInfo& q) 
 }
 
 // pad() with expandScalesAndZP (type_interfaces.cpp:295-321, quantization.cpp:56-100)
-static TensorType padded(const TensorType& in, const std::vector<int64_t>& before, const std::vector<int64_t>& after) {
+static TensorType padded(const TensorType& in, const Dims& before, const Dims& after) {
     if (before.size() != after.size()) refThrow("Got non consistent 'padBefore' and 'padAfter' values");
     if (before.size() != in.shape.size()) refThrow("Paddings and input shape are not consistent");
     TensorType out = in;
@@ -187,7 +187,7 @@ static TensorType padded(const TensorType& in, const std::vector<int64_t>& befor
 }
 
 // extractDenseTile with tileScalesAndZP (type_interfaces.cpp:263-279, quantization.cpp:106-130)
-static TensorType tiled(const TensorType& in, const std::vector<int64_t>& offset, const std::vector<int64_t>& shape) {
+static TensorType tiled(const TensorType& in, const Dims& offset, const Dims& shape) {
     TensorType out = in;
     out.shape = shape;
     if (in.q.kind == B200C_Q_PER_AXIS) {
@@ -331,14 +331,14 @@ TensorType inferOne(const Transformation& x, const TensorType& in) {
             refThrow("Value cannot be broadcasted due to new value's size is less than old one: %lld < %lld",
                      static_cast<long long>(x.i1), static_cast<long long>(in.shape[x.i0]));
         }
-        std::vector<int64_t> none(in.rank(), 0), after(in.rank(), 0);
+        Dims none(in.rank(), 0), after(in.rank(), 0);
         after[x.i0] = x.i1 - in.shape[x.i0];
         return padded(in, none, after);
     }
 
     case B200C_X_TRANSPOSE: {  // transpose.cpp:67-86
         if (static_cast<int>(x.a.size()) != in.rank()) refThrow("DimsOrder doesn't match type");
-        std::vector<int64_t> shape(in.rank());
+        Dims shape(in.rank());
         std::vector<bool> seen(in.rank(), false);
         for (int k = 0; k < in.rank(); ++k) {
             const int64_t d = x.a[k];
@@ -360,7 +360,7 @@ TensorType inferOne(const Transformation& x, const TensorType& in) {
         if (in.rank() != 4) refThrow("Got invalid tensor rank '4'");
         if (x.a.size() < 2) throw BadArg("ExpandDilated needs two dilations");
         if (x.a[0] < 1 || x.a[1] < 1) throw BadArg("ExpandDilated: dilations must be positive");
-        std::vector<int64_t> shape = in.shape;
+        Dims shape = in.shape;
         shape[2] = in.shape[2] + (in.shape[2] - 1) * (x.a[0] - 1);
         shape[3] = in.shape[3] + (in.shape[3] - 1) * (x.a[1] - 1);
         return withShape(in, shape);

@@ -78,7 +78,7 @@ static void contiguousStrides(View& v) {
     }
 }
 
-static void setShape(View& v, const std::vector<int64_t>& memShape) {
+static void setShape(View& v, const Dims& memShape) {
     v.rank = static_cast<int>(memShape.size());
     for (int k = 0; k < v.rank; ++k) v.shape[k] = memShape[k];
 }
