@@ -292,14 +292,17 @@ def main():
     ap.add_argument("--instances", type=int, default=None, help="independent instances per step for cfg1..cfg4")
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--gather", default="pull", choices=["pull", "nccl"],
-                    help="multi-rank exchange: rank 0 pulls peers' slots through CUDA IPC with device copies, or NCCL send/recv")
+    ap.add_argument("--gather", default="auto", choices=["auto", "pull", "nccl"],
+                    help="multi-rank exchange: rank 0 pulls peers' slots through CUDA IPC with device copies, or NCCL "
+                         "send/recv; auto = NCCL for two ranks (one peer: its copy kernels cost less than they gain), pull beyond")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-sample-elements", type=int, default=220_000_000, help="elements of the CPU sample")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gather == "auto":
+        args.gather = "nccl" if world <= 2 else "pull"
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.workload == "llama7b":
         decls = llama7b_decls(layers=args.layers)
@@ -364,10 +367,11 @@ def main():
     # (rates: 4-5 TB/s of algorithmic bytes for rank 0's kernels while it receives, 750 GB/s for the link; input bytes x 2 and
     # x 0.5 approximate algorithmic and blob bytes of a constant before anything has run).
     total_in = sum(d.nbytes for d in decls)
-    # rank 0's kernels keep their pace while copy engines bring the peers' slots in; NCCL's receive
-    # kernels take SMs and memory bandwidth from them
-    rate = 5.0e12 if args.gather == "pull" else 4.0e12
-    weights = gather_aware_weights(world, compute_seconds=2.0 * total_in / rate, transfer_seconds=0.5 * total_in / 0.75e12)
+    # rank 0's kernels keep their pace while copy engines bring the peers' slots in (measured: the copies
+    # then run at about 500 GB/s, both GPUs' memory being busy); NCCL's receive kernels take SMs and
+    # memory bandwidth from the fold kernels but move the bytes faster
+    rate, link = (5.0e12, 0.5e12) if args.gather == "pull" else (4.0e12, 0.75e12)
+    weights = gather_aware_weights(world, compute_seconds=2.0 * total_in / rate, transfer_seconds=0.5 * total_in / link)
     owner = partition(decls, world, weights)
     mine = [d for d, o in zip(decls, owner) if o == rank]
     folder = ShardFolder(backend, mine)  # whole-shard layout (sizes, bounds); also the N=1 path
@@ -388,7 +392,7 @@ def main():
     # With several ranks the shard is cut into chunks: while chunk c+1 is folded and compressed, chunk
     # c's segments already travel to rank 0 (NCCL send/recv over NVLink), so the gather hides behind
     # the compute as far as rank 0's ingress bandwidth allows.
-    nchunks = 1 if world == 1 else 8
+    nchunks = 1 if world == 1 else (8 if args.gather == "pull" else 4)
     # rank 0's slots are produced where they stay, so in pull mode it has nothing to pipeline: one chunk
     my_chunks = 1 if (rank == 0 and args.gather == "pull") else nchunks
     per_chunk = (sum(d.nbytes for d in mine) + my_chunks - 1) // my_chunks if mine else 1

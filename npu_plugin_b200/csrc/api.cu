@@ -66,9 +66,10 @@ void uploadSmall(Context* ctx, void* dst, const void* src, size_t n) {
         std::memcpy(dst, src, n);
         return;
     }
+    const int set = ctx->stageSet;
     const size_t need = (n + 63) / 64 * 64;
     Context::StageChunk* c = nullptr;
-    for (auto& k : ctx->stage) {
+    for (auto& k : ctx->stage[set]) {
         if (k.used + need <= k.size) {
             c = &k;
             break;
@@ -85,34 +86,39 @@ void uploadSmall(Context* ctx, void* dst, const void* src, size_t n) {
             throw NoMem(std::string("cudaHostAlloc of staging memory failed: ") + cudaGetErrorString(e));
         }
         nk.ptr = static_cast<char*>(p);
-        ctx->stage.push_back(nk);
-        c = &ctx->stage.back();
+        ctx->stage[set].push_back(nk);
+        c = &ctx->stage[set].back();
     }
     char* at = c->ptr + c->used;
     c->used += need;
     std::memcpy(at, src, n);
     B2_CUDA(cudaMemcpyAsync(dst, at, n, cudaMemcpyHostToDevice, ctx->stream));
-    if (!ctx->stageDone) B2_CUDA(cudaEventCreateWithFlags(&ctx->stageDone, cudaEventDisableTiming));
-    B2_CUDA(cudaEventRecord(ctx->stageDone, ctx->stream));
-    ctx->stagePending = true;
+    if (!ctx->stageDone[set]) B2_CUDA(cudaEventCreateWithFlags(&ctx->stageDone[set], cudaEventDisableTiming));
+    B2_CUDA(cudaEventRecord(ctx->stageDone[set], ctx->stream));
+    ctx->stagePending[set] = true;
 }
 
-// Start of a call: the staging chunks may be refilled once the uploads of the previous call are done.
+// Start of a call: switch to the other set of staging chunks; its last user was the call before the
+// previous one.
 void resetStage(Context* ctx) {
-    if (ctx->stagePending) {
-        B2_CUDA(cudaEventSynchronize(ctx->stageDone));
-        ctx->stagePending = false;
+    const int set = ctx->stageSet ^ 1;
+    if (ctx->stagePending[set]) {
+        B2_CUDA(cudaEventSynchronize(ctx->stageDone[set]));
+        ctx->stagePending[set] = false;
     }
-    for (auto& k : ctx->stage) k.used = 0;
+    for (auto& k : ctx->stage[set]) k.used = 0;
+    ctx->stageSet = set;
 }
 
 void releaseStage(Context* ctx) {
-    if (ctx->stagePending) cudaEventSynchronize(ctx->stageDone);
-    ctx->stagePending = false;
-    for (auto& k : ctx->stage) cudaFreeHost(k.ptr);
-    ctx->stage.clear();
-    if (ctx->stageDone) cudaEventDestroy(ctx->stageDone);
-    ctx->stageDone = nullptr;
+    for (int set = 0; set < 2; ++set) {
+        if (ctx->stagePending[set]) cudaEventSynchronize(ctx->stageDone[set]);
+        ctx->stagePending[set] = false;
+        for (auto& k : ctx->stage[set]) cudaFreeHost(k.ptr);
+        ctx->stage[set].clear();
+        if (ctx->stageDone[set]) cudaEventDestroy(ctx->stageDone[set]);
+        ctx->stageDone[set] = nullptr;
+    }
 }
 
 void copyD2H(Context* ctx, void* dst, const void* src, size_t n) {
@@ -640,15 +646,19 @@ int b200c_fold_batch(b200c_ctx* h, b200c_fold_item* items, int count, int data_o
                         failedAt[id] = first;
                         return;
                     }
-                    for (;;) {
-                        const int i = next.fetch_add(1);
-                        if (i >= last) break;
-                        try {
-                            foldItem(w, i, later[id]);
-                        } catch (...) {
-                            failure[id] = std::current_exception();
-                            failedAt[id] = i;
-                            break;
+                    // runs of 16 consecutive items per grab: neighbours share cache lines of the item array
+                    for (bool stop = false; !stop;) {
+                        const int i0 = next.fetch_add(16);
+                        if (i0 >= last) break;
+                        for (int i = i0; i < std::min(i0 + 16, last); ++i) {
+                            try {
+                                foldItem(w, i, later[id]);
+                            } catch (...) {
+                                failure[id] = std::current_exception();
+                                failedAt[id] = i;
+                                stop = true;
+                                break;
+                            }
                         }
                     }
                 });

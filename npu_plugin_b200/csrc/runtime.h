@@ -142,15 +142,17 @@ struct Context {
     // (same stream and error word, own scratch arena and launch queues)
     PlanPool* pool = nullptr;
     std::vector<Context*> workers;
-    // pinned staging for the library's own small uploads (tables, launch parameter arrays): chunks are
-    // filled front to back during a call and reused by the next call once `stageDone` has passed
+    // pinned staging for the library's own small uploads (tables, launch parameter arrays): two sets of
+    // chunks used by alternate calls; a set is refilled only after the uploads of the call that used it
+    // last (two calls ago) have passed, so back-to-back asynchronous calls never wait for each other
     struct StageChunk {
         char* ptr;
         size_t size, used;
     };
-    std::vector<StageChunk> stage;
-    cudaEvent_t stageDone = nullptr;
-    bool stagePending = false;
+    std::vector<StageChunk> stage[2];
+    cudaEvent_t stageDone[2] = {nullptr, nullptr};
+    bool stagePending[2] = {false, false};
+    int stageSet = 0;
 };
 
 

@@ -448,14 +448,12 @@ __global__ void __launch_bounds__(256) sparseScatterBatchKernel(const SparseItem
     long long outPos = it.offsets[c];
     int fill = 0;
     bool overflow = false;
+    uint4 ahead = lane < nvec ? __ldg(row + lane) : make_uint4(0, 0, 0, 0);  // the next round's vector is always in flight
     for (long long base = 0; base < nvec; base += 32) {
         const long long v = base + lane;
-        uint4 x = make_uint4(0, 0, 0, 0);
-        unsigned int m = 0;
-        if (v < nvec) {
-            x = __ldg(row + v);
-            m = neMask16(x, sv4);
-        }
+        const uint4 x = ahead;
+        if (v + 32 < nvec) ahead = __ldg(row + v + 32);
+        const unsigned int m = v < nvec ? neMask16(x, sv4) : 0u;
         const int cnt = __popc(m);
         int incl = cnt;
         for (int o = 1; o < 32; o <<= 1) {
