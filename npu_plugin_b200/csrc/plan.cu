@@ -1145,8 +1145,12 @@ size_t Planner::emitCopyTo(void* dst, size_t cap, int swizzleKey, int64_t totalB
         return static_cast<size_t>(target);
     }
     if (p.totalBytes > 0 && p.outMode == OUT_RAW && isPlain(v)) {
-        // nothing to compute: a device copy, or the chunk-rotating copy when swizzled
-        if (p.swizzleKey < 0) {
+        // nothing to compute: a device copy, or the chunk-rotating copy when swizzled.  Inside a batched
+        // fold, small pass-through constants and swizzle-only chains join the one tile launch instead of
+        // paying a copy call each.
+        if (_ctx->batching && _emittingFinal && !B2_EMU(_ctx) && dataBytes <= (16ll << 20) && n > 0) {
+            runGeneric(p);
+        } else if (p.swizzleKey < 0) {
             copyD2D(_ctx, dst, v.src, static_cast<size_t>(dataBytes));
             if (p.totalBytes > dataBytes) {
                 fillBytes(_ctx, static_cast<char*>(dst) + dataBytes, 0, static_cast<size_t>(p.totalBytes - dataBytes));

@@ -436,12 +436,23 @@ __device__ __forceinline__ void rowQuantSmemBody(const RowQuantParams& p, long l
             const int nvec = L / PER;
             const uint4* src4 = reinterpret_cast<const uint4*>(src);
             uint4* sm4 = reinterpret_cast<uint4*>(rowSm);
-            for (int v = t; v < nvec; v += TPR) {
-                const uint4 xv = __ldg(src4 + v);
-                sm4[v + ((v * PER) >> p.padLog2)] = xv;  // padLog2 is 31 when the row is not padded
-                const T* e = reinterpret_cast<const T*>(&xv);
+            // four independent 128-bit loads per thread and round
+            for (int v0 = t; v0 < nvec; v0 += 4 * TPR) {
+                uint4 xv[4];
 #pragma unroll
-                for (int i = 0; i < PER; ++i) accum(s, elemToFloat<T>(e[i]));
+                for (int r = 0; r < 4; ++r) {
+                    const int v = v0 + r * TPR;
+                    if (v < nvec) xv[r] = __ldg(src4 + v);
+                }
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const int v = v0 + r * TPR;
+                    if (v >= nvec) continue;
+                    sm4[v + ((v * PER) >> p.padLog2)] = xv[r];  // padLog2 is 31 when the row is not padded
+                    const T* e = reinterpret_cast<const T*>(&xv[r]);
+#pragma unroll
+                    for (int i = 0; i < PER; ++i) accum(s, elemToFloat<T>(e[i]));
+                }
             }
         } else {
             for (int j = t; j < L; j += TPR) {

@@ -75,6 +75,9 @@ CHAINS = [
     ((6, 4), A.F16, DimsOrder.NC, [Transform(A.X_TRANSPOSE, a=(1, 0)), Transform(A.X_RESHAPE, b=(1, 4, 6, 1)),
                                    Transform(A.X_BIT_PACK, i0=4)]),
     ((1, 9, 2), A.F32, DimsOrder.CHW, [Transform(A.X_RESHAPE, b=(1, 3, 3, 2)), Transform(A.X_BROADCAST, i0=0, i1=4)]),
+    ((4, 3, 5, 5), A.SI8, DimsOrder.NCHW, [Transform(A.X_QUANT_CAST, elem=UniformQuantizedType(A.SI8, A.F16, 0.25, 3)),
+                                           Transform(A.X_EXPAND_DILATED, a=(2, 3)), Transform(A.X_REVERSE, i0=1)]),
+    ((16, 1, 1, 4), A.SI32, DimsOrder.NCHW, [Transform(A.X_RELOCATE_WEIGHTS_TABLE, a=(0, 8), b=(100, 200), i0=5000)]),
 ]
 
 

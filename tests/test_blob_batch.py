@@ -197,3 +197,36 @@ def test_weighted_partition_follows_the_shares():
     # cheap transfers: an equal split
     assert gather_aware_weights(4, 5.0, 0.1) == [0.25] * 4
     assert gather_aware_weights(1, 5.0, 9.0) == [1.0]
+
+
+@gpu_only
+def test_two_contexts_fold_concurrently(oracle):
+    """Calls on different contexts may run at the same time (the reference folds from many threads):
+    two host threads, each with a context of its own, fold different constants and both match the oracle."""
+    import threading
+    from npu_plugin_b200.const import ContentAttr, CudaBackend
+    rng = np.random.default_rng(33)
+    ws = [rng.normal(0, 0.02, (48, 2048, 1, 1)).astype(np.float16) for _ in range(2)]
+    results, errors = [None, None], []
+
+    def build(backend, w):
+        a = ContentAttr.get(w, NDType(w.shape, A.F16), backend=backend).quantizeSynth(A.QSYNTH_SYM_I8)
+        q = UniformQuantizedPerAxisType(A.SI8, A.F16, [1.0] * 48, [0] * 48, 0, -127, 127)
+        return a.convertElemType(A.SI8).quantCast(q).reorder(DimsOrder.NHWC).swizzleConstant(5, 3)
+
+    def work(k):
+        try:
+            be = CudaBackend(0)
+            for _ in range(20):
+                results[k] = build(be, ws[k]).fold().copyTo()
+        except Exception as e:  # surfaced below
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(k,)) for k in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for k in range(2):
+        assert np.array_equal(results[k], build(oracle, ws[k]).fold().copyTo())
