@@ -526,7 +526,7 @@ __device__ __forceinline__ void rowQuantSmemBody(const RowQuantParams& p, long l
 }
 
 template <typename T, int TPR, int SCHEME>
-__global__ void __launch_bounds__(256) rowQuantSmemKernel(const __grid_constant__ RowQuantParams p) {
+__global__ void __launch_bounds__(256, 4) rowQuantSmemKernel(const __grid_constant__ RowQuantParams p) {
     extern __shared__ __align__(16) unsigned char smemRaw[];
     __shared__ float redMx[8], redMn[8], redAm[8], redOdd[8];
     constexpr int ROWS_PER_CTA = 256 / TPR;
@@ -538,7 +538,7 @@ __global__ void __launch_bounds__(256) rowQuantSmemKernel(const __grid_constant_
 }
 
 template <typename T, int TPR, int SCHEME>
-__global__ void __launch_bounds__(256) rowQuantSmemBatchKernel(const RowQuantParams* __restrict__ items,
+__global__ void __launch_bounds__(256, 4) rowQuantSmemBatchKernel(const RowQuantParams* __restrict__ items,
                                                                const long long* __restrict__ groupStart, int nitems) {
     extern __shared__ __align__(16) unsigned char smemRaw[];
     __shared__ float redMx[8], redMn[8], redAm[8], redOdd[8];
@@ -647,6 +647,17 @@ template <typename T, int TPR, int SCHEME>
 void launchSmemT(Context* ctx, const RowQuantParams* one, const RowQuantParams* itemsDev, const long long* startDev,
                  int nitems, long long totalGroups, size_t smem) {
     constexpr int ROWS_PER_CTA = 256 / TPR;
+    {
+        // as much shared memory per SM as the part offers: the staged rows, not the L1, bound the residency
+        static bool carved = false;
+        if (!carved) {
+            carved = true;
+            cudaFuncSetAttribute(rowQuantSmemKernel<T, TPR, SCHEME>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared);
+            cudaFuncSetAttribute(rowQuantSmemBatchKernel<T, TPR, SCHEME>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared);
+        }
+    }
     if (smem > 48 * 1024) {
         B2_CUDA(cudaFuncSetAttribute(rowQuantSmemKernel<T, TPR, SCHEME>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(smem)));
