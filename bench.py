@@ -14,6 +14,7 @@ Prints ONE JSON line (rank 0).
 """
 import argparse
 import ctypes as C
+import datetime
 import gc
 import json
 import os
@@ -364,14 +365,17 @@ def main():
 
     # Every other rank's slots must enter rank 0 through its NVLink ingress, so rank 0 takes the larger
     # share of the constants: its compute time for that share balances the ingress time of the rest
-    # (rates: 4-5 TB/s of algorithmic bytes for rank 0's kernels while it receives, 750 GB/s for the link; input bytes x 2 and
-    # x 0.5 approximate algorithmic and blob bytes of a constant before anything has run).
+    # (rates: 5 TB/s of algorithmic bytes for the kernels, 750 GB/s for the link; input bytes x 2 and x 0.5
+    # approximate algorithmic and blob bytes of a constant before anything has run).  A larger share for
+    # rank 0 measured worse: transfers crawl while rank 0's kernels keep its memory busy.
     total_in = sum(d.nbytes for d in decls)
-    # rank 0's kernels keep their pace while copy engines bring the peers' slots in (measured: the copies
-    # then run at about 500 GB/s, both GPUs' memory being busy); NCCL's receive kernels take SMs and
-    # memory bandwidth from the fold kernels but move the bytes faster
-    rate, link = (5.0e12, 0.5e12) if args.gather == "pull" else (4.0e12, 0.75e12)
+    rate, link = 5.0e12, 0.75e12  # measured best at two ranks in both gather modes (rank 0 keeps 62.5 %)
     weights = gather_aware_weights(world, compute_seconds=2.0 * total_in / rate, transfer_seconds=0.5 * total_in / link)
+    if args.gather == "pull" and world > 1:
+        # copy-engine transfers into a GPU whose kernels saturate its memory make little progress until
+        # those kernels end (measured), so compute and transfer add up instead of overlapping: rank 0 keeps
+        # nearly everything and the peers take the rest
+        weights = [0.9] + [0.1 / (world - 1)] * (world - 1)
     owner = partition(decls, world, weights)
     mine = [d for d, o in zip(decls, owner) if o == rank]
     folder = ShardFolder(backend, mine)  # whole-shard layout (sizes, bounds); also the N=1 path
@@ -420,7 +424,9 @@ def main():
     # place and receives the others' next to them.
     gathered, place = None, None
     if world > 1:
-        pg_sizes = dist.new_group(backend="gloo")  # set-up only: the chunk sizes of every rank
+        # host-side group: chunk sizes at set-up, readiness notes and releases of the pull mode; a short
+        # time limit turns a stuck exchange into an error instead of a hang
+        pg_sizes = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=180))
         mine_sizes = torch.tensor([f.folded_bytes if f is not None else 0 for f in cf], dtype=torch.int64)
         all_sizes = [torch.zeros(nchunks, dtype=torch.int64) for _ in range(world)]
         dist.all_gather(all_sizes, mine_sizes, group=pg_sizes)
