@@ -45,9 +45,15 @@ __device__ __forceinline__ void copyTile(const GenParams& g, long long srcElem, 
     const long long bytes = static_cast<long long>(nx) * es;
     const bool vec = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) | static_cast<uintptr_t>(outByte)) & 15) == 0;
     const long long nvec = vec ? bytes / 16 : 0;
-    for (long long v = threadIdx.x; v < nvec; v += kTileThreads) {
-        const uint4 x = __ldg(reinterpret_cast<const uint4*>(src) + v);
-        *reinterpret_cast<uint4*>(dst + swz(outByte + v * 16, g.swizzleKey)) = x;
+    for (long long v0 = threadIdx.x; v0 < nvec; v0 += 4 * kTileThreads) {  // four loads in flight per thread
+        uint4 x[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if (v0 + r * kTileThreads < nvec) x[r] = __ldg(reinterpret_cast<const uint4*>(src) + v0 + r * kTileThreads);
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if (v0 + r * kTileThreads < nvec)
+                *reinterpret_cast<uint4*>(dst + swz(outByte + (v0 + r * kTileThreads) * 16, g.swizzleKey)) = x[r];
     }
     for (long long b = nvec * 16 + threadIdx.x; b < bytes; b += kTileThreads) dst[swz(outByte + b, g.swizzleKey)] = src[b];
 }
@@ -86,7 +92,15 @@ __device__ __forceinline__ void transposeTile(const GenParams& g, long long srcE
         if (threadIdx.x < head) smem[phase + threadIdx.x] = src[threadIdx.x];
         const uint4* s4 = reinterpret_cast<const uint4*>(src + head);
         uint4* d4 = reinterpret_cast<uint4*>(smem + phase + head);
-        for (int v = threadIdx.x; v < nvec; v += kTileThreads) d4[v] = __ldg(s4 + v);
+        for (int v0 = threadIdx.x; v0 < nvec; v0 += 4 * kTileThreads) {  // four loads in flight per thread
+            uint4 x[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+                if (v0 + r * kTileThreads < nvec) x[r] = __ldg(s4 + v0 + r * kTileThreads);
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+                if (v0 + r * kTileThreads < nvec) d4[v0 + r * kTileThreads] = x[r];
+        }
         if (threadIdx.x < bytes - tailAt) smem[phase + tailAt + threadIdx.x] = src[tailAt + threadIdx.x];
     }
     __syncthreads();
