@@ -177,6 +177,7 @@ B200C_API void b200c_destroy(b200c_ctx* ctx);
  * restores the context's own stream.                                          */
 B200C_API int b200c_set_stream(b200c_ctx* ctx, void* stream);
 B200C_API void* b200c_get_stream(b200c_ctx* ctx);
+/* Waits for the context's stream (and its transfer stream, if used) and reports device-side errors. */
 B200C_API int b200c_synchronize(b200c_ctx* ctx);
 /* Number of kernels of this library launched through the context so far.     */
 B200C_API int64_t b200c_launch_count(b200c_ctx* ctx);
@@ -284,9 +285,10 @@ B200C_API int b200c_btc_decompress(b200c_ctx* ctx, const void* in, size_t n, int
  *  - n may be at most B200C_NOALLOC_MAX_INPUT bytes (16 MiB); larger inputs are refused with
  *    B200C_ERR_CAPACITY and a message saying so.  cap must be at least b200c_btc_bound(n).
  *  - `device` is the CUDA device of in/out, `stream` a cudaStream_t on it (NULL: the default
- *    stream).  The call returns after the stream has finished the work.
- *  - The first call on a device looks up the address of the fixed buffer; make that first call
- *    outside any stream capture.
+ *    stream).  The call blocks until the stream has finished the work and reads the result size
+ *    back, so it must never be made while `stream` is being captured.  The calling thread's current
+ *    device is the same after the call as before it.
+ *  - The first call on a device also looks up the address of the fixed buffer (once per device).
  *  - All calls on one device share the fixed buffer.  Each call rewrites what it reads, so calls
  *    may follow one another freely, but two calls whose GPU work overlaps (two threads, two
  *    streams) race on it: serialise them.
@@ -314,12 +316,90 @@ B200C_API int b200c_btc_compress_batch(b200c_ctx* ctx, int count, const void* co
 B200C_API int b200c_btc_compress_inplace_batch(b200c_ctx* ctx, int count, void* const* bufs_dev, const size_t* sizes,
                                                size_t* out_sizes, int32_t* compressed);
 
+/* ---- splat detection -------------------------------------------------------------
+ * "All elements equal" test of a raw buffer: detectSplatElementWise, which the reference runs when
+ * it wraps a dense resource (src/vpux_compiler/src/dialect/const/attributes/content.cpp:103-137,
+ * called from wrapBaseContent :143-159) -- there a memcmp loop over the elements, here one
+ * reduction kernel.  elem_bytes is 1, 2, 4 or 8.  *is_splat = 1 when every element equals the
+ * first (a single element is a splat; an empty buffer is not, as in detectSplatManually).  Errors
+ * as the reference throws them: fewer bytes than one element, or a length that is not a multiple
+ * of the element size.  A caller passes the answer on as `is_splat` of b200c_fold together with
+ * nbytes = elem_bytes.                                                                          */
+B200C_API int b200c_detect_splat(b200c_ctx* ctx, const void* data, size_t nbytes, int elem_bytes, int data_on_device,
+                                 int* is_splat);
+
+/* ---- multi-GPU exchange --------------------------------------------------------------
+ * The reference writes every constant of a model into one blob from a parallel loop in one
+ * process (serializeBinaryData, src/vpux_compiler/src/dialect/VPUIP/graph-schema/export.cpp:465-479).
+ * When the constants are sharded over the GPUs of one machine, one process per GPU, these calls
+ * carry the finished slots into the blob buffer of the assembling rank over NVLink.  They have no
+ * further counterpart in the reference (which is a single process).
+ *
+ * b200c_ipc_export describes a range of a b200c_dev_alloc allocation so that another process on
+ * the same machine can map it with b200c_ipc_open (CUDA IPC; peer access is enabled on demand);
+ * the returned pointer is valid in device code and in the copy calls below.
+ *
+ * b200c_copy_segments_async queues `count` copies src -> dst on the context's transfer stream,
+ * ordered after everything queued on the context's stream so far; it returns at once.  dst may
+ * be a mapped peer range (push over NVLink) or pinned host memory (download).
+ *   wait_flag/wait_value : if not NULL, a device word of this GPU; the copies start only when it
+ *                          holds at least wait_value (the assembling rank's release of its buffer);
+ *   done_flag/done_value : if not NULL, a device word (usually in the peer's memory) that
+ *                          receives done_value after all bytes have landed;
+ *   mode 0               : a copy kernel with plain 128-bit loads and stores (`ctas` CTAs; peer
+ *                          memory is only ever stored to); a wait that times out cancels the copy;
+ *   mode 1               : the copy engine (one cudaMemcpyAsync per segment).
+ * b200c_wait_flags queues, on the context's stream, a bounded wait until each of `count`
+ * consecutive device words holds at least `value`; b200c_signal_flags queues stores of `value`
+ * to the given device words (peer memory allowed).  No wait spins for more than timeout_ms:
+ * it then records the failure and lets the stream continue.  b200c_exchange_status waits for
+ * both streams and returns the failures since the last call in *timed_out (bit 0: a release
+ * wait of a pusher, bit 1: a done wait of the assembling rank) -- the caller turns a non-zero
+ * value into its own error.                                                                      */
+typedef struct b200c_ipc_handle {
+    unsigned char handle[64];
+    uint64_t offset; /* of the exported address inside the allocation */
+    uint64_t size;
+} b200c_ipc_handle;
+typedef struct b200c_copy_seg {
+    const void* src;
+    void* dst;
+    size_t n;
+} b200c_copy_seg;
+B200C_API int b200c_ipc_export(b200c_ctx* ctx, void* dev_ptr, size_t size, b200c_ipc_handle* out);
+B200C_API int b200c_ipc_open(b200c_ctx* ctx, const b200c_ipc_handle* h, void** mapped);
+B200C_API int b200c_ipc_close(b200c_ctx* ctx, void* mapped);
+B200C_API int b200c_copy_segments_async(b200c_ctx* ctx, const b200c_copy_seg* segs, int count, const uint64_t* wait_flag,
+                                        uint64_t wait_value, uint64_t* done_flag, uint64_t done_value,
+                                        unsigned timeout_ms, int mode, int ctas);
+B200C_API int b200c_wait_flags(b200c_ctx* ctx, const uint64_t* flags_dev, int count, uint64_t value, unsigned timeout_ms);
+B200C_API int b200c_signal_flags(b200c_ctx* ctx, uint64_t* const* targets, int count, uint64_t value);
+B200C_API int b200c_exchange_status(b200c_ctx* ctx, int* timed_out);
+/* Makes the context's stream wait (on the device, without blocking the host) for everything queued
+ * on its transfer stream so far: a pusher calls it before it overwrites slots it has pushed, the
+ * assembling rank before it releases a buffer whose download is still queued.                      */
+B200C_API int b200c_stream_join(b200c_ctx* ctx);
+
+/* ---- buffer digest -------------------------------------------------------------------
+ * 64-bit digest of each of `count` device buffers (no counterpart in the reference; a
+ * measurement aid): used to show that the blob assembled from N GPUs holds the same bytes per
+ * constant as the one folded on a single GPU, without moving gigabytes to the host.
+ *   digest(bytes, n) = mix(0x9E3779B97F4A7C15 * (n + 1) + sum_j mix(word_j ^ (0xD6E8FEB86659FD93 * (j + 1))))
+ * over the little-endian 64-bit words of the buffer (the last one zero-extended), modulo 2^64,
+ * mix = the splitmix64 finaliser.  out: host array; the call synchronises.                       */
+B200C_API int b200c_digest64_batch(b200c_ctx* ctx, int count, const void* const* bufs_dev, const size_t* sizes,
+                                   uint64_t* out);
+
 /* ---- synthetic weights ----------------------------------------------------------
  * Counter-based seeded generator (Philox-4x32-10 keyed by seed and stream)
- * used by the benchmark so that inputs never cross PCIe.  dist: 0 = normal
- * (p0 = sigma), 1 = uniform int8 in [-127,127] with Bernoulli(p0) zeros,
- * 2 = discretised Laplace(0, p0) clipped to [-127,127] with a fraction p1 of
- * exact zeros.  dtype: B200C_F32, B200C_F16 or B200C_SI8.                    */
+ * used by the benchmark so that inputs never cross PCIe (no counterpart in the
+ * reference; the benchmark configurations only name distributions and a seed).
+ * dist: 0 = normal (p0 = sigma, Box-Muller), 1 = uniform int8 in [-127,127] with
+ * Bernoulli(p0) zeros, 2 = discretised Laplace(0, p0) clipped to [-127,127] with a
+ * fraction p1 of exact zeros.  dtype: B200C_F32, B200C_F16 or B200C_SI8.  Element i
+ * depends only on (seed, stream_id, i).  The logarithm, sine and cosine are fixed
+ * polynomial evaluations in IEEE single precision (no math library), so a CPU
+ * restatement produces the same bytes.                                        */
 B200C_API int b200c_synth_fill(b200c_ctx* ctx, void* dst_dev, int64_t count, int32_t dtype, int32_t dist, double p0,
                      double p1, uint64_t seed, uint64_t stream_id);
 
@@ -328,6 +408,7 @@ B200C_API int b200c_dev_alloc(b200c_ctx* ctx, size_t n, void** out);
 B200C_API int b200c_dev_free(b200c_ctx* ctx, void* p);
 B200C_API int b200c_host_alloc_pinned(size_t n, void** out);
 B200C_API int b200c_host_free_pinned(void* p);
+B200C_API int b200c_dev_memset(b200c_ctx* ctx, void* dst_dev, int value, size_t n); /* queued on the context's stream */
 B200C_API int b200c_memcpy_h2d(b200c_ctx* ctx, void* dst_dev, const void* src, size_t n);
 B200C_API int b200c_memcpy_d2h(b200c_ctx* ctx, void* dst, const void* src_dev, size_t n);
 

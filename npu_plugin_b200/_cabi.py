@@ -111,6 +111,14 @@ class b200c_fold_item(C.Structure):
     ]
 
 
+class b200c_ipc_handle(C.Structure):
+    _fields_ = [("handle", C.c_ubyte * 64), ("offset", C.c_uint64), ("size", C.c_uint64)]
+
+
+class b200c_copy_seg(C.Structure):
+    _fields_ = [("src", C.c_void_p), ("dst", C.c_void_p), ("n", C.c_size_t)]
+
+
 # name -> (restype, argtypes) of every symbol include/b200const.h declares
 _P = C.POINTER
 SYMBOLS = {
@@ -143,16 +151,27 @@ SYMBOLS = {
                                                    _P(C.c_int32)]),
     "b200c_synth_fill": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_double, C.c_double,
                                    C.c_uint64, C.c_uint64]),
+    "b200c_detect_splat": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, _P(C.c_int)]),
+    "b200c_digest64_batch": (C.c_int, [C.c_void_p, C.c_int, _P(C.c_void_p), _P(C.c_size_t), _P(C.c_uint64)]),
+    "b200c_ipc_export": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, _P(b200c_ipc_handle)]),
+    "b200c_ipc_open": (C.c_int, [C.c_void_p, _P(b200c_ipc_handle), _P(C.c_void_p)]),
+    "b200c_ipc_close": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b200c_copy_segments_async": (C.c_int, [C.c_void_p, _P(b200c_copy_seg), C.c_int, C.c_void_p, C.c_uint64, C.c_void_p,
+                                            C.c_uint64, C.c_uint, C.c_int, C.c_int]),
+    "b200c_wait_flags": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_uint64, C.c_uint]),
+    "b200c_signal_flags": (C.c_int, [C.c_void_p, _P(C.c_void_p), C.c_int, C.c_uint64]),
+    "b200c_exchange_status": (C.c_int, [C.c_void_p, _P(C.c_int)]),
+    "b200c_stream_join": (C.c_int, [C.c_void_p]),
     "b200c_dev_alloc": (C.c_int, [C.c_void_p, C.c_size_t, _P(C.c_void_p)]),
     "b200c_dev_free": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200c_host_alloc_pinned": (C.c_int, [C.c_size_t, _P(C.c_void_p)]),
     "b200c_host_free_pinned": (C.c_int, [C.c_void_p]),
+    "b200c_dev_memset": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_size_t]),
     "b200c_memcpy_h2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
     "b200c_memcpy_d2h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
 }
 
-LIB_PATH = os.environ.get("B200C_LIBRARY_PATH") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc",
-                                                                "libb200const.so")
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc", "libb200const.so")
 _lib = None
 
 

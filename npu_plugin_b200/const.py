@@ -409,6 +409,101 @@ class CudaBackend:
     def launch_count(self):
         return self.lib.b200c_launch_count(self.ctx)
 
+    def synchronize(self):
+        raise_for(self.lib.b200c_synchronize(self.ctx), self._err())
+
+    def detect_splat(self, data, elem_bytes):
+        """detectSplatElementWise (content.cpp:103-137) on a host array."""
+        buf = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        flag = C.c_int()
+        raise_for(self.lib.b200c_detect_splat(self.ctx, buf.ctypes.data if buf.size else None, buf.size, elem_bytes, 0,
+                                              C.byref(flag)), self._err())
+        return bool(flag.value)
+
+    # ---- device memory and the multi-GPU exchange (thin wrappers; pointers are plain integers)
+    def dev_alloc(self, nbytes):
+        p = C.c_void_p()
+        raise_for(self.lib.b200c_dev_alloc(self.ctx, max(1, int(nbytes)), C.byref(p)), self._err())
+        return p.value
+
+    def dev_free(self, ptr):
+        if ptr:
+            self.lib.b200c_dev_free(self.ctx, ptr)
+
+    def pinned_alloc(self, nbytes):
+        p = C.c_void_p()
+        raise_for(self.lib.b200c_host_alloc_pinned(max(1, int(nbytes)), C.byref(p)), self._err())
+        return p.value
+
+    def pinned_free(self, ptr):
+        if ptr:
+            self.lib.b200c_host_free_pinned(ptr)
+
+    def upload(self, dev_ptr, array):
+        a = np.ascontiguousarray(array).view(np.uint8).reshape(-1)
+        raise_for(self.lib.b200c_memcpy_h2d(self.ctx, dev_ptr, a.ctypes.data, a.size), self._err())
+
+    def download(self, dev_ptr, nbytes):
+        out = np.zeros(int(nbytes), np.uint8)
+        raise_for(self.lib.b200c_memcpy_d2h(self.ctx, out.ctypes.data, dev_ptr, out.size), self._err())
+        return out
+
+    def fill_zero(self, dev_ptr, nbytes):
+        raise_for(self.lib.b200c_dev_memset(self.ctx, dev_ptr, 0, int(nbytes)), self._err())
+        self.synchronize()
+
+    def synth_fill(self, dev_ptr, count, dtype, dist, p0, p1, seed, stream_id):
+        raise_for(self.lib.b200c_synth_fill(self.ctx, dev_ptr, int(count), dtype, dist, p0, p1, seed, stream_id), self._err())
+
+    def digest64(self, ptrs, sizes):
+        n = len(ptrs)
+        if n == 0:
+            return []
+        pa = (C.c_void_p * n)(*ptrs)
+        sa = (C.c_size_t * n)(*sizes)
+        out = (C.c_uint64 * n)()
+        raise_for(self.lib.b200c_digest64_batch(self.ctx, n, pa, sa, out), self._err())
+        return [int(v) for v in out]
+
+    def ipc_export(self, dev_ptr, nbytes):
+        h = A.b200c_ipc_handle()
+        raise_for(self.lib.b200c_ipc_export(self.ctx, dev_ptr, int(nbytes), C.byref(h)), self._err())
+        return bytes(h)
+
+    def ipc_open(self, desc):
+        h = A.b200c_ipc_handle.from_buffer_copy(desc)
+        p = C.c_void_p()
+        raise_for(self.lib.b200c_ipc_open(self.ctx, C.byref(h), C.byref(p)), self._err())
+        return p.value
+
+    def ipc_close(self, mapped):
+        self.lib.b200c_ipc_close(self.ctx, mapped)
+
+    def copy_segments_async(self, segs, wait_flag=None, wait_value=0, done_flag=None, done_value=0, timeout_ms=5000,
+                            mode=0, ctas=64):
+        """segs: (src pointer, dst pointer, bytes) triples; see b200c_copy_segments_async."""
+        n = len(segs)
+        arr = (A.b200c_copy_seg * max(1, n))()
+        for i, (src, dst, nb) in enumerate(segs):
+            arr[i].src, arr[i].dst, arr[i].n = src, dst, nb
+        raise_for(self.lib.b200c_copy_segments_async(self.ctx, arr, n, wait_flag, wait_value, done_flag, done_value,
+                                                     timeout_ms, mode, ctas), self._err())
+
+    def wait_flags(self, flags_ptr, count, value, timeout_ms=5000):
+        raise_for(self.lib.b200c_wait_flags(self.ctx, flags_ptr, count, value, timeout_ms), self._err())
+
+    def signal_flags(self, targets, value):
+        arr = (C.c_void_p * max(1, len(targets)))(*targets)
+        raise_for(self.lib.b200c_signal_flags(self.ctx, arr, len(targets), value), self._err())
+
+    def stream_join(self):
+        raise_for(self.lib.b200c_stream_join(self.ctx), self._err())
+
+    def exchange_status(self):
+        st = C.c_int()
+        raise_for(self.lib.b200c_exchange_status(self.ctx, C.byref(st)), self._err())
+        return st.value
+
 
 _default_backend = None
 

@@ -23,13 +23,6 @@ static thread_local std::string t_lastError;
 // ---------------------------------------------------------------------------- memory
 void* devMalloc(Context* ctx, size_t bytes) {
     if (bytes == 0) bytes = 1;
-#ifdef B200C_HOST_EMULATION
-    if (B2_EMU(ctx)) {
-        void* p = std::malloc(bytes);
-        if (!p) throw NoMem("host allocation failed");
-        return p;
-    }
-#endif
     (void)ctx;
     void* p = nullptr;
     const cudaError_t e = cudaMalloc(&p, bytes);
@@ -42,30 +35,16 @@ void* devMalloc(Context* ctx, size_t bytes) {
 
 void devFree(Context* ctx, void* p) {
     if (!p) return;
-#ifdef B200C_HOST_EMULATION
-    if (B2_EMU(ctx)) {
-        std::free(p);
-        return;
-    }
-#endif
     (void)ctx;
     cudaFree(p);
 }
 
 void copyH2D(Context* ctx, void* dst, const void* src, size_t n) {
     if (n == 0) return;
-    if (B2_EMU(ctx)) {
-        std::memcpy(dst, src, n);
-        return;
-    }
     B2_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, ctx->stream));
 }
 void uploadSmall(Context* ctx, void* dst, const void* src, size_t n) {
     if (n == 0) return;
-    if (B2_EMU(ctx)) {
-        std::memcpy(dst, src, n);
-        return;
-    }
     const int set = ctx->stageSet;
     const size_t need = (n + 63) / 64 * 64;
     Context::StageChunk* c = nullptr;
@@ -123,30 +102,17 @@ void releaseStage(Context* ctx) {
 
 void copyD2H(Context* ctx, void* dst, const void* src, size_t n) {
     if (n == 0) return;
-    if (B2_EMU(ctx)) {
-        std::memcpy(dst, src, n);
-        return;
-    }
     B2_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToHost, ctx->stream));
 }
 void copyD2D(Context* ctx, void* dst, const void* src, size_t n) {
     if (n == 0) return;
-    if (B2_EMU(ctx)) {
-        std::memmove(dst, src, n);
-        return;
-    }
     B2_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToDevice, ctx->stream));
 }
 void fillBytes(Context* ctx, void* dst, int value, size_t n) {
     if (n == 0) return;
-    if (B2_EMU(ctx)) {
-        std::memset(dst, value, n);
-        return;
-    }
     B2_CUDA(cudaMemsetAsync(dst, value, n, ctx->stream));
 }
 void syncStream(Context* ctx) {
-    if (B2_EMU(ctx)) return;
     B2_CUDA(cudaStreamSynchronize(ctx->stream));
 }
 
@@ -169,16 +135,11 @@ static const char* errText(int code) {
 
 void checkDeviceError(Context* ctx) {
     int code = E_NONE;
-    if (B2_EMU(ctx)) {
-        code = *ctx->errWord;
-        *ctx->errWord = E_NONE;
-    } else {
-        B2_CUDA(cudaMemcpyAsync(ctx->errHost, ctx->errWord, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
-        B2_CUDA(cudaStreamSynchronize(ctx->stream));
-        code = *ctx->errHost;
-        if (code != E_NONE) {
-            B2_CUDA(cudaMemsetAsync(ctx->errWord, 0, sizeof(int), ctx->stream));
-        }
+    B2_CUDA(cudaMemcpyAsync(ctx->errHost, ctx->errWord, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    B2_CUDA(cudaStreamSynchronize(ctx->stream));
+    code = *ctx->errHost;
+    if (code != E_NONE) {
+        B2_CUDA(cudaMemsetAsync(ctx->errWord, 0, sizeof(int), ctx->stream));
     }
     if (code != E_NONE) throw RefThrow(errText(code));
 }
@@ -339,7 +300,7 @@ static int planThreads() {
 }
 
 static void ensurePool(Context* ctx) {
-    if (ctx->pool || B2_EMU(ctx)) return;
+    if (ctx->pool) return;
     const int n = planThreads();
     if (n < 2) return;
     for (int i = 0; i < n; ++i) {
@@ -370,10 +331,8 @@ struct CallScope {
     Context* ctx;
     std::unique_lock<std::mutex> lock;
     explicit CallScope(Context* c): ctx(c), lock(c->mu) {
-        if (!B2_EMU(ctx)) {
-            const cudaError_t e = cudaSetDevice(ctx->device);
-            if (e != cudaSuccess) throw CudaFail(std::string("cudaSetDevice: ") + cudaGetErrorString(e));
-        }
+        const cudaError_t e = cudaSetDevice(ctx->device);
+        if (e != cudaSuccess) throw CudaFail(std::string("cudaSetDevice: ") + cudaGetErrorString(e));
         ctx->arena.reset();
         resetStage(ctx);
     }
@@ -390,11 +349,7 @@ const char* b200c_last_error(void) {
 }
 
 const char* b200c_version(void) {
-#ifdef B200C_HOST_EMULATION
-    return "b200const 0.1 (host-emulation debug build)";
-#else
     return "b200const 0.1 (sm_100a)";
-#endif
 }
 
 int b200c_create(int device, b200c_ctx** out) {
@@ -402,33 +357,24 @@ int b200c_create(int device, b200c_ctx** out) {
         if (!out) throw BadArg("null output pointer");
         auto ctx = std::make_unique<Context>();
         ctx->device = device;
-#ifdef B200C_HOST_EMULATION
-        const char* emu = std::getenv("B200C_EMULATE");
-        ctx->emulated = emu && emu[0] == '1';
-#endif
-        if (B2_EMU(ctx)) {
-            ctx->errWord = static_cast<int*>(std::calloc(1, sizeof(int)));
-            ctx->errHost = ctx->errWord;
-        } else {
-            int count = 0;
-            cudaError_t e = cudaGetDeviceCount(&count);
-            if (e != cudaSuccess || count == 0) {
-                cudaGetLastError();
-                throw CudaFail(std::string("no usable CUDA device: ") + (e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0"));
-            }
-            if (device < 0 || device >= count) throw BadArg("device index out of range");
-            B2_CUDA(cudaSetDevice(device));
-            cudaDeviceProp prop;
-            B2_CUDA(cudaGetDeviceProperties(&prop, device));
-            ctx->smCount = prop.multiProcessorCount;
-            ctx->l2Bytes = static_cast<size_t>(prop.l2CacheSize);
-            B2_CUDA(cudaStreamCreateWithFlags(&ctx->ownStream, cudaStreamNonBlocking));
-            ctx->stream = ctx->ownStream;
-            B2_CUDA(cudaMalloc(&ctx->errWord, sizeof(int)));
-            B2_CUDA(cudaMemset(ctx->errWord, 0, sizeof(int)));
-            B2_CUDA(cudaMallocHost(&ctx->errHost, sizeof(int)));
-            *ctx->errHost = 0;
+        int count = 0;
+        cudaError_t e = cudaGetDeviceCount(&count);
+        if (e != cudaSuccess || count == 0) {
+            cudaGetLastError();
+            throw CudaFail(std::string("no usable CUDA device: ") + (e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0"));
         }
+        if (device < 0 || device >= count) throw BadArg("device index out of range");
+        B2_CUDA(cudaSetDevice(device));
+        cudaDeviceProp prop;
+        B2_CUDA(cudaGetDeviceProperties(&prop, device));
+        ctx->smCount = prop.multiProcessorCount;
+        ctx->l2Bytes = static_cast<size_t>(prop.l2CacheSize);
+        B2_CUDA(cudaStreamCreateWithFlags(&ctx->ownStream, cudaStreamNonBlocking));
+        ctx->stream = ctx->ownStream;
+        B2_CUDA(cudaMalloc(&ctx->errWord, sizeof(int)));
+        B2_CUDA(cudaMemset(ctx->errWord, 0, sizeof(int)));
+        B2_CUDA(cudaMallocHost(&ctx->errHost, sizeof(int)));
+        *ctx->errHost = 0;
         *out = reinterpret_cast<b200c_ctx*>(ctx.release());
     });
 }
@@ -436,18 +382,15 @@ int b200c_create(int device, b200c_ctx** out) {
 void b200c_destroy(b200c_ctx* h) {
     if (!h) return;
     Context* ctx = reinterpret_cast<Context*>(h);
-    if (B2_EMU(ctx)) {
-        std::free(ctx->errWord);
-    } else {
-        cudaSetDevice(ctx->device);
-        cudaStreamSynchronize(ctx->stream);
-        if (ctx->errWord) cudaFree(ctx->errWord);
-        if (ctx->errHost) cudaFreeHost(ctx->errHost);
-    }
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->errWord) cudaFree(ctx->errWord);
+    if (ctx->errHost) cudaFreeHost(ctx->errHost);
     destroyPool(ctx);
-    if (!B2_EMU(ctx)) releaseStage(ctx);
+    releaseExchange(ctx);
+    releaseStage(ctx);
     ctx->arena.releaseAll();  // frees the blocks while the device is still current
-    if (!B2_EMU(ctx) && ctx->ownStream) cudaStreamDestroy(ctx->ownStream);
+    if (ctx->ownStream) cudaStreamDestroy(ctx->ownStream);
     delete ctx;
 }
 
@@ -469,7 +412,8 @@ int b200c_synchronize(b200c_ctx* h) {
         if (!h) throw BadArg("null context");
         Context* ctx = reinterpret_cast<Context*>(h);
         std::lock_guard<std::mutex> lock(ctx->mu);
-        if (!B2_EMU(ctx)) B2_CUDA(cudaSetDevice(ctx->device));
+        B2_CUDA(cudaSetDevice(ctx->device));
+        if (ctx->xferStream) B2_CUDA(cudaStreamSynchronize(ctx->xferStream));
         syncStream(ctx);
         checkDeviceError(ctx);
     });
@@ -572,7 +516,7 @@ int b200c_fold_batch(b200c_ctx* h, b200c_fold_item* items, int count, int data_o
                 q->queuedBytes = 0;
             }
         } guard{ctx};
-        ctx->batching = out_on_device != 0 && !B2_EMU(ctx);
+        ctx->batching = out_on_device != 0;
         ctx->queuedBytes = 0;
         typedef std::vector<std::pair<int, const long long*>> Deferred;  // items whose size is read back at the end
         Deferred deferred;
@@ -843,6 +787,125 @@ int b200c_btc_compress_inplace_batch(b200c_ctx* h, int count, void* const* bufs_
     });
 }
 
+// ---------------------------------------------------------------------------- splat detection, digest
+int b200c_detect_splat(b200c_ctx* h, const void* data, size_t nbytes, int elem_bytes, int data_on_device, int* is_splat) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        if (!is_splat) throw BadArg("null result pointer");
+        if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4 && elem_bytes != 8) throw BadArg("element size must be 1, 2, 4 or 8 bytes");
+        *is_splat = 0;
+        if (nbytes == 0) return;  // detectSplatManually: empty data is not a splat
+        if (!data) throw BadArg("null data pointer");
+        if (nbytes < static_cast<size_t>(elem_bytes)) refThrow("The data must contain at least one element");
+        if (nbytes % elem_bytes) refThrow("The data array has unexpected length");
+        if (nbytes == static_cast<size_t>(elem_bytes)) {
+            *is_splat = 1;
+            return;
+        }
+        Context* ctx = reinterpret_cast<Context*>(h);
+        CallScope scope(ctx);
+        const void* dev = data;
+        if (!data_on_device) {
+            void* d = ctx->arena.alloc(nbytes);
+            copyH2D(ctx, d, data, nbytes);
+            dev = d;
+        }
+        *is_splat = probeSplat(ctx, dev, nbytes, elem_bytes) ? 1 : 0;
+    });
+}
+
+int b200c_digest64_batch(b200c_ctx* h, int count, const void* const* bufs_dev, const size_t* sizes, uint64_t* out) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        if (count < 0 || (count > 0 && (!bufs_dev || !sizes || !out))) throw BadArg("bad digest arguments");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        CallScope scope(ctx);
+        static_assert(sizeof(uint64_t) == sizeof(unsigned long long), "64-bit words");
+        digestBatch(ctx, count, bufs_dev, sizes, reinterpret_cast<unsigned long long*>(out));
+    });
+}
+
+// ---------------------------------------------------------------------------- multi-GPU exchange
+int b200c_ipc_export(b200c_ctx* h, void* dev_ptr, size_t size, b200c_ipc_handle* out) {
+    return guarded([&] {
+        if (!h || !dev_ptr || !out) throw BadArg("null pointer");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        B2_CUDA(cudaSetDevice(ctx->device));
+        unsigned long long off = 0;
+        ipcExport(ctx, dev_ptr, size, out->handle, &off);
+        out->offset = off;
+        out->size = size;
+    });
+}
+int b200c_ipc_open(b200c_ctx* h, const b200c_ipc_handle* in, void** mapped) {
+    return guarded([&] {
+        if (!h || !in || !mapped) throw BadArg("null pointer");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        B2_CUDA(cudaSetDevice(ctx->device));
+        *mapped = ipcOpen(ctx, in->handle, in->offset);
+    });
+}
+int b200c_ipc_close(b200c_ctx* h, void* mapped) {
+    return guarded([&] {
+        if (!h || !mapped) throw BadArg("null pointer");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        B2_CUDA(cudaSetDevice(ctx->device));
+        ipcClose(ctx, mapped);
+    });
+}
+int b200c_copy_segments_async(b200c_ctx* h, const b200c_copy_seg* segs, int count, const uint64_t* wait_flag, uint64_t wait_value,
+                              uint64_t* done_flag, uint64_t done_value, unsigned timeout_ms, int mode, int ctas) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        if (count < 0 || (count > 0 && !segs)) throw BadArg("bad segment list");
+        if (mode != 0 && mode != 1) throw BadArg("mode must be 0 (kernel) or 1 (copy engine)");
+        for (int i = 0; i < count; ++i)
+            if (segs[i].n && (!segs[i].src || !segs[i].dst)) throw BadArg("null segment pointer");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        B2_CUDA(cudaSetDevice(ctx->device));
+        pushSegments(ctx, segs, count, reinterpret_cast<const unsigned long long*>(wait_flag), wait_value,
+                     reinterpret_cast<unsigned long long*>(done_flag), done_value, timeout_ms, mode, ctas > 0 ? ctas : 64);
+    });
+}
+int b200c_wait_flags(b200c_ctx* h, const uint64_t* flags_dev, int count, uint64_t value, unsigned timeout_ms) {
+    return guarded([&] {
+        if (!h || (count > 0 && !flags_dev)) throw BadArg("null pointer");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        B2_CUDA(cudaSetDevice(ctx->device));
+        waitFlags(ctx, reinterpret_cast<const unsigned long long*>(flags_dev), count, value, timeout_ms);
+    });
+}
+int b200c_signal_flags(b200c_ctx* h, uint64_t* const* targets, int count, uint64_t value) {
+    return guarded([&] {
+        if (!h || (count > 0 && !targets)) throw BadArg("null pointer");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        CallScope scope(ctx);
+        signalFlags(ctx, reinterpret_cast<unsigned long long* const*>(targets), count, value);
+    });
+}
+int b200c_stream_join(b200c_ctx* h) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        if (!ctx->xferStream) return;
+        B2_CUDA(cudaSetDevice(ctx->device));
+        B2_CUDA(cudaEventRecord(ctx->xferEvent, ctx->xferStream));
+        B2_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->xferEvent, 0));
+    });
+}
+int b200c_exchange_status(b200c_ctx* h, int* timed_out) {
+    return guarded([&] {
+        if (!h || !timed_out) throw BadArg("null pointer");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        B2_CUDA(cudaSetDevice(ctx->device));
+        *timed_out = exchangeStatus(ctx);
+    });
+}
+
 // ---------------------------------------------------------------------------- synthetic weights
 int b200c_synth_fill(b200c_ctx* h, void* dst_dev, int64_t count, int32_t dtype, int32_t dist, double p0, double p1,
                      uint64_t seed, uint64_t stream_id) {
@@ -850,7 +913,7 @@ int b200c_synth_fill(b200c_ctx* h, void* dst_dev, int64_t count, int32_t dtype, 
         if (!h) throw BadArg("null context");
         Context* ctx = reinterpret_cast<Context*>(h);
         std::lock_guard<std::mutex> lock(ctx->mu);
-        if (!B2_EMU(ctx)) B2_CUDA(cudaSetDevice(ctx->device));
+        B2_CUDA(cudaSetDevice(ctx->device));
         if (count > 0 && !dst_dev) throw BadArg("null destination");
         if (dist < 0 || dist > 2) throw BadArg("unknown distribution");
         launchSynthFill(ctx, dst_dev, count, dtype, dist, p0, p1, seed, stream_id);
@@ -862,15 +925,17 @@ int b200c_dev_alloc(b200c_ctx* h, size_t n, void** out) {
     return guarded([&] {
         if (!h || !out) throw BadArg("null pointer");
         Context* ctx = reinterpret_cast<Context*>(h);
-        if (!B2_EMU(ctx)) B2_CUDA(cudaSetDevice(ctx->device));
+        B2_CUDA(cudaSetDevice(ctx->device));
         *out = devMalloc(ctx, n);
+        registerAllocation(*out, n ? n : 1);
     });
 }
 int b200c_dev_free(b200c_ctx* h, void* p) {
     return guarded([&] {
         if (!h) throw BadArg("null context");
         Context* ctx = reinterpret_cast<Context*>(h);
-        if (!B2_EMU(ctx)) B2_CUDA(cudaSetDevice(ctx->device));
+        B2_CUDA(cudaSetDevice(ctx->device));
+        unregisterAllocation(p);
         devFree(ctx, p);
     });
 }
@@ -891,12 +956,21 @@ int b200c_host_free_pinned(void* p) {
         if (p) B2_CUDA(cudaFreeHost(p));
     });
 }
+int b200c_dev_memset(b200c_ctx* h, void* dst_dev, int value, size_t n) {
+    return guarded([&] {
+        if (!h || (n && !dst_dev)) throw BadArg("null pointer");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        B2_CUDA(cudaSetDevice(ctx->device));
+        fillBytes(ctx, dst_dev, value, n);
+    });
+}
 int b200c_memcpy_h2d(b200c_ctx* h, void* dst_dev, const void* src, size_t n) {
     return guarded([&] {
         if (!h) throw BadArg("null context");
         Context* ctx = reinterpret_cast<Context*>(h);
         std::lock_guard<std::mutex> lock(ctx->mu);
-        if (!B2_EMU(ctx)) B2_CUDA(cudaSetDevice(ctx->device));
+        B2_CUDA(cudaSetDevice(ctx->device));
         copyH2D(ctx, dst_dev, src, n);
         syncStream(ctx);
     });
@@ -906,7 +980,7 @@ int b200c_memcpy_d2h(b200c_ctx* h, void* dst, const void* src_dev, size_t n) {
         if (!h) throw BadArg("null context");
         Context* ctx = reinterpret_cast<Context*>(h);
         std::lock_guard<std::mutex> lock(ctx->mu);
-        if (!B2_EMU(ctx)) B2_CUDA(cudaSetDevice(ctx->device));
+        B2_CUDA(cudaSetDevice(ctx->device));
         copyD2H(ctx, dst, src_dev, n);
         syncStream(ctx);
     });

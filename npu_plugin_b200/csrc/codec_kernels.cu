@@ -570,75 +570,6 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
     uploadSmall(ctx, jobsDev, jobs.data(), sizeof(CodecJobDev) * count);
     uploadSmall(ctx, tileJobDev, tileJob.data(), sizeof(unsigned int) * ntiles);
 
-#ifdef B200C_HOST_EMULATION
-    if (B2_EMU(ctx)) {
-        // serial restatement of the three kernels on the same padded index space
-        for (unsigned long long tile = 0; tile < ntiles; ++tile) {
-            const CodecJobDev& job = jobsDev[tileJobDev[tile]];
-            const unsigned long long tileFirst = (tile - job.firstBlock / kTileBlocks) * kTileBlocks;
-            unsigned int sum = 0;
-            for (int i = 0; i < kTileBlocks; ++i) {
-                const unsigned long long g = tile * kTileBlocks + i, blk = tileFirst + i;
-                summary[g] = 0;
-                if (blk < job.nblocks) {
-                    unsigned char b[kCodecBlock], hd, bs;
-                    loadBlock(job, blk, b);
-                    const int sz = codecChoose(b, &hd, &bs);
-                    summary[g] = hd | (static_cast<unsigned int>(bs) << 8) | (static_cast<unsigned int>(sz) << 16);
-                }
-                sum += summary[g] >> 16;
-            }
-            tileSums[tile] = sum;
-        }
-        unsigned long long run = 0;
-        for (unsigned long long t = 0; t < ntiles; ++t) {
-            tileOffsets[t] = run;
-            run += tileSums[t];
-        }
-        tileOffsets[ntiles] = run;
-        layoutJobs(jobsDev, count, tileOffsets, outCap, rawFallback, ctx->errWord);
-        std::vector<unsigned char> tempOut;
-        if (inPlace) {
-            size_t need = 64;
-            for (int j = 0; j < count; ++j) need = std::max<size_t>(need, jobsDev[j].outBase + jobsDev[j].outBytes + 64);
-            tempOut.resize(need);
-            outDev = tempOut.data();
-        }
-        for (unsigned long long tile = 0; tile < ntiles; ++tile) {
-            const CodecJobDev& job = jobsDev[tileJobDev[tile]];
-            if (job.outBytes == 0) continue;
-            unsigned char* dst = outDev + job.outBase;
-            const unsigned long long jobFirstTile = job.firstBlock / kTileBlocks;
-            const unsigned long long tileFirst = (tile - jobFirstTile) * kTileBlocks;
-            if (rawFallback == 1 && job.notSmaller) {
-                if (tileFirst == 0) std::memcpy(dst, job.in, job.n);
-                continue;
-            }
-            unsigned char* records = dst + kCodecHeaderBytes + 4 * job.nsuper;
-            unsigned long long at = tileOffsets[tile] - tileOffsets[jobFirstTile];
-            if (tileFirst == 0) writeStreamHeader(job, dst);
-            for (int i = 0; i < kTileBlocks; ++i) {
-                const unsigned long long g = tile * kTileBlocks + i, blk = tileFirst + i;
-                if (blk >= job.nblocks) break;
-                unsigned char b[kCodecBlock];
-                loadBlock(job, blk, b);
-                if (blk % kCodecSuper == 0) putU32(dst + kCodecHeaderBytes + 4 * (blk / kCodecSuper), static_cast<unsigned int>(at));
-                codecWriteRecord(b, static_cast<unsigned char>(summary[g]), static_cast<unsigned char>(summary[g] >> 8), records + at);
-                at += summary[g] >> 16;
-            }
-            if (tileFirst + kTileBlocks >= job.nblocks) {
-                for (unsigned long long a = kCodecHeaderBytes + 4 * job.nsuper + job.recordsBytes; a < job.streamBytes; ++a) dst[a] = 0;
-            }
-        }
-        ctx->launches += 3;
-        std::memcpy(jobs.data(), jobsDev, sizeof(CodecJobDev) * count);
-        if (inPlace) {
-            for (int j = 0; j < count; ++j) {
-                if (jobs[j].outBytes) std::memcpy(const_cast<unsigned char*>(jobs[j].in), outDev + jobs[j].outBase, jobs[j].outBytes);
-            }
-        }
-    } else
-#endif
     {
         const int grid = static_cast<int>(std::max<unsigned long long>(1, std::min<unsigned long long>(ntiles, ctx->smCount * 8ULL)));
         codecAnalyzeKernel<<<grid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, ntiles, summary, tileSums);
@@ -729,7 +660,18 @@ void codecCompressNoAlloc(int device, const unsigned char* inDev, size_t n, unsi
     }
     if (cap < codecBound(n)) throw Capacity("output capacity below b200c_btc_bound(n)");
     if (device < 0 || device >= kNoAllocMaxDevices) throw BadArg("device index out of range");
-    B2_CUDA(cudaSetDevice(device));
+    // the caller's current device is put back when the call returns, whichever way it returns
+    struct DeviceScope {
+        int previous = -1;
+        explicit DeviceScope(int d) {
+            B2_CUDA(cudaGetDevice(&previous));
+            if (previous != d) B2_CUDA(cudaSetDevice(d));
+        }
+        ~DeviceScope() {
+            int now = -1;
+            if (previous >= 0 && cudaGetDevice(&now) == cudaSuccess && now != previous) cudaSetDevice(previous);
+        }
+    } deviceScope(device);
 
     unsigned char* scratch = nullptr;
     {
@@ -750,7 +692,12 @@ void codecCompressNoAlloc(int device, const unsigned char* inDev, size_t n, unsi
     unsigned long long* tileOffsets = reinterpret_cast<unsigned long long*>(scratch + 2048);
     int* errDev = reinterpret_cast<int*>(scratch + 3072);
     unsigned int* summary = reinterpret_cast<unsigned int*>(scratch + kNoAllocSmall);
-    static_assert(sizeof(CodecJobDev) <= 256 && kNoAllocMaxTiles * 4 <= 768 && (kNoAllocMaxTiles + 1) * 8 <= 1024, "layout");
+    // slots: job record [0, 256), tile table and emit list [256, 1024), tile sums [1024, 2048),
+    // tile offsets [2048, 3072), error word at 3072, summaries from kNoAllocSmall
+    static_assert(sizeof(CodecJobDev) <= 256 && 2 * kNoAllocMaxTiles * 4 <= 768 && (kNoAllocMaxTiles + 1) * 4 <= 1024 &&
+                          (kNoAllocMaxTiles + 1) * 8 <= 1024 && kNoAllocSmall >= 3072 + sizeof(int) &&
+                          kNoAllocMaxTiles * kTileBlocks * kCodecBlock >= kNoAllocMaxInput,
+                  "layout of the fixed scratch buffer");
 
     CodecJobDev job;
     std::memset(&job, 0, sizeof(job));
@@ -816,6 +763,13 @@ B2_HD void decodeGroup(const DecodeParams& p, unsigned long long s) {
             bad = 1;
             break;
         }
+        // a SPARSE record's size is read from its 8 mask bytes: they must lie inside the stream before
+        // they are looked at; modes above SPARSE do not exist
+        const int headerMode = records[at] >> 5;
+        if (headerMode > 4 || (headerMode == 4 && at + 9 > limit)) {
+            bad = 1;
+            break;
+        }
         const int need = codecRecordSize(records[at], records + at + 1);
         if (at + need > limit) {
             bad = 1;
@@ -867,12 +821,6 @@ size_t codecDecompress(Context* ctx, const unsigned char* inDev, size_t n, unsig
         refThrow("codec: inconsistent stream header");
     }
     if (p.n > cap) throw Capacity("codec: output capacity too small");
-#ifdef B200C_HOST_EMULATION
-    if (B2_EMU(ctx)) {
-        for (unsigned long long s = 0; s < p.nsuper; ++s) decodeGroup(p, s);
-        ++ctx->launches;
-    } else
-#endif
     {
         const int grid = static_cast<int>(std::max<unsigned long long>(1, std::min<unsigned long long>((p.nsuper + 63) / 64, ctx->smCount * 16ULL)));
         codecDecodeKernel<<<grid, 64, 0, ctx->stream>>>(p);

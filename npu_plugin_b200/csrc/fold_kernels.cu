@@ -25,13 +25,6 @@ __global__ void __launch_bounds__(256) foldGenericKernel(const __grid_constant__
 void launchGeneric(Context* ctx, const GenParams& p) {
     const long long units = p.outUnits + std::max<long long>(0, p.totalBytes - p.dataBytes);
     if (units <= 0) return;
-#ifdef B200C_HOST_EMULATION
-    if (B2_EMU(ctx)) {
-        for (long long u = 0; u < units; ++u) genericUnit(p, u);
-        ++ctx->launches;
-        return;
-    }
-#endif
     foldGenericKernel<<<gridFor(ctx, units, 256, 8), 256, 0, ctx->stream>>>(p, units);
     B2_CUDA(cudaGetLastError());
     ++ctx->launches;
@@ -69,13 +62,6 @@ void launchExpandDilated(Context* ctx, const void* src, void* dst, int es, long 
     if (n <= 0) return;
     const unsigned char* s = static_cast<const unsigned char*>(src);
     unsigned char* d = static_cast<unsigned char*>(dst);
-#ifdef B200C_HOST_EMULATION
-    if (B2_EMU(ctx)) {
-        for (long long o = 0; o < n; ++o) expandDilatedUnit(s, d, es, ky, kx, dky, dkx, d0, d1, fill, o);
-        ++ctx->launches;
-        return;
-    }
-#endif
     expandDilatedKernel<<<gridFor(ctx, n, 256, 8), 256, 0, ctx->stream>>>(s, d, es, ky, kx, dky, dkx, d0, d1, fill, n);
     B2_CUDA(cudaGetLastError());
     ++ctx->launches;
@@ -121,13 +107,6 @@ __global__ void __launch_bounds__(256) relocateWeightsTableKernel(const __grid_c
 
 void launchRelocateWeightsTable(Context* ctx, const RelocateParams& p) {
     if (p.oc <= 0) return;
-#ifdef B200C_HOST_EMULATION
-    if (B2_EMU(ctx)) {
-        for (long long oc = 0; oc < p.oc; ++oc) relocateUnit(p, oc);
-        ++ctx->launches;
-        return;
-    }
-#endif
     relocateWeightsTableKernel<<<gridFor(ctx, p.oc, 256, 8), 256, 0, ctx->stream>>>(p);
     B2_CUDA(cudaGetLastError());
     ++ctx->launches;
@@ -211,26 +190,6 @@ __global__ void __launch_bounds__(256) rowStatsKernel(const __grid_constant__ Ro
 }
 
 void launchRowStats(Context* ctx, const RowStatsParams& rp) {
-#ifdef B200C_HOST_EMULATION
-    if (B2_EMU(ctx)) {
-        for (long long row = 0; row < rp.rows; ++row) {
-            RowAcc a{-INFINITY, INFINITY, 0.0f};
-            int err = E_NONE;
-            long long coord[kMaxDims];
-            for (long long j = 0; j < rp.rowElems; ++j) {
-                rowCoords(rp, row, j, coord);
-                const float w = toFloatChecked(evalAt(rp.view, coord, err), err);
-                a.mx = std::fmax(a.mx, w);
-                a.mn = std::fmin(a.mn, w);
-                a.amax = std::fmax(a.amax, std::fabs(w));
-            }
-            rowFinish(rp, row, a);
-            if (err != E_NONE && *rp.view.err == E_NONE) *rp.view.err = err;
-        }
-        ++ctx->launches;
-        return;
-    }
-#endif
     const int grid = static_cast<int>(std::min<long long>(rp.rows, static_cast<long long>(ctx->smCount) * 8));
     rowStatsKernel<<<grid, 256, 0, ctx->stream>>>(rp);
     B2_CUDA(cudaGetLastError());
@@ -270,13 +229,6 @@ void launchSwizzleCopy(Context* ctx, const void* src, long long srcBytes, void* 
     if (chunks <= 0) return;
     const unsigned char* s = static_cast<const unsigned char*>(src);
     unsigned char* d = static_cast<unsigned char*>(dst);
-#ifdef B200C_HOST_EMULATION
-    if (B2_EMU(ctx)) {
-        for (long long c = 0; c < chunks; ++c) swizzleChunk(s, srcBytes, d, c, key, tailByte);
-        ++ctx->launches;
-        return;
-    }
-#endif
     const int aligned = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0;
     swizzleCopyKernel<<<gridFor(ctx, chunks, 256, 8), 256, 0, ctx->stream>>>(s, srcBytes, d, chunks, key, tailByte,
                                                                               aligned);
@@ -333,13 +285,6 @@ void launchSubViewBits(Context* ctx, const void* src, void* dst, int rank, const
     p.base = base;
     p.outBits = outBits;
     const long long bytes = (outBits + 7) / 8;
-#ifdef B200C_HOST_EMULATION
-    if (B2_EMU(ctx)) {
-        for (long long i = 0; i < bytes; ++i) subViewByte(p, i);
-        ++ctx->launches;
-        return;
-    }
-#endif
     subViewBitsKernel<<<gridFor(ctx, bytes, 256, 8), 256, 0, ctx->stream>>>(p, bytes);
     B2_CUDA(cudaGetLastError());
     ++ctx->launches;

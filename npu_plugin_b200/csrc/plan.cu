@@ -223,8 +223,8 @@ void Planner::runGeneric(const GenParams& p) {
     flushPendingStats();
     ImmediateLaunches scope(_ctx, !_emittingFinal);
     TileItem item;
-    if (!B2_EMU(_ctx) && tryLaunchDequantRows(_ctx, p)) return;
-    if (!B2_EMU(_ctx) && makeTileItem(p, &item)) {
+    if (tryLaunchDequantRows(_ctx, p)) return;
+    if (makeTileItem(p, &item)) {
         launchTile(_ctx, item);
     } else {
         launchGeneric(_ctx, p);
@@ -746,7 +746,7 @@ void Planner::quantizeSynth(const Transformation& x, const TensorType& outType) 
         const bool rowsContiguous = isPlain(v) && !_s.splat && rowDim == 0 &&
                                     (v.srcTag == T_F16 || v.srcTag == T_F32) &&
                                     static_cast<size_t>(rp.rowElems) * tagBytes(v.srcTag) <= rowQuantMaxRowBytes();
-        if (rowsContiguous && !B2_EMU(_ctx)) {
+        if (rowsContiguous) {
             _pending.active = true;
             _pending.stats = rp;
             _pending.src = v.src;
@@ -835,7 +835,7 @@ void Planner::getSparsityMap(const TensorType& outType, int swizzleKey) {
     const size_t bytes = static_cast<size_t>(oc * outBits / 8);
     void* dst = nullptr;
     const bool swzNext = finalSwizzleFollows();
-    if (!B2_EMU(_ctx) && bytes > 0 && tagBytes(tag) == 1 && work % 16 == 0 && _finalDst && (_isLast || swzNext) &&
+    if (bytes > 0 && tagBytes(tag) == 1 && work % 16 == 0 && _finalDst && (_isLast || swzNext) &&
         ((reinterpret_cast<uintptr_t>(dense) | reinterpret_cast<uintptr_t>(_finalDst)) & 15) == 0) {
         // 8-bit elements and the result is the caller's output: one (batched) launch writes the map
         // where it belongs, through the swizzle rotation when the chain ends in SwizzleConstant
@@ -906,7 +906,7 @@ void Planner::sparsify(const Transformation& x) {  // sparsify.cpp:115-186
     const void* dense = denseAs(tag);
 
     const bool swzNext = finalSwizzleFollows();
-    if (!B2_EMU(_ctx) && eb == 1 && oc > 0 && work > 0 && work % 16 == 0 && _finalDst && (_isLast || swzNext) &&
+    if (eb == 1 && oc > 0 && work > 0 && work % 16 == 0 && _finalDst && (_isLast || swzNext) &&
         ((reinterpret_cast<uintptr_t>(dense) | reinterpret_cast<uintptr_t>(_finalDst)) & 15) == 0 &&
         (x.hasAux || _ctx->batching)) {
         // 8-bit elements and the result is the caller's output: count, channel offsets and the
@@ -1148,7 +1148,7 @@ size_t Planner::emitCopyTo(void* dst, size_t cap, int swizzleKey, int64_t totalB
         // nothing to compute: a device copy, or the chunk-rotating copy when swizzled.  Inside a batched
         // fold, small pass-through constants and swizzle-only chains join the one tile launch instead of
         // paying a copy call each.
-        if (_ctx->batching && _emittingFinal && !B2_EMU(_ctx) && dataBytes <= (16ll << 20) && n > 0) {
+        if (_ctx->batching && _emittingFinal && dataBytes <= (16ll << 20) && n > 0) {
             runGeneric(p);
         } else if (p.swizzleKey < 0) {
             copyD2D(_ctx, dst, v.src, static_cast<size_t>(dataBytes));

@@ -21,6 +21,7 @@
 #include "runtime.h"
 
 #include <algorithm>
+#include <atomic>
 
 namespace b200c {
 
@@ -648,10 +649,12 @@ void launchSmemT(Context* ctx, const RowQuantParams* one, const RowQuantParams* 
                  int nitems, long long totalGroups, size_t smem) {
     constexpr int ROWS_PER_CTA = 256 / TPR;
     {
-        // as much shared memory per SM as the part offers: the staged rows, not the L1, bound the residency
-        static bool carved = false;
-        if (!carved) {
-            carved = true;
+        // as much shared memory per SM as the part offers: the staged rows, not the L1, bound the residency.
+        // Function attributes belong to a device: one bit per device, set once by whichever thread gets there
+        // first (a second thread setting the same attribute again is harmless).
+        static std::atomic<unsigned long long> carved{0};
+        const unsigned long long bit = 1ull << (ctx->device & 63);
+        if (!(carved.fetch_or(bit) & bit)) {
             cudaFuncSetAttribute(rowQuantSmemKernel<T, TPR, SCHEME>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared);
             cudaFuncSetAttribute(rowQuantSmemBatchKernel<T, TPR, SCHEME>, cudaFuncAttributePreferredSharedMemoryCarveout,

@@ -1,6 +1,7 @@
 // Per-context runtime state: stream, scratch arena, error word, launch accounting.
 #pragma once
 
+#include "../../include/b200const.h"
 #include "ctype.h"
 #include "view.h"
 
@@ -20,15 +21,6 @@ namespace b200c {
             throw ::b200c::CudaFail(std::string(#call) + ": " + cudaGetErrorString(e_));           \
         }                                                                                          \
     } while (0)
-
-// Debug build only (B200C_HOST_EMULATION): kernels written as per-unit functions can be run on the
-// host to exercise the planner without a GPU.  The shipped library is never built with this macro,
-// and B2_EMU() is then the constant false.
-#ifdef B200C_HOST_EMULATION
-#define B2_EMU(ctx) ((ctx)->emulated)
-#else
-#define B2_EMU(ctx) false
-#endif
 
 struct Context;
 
@@ -131,7 +123,6 @@ struct Context {
     int64_t launches = 0;
     int smCount = 148;
     size_t l2Bytes = 0;
-    bool emulated = false;
     bool batching = false;                 // inside b200c_fold_batch: fused quantiser launches are queued
     std::vector<RowQuantParams> rqBatch;
     std::vector<TileItem> tileBatch;
@@ -153,6 +144,23 @@ struct Context {
     cudaEvent_t stageDone[2] = {nullptr, nullptr};
     bool stagePending[2] = {false, false};
     int stageSet = 0;
+    // multi-GPU exchange (exchange_kernels.cu), created on first use: a second stream for pushes and
+    // downloads, completion counters of the push kernels (each reset by its last CTA), the status word
+    // of the bounded waits, and a ring of parameter buffers the arena's rewinding cannot touch
+    static constexpr unsigned kXferCounters = 256, kXferParamSlots = 8;
+    struct XferParams {
+        void* dev = nullptr;
+        void* host = nullptr;
+        size_t bytes = 0;
+        cudaEvent_t done = nullptr;
+        bool pending = false;
+    };
+    cudaStream_t xferStream = nullptr;
+    cudaEvent_t xferEvent = nullptr;
+    unsigned int* xferCounters = nullptr;
+    int* xferStatus = nullptr;
+    unsigned xferCounterNext = 0, xferSlotNext = 0;
+    XferParams xferParams[kXferParamSlots];
 };
 
 
@@ -186,7 +194,7 @@ __device__ __forceinline__ int findBatchItem(const long long* __restrict__ start
 }
 #endif
 
-// device memory through the context (host malloc under emulation)
+// device memory through the context
 void* devMalloc(Context* ctx, size_t bytes);
 void devFree(Context* ctx, void* p);
 void copyH2D(Context* ctx, void* dst, const void* src, size_t n);
@@ -296,6 +304,24 @@ size_t codecNoAllocMaxInput();
 void codecCompressNoAlloc(int device, const unsigned char* inDev, size_t n, unsigned char* outDev, size_t cap,
                           cudaStream_t stream, size_t* outN, bool* notSmaller);
 size_t codecDecompress(Context* ctx, const unsigned char* inDev, size_t n, unsigned char* outDev, size_t cap);
+
+// whole-buffer reductions (probe_kernels.cu)
+bool probeSplat(Context* ctx, const void* dataDev, size_t nbytes, int elemBytes);
+void digestBatch(Context* ctx, int count, const void* const* bufs, const size_t* sizes, unsigned long long* out);
+
+// multi-GPU exchange (exchange_kernels.cu)
+void registerAllocation(void* p, size_t n);
+void unregisterAllocation(void* p);
+void ipcExport(Context* ctx, void* devPtr, size_t size, unsigned char handle[64], unsigned long long* offset);
+void* ipcOpen(Context* ctx, const unsigned char handle[64], unsigned long long offset);
+void ipcClose(Context* ctx, void* mapped);
+void pushSegments(Context* ctx, const b200c_copy_seg* segs, int count, const unsigned long long* waitFlag,
+                  unsigned long long waitValue, unsigned long long* doneFlag, unsigned long long doneValue,
+                  unsigned int timeoutMs, int mode, int ctas);
+void waitFlags(Context* ctx, const unsigned long long* flagsDev, int count, unsigned long long value, unsigned int timeoutMs);
+void signalFlags(Context* ctx, unsigned long long* const* targets, int count, unsigned long long value);
+int exchangeStatus(Context* ctx);
+void releaseExchange(Context* ctx);
 
 // synthetic weights
 void launchSynthFill(Context* ctx, void* dst, long long count, int dtype, int dist, double p0, double p1,

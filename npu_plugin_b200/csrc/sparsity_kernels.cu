@@ -93,13 +93,6 @@ void launchSparsityMap(Context* ctx, const void* src, int tag, long long oc, lon
     p.swizzleKey = swizzleKey;
     const long long bytes = oc * p.outBytesPerOC;
     if (bytes <= 0) return;
-#ifdef B200C_HOST_EMULATION
-    if (B2_EMU(ctx)) {
-        for (long long i = 0; i < bytes; ++i) mapByte(p, i);
-        ++ctx->launches;
-        return;
-    }
-#endif
     const bool fast = tagBytes(tag) == 1 && work % 16 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
                       (reinterpret_cast<uintptr_t>(dstBits) & 1) == 0;
     if (fast) {
@@ -150,17 +143,6 @@ __global__ void __launch_bounds__(256) countNonSparseKernel(const void* __restri
 void launchCountNonSparse(Context* ctx, const void* src, int tag, long long oc, long long work,
                           unsigned long long sparseBits, long long* counts) {
     if (oc <= 0) return;
-#ifdef B200C_HOST_EMULATION
-    if (B2_EMU(ctx)) {
-        for (long long c = 0; c < oc; ++c) {
-            long long n = 0;
-            for (long long j = 0; j < work; ++j) n += differs(src, c * work + j, tag, sparseBits);
-            counts[c] = n;
-        }
-        ++ctx->launches;
-        return;
-    }
-#endif
     const int grid = static_cast<int>(std::min<long long>(oc, ctx->smCount * 8LL));
     countNonSparseKernel<<<grid, 256, 0, ctx->stream>>>(src, tag, oc, work, sparseBits, counts);
     B2_CUDA(cudaGetLastError());
@@ -208,18 +190,6 @@ __global__ void __launch_bounds__(1024) sparsifyOffsetsKernel(const long long* _
 
 void launchSparsifyOffsets(Context* ctx, const long long* counts, long long oc, int elemBytes, long long* offsets,
                            long long* total) {
-#ifdef B200C_HOST_EMULATION
-    if (B2_EMU(ctx)) {
-        long long run = 0;
-        for (long long c = 0; c < oc; ++c) {
-            offsets[c] = run;
-            run += (counts[c] * elemBytes + 15) & ~15ll;
-        }
-        *total = run;
-        ++ctx->launches;
-        return;
-    }
-#endif
     sparsifyOffsetsKernel<<<1, 1024, 0, ctx->stream>>>(counts, oc, elemBytes, offsets, total);
     B2_CUDA(cudaGetLastError());
     ++ctx->launches;
@@ -272,26 +242,6 @@ void launchSparsifyScatter(Context* ctx, const void* src, int tag, long long oc,
                            unsigned long long sparseBits, const long long* offsets, void* dst, long long dstBytes,
                            int swizzleKey, int* err) {
     if (oc <= 0 || work <= 0) return;
-#ifdef B200C_HOST_EMULATION
-    if (B2_EMU(ctx)) {
-        const int eb = tagBytes(tag);
-        for (long long c = 0; c < oc; ++c) {
-            long long at = offsets[c];
-            for (long long j = 0; j < work; ++j) {
-                const long long idx = c * work + j;
-                if (!differs(src, idx, tag, sparseBits)) continue;
-                if (at + eb > dstBytes) {
-                    if (*err == E_NONE) *err = E_SPARSE_OVERFLOW;
-                } else {
-                    storeRawAt(dst, swizzleAddr(at, swizzleKey), eb, loadRaw(src, idx, tag));
-                }
-                at += eb;
-            }
-        }
-        ++ctx->launches;
-        return;
-    }
-#endif
     const int grid = static_cast<int>(std::min<long long>(oc, ctx->smCount * 8LL));
     sparsifyScatterKernel<<<grid, 256, 0, ctx->stream>>>(src, tag, oc, work, sparseBits, offsets,
                                                          static_cast<unsigned char*>(dst), dstBytes, swizzleKey, err);

@@ -31,21 +31,71 @@ __device__ __forceinline__ Philox4 philox4x32_10(unsigned long long counter, uns
     return Philox4{c0, c1, c2, c3};
 }
 
-__device__ __forceinline__ float uniform01(unsigned int u) {  // (0, 1]
+__device__ __forceinline__ float uniform01(unsigned int u) {  // (0, 1]: (k + 1) * 2^-24 for the top 24 bits k
     return (static_cast<float>(u >> 8) + 1.0f) * (1.0f / 16777216.0f);
+}
+
+// The generator is specified down to the rounding of every operation, so that a CPU restatement
+// produces the same bytes: only IEEE single-precision add / multiply / divide / square root (each
+// rounded to nearest, never fused -- the library is built with --fmad=false) and integer arithmetic.
+// No math-library function is involved.
+
+// ln(u) for a normal float u in (0, 1]:  u = m * 2^e with m in (sqrt(1/2), sqrt(2)],
+// ln m = 2 atanh(s), s = (m - 1) / (m + 1), |s| <= 0.1716, series up to s^9 (next term < 2e-9 relative).
+__device__ __forceinline__ float synthLog(float u) {
+    const unsigned int bits = __float_as_uint(u);
+    int e = static_cast<int>(bits >> 23) - 127;
+    float m = __uint_as_float((bits & 0x007FFFFFu) | 0x3F800000u);
+    if (m > 1.41421354f) {
+        m = m * 0.5f;
+        e += 1;
+    }
+    const float s = (m - 1.0f) / (m + 1.0f);
+    const float t = s * s;
+    float p = 0.111111112f;
+    p = p * t + 0.142857149f;
+    p = p * t + 0.2f;
+    p = p * t + 0.333333343f;
+    const float lnm = 2.0f * (s + s * (t * p));
+    return lnm + static_cast<float>(e) * 0.693147182f;
+}
+
+// cos and sin of 2*pi*(k / 2^24) for a 24-bit turn fraction k: the top three bits pick the octant, the
+// low 21 bits (mirrored in odd octants) give an angle in [0, pi/4] for the Taylor polynomials.
+__device__ __forceinline__ void synthSinCosTurn(unsigned int k, float* sn, float* cs) {
+    const unsigned int oct = (k >> 21) & 7u, r = k & 0x1FFFFFu;
+    const unsigned int rr = (oct & 1u) ? (0x200000u - r) : r;
+    const float x = static_cast<float>(rr) * 3.74507039e-07f;  // (pi / 4) / 2^21
+    const float t = x * x;
+    float ps = 2.75573192e-06f;            // 1/9!
+    ps = ps * t - 1.98412701e-04f;         // 1/7!
+    ps = ps * t + 8.33333377e-03f;         // 1/5!
+    ps = ps * t - 0.166666672f;            // 1/3!
+    const float sx = x + x * (t * ps);
+    float pc = -2.75573200e-07f;           // 1/10!
+    pc = pc * t + 2.48015876e-05f;         // 1/8!
+    pc = pc * t - 1.38888892e-03f;         // 1/6!
+    pc = pc * t + 4.16666679e-02f;         // 1/4!
+    pc = pc * t - 0.5f;
+    const float cx = 1.0f + t * pc;
+    // octants 0,3,4,7 keep (cos, sin) of the reduced angle, 1,2,5,6 swap them; signs follow the quadrant
+    const bool swap = ((oct + 1u) & 2u) != 0;
+    const float c = swap ? sx : cx, sv = swap ? cx : sx;
+    *cs = ((oct + 2u) & 4u) ? -c : c;      // cosine is negative in octants 2..5
+    *sn = (oct & 4u) ? -sv : sv;           // sine is negative in octants 4..7
 }
 
 // four samples per counter value
 __device__ __forceinline__ void synthFour(int dist, float p0, float p1, Philox4 r, float* out) {
     if (dist == 0) {  // normal(0, p0): two Box-Muller pairs
-        const float r0 = sqrtf(-2.0f * logf(uniform01(r.x))), r1 = sqrtf(-2.0f * logf(uniform01(r.z)));
+        const float r0 = sqrtf(-2.0f * synthLog(uniform01(r.x))), r1 = sqrtf(-2.0f * synthLog(uniform01(r.z)));
         float s0, c0, s1, c1;
-        sincospif(2.0f * uniform01(r.y), &s0, &c0);
-        sincospif(2.0f * uniform01(r.w), &s1, &c1);
-        out[0] = p0 * r0 * c0;
-        out[1] = p0 * r0 * s0;
-        out[2] = p0 * r1 * c1;
-        out[3] = p0 * r1 * s1;
+        synthSinCosTurn(((r.y >> 8) + 1u) & 0xFFFFFFu, &s0, &c0);
+        synthSinCosTurn(((r.w >> 8) + 1u) & 0xFFFFFFu, &s1, &c1);
+        out[0] = (p0 * r0) * c0;
+        out[1] = (p0 * r0) * s0;
+        out[2] = (p0 * r1) * c1;
+        out[3] = (p0 * r1) * s1;
     } else if (dist == 1) {  // uniform integer in [-127, 127], zero with probability p0
         const unsigned int v[4] = {r.x, r.y, r.z, r.w};
         const unsigned int cut = static_cast<unsigned int>(fminf(p0, 1.0f) * 65535.0f);
@@ -60,7 +110,7 @@ __device__ __forceinline__ void synthFour(int dist, float p0, float p1, Philox4 
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float u = uniform01(v[i] & 0xFFFFFF00u);
-            const float mag = -p0 * logf(u);
+            const float mag = -(p0 * synthLog(u));
             float q = rintf((v[i] & 0x80u) ? -mag : mag);
             q = fminf(fmaxf(q, -127.0f), 127.0f);
             out[i] = ((v[i] & 0x7Fu) * 2u < cut) ? 0.0f : q;
@@ -101,7 +151,6 @@ __global__ void __launch_bounds__(256) synthFillKernel(T* __restrict__ dst, long
 void launchSynthFill(Context* ctx, void* dst, long long count, int dtype, int dist, double p0, double p1,
                      unsigned long long seed, unsigned long long stream) {
     if (count <= 0) return;
-    if (B2_EMU(ctx)) throw NotBuilt("synthetic fill needs a device");
     const long long groups = (count + 3) >> 2;
     const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>((groups + 255) / 256, ctx->smCount * 16LL)));
     const float a = static_cast<float>(p0), b = static_cast<float>(p1);

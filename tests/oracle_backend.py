@@ -39,6 +39,10 @@ def _load():
     lib.orc_btc_bound.argtypes = [C.c_size_t, _P(C.c_size_t)]
     lib.orc_btc_compress.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, _P(C.c_size_t)]
     lib.orc_btc_decompress.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, _P(C.c_size_t)]
+    lib.orc_synth_fill.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_double, C.c_double, C.c_uint64,
+                                   C.c_uint64]
+    lib.orc_digest64.restype = C.c_uint64
+    lib.orc_digest64.argtypes = [C.c_void_p, C.c_uint64]
     lib.orc_f32_to_f16.restype = C.c_uint16
     lib.orc_f32_to_f16.argtypes = [C.c_float]
     lib.orc_f16_to_f32.restype = C.c_float
@@ -136,3 +140,63 @@ class OracleBackend:
         rc = self.lib.orc_btc_decompress(buf.ctypes.data, buf.size, out.ctypes.data, n_out, C.byref(n))
         K.raise_for(rc, self._err())
         return out[:n.value]
+
+    def synth_fill(self, count, dtype, dist, p0, p1, seed, stream_id):
+        """CPU twin of b200c_synth_fill: the same bytes as the device generator."""
+        out = np.zeros(int(count) * A.dtype_bits(dtype) // 8, dtype=np.uint8)
+        rc = self.lib.orc_synth_fill(out.ctypes.data, int(count), dtype, dist, p0, p1, seed, stream_id)
+        if rc != 0:
+            raise ValueError("orc_synth_fill: bad arguments")
+        return out
+
+    def synth_of(self, decl, seed):
+        dt, dist, p0, p1 = decl.synth
+        return self.synth_fill(decl.nbytes * 8 // A.dtype_bits(dt), dt, dist, p0, p1, seed, decl.stream)
+
+    def digest64(self, data):
+        buf = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        return int(self.lib.orc_digest64(buf.ctypes.data if buf.size else None, buf.size))
+
+
+class OracleShardFolder:
+    """CPU stand-in for npu_plugin_b200.blob.ShardFolder with the same interface: "pointers" are addresses
+    of host memory, folding and compression run in the oracle.  Lets the sharded whole-model routine run
+    on CPU ranks (gloo) with real folded bytes."""
+
+    def __init__(self, backend, decls):
+        from npu_plugin_b200.blob import MIN_COMPRESS_BYTES, SEGMENT_ALIGN
+        self.b, self.decls = backend, decls
+        self.folded_offsets, self.folded_sizes = [], []
+        at = 0
+        for d in decls:
+            size = backend.infer_type(d.base_type, d.transforms).getTotalAllocSize()
+            self.folded_offsets.append(at)
+            self.folded_sizes.append(size)
+            at = (at + size + SEGMENT_ALIGN - 1) // SEGMENT_ALIGN * SEGMENT_ALIGN
+        self.folded_bytes = max(at, 1)
+        self.comp_idx = [i for i, d in enumerate(decls) if d.compress and self.folded_sizes[i] >= MIN_COMPRESS_BYTES]
+
+    @staticmethod
+    def _view(ptr, n):
+        return np.ctypeslib.as_array((C.c_ubyte * max(1, n)).from_address(ptr))[:n]
+
+    def fold(self, data_ptrs, folded_ptr, data_on_device=True, side_ptrs=None, max_batch_bytes=None):
+        for i, d in enumerate(self.decls):
+            x = self._view(data_ptrs[i], d.nbytes)
+            ts = d.transforms
+            for t in ts:
+                if t.kind == A.X_QUANTIZE_SYNTH:
+                    oc = d.base_type.shape[0]
+                    t.side0, t.side1 = np.zeros(oc, np.float32), np.zeros(oc, np.int32)
+            out = self.b.fold(d.base_type, x, d.is_splat, ts).copyTo()
+            self._view(folded_ptr + self.folded_offsets[i], self.folded_sizes[i])[:out.size] = out
+
+    def compress_inplace(self, folded_ptr):
+        size, flag = list(self.folded_sizes), [False] * len(self.decls)
+        for i in self.comp_idx:
+            slot = self._view(folded_ptr + self.folded_offsets[i], self.folded_sizes[i])
+            stream, not_smaller = self.b.btc_compress(slot.copy())
+            if not not_smaller:
+                slot[:stream.size] = stream
+                size[i], flag[i] = stream.size, True
+        return [(i, self.folded_offsets[i], size[i], flag[i]) for i in range(len(self.decls))]
