@@ -327,21 +327,20 @@ def run_e2e(torch, dist, backend, stream, decls, rank, world, comm, args, algori
     side = [(a.data_ptr(), z.data_ptr()) if a is not None else None for a, z in zip(scales, zps)]
     host_blob = torch.empty(sf.layout.blob_bytes, dtype=torch.uint8, pin_memory=True) if rank == 0 else None
     in_ptrs = [h.data_ptr() for h in host_in]
-    blob = sf.t.blob_ptr()
     state = {"d2h": 0, "table": None}
 
     def step():
         d2h = [0]
 
         def hooks(name, k):
-            if name == "codec1" and rank == 0:  # rank 0's own chunk is complete: it goes home while the next one uploads
-                off, n = sf.chunk_span(0, k)
-                backend.copy_segments_async([(blob + off, host_blob.data_ptr() + off, n)], mode=1)
-                d2h[0] += n
+            # rank 0's chunk k is complete: it goes home, and so do the peers' chunks k once they have arrived,
+            # while the next chunk uploads
+            if name == "codec1" and rank == 0:
+                d2h[0] += sf.download_chunk(host_blob.data_ptr(), k)
 
         rows = sf.step(in_ptrs, side, False, hooks, max_batch_bytes=1 << 30)
         if rank == 0:
-            d2h[0] += sf.download(host_blob.data_ptr(), own=False)
+            d2h[0] += sf.download(host_blob.data_ptr(), first_chunk=len(sf.folders))
             state["table"] = sf.collect(rows)
             backend.stream_join()  # the release follows the download of the blob
             sf.release()
@@ -437,8 +436,8 @@ def main():
                     help="share of the constants rank 0 keeps when several ranks push into its blob (default: balances its "
                          "compute against its NVLink ingress)")
     ap.add_argument("--chunks", type=int, default=4, help="chunks a pushing rank cuts its share into")
-    ap.add_argument("--push-mode", type=int, default=0, choices=[0, 1], help="0: copy kernel, 1: copy engine")
-    ap.add_argument("--push-ctas", type=int, default=64)
+    ap.add_argument("--push-mode", type=int, default=2, choices=[0, 1, 2], help="0: copy kernel, 1: copy engine, 2: bulk-copy kernel")
+    ap.add_argument("--push-ctas", type=int, default=32)
     ap.add_argument("--exchange-timeout-ms", type=int, default=20000)
     args = ap.parse_args()
 

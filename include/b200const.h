@@ -348,13 +348,20 @@ B200C_API int b200c_detect_splat(b200c_ctx* ctx, const void* data, size_t nbytes
  *                          receives done_value after all bytes have landed;
  *   mode 0               : a copy kernel with plain 128-bit loads and stores (`ctas` CTAs; peer
  *                          memory is only ever stored to); a wait that times out cancels the copy;
- *   mode 1               : the copy engine (one cudaMemcpyAsync per segment).
- * b200c_wait_flags queues, on the context's stream, a bounded wait until each of `count`
- * consecutive device words holds at least `value`; b200c_signal_flags queues stores of `value`
+ *   mode 1               : the copy engine (one cudaMemcpyAsync per segment);
+ *   mode 2               : a copy kernel built on the SM's bulk-copy unit (cp.async.bulk through a
+ *                          shared-memory ring, no multicast): the form for a pusher whose SMs
+ *                          fold the next chunk meanwhile, since stalled NVLink stores then queue
+ *                          in the copy unit instead of the load/store pipeline.  Same cancel rule
+ *                          as mode 0; a copy that stalls inside the kernel sets bit 2 of the status.
+ * b200c_wait_flags queues, on the context's stream (or, with on_transfer_stream != 0, on its
+ * transfer stream, so that only the copies queued there afterwards are held back), a bounded wait
+ * until each of `count` consecutive device words holds at least `value`; b200c_signal_flags queues
+ * stores of `value`
  * to the given device words (peer memory allowed).  No wait spins for more than timeout_ms:
  * it then records the failure and lets the stream continue.  b200c_exchange_status waits for
  * both streams and returns the failures since the last call in *timed_out (bit 0: a release
- * wait of a pusher, bit 1: a done wait of the assembling rank) -- the caller turns a non-zero
+ * wait of a pusher, bit 1: a done wait of the assembling rank, bit 2: a stalled bulk copy) -- the caller turns a non-zero
  * value into its own error.                                                                      */
 typedef struct b200c_ipc_handle {
     unsigned char handle[64];
@@ -372,7 +379,8 @@ B200C_API int b200c_ipc_close(b200c_ctx* ctx, void* mapped);
 B200C_API int b200c_copy_segments_async(b200c_ctx* ctx, const b200c_copy_seg* segs, int count, const uint64_t* wait_flag,
                                         uint64_t wait_value, uint64_t* done_flag, uint64_t done_value,
                                         unsigned timeout_ms, int mode, int ctas);
-B200C_API int b200c_wait_flags(b200c_ctx* ctx, const uint64_t* flags_dev, int count, uint64_t value, unsigned timeout_ms);
+B200C_API int b200c_wait_flags(b200c_ctx* ctx, const uint64_t* flags_dev, int count, uint64_t value, unsigned timeout_ms,
+                               int on_transfer_stream);
 B200C_API int b200c_signal_flags(b200c_ctx* ctx, uint64_t* const* targets, int count, uint64_t value);
 B200C_API int b200c_exchange_status(b200c_ctx* ctx, int* timed_out);
 /* Makes the context's stream wait (on the device, without blocking the host) for everything queued

@@ -489,8 +489,8 @@ class CudaBackend:
         raise_for(self.lib.b200c_copy_segments_async(self.ctx, arr, n, wait_flag, wait_value, done_flag, done_value,
                                                      timeout_ms, mode, ctas), self._err())
 
-    def wait_flags(self, flags_ptr, count, value, timeout_ms=5000):
-        raise_for(self.lib.b200c_wait_flags(self.ctx, flags_ptr, count, value, timeout_ms), self._err())
+    def wait_flags(self, flags_ptr, count, value, timeout_ms=5000, on_transfer_stream=False):
+        raise_for(self.lib.b200c_wait_flags(self.ctx, flags_ptr, count, value, timeout_ms, int(on_transfer_stream)), self._err())
 
     def signal_flags(self, targets, value):
         arr = (C.c_void_p * max(1, len(targets)))(*targets)

@@ -858,7 +858,7 @@ int b200c_copy_segments_async(b200c_ctx* h, const b200c_copy_seg* segs, int coun
     return guarded([&] {
         if (!h) throw BadArg("null context");
         if (count < 0 || (count > 0 && !segs)) throw BadArg("bad segment list");
-        if (mode != 0 && mode != 1) throw BadArg("mode must be 0 (kernel) or 1 (copy engine)");
+        if (mode < 0 || mode > 2) throw BadArg("mode must be 0 (copy kernel), 1 (copy engine) or 2 (bulk-copy kernel)");
         for (int i = 0; i < count; ++i)
             if (segs[i].n && (!segs[i].src || !segs[i].dst)) throw BadArg("null segment pointer");
         Context* ctx = reinterpret_cast<Context*>(h);
@@ -868,13 +868,14 @@ int b200c_copy_segments_async(b200c_ctx* h, const b200c_copy_seg* segs, int coun
                      reinterpret_cast<unsigned long long*>(done_flag), done_value, timeout_ms, mode, ctas > 0 ? ctas : 64);
     });
 }
-int b200c_wait_flags(b200c_ctx* h, const uint64_t* flags_dev, int count, uint64_t value, unsigned timeout_ms) {
+int b200c_wait_flags(b200c_ctx* h, const uint64_t* flags_dev, int count, uint64_t value, unsigned timeout_ms,
+                     int on_transfer_stream) {
     return guarded([&] {
         if (!h || (count > 0 && !flags_dev)) throw BadArg("null pointer");
         Context* ctx = reinterpret_cast<Context*>(h);
         std::lock_guard<std::mutex> lock(ctx->mu);
         B2_CUDA(cudaSetDevice(ctx->device));
-        waitFlags(ctx, reinterpret_cast<const unsigned long long*>(flags_dev), count, value, timeout_ms);
+        waitFlags(ctx, reinterpret_cast<const unsigned long long*>(flags_dev), count, value, timeout_ms, on_transfer_stream != 0);
     });
 }
 int b200c_signal_flags(b200c_ctx* h, uint64_t* const* targets, int count, uint64_t value) {

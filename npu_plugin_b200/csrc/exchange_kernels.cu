@@ -14,6 +14,7 @@
 #include "runtime.h"
 
 #include <algorithm>
+#include <atomic>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -185,6 +186,149 @@ __global__ void __launch_bounds__(256) pushSegmentsKernel(const CopySeg* __restr
     }
 }
 
+// ---- bulk-copy form of the push ---------------------------------------------------------------
+// The same transfer with the copy done by the SM's bulk-copy (TMA) unit instead of its load/store
+// pipeline: one thread per CTA streams 16 KB tiles local HBM -> shared memory -> peer memory through an
+// 8-stage ring (cp.async.bulk with an mbarrier per stage on the way in, bulk groups on the way out).
+// Plain stores that wait on NVLink fill the load/store queues of their SM and slow every other CTA
+// resident there -- a pushing rank folds its next chunk at the same time -- while bulk copies queue
+// in the copy unit and leave those queues alone.  No multicast, no tensor map: untiled bulk copies
+// with 16-byte aligned addresses and sizes; everything else (tails, unaligned or host-resident
+// segments) takes plain loads and stores from the CTA's other warps.
+constexpr unsigned int kBulkTile = 16384;
+constexpr int kBulkStages = 8;
+
+__device__ __forceinline__ unsigned int smemAddr(const void* p) {
+    return static_cast<unsigned int>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ bool barTryWait(unsigned int bar, unsigned int parity) {
+    unsigned int ok;
+    asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+    return ok != 0;
+}
+// bounded: gives up after the time limit (checked every 256 polls) or a fixed number of polls
+__device__ bool barWaitBounded(unsigned int bar, unsigned int parity, unsigned long long timeoutNs) {
+    const unsigned long long t0 = globalTimerNs();
+    for (unsigned int polls = 0; polls < (1u << 26); ++polls) {
+        if (barTryWait(bar, parity)) return true;
+        if ((polls & 255u) == 255u && globalTimerNs() - t0 > timeoutNs) return false;
+    }
+    return false;
+}
+
+__device__ __forceinline__ int findSeg(const CopySeg* __restrict__ segs, int n, unsigned long long tile) {
+    int lo = 0, hi = n - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (segs[mid].firstTile <= tile) {
+            lo = mid;
+        } else {
+            hi = mid - 1;
+        }
+    }
+    return lo;
+}
+
+__global__ void __launch_bounds__(128) pushBulkKernel(const CopySeg* __restrict__ bulk, int nbulk, unsigned long long nbulkTiles,
+                                                      const CopySeg* __restrict__ ragged, int nragged,
+                                                      const unsigned long long* waitFlag, unsigned long long waitValue,
+                                                      unsigned long long* doneFlag, unsigned long long doneValue,
+                                                      unsigned long long timeoutNs, unsigned int* counter, int* status) {
+    extern __shared__ __align__(128) unsigned char ring[];
+    __shared__ __align__(8) unsigned long long bars[kBulkStages];
+    __shared__ unsigned char* dstOf[kBulkStages];
+    __shared__ unsigned int bytesOf[kBulkStages];
+    __shared__ int go;
+    if (threadIdx.x == 0) {
+        go = 1;
+        for (int s = 0; s < kBulkStages; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smemAddr(&bars[s])) : "memory");
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (waitFlag && !boundedWait(waitFlag, waitValue, timeoutNs)) {
+            go = 0;
+            atomicOr(status, 1);
+        }
+    }
+    __syncthreads();
+    if (go && threadIdx.x == 0) {
+        // tiles blockIdx.x, blockIdx.x + gridDim.x, ... ; tile i of this CTA uses stage i % kBulkStages
+        const unsigned long long nmine = nbulkTiles > blockIdx.x ? (nbulkTiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        auto issueLoad = [&](unsigned long long i) {
+            const unsigned long long tile = blockIdx.x + i * gridDim.x;
+            const CopySeg sg = bulk[findSeg(bulk, nbulk, tile)];
+            const unsigned long long lo = (tile - sg.firstTile) * kBulkTile;
+            const unsigned int bytes = static_cast<unsigned int>(min(static_cast<unsigned long long>(kBulkTile), sg.n - lo));
+            const int st = static_cast<int>(i % kBulkStages);
+            dstOf[st] = sg.dst + lo;
+            bytesOf[st] = bytes;
+            const unsigned int bar = smemAddr(&bars[st]);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 smemAddr(ring + static_cast<size_t>(st) * kBulkTile)),
+                         "l"(sg.src + lo), "r"(bytes), "r"(bar)
+                         : "memory");
+        };
+        unsigned long long issued = 0;
+        for (; issued < nmine && issued < static_cast<unsigned long long>(kBulkStages - 1); ++issued) issueLoad(issued);
+        bool ok = true;
+        unsigned long long i = 0;
+        for (; i < nmine; ++i) {
+            const int st = static_cast<int>(i % kBulkStages);
+            if (!barWaitBounded(smemAddr(&bars[st]), static_cast<unsigned int>((i / kBulkStages) & 1), timeoutNs)) {
+                ok = false;
+                break;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dstOf[st]),
+                         "r"(smemAddr(ring + static_cast<size_t>(st) * kBulkTile)), "r"(bytesOf[st])
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            if (issued < nmine) {
+                // the stage of tile i - 1 is refilled: its store must have read the shared memory (at most the
+                // store just issued may still be pending)
+                asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                issueLoad(issued);
+                ++issued;
+            }
+        }
+        if (!ok) {
+            // a load never arrived: record it, give the loads still in flight a bounded chance to land (they
+            // write this CTA's shared memory), raise no flag
+            atomicOr(status, 4);
+            for (unsigned long long j = i + 1; j < issued; ++j) {
+                barWaitBounded(smemAddr(&bars[j % kBulkStages]), static_cast<unsigned int>((j / kBulkStages) & 1), timeoutNs);
+            }
+            go = 0;
+        }
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        asm volatile("fence.proxy.async;" ::: "memory");
+    } else if (go && threadIdx.x >= 32) {
+        for (int r = blockIdx.x; r < nragged; r += gridDim.x) {
+            const CopySeg sg = ragged[r];
+            for (unsigned long long b = threadIdx.x - 32; b < sg.n; b += blockDim.x - 32) sg.dst[b] = sg.src[b];
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int fine = go;
+        const unsigned int prev = atomicAdd(counter, fine ? 1u : 0x10000u);  // a failed CTA poisons the count
+        if ((prev & 0xFFFFu) + (prev >> 16) == gridDim.x - 1) {
+            *counter = 0;
+            __threadfence_system();
+            if (doneFlag && fine && (prev >> 16) == 0) *reinterpret_cast<volatile unsigned long long*>(doneFlag) = doneValue;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(32) waitFlagsKernel(const unsigned long long* flags, int count, unsigned long long value,
                                                       unsigned long long timeoutNs, int* status) {
     for (int i = threadIdx.x; i < count; i += 32) {
@@ -227,6 +371,81 @@ void releaseExchange(Context* ctx) {
     ctx->xferStatus = nullptr;
 }
 
+// parameter ring of the exchange: a slot whose previous user has finished, grown to `bytes`
+static Context::XferParams* takeParamSlot(Context* ctx, size_t bytes) {
+    Context::XferParams* slot = &ctx->xferParams[ctx->xferSlotNext++ % Context::kXferParamSlots];
+    if (!slot->done) B2_CUDA(cudaEventCreateWithFlags(&slot->done, cudaEventDisableTiming));
+    if (slot->pending) {
+        B2_CUDA(cudaEventSynchronize(slot->done));
+        slot->pending = false;
+    }
+    if (slot->bytes < bytes) {
+        if (slot->dev) cudaFree(slot->dev);
+        if (slot->host) cudaFreeHost(slot->host);
+        slot->dev = slot->host = nullptr;
+        slot->bytes = std::max<size_t>(bytes * 2, 1 << 16);
+        B2_CUDA(cudaMalloc(&slot->dev, slot->bytes));
+        B2_CUDA(cudaMallocHost(&slot->host, slot->bytes));
+    }
+    return slot;
+}
+
+static void pushSegmentsBulk(Context* ctx, const b200c_copy_seg* segs, int count, const unsigned long long* waitFlag,
+                             unsigned long long waitValue, unsigned long long* doneFlag, unsigned long long doneValue,
+                             unsigned long long timeoutNs, int ctas, unsigned int* counter) {
+    std::vector<CopySeg> bulk, ragged;
+    unsigned long long ntiles = 0;
+    for (int i = 0; i < count; ++i) {
+        if (segs[i].n == 0) continue;
+        const unsigned char* src = static_cast<const unsigned char*>(segs[i].src);
+        unsigned char* dst = static_cast<unsigned char*>(segs[i].dst);
+        unsigned long long body = 0;
+        if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0 && segs[i].n >= 4096) {
+            // the bulk unit reads device memory only: a host-resident source takes the plain path
+            cudaPointerAttributes attr;
+            if (cudaPointerGetAttributes(&attr, src) == cudaSuccess && attr.type == cudaMemoryTypeDevice) {
+                body = segs[i].n & ~15ull;
+            } else {
+                cudaGetLastError();
+            }
+        }
+        if (body) {
+            CopySeg s{src, dst, body, ntiles};
+            ntiles += (body + kBulkTile - 1) / kBulkTile;
+            bulk.push_back(s);
+        }
+        if (segs[i].n > body) ragged.push_back(CopySeg{src + body, dst + body, segs[i].n - body, 0});
+    }
+    static std::atomic<unsigned long long> attrSet{0};
+    const unsigned long long bit = 1ull << (ctx->device & 63);
+    if (!(attrSet.fetch_or(bit) & bit)) {
+        B2_CUDA(cudaFuncSetAttribute(pushBulkKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkStages * kBulkTile));
+    }
+    CopySeg *bulkDev = nullptr, *raggedDev = nullptr;
+    Context::XferParams* slot = nullptr;
+    if (!bulk.empty() || !ragged.empty()) {
+        const size_t bytes = sizeof(CopySeg) * (bulk.size() + ragged.size());
+        slot = takeParamSlot(ctx, bytes);
+        CopySeg* h = static_cast<CopySeg*>(slot->host);
+        std::copy(bulk.begin(), bulk.end(), h);
+        std::copy(ragged.begin(), ragged.end(), h + bulk.size());
+        B2_CUDA(cudaMemcpyAsync(slot->dev, slot->host, bytes, cudaMemcpyHostToDevice, ctx->xferStream));
+        bulkDev = static_cast<CopySeg*>(slot->dev);
+        raggedDev = bulkDev + bulk.size();
+    }
+    const unsigned long long want = std::max<unsigned long long>(ntiles / 4, ragged.empty() ? 1 : std::min<size_t>(ragged.size(), 8));
+    const int grid = static_cast<int>(std::max<unsigned long long>(1, std::min<unsigned long long>(want, static_cast<unsigned long long>(std::max(1, ctas)))));
+    pushBulkKernel<<<grid, 128, kBulkStages * kBulkTile, ctx->xferStream>>>(bulkDev, static_cast<int>(bulk.size()), ntiles, raggedDev,
+                                                                          static_cast<int>(ragged.size()), waitFlag, waitValue, doneFlag,
+                                                                          doneValue, timeoutNs, counter, ctx->xferStatus);
+    B2_CUDA(cudaGetLastError());
+    ++ctx->launches;
+    if (slot) {
+        B2_CUDA(cudaEventRecord(slot->done, ctx->xferStream));
+        slot->pending = true;
+    }
+}
+
 void pushSegments(Context* ctx, const b200c_copy_seg* segs, int count, const unsigned long long* waitFlag,
                   unsigned long long waitValue, unsigned long long* doneFlag, unsigned long long doneValue,
                   unsigned int timeoutMs, int mode, int ctas) {
@@ -236,6 +455,10 @@ void pushSegments(Context* ctx, const b200c_copy_seg* segs, int count, const uns
     B2_CUDA(cudaStreamWaitEvent(ctx->xferStream, ctx->xferEvent, 0));
     const unsigned long long timeoutNs = static_cast<unsigned long long>(timeoutMs) * 1000000ull;
     auto nextCounter = [&] { return ctx->xferCounters + (ctx->xferCounterNext++ % Context::kXferCounters); };
+    if (mode == 2) {
+        pushSegmentsBulk(ctx, segs, count, waitFlag, waitValue, doneFlag, doneValue, timeoutNs, ctas, nextCounter());
+        return;
+    }
     std::vector<CopySeg> host;
     std::vector<unsigned int> tileSeg;
     unsigned long long ntiles = 0;
@@ -276,20 +499,7 @@ void pushSegments(Context* ctx, const b200c_copy_seg* segs, int count, const uns
         // by the next call while this kernel may still be queued on the other stream.
         const size_t tileAt = (sizeof(CopySeg) * host.size() + 15) / 16 * 16;
         const size_t bytes = tileAt + sizeof(unsigned int) * ntiles;
-        slot = &ctx->xferParams[ctx->xferSlotNext++ % Context::kXferParamSlots];
-        if (!slot->done) B2_CUDA(cudaEventCreateWithFlags(&slot->done, cudaEventDisableTiming));
-        if (slot->pending) {
-            B2_CUDA(cudaEventSynchronize(slot->done));
-            slot->pending = false;
-        }
-        if (slot->bytes < bytes) {
-            if (slot->dev) cudaFree(slot->dev);
-            if (slot->host) cudaFreeHost(slot->host);
-            slot->dev = slot->host = nullptr;
-            slot->bytes = std::max<size_t>(bytes * 2, 1 << 16);
-            B2_CUDA(cudaMalloc(&slot->dev, slot->bytes));
-            B2_CUDA(cudaMallocHost(&slot->host, slot->bytes));
-        }
+        slot = takeParamSlot(ctx, bytes);
         char* h = static_cast<char*>(slot->host);
         std::memcpy(h, host.data(), sizeof(CopySeg) * host.size());
         std::memcpy(h + tileAt, tileSeg.data(), sizeof(unsigned int) * ntiles);
@@ -308,10 +518,11 @@ void pushSegments(Context* ctx, const b200c_copy_seg* segs, int count, const uns
     }
 }
 
-void waitFlags(Context* ctx, const unsigned long long* flagsDev, int count, unsigned long long value, unsigned int timeoutMs) {
+void waitFlags(Context* ctx, const unsigned long long* flagsDev, int count, unsigned long long value, unsigned int timeoutMs,
+               bool onTransferStream) {
     ensureExchange(ctx);
     if (count <= 0) return;
-    waitFlagsKernel<<<1, 32, 0, ctx->stream>>>(flagsDev, count, value, static_cast<unsigned long long>(timeoutMs) * 1000000ull,
+    waitFlagsKernel<<<1, 32, 0, onTransferStream ? ctx->xferStream : ctx->stream>>>(flagsDev, count, value, static_cast<unsigned long long>(timeoutMs) * 1000000ull,
                                                ctx->xferStatus);
     B2_CUDA(cudaGetLastError());
     ++ctx->launches;

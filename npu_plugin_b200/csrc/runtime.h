@@ -318,7 +318,8 @@ void ipcClose(Context* ctx, void* mapped);
 void pushSegments(Context* ctx, const b200c_copy_seg* segs, int count, const unsigned long long* waitFlag,
                   unsigned long long waitValue, unsigned long long* doneFlag, unsigned long long doneValue,
                   unsigned int timeoutMs, int mode, int ctas);
-void waitFlags(Context* ctx, const unsigned long long* flagsDev, int count, unsigned long long value, unsigned int timeoutMs);
+void waitFlags(Context* ctx, const unsigned long long* flagsDev, int count, unsigned long long value, unsigned int timeoutMs,
+               bool onTransferStream);
 void signalFlags(Context* ctx, unsigned long long* const* targets, int count, unsigned long long value);
 int exchangeStatus(Context* ctx);
 void releaseExchange(Context* ctx);

@@ -101,11 +101,14 @@ class ShardedFolder:
     decls     : every ConstantDecl of the model, identical on all ranks
     transport : moves finished chunks to rank 0 (PushTransport on GPUs)
     weights   : shares of the work per rank for partition(); default: rank 0's share balances its compute
-                against the ingress of everything the other ranks produce (gather_aware_weights)
+                against the ingress of everything the other ranks produce (gather_aware_weights with the
+                measured rates: about 5 TB/s of algorithmic bytes for the kernels, and 0.54 TB/s of blob bytes
+                entering rank 0 while its own kernels keep its memory busy -- the link itself sustains about
+                0.62 TB/s then, the rest is the start-up before the first chunk of a step is ready)
     """
 
     def __init__(self, backend, decls, rank, world, transport, weights=None, nchunks=None, folder_cls=ShardFolder,
-                 compute_rate=5.0e12, link_rate=0.70e12, rank0_chunks=1):
+                 compute_rate=5.0e12, link_rate=0.54e12, rank0_chunks=1):
         self.b, self.decls, self.rank, self.world, self.t = backend, decls, rank, world, transport
         if weights is None:
             total_in = sum(d.nbytes for d in decls)
@@ -170,27 +173,32 @@ class ShardedFolder:
         hi = L.chunk_off[r][k + 1] if k + 1 < len(L.chunk_off[r]) else L.region_bytes[r]
         return L.region_off[r] + lo, hi - lo
 
-    def download(self, host_ptr, own=True):
-        """Rank 0: queues the copy of the whole blob into (pinned) host memory at the same offsets, chunk by
-        chunk behind the bounded wait for that chunk, so early chunks cross PCIe while later ones still
-        arrive over NVLink.  Returns the bytes queued.  Follow with collect()."""
+    def download_chunk(self, host_ptr, k, own=True):
+        """Rank 0: queues, on the transfer stream, the copy of chunk k of every rank into (pinned) host memory
+        at the blob's own offsets -- rank 0's chunk k as soon as the context's stream has produced it, the
+        peers' chunk k behind a bounded wait for their flags.  The context's stream is never held back, so
+        early chunks cross PCIe while later ones are still being folded or still arrive over NVLink.
+        Returns the bytes queued."""
         assert self.rank == 0
-        L, blob = self.layout, self.t.blob_ptr()
-        total = 0
-        if own:
-            total = L.region_bytes[0]
-            self.b.copy_segments_async([(blob, host_ptr, L.region_bytes[0])], mode=1)
-        for k in range(L.nchunks):
-            self.t.wait_chunk(self, k)
-            segs = []
-            for r in range(1, self.world):
-                if k < len(L.chunks[r]):
-                    off, n = self.chunk_span(r, k)
-                    segs.append((blob + off, host_ptr + off, n))
-                    total += n
-            if segs:
-                self.b.copy_segments_async(segs, mode=1)
+        L, blob, total = self.layout, self.t.blob_ptr(), 0
+        if own and k < len(L.chunks[0]):
+            off, n = self.chunk_span(0, k)
+            self.b.copy_segments_async([(blob + off, host_ptr + off, n)], mode=1)
+            total += n
+        segs = []
+        for r in range(1, self.world):
+            if k < len(L.chunks[r]):
+                off, n = self.chunk_span(r, k)
+                segs.append((blob + off, host_ptr + off, n))
+                total += n
+        if segs:
+            self.t.wait_chunk(self, k, on_transfer_stream=True)
+            self.b.copy_segments_async(segs, mode=1)
         return total
+
+    def download(self, host_ptr, first_chunk=0):
+        """Rank 0: download_chunk for every chunk from first_chunk on.  Follow with collect()."""
+        return sum(self.download_chunk(host_ptr, k) for k in range(first_chunk, self.layout.nchunks))
 
     def collect(self, own_rows):
         """Rank 0: waits (bounded) until every peer's chunks of this step have arrived and returns the full
@@ -290,11 +298,13 @@ class PushTransport:
         if status:
             raise ExchangeError(f"exchange timed out on rank {sf.rank} (status {status})")
 
-    def wait_chunk(self, sf, k):
-        """Rank 0: queue the bounded wait for chunk k of every peer on the context's stream."""
+    def wait_chunk(self, sf, k, on_transfer_stream=False):
+        """Rank 0: queue the bounded wait for chunk k of every peer on the context's stream (or on its transfer
+        stream, where it holds back only the downloads queued after it)."""
         L = sf.layout
         if L.world > 1:
-            sf.b.wait_flags(self.buffer + L.flags_off + (k * L.world + 1) * 8, L.world - 1, sf.seq, self.timeout_ms)
+            sf.b.wait_flags(self.buffer + L.flags_off + (k * L.world + 1) * 8, L.world - 1, sf.seq, self.timeout_ms,
+                            on_transfer_stream)
 
     def collect(self, sf):
         b, L = sf.b, sf.layout
@@ -359,7 +369,7 @@ class SingleTransport:
     def finish_step(self, sf, chunks_done):
         pass
 
-    def wait_chunk(self, sf, k):
+    def wait_chunk(self, sf, k, on_transfer_stream=False):
         pass
 
     def check(self, sf):

@@ -18,7 +18,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("mode", [0, 1, 2])
 def test_copy_segments_and_flags(gpu, mode):
     rng = np.random.default_rng(8)
     n = 3_000_000
@@ -61,11 +61,12 @@ def test_bounded_waits_run_out_and_report(gpu):
         assert time.time() - t0 < 5.0
         assert gpu.exchange_status() == 0  # reading the status clears it
         # a pusher's side: the release never comes -> nothing is stored, no done flag is raised
-        gpu.copy_segments_async([(src, dst, 4096)], wait_flag=flags + 64, wait_value=1, done_flag=flags, done_value=9,
-                                timeout_ms=300, mode=0, ctas=4)
-        assert gpu.exchange_status() & 1
-        assert not gpu.download(dst, 4096).any()
-        assert gpu.download(flags, 8).view(np.uint64)[0] == 0
+        for mode in (0, 2):
+            gpu.copy_segments_async([(src, dst, 4096)], wait_flag=flags + 64, wait_value=1, done_flag=flags, done_value=9,
+                                    timeout_ms=300, mode=mode, ctas=4)
+            assert gpu.exchange_status() & 1
+            assert not gpu.download(dst, 4096).any()
+            assert gpu.download(flags, 8).view(np.uint64)[0] == 0
         # the context is still usable
         gpu.copy_segments_async([(src, dst, 4096)], done_flag=flags, done_value=9, mode=0, ctas=4)
         gpu.wait_flags(flags, 1, 9, timeout_ms=2000)
