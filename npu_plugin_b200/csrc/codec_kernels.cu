@@ -20,7 +20,6 @@ size_t codecBound(size_t n) {
 // Blocks are indexed in a padded space in which every buffer starts on a tile boundary
 // (kTileBlocks blocks), so one tile never straddles two buffers.
 constexpr int kTileBlocks = 4096;
-constexpr int kIterBlocks = 256;  // blocks per CTA iteration: 256 threads, one 64-byte block each
 
 B2_HD void loadBlock(const CodecJobDev& job, unsigned long long blk, unsigned char* b) {
     const unsigned long long first = blk * kCodecBlock;
@@ -363,38 +362,98 @@ B2_HD void writeStreamHeader(const CodecJobDev& job, unsigned char* dst) {
 }
 
 // One CTA per tile of a buffer that is being compressed.  Record offsets inside the tile come from
-// a block-wide exclusive scan of the tile's record sizes added to the tile's global offset.  Every
-// iteration encodes 64 blocks into a shared-memory window laid out like the output (same 16-byte
-// phase), which is then copied out with 128-bit stores.
-__global__ void __launch_bounds__(256) codecEmitKernel(const CodecJobDev* __restrict__ jobs,
+// a block-wide exclusive scan of the tile's record sizes added to the tile's global offset.  An
+// iteration covers 256 consecutive blocks, one per thread, whose records are built in a
+// shared-memory window laid out like the output (same 16-byte phase) and then copied out with
+// 128-bit stores.
+//
+// The lanes of a warp must not hold blocks of different modes, or the warp runs every encoder one
+// after the other.  So the blocks of an iteration are handed out in class order -- RAW, then CONST
+// and PACKU, then PACKS, then SPARSE -- through an index list built with warp ballots: only indices
+// are sorted, every thread loads its 64 bytes straight from global memory, and at most three warps
+// of an iteration straddle a class boundary.
+constexpr int kEmitClasses = 4;
+// A CTA of 128 threads takes a quarter of a tile (1024 blocks) in iterations of 128 blocks: small CTAs
+// mean many independent barrier domains per SM, which is what hides the chain summary -> order ->
+// load -> encode -> copy-out of one iteration.
+constexpr int kEmitThreads = 128;
+constexpr int kEmitSub = 1024;                          // blocks per CTA
+constexpr int kEmitSubsPerTile = kTileBlocks / kEmitSub;
+constexpr int kEmitWarps = kEmitThreads / 32;
+
+__device__ __forceinline__ int emitClass(unsigned int header) {
+    const unsigned int mode = header >> 5;
+    return mode == 0 ? 0 : (mode <= 2 ? 1 : (mode == 3 ? 2 : 3));
+}
+
+// the 64-bit word holding the eight w-bit fields of one group of eight bytes (a: bytes 0..3, b: 4..7)
+__device__ __forceinline__ unsigned long long packGroup(unsigned int a, unsigned int b, int w) {
+    const int sh = 8 - w;
+    const unsigned int pa = (a & 0x00FF00FFu) | ((a & 0xFF00FF00u) >> sh);
+    const unsigned int pb = (b & 0x00FF00FFu) | ((b & 0xFF00FF00u) >> sh);
+    const unsigned int qa = (pa & 0xFFFFu) | ((pa >> 16) << (2 * w));
+    const unsigned int qb = (pb & 0xFFFFu) | ((pb >> 16) << (2 * w));
+    return static_cast<unsigned long long>(qa) | (static_cast<unsigned long long>(qb) << (4 * w));
+}
+
+__device__ __forceinline__ void storeGroup(unsigned char* g8, unsigned long long packed, int w) {
+    const unsigned int plo = static_cast<unsigned int>(packed), phi = static_cast<unsigned int>(packed >> 32);
+#pragma unroll
+    for (int j = 0; j < 7; ++j) {
+        if (j < w) g8[j] = static_cast<unsigned char>((j < 4 ? plo : phi) >> (8 * (j & 3)));
+    }
+}
+
+__global__ void __launch_bounds__(kEmitThreads) codecEmitKernel(const CodecJobDev* __restrict__ jobs,
                                                        const unsigned int* __restrict__ tileJob,
                                                        const unsigned int* __restrict__ emitTiles,
                                                        unsigned long long nEmitTiles,
                                                        const unsigned int* __restrict__ summary,
                                                        const unsigned long long* __restrict__ tileOffsets,
                                                        unsigned char* __restrict__ out) {
-    __shared__ unsigned int relOff[kTileBlocks + 1];                        // record offsets inside the tile
-    __shared__ __align__(16) unsigned char window[kIterBlocks * 65 + 48];   // one iteration's records
-    __shared__ unsigned int warpTot[8];
-    const int grp = threadIdx.x >> 2, lane4 = threadIdx.x & 3;
+    __shared__ unsigned int relOff[kEmitSub + 1];                           // record offsets inside the tile
+    __shared__ __align__(16) unsigned char window[kEmitThreads * 65 + 48];  // one iteration's records
+    __shared__ unsigned int warpTot[kEmitWarps];
+    __shared__ unsigned int sumW[kEmitThreads];      // summary words of the iteration's blocks
+    __shared__ unsigned char order[kEmitThreads];    // block indices of the iteration in class order
+    __shared__ unsigned int warpCnt[kEmitWarps][kEmitClasses];
+    __shared__ unsigned int compactSel[16];          // byte-permute selector that moves the kept bytes of a word down
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x < 16) {
+        unsigned int sel = 0, k = 0;
+        for (unsigned int b = 0; b < 4; ++b) {
+            if (threadIdx.x & (1u << b)) sel |= b << (4 * k++);
+        }
+        for (; k < 4; ++k) sel |= 4u << (4 * k);  // byte 0 of the second operand: zero
+        compactSel[threadIdx.x] = sel;
+    }
 
-    for (unsigned long long e = blockIdx.x; e < nEmitTiles; e += gridDim.x) {
-        const unsigned long long tile = emitTiles[e];
+    for (unsigned long long e = blockIdx.x; e < nEmitTiles * kEmitSubsPerTile; e += gridDim.x) {
+        const unsigned long long tile = emitTiles[e / kEmitSubsPerTile];
+        const int sub = static_cast<int>(e % kEmitSubsPerTile);
         const CodecJobDev& job = jobs[tileJob[tile]];
         const bool vec = (reinterpret_cast<uintptr_t>(job.in) & 15) == 0;
         const unsigned long long jobFirstTile = job.firstBlock / kTileBlocks;
-        const unsigned long long tileFirst = (tile - jobFirstTile) * kTileBlocks;  // first block of the tile in the job
+        // first block of this CTA's share in the job
+        const unsigned long long tileFirst = (tile - jobFirstTile) * kTileBlocks + static_cast<unsigned long long>(sub) * kEmitSub;
+        if (tileFirst >= job.nblocks) continue;  // uniform over the CTA
         unsigned char* dst = out + job.outBase;
         unsigned char* records = dst + kCodecHeaderBytes + 4 * job.nsuper;
-        const unsigned long long tileRel = tileOffsets[tile] - tileOffsets[jobFirstTile];
+        const unsigned int* tileSummary = summary + tile * kTileBlocks;
 
-        // exclusive scan of the 4096 record sizes: 16 per thread
+        // record bytes of the tile's blocks in front of this share, then the exclusive scan of the share's
+        // 1024 record sizes (8 per thread)
+        unsigned int lead = 0;
         {
-            const uint4* sm4 = reinterpret_cast<const uint4*>(summary + tile * kTileBlocks + threadIdx.x * 16);
-            unsigned int local[16], s = 0;
+            const uint4* pre4 = reinterpret_cast<const uint4*>(tileSummary);
+            for (int q = threadIdx.x; q < sub * (kEmitSub / 4); q += kEmitThreads) {
+                const uint4 v = pre4[q];
+                lead += (v.x >> 16) + (v.y >> 16) + (v.z >> 16) + (v.w >> 16);
+            }
+            const uint4* sm4 = reinterpret_cast<const uint4*>(tileSummary + sub * kEmitSub + threadIdx.x * 8);
+            unsigned int local[8], s = 0;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
+            for (int q = 0; q < 2; ++q) {
                 const uint4 v = sm4[q];
                 const unsigned int w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -408,89 +467,120 @@ __global__ void __launch_bounds__(256) codecEmitKernel(const CodecJobDev* __rest
                 const unsigned int x = __shfl_up_sync(0xFFFFFFFFu, incl, o);
                 if (lane >= o) incl += x;
             }
+            for (int o = 16; o > 0; o >>= 1) lead += __shfl_xor_sync(0xFFFFFFFFu, lead, o);
+            __syncthreads();  // the previous share's readers of warpTot and relOff are done
             if (lane == 31) warpTot[warp] = incl;
+            if (lane == 0) warpCnt[warp][0] = lead;
             __syncthreads();
             unsigned int before = incl - s;
             for (int wv = 0; wv < warp; ++wv) before += warpTot[wv];
+            lead = 0;
+            for (int wv = 0; wv < kEmitWarps; ++wv) lead += warpCnt[wv][0];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) relOff[threadIdx.x * 16 + i] = before + local[i];
-            if (threadIdx.x == 255) relOff[kTileBlocks] = before + s;
+            for (int i = 0; i < 8; ++i) relOff[threadIdx.x * 8 + i] = before + local[i];
+            if (threadIdx.x == kEmitThreads - 1) relOff[kEmitSub] = before + s;
             __syncthreads();
         }
+        const unsigned long long tileRel = tileOffsets[tile] - tileOffsets[jobFirstTile] + lead;
 
         if (tileFirst == 0 && threadIdx.x == 0) writeStreamHeader(job, dst);
 
-        // one 64-byte block per thread and iteration; the next iteration's block is loaded while the
-        // current one is encoded
-        auto loadMine = [&](int it, uint4 (&v)[4]) {
-            const unsigned long long blk = tileFirst + static_cast<unsigned long long>(it) * kIterBlocks + threadIdx.x;
-            if (it < kTileBlocks / kIterBlocks && blk < job.nblocks) {
+        for (int it = 0; it < kEmitSub / kEmitThreads; ++it) {
+            const unsigned long long blk0 = tileFirst + static_cast<unsigned long long>(it) * kEmitThreads;
+            if (blk0 >= job.nblocks) break;
+            const unsigned int winStart = relOff[it * kEmitThreads];
+            const unsigned int winEnd = relOff[(it + 1) * kEmitThreads];
+            const unsigned long long outStart = tileRel + winStart;  // offset inside the records area
+            const unsigned int phase = static_cast<unsigned int>(reinterpret_cast<uintptr_t>(records + outStart) & 15);
+
+            // ---- the iteration's blocks in class order
+            unsigned int nvalid;
+            {
+                const int bi = threadIdx.x;
+                const unsigned long long blk = blk0 + bi;
+                const bool valid = blk < job.nblocks;
+                unsigned int word = 0;
+                if (valid) {
+                    word = tileSummary[sub * kEmitSub + it * kEmitThreads + bi];
+                    if ((bi & (kCodecSuper - 1)) == 0) {  // first block of an index group of 64
+                        putU32(dst + kCodecHeaderBytes + 4 * (blk / kCodecSuper),
+                               static_cast<unsigned int>(tileRel + relOff[it * kEmitThreads + bi]));
+                    }
+                }
+                sumW[bi] = word;
+                const int cls = valid ? emitClass(word & 0xFFu) : -1;
+                unsigned int mine = 0;
+#pragma unroll
+                for (int c = 0; c < kEmitClasses; ++c) {
+                    const unsigned int m = __ballot_sync(0xFFFFFFFFu, cls == c);
+                    if (lane == 0) warpCnt[warp][c] = __popc(m);
+                    if (cls == c) mine = m;
+                }
+                __syncthreads();
+                unsigned int pos = __popc(mine & ((1u << lane) - 1u)), total = 0;
+#pragma unroll
+                for (int c = 0; c < kEmitClasses; ++c) {
+#pragma unroll
+                    for (int wv = 0; wv < kEmitWarps; ++wv) {
+                        const unsigned int n = warpCnt[wv][c];
+                        total += n;
+                        if (c < cls || (c == cls && wv < warp)) pos += n;
+                    }
+                }
+                nvalid = total;
+                if (valid) order[pos] = static_cast<unsigned char>(bi);
+                __syncthreads();
+            }
+
+            if (threadIdx.x < nvalid) {
+                const int bi = order[threadIdx.x];
+                const unsigned long long blk = blk0 + bi;
+                unsigned int words[16];
                 if (vec && (blk + 1) * kCodecBlock <= job.n) {
                     const uint4* p4 = reinterpret_cast<const uint4*>(job.in + blk * kCodecBlock);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) v[k] = __ldg(p4 + k);
+                    for (int k = 0; k < 4; ++k) {
+                        const uint4 q = __ldg(p4 + k);
+                        words[4 * k] = q.x;
+                        words[4 * k + 1] = q.y;
+                        words[4 * k + 2] = q.z;
+                        words[4 * k + 3] = q.w;
+                    }
                 } else {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) v[k] = loadLane16(job.in, job.n, blk, k, false);
+                    for (int k = 0; k < 4; ++k) {
+                        const uint4 q = loadLane16(job.in, job.n, blk, k, false);
+                        words[4 * k] = q.x;
+                        words[4 * k + 1] = q.y;
+                        words[4 * k + 2] = q.z;
+                        words[4 * k + 3] = q.w;
+                    }
                 }
-            }
-        };
-        uint4 nxt[4] = {};
-        loadMine(0, nxt);
-        for (int it = 0; it < kTileBlocks / kIterBlocks; ++it) {
-            const unsigned long long blk0 = tileFirst + static_cast<unsigned long long>(it) * kIterBlocks;
-            if (blk0 >= job.nblocks) break;
-            const unsigned int winStart = relOff[it * kIterBlocks];
-            const unsigned int winEnd = relOff[(it + 1) * kIterBlocks];
-            const unsigned long long outStart = tileRel + winStart;  // offset inside the records area
-            const unsigned int phase = static_cast<unsigned int>(reinterpret_cast<uintptr_t>(records + outStart) & 15);
-            const int bi = threadIdx.x;
-            const unsigned long long blk = blk0 + bi;
-            uint4 cur[4] = {nxt[0], nxt[1], nxt[2], nxt[3]};
-            loadMine(it + 1, nxt);
-            if (blk < job.nblocks) {
-                const unsigned long long g = tile * kTileBlocks + static_cast<unsigned long long>(it) * kIterBlocks + bi;
-                const unsigned int word = summary[g];
+                const unsigned int word = sumW[bi];
                 const unsigned int header = word & 0xFFu, base = (word >> 8) & 0xFFu;
                 const int mode = header >> 5, w = header & 31;
-                unsigned char* rec = window + phase + (relOff[it * kIterBlocks + bi] - winStart);
-                const unsigned int words[16] = {cur[0].x, cur[0].y, cur[0].z, cur[0].w, cur[1].x, cur[1].y, cur[1].z, cur[1].w,
-                                                cur[2].x, cur[2].y, cur[2].z, cur[2].w, cur[3].x, cur[3].y, cur[3].z, cur[3].w};
+                unsigned char* rec = window + phase + (relOff[it * kEmitThreads + bi] - winStart);
                 rec[0] = static_cast<unsigned char>(header);
                 if (mode == 0) {
 #pragma unroll
                     for (int i = 0; i < 64; ++i) rec[1 + i] = static_cast<unsigned char>(words[i >> 2] >> (8 * (i & 3)));
                 } else if (mode == 1) {
                     rec[1] = static_cast<unsigned char>(base);
-                } else if (mode == 2 || mode == 3) {
-                    const int skip = mode == 2 ? 2 : 1;
-                    if (mode == 2) rec[1] = static_cast<unsigned char>(base);
-                    // field values of four bytes at a time: (b - base) & 0xFF per byte, or the zigzag code
-                    const unsigned int base4 = base * 0x01010101u;
-                    const unsigned int W1 = 1u << w, W2 = W1 << w, W4 = W2 << (2 * w);  // w <= 7: W4 <= 2^28
+                } else if (mode == 2) {
+                    rec[1] = static_cast<unsigned char>(base);
+                    const unsigned int base4 = base * 0x01010101u, lowBase = base4 & 0x7F7F7F7Fu, notBase = ~base4;
 #pragma unroll
                     for (int gq = 0; gq < 8; ++gq) {  // eight 8-element groups, w bytes each
-                        unsigned int lo = words[gq * 2], hi = words[gq * 2 + 1];
-                        if (mode == 2) {
-                            // per-byte subtraction without borrows across bytes
-                            lo = ((lo | 0x80808080u) - (base4 & 0x7F7F7F7Fu)) ^ ((lo ^ ~base4) & 0x80808080u);
-                            hi = ((hi | 0x80808080u) - (base4 & 0x7F7F7F7Fu)) ^ ((hi ^ ~base4) & 0x80808080u);
-                        } else {
-                            lo = zigzag4(lo);
-                            hi = zigzag4(hi);
-                        }
-                        // value k goes to bits [k*w, k*w + w): pairs, quads and the final 64-bit word by multiply-add
-                        const unsigned int f0 = lo & 0xFFu, f1 = (lo >> 8) & 0xFFu, f2 = (lo >> 16) & 0xFFu, f3 = lo >> 24;
-                        const unsigned int f4 = hi & 0xFFu, f5 = (hi >> 8) & 0xFFu, f6 = (hi >> 16) & 0xFFu, f7 = hi >> 24;
-                        const unsigned int q0 = (f3 * W1 + f2) * W2 + (f1 * W1 + f0);
-                        const unsigned int q1 = (f7 * W1 + f6) * W2 + (f5 * W1 + f4);
-                        const unsigned long long packed = static_cast<unsigned long long>(q1) * W4 + q0;
-                        const unsigned int plo = static_cast<unsigned int>(packed), phi = static_cast<unsigned int>(packed >> 32);
-                        unsigned char* g8 = rec + skip + gq * w;
+                        // (b - base) & 0xFF per byte without borrows across bytes
+                        const unsigned int lo = words[gq * 2], hi = words[gq * 2 + 1];
+                        const unsigned int flo = ((lo | 0x80808080u) - lowBase) ^ ((lo ^ notBase) & 0x80808080u);
+                        const unsigned int fhi = ((hi | 0x80808080u) - lowBase) ^ ((hi ^ notBase) & 0x80808080u);
+                        storeGroup(rec + 2 + gq * w, packGroup(flo, fhi, w), w);
+                    }
+                } else if (mode == 3) {
 #pragma unroll
-                        for (int j = 0; j < 7; ++j) {
-                            if (j < w) g8[j] = static_cast<unsigned char>((j < 4 ? plo : phi) >> (8 * (j & 3)));
-                        }
+                    for (int gq = 0; gq < 8; ++gq) {
+                        storeGroup(rec + 1 + gq * w, packGroup(zigzag4(words[gq * 2]), zigzag4(words[gq * 2 + 1]), w), w);
                     }
                 } else {  // sparse: 8 mask bytes, then the non-zero bytes in order
                     unsigned char* nz = rec + 9;
@@ -498,17 +588,21 @@ __global__ void __launch_bounds__(256) codecEmitKernel(const CodecJobDev* __rest
                     for (int q = 0; q < 8; ++q) {
                         unsigned int m8 = 0;
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const unsigned int b = (words[q * 2 + (i >> 2)] >> (8 * (i & 3))) & 0xFFu;
-                            m8 |= static_cast<unsigned int>(b != 0) << i;
-                            if (b != 0) *nz++ = static_cast<unsigned char>(b);
+                        for (int h = 0; h < 2; ++h) {
+                            const unsigned int v = words[q * 2 + h];
+                            const unsigned int t = (((v & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | v) & 0x80808080u;
+                            const unsigned int m = ((t >> 7) * 0x01020408u) >> 24;  // bit k: byte k of the word is non-zero
+                            const unsigned int kept = __byte_perm(v, 0u, compactSel[m]);
+                            const int n = __popc(m);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                if (k < n) nz[k] = static_cast<unsigned char>(kept >> (8 * k));
+                            }
+                            nz += n;
+                            m8 |= m << (4 * h);
                         }
                         rec[1 + q] = static_cast<unsigned char>(m8);
                     }
-                }
-                if ((bi & (kCodecSuper - 1)) == 0) {  // first block of an index group of 64
-                    putU32(dst + kCodecHeaderBytes + 4 * (blk / kCodecSuper),
-                           static_cast<unsigned int>(tileRel + relOff[it * kIterBlocks + bi]));
                 }
             }
             __syncthreads();
@@ -528,8 +622,8 @@ __global__ void __launch_bounds__(256) codecEmitKernel(const CodecJobDev* __rest
             }
             __syncthreads();
         }
-        // trailing zero bytes of the stream (32-byte alignment), written by the buffer's last tile
-        if (tileFirst + kTileBlocks >= job.nblocks) {
+        // trailing zero bytes of the stream (32-byte alignment), written by the CTA that holds the buffer's last block
+        if (tileFirst + kEmitSub >= job.nblocks) {
             for (unsigned long long a = kCodecHeaderBytes + 4 * job.nsuper + job.recordsBytes + threadIdx.x; a < job.streamBytes;
                  a += blockDim.x) {
                 dst[a] = 0;
@@ -604,13 +698,14 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
         if (!emitTiles.empty()) {
             unsigned int* emitDev = static_cast<unsigned int*>(ctx->arena.alloc(sizeof(unsigned int) * emitTiles.size()));
             uploadSmall(ctx, emitDev, emitTiles.data(), sizeof(unsigned int) * emitTiles.size());
-            const int egrid = static_cast<int>(std::min<unsigned long long>(emitTiles.size(), ctx->smCount * 4ULL));
-            codecEmitKernel<<<egrid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, emitDev, emitTiles.size(), summary,
+            const int egrid = static_cast<int>(std::min<unsigned long long>(emitTiles.size() * kEmitSubsPerTile, ctx->smCount * 16ULL));
+            const int cgrid = static_cast<int>(std::min<unsigned long long>(emitTiles.size(), ctx->smCount * 4ULL));
+            codecEmitKernel<<<egrid, kEmitThreads, 0, ctx->stream>>>(jobsDev, tileJobDev, emitDev, emitTiles.size(), summary,
                                                             tileOffsets, outDev);
             B2_CUDA(cudaGetLastError());
             ++ctx->launches;
             if (inPlace) {
-                codecCopyBackKernel<<<egrid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, emitDev, emitTiles.size(), outDev);
+                codecCopyBackKernel<<<cgrid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, emitDev, emitTiles.size(), outDev);
                 B2_CUDA(cudaGetLastError());
                 ++ctx->launches;
             }
@@ -725,8 +820,8 @@ void codecCompressNoAlloc(int device, const unsigned char* inDev, size_t n, unsi
     // the emit kernel reads its tile list from the table slot, which the analysis no longer needs
     B2_CUDA(cudaMemcpyAsync(tileJobDev + kNoAllocMaxTiles, emitTiles, sizeof(unsigned int) * ntiles, cudaMemcpyHostToDevice,
                             stream));
-    codecEmitKernel<<<grid, 256, 0, stream>>>(jobDev, tileJobDev, tileJobDev + kNoAllocMaxTiles, ntiles, summary, tileOffsets,
-                                              outDev);
+    codecEmitKernel<<<grid * kEmitSubsPerTile, kEmitThreads, 0, stream>>>(jobDev, tileJobDev, tileJobDev + kNoAllocMaxTiles, ntiles,
+                                                                          summary, tileOffsets, outDev);
     B2_CUDA(cudaGetLastError());
     int err = 0;
     B2_CUDA(cudaMemcpyAsync(&job, jobDev, sizeof(job), cudaMemcpyDeviceToHost, stream));
