@@ -326,6 +326,13 @@ public:
         s.aux = numElems;
         return add(std::move(s));
     }
+    // ContentAttr::changeShapeAndElemType(newShape, newElemType); q != nullptr: a quantised element type
+    ContentAttr changeShapeAndElemType(const std::vector<int64_t>& shape, int dtype, const QuantParams* q = nullptr) const {
+        Step s(B200C_X_CHANGE_SHAPE_AND_ELEM_TYPE);
+        fill(s.x.b, shape, &s.x.n);
+        s.type = q ? NDType({}, dtype, *q) : NDType({}, dtype);
+        return add(std::move(s));
+    }
     ContentAttr bitPack(int64_t width) const {
         Step s(B200C_X_BIT_PACK);
         s.x.i0 = width;
@@ -459,6 +466,101 @@ private:
     bool _splat = false;
     std::vector<Step> _steps;
 };
+
+// vpux::Const::DeclareOp (src/vpux_compiler/src/dialect/const/ops.cpp): a result type plus a ContentAttr.
+// The constructor runs the op's verifier (ops.cpp:164-193): shape (skipped for a swizzled result type, whose
+// content may have been flattened), element type (a mismatch is accepted when the result type is quantised or
+// the attribute's element type is an integer) and DimsOrder must agree with the attribute's inferred type.
+class DeclareOp {
+public:
+    DeclareOp(NDType resultType, ContentAttr attr, bool swizzled = false)
+            : _type(std::move(resultType)), _attr(std::move(attr)), _swizzled(swizzled) {
+        verify();
+    }
+    const ContentAttr& getContentAttr() const {
+        return _attr;
+    }
+    const NDType& getType() const {
+        return _type;
+    }
+    bool isSwizzled() const {
+        return _swizzled;
+    }
+    // DeclareOp::getContent(): fold of the attribute
+    Content getContent(const Backend& be) const {
+        return _attr.fold(be);
+    }
+    // DeclareOp::getBinarySize (ops.cpp:114-118)
+    size_t getBinarySize() const {
+        return static_cast<size_t>(_attr.getType().getTotalAllocSize());
+    }
+    // DeclareOp::serialize (ops.cpp:97-108): the copyTo bytes in a zero-initialised buffer of the folded type's size
+    // are appended to the section
+    void serialize(const Backend& be, std::vector<uint8_t>& section) const {
+        const Content cnt = getContent(be);
+        const size_t size = static_cast<size_t>(cnt.getType().getTotalAllocSize());
+        const size_t at = section.size();
+        section.resize(at + size, 0);
+        cnt.copyTo(section.data() + at, size);
+    }
+    void verify() const {
+        const NDType attrType = _attr.getType();
+        if (!_swizzled && attrType.shape != _type.shape) {
+            throw Error(B200C_ERR_THROW, "'Const.Declare' has mismatch in value shape and result shape");
+        }
+        const bool sameElem = attrType.dtype == _type.dtype && attrType.quant.kind == _type.quant.kind &&
+                              attrType.quant.scales == _type.quant.scales && attrType.quant.zps == _type.quant.zps &&
+                              attrType.quant.axis == _type.quant.axis && attrType.quant.qmin == _type.quant.qmin &&
+                              attrType.quant.qmax == _type.quant.qmax;
+        if (!sameElem) {
+            const int cls = B200C_DTYPE_CLASS(attrType.dtype);
+            const bool attrIsInteger = attrType.quant.kind == B200C_Q_NONE &&
+                                       (cls == B200C_CLS_INT || cls == B200C_CLS_SINT || cls == B200C_CLS_UINT);
+            if (_type.quant.kind == B200C_Q_NONE && !attrIsInteger) {
+                throw Error(B200C_ERR_THROW, "'Const.Declare' has mismatch in value element type and result element type");
+            }
+        }
+        if (!(attrType.order == _type.order)) {
+            throw Error(B200C_ERR_THROW, "'Const.Declare' has mismatch in value DimsOrder and result DimsOrder");
+        }
+    }
+
+private:
+    NDType _type;
+    ContentAttr _attr;
+    bool _swizzled;
+};
+
+// One op of ConstantFoldingPass::safeRunOnFunc
+// (src/vpux_compiler/src/dialect/const/passes/constant_folding.cpp:27-77): the folded bytes become the base content
+// of a new DeclareOp with the same result type.  A sub-byte element type (more than 1, fewer than 8 bits) cannot be
+// the storage of a dense attribute: its packed bytes are kept as [1,1,1,N] ui8 plus ChangeShapeAndElemType back to
+// the op's shape and element type.  A quantised result is stored under its normalised storage integer.
+inline DeclareOp foldConstant(const Backend& be, const DeclareOp& op) {
+    const Content content = op.getContent(be);
+    const NDType& ct = content.getType();
+    const size_t size = static_cast<size_t>(ct.getTotalAllocSize());
+    std::vector<uint8_t> buf(size, 0);
+    content.copyTo(buf.data(), size);
+    const int bits = B200C_DTYPE_BITS(ct.dtype);
+    if (bits > 1 && bits < 8) {
+        NDType base({1, 1, 1, static_cast<int64_t>(size)}, B200C_UI8, ct.order);
+        const NDType& orig = op.getType();
+        ContentAttr a = ContentAttr::get(buf.data(), size, base)
+                                .changeShapeAndElemType(orig.shape, orig.dtype, orig.quant.kind != B200C_Q_NONE ? &orig.quant : nullptr);
+        return DeclareOp(orig, std::move(a), op.isSwizzled());
+    }
+    NDType base(ct.shape, ct.dtype, ct.order);  // quantisation parameters dropped: the storage integer type
+    return DeclareOp(op.getType(), ContentAttr::get(buf.data(), size, base), op.isSwizzled());
+}
+
+// detectSplatElementWise, run by the reference when it wraps a dense resource
+// (src/vpux_compiler/src/dialect/const/attributes/content.cpp:103-137): true when all elements are equal
+inline bool detectSplat(const Backend& be, const void* data, size_t nbytes, int elemBytes) {
+    int flag = 0;
+    check(b200c_detect_splat(be.ctx(), data, nbytes, elemBytes, /*data_on_device=*/0, &flag));
+    return flag != 0;
+}
 
 // vpux::BitCompactorCodec::compress (src/vpux_compiler/src/utils/bit_compactor_codec.cpp:15-42):
 // returns false (mlir::failure) when the stream would not be smaller than the input

@@ -655,17 +655,79 @@ class ContentAttr:
 
 
 class DeclareOp:
-    """Const::DeclareOp (src/vpux_compiler/src/dialect/const/ops.cpp:88-91): holds a ContentAttr;
-    getContent() folds it."""
+    """Const::DeclareOp (src/vpux_compiler/src/dialect/const/ops.cpp): a result type plus a ContentAttr.
 
-    def __init__(self, contentAttr):
-        self._attr = contentAttr
+    getContent() folds the attribute (ops.cpp:88-91 via getContentAttr().fold()); the verifier compares the
+    attribute's inferred type with the result type (ops.cpp:164-193); serialize() appends the copyTo bytes to an
+    ELF constants section and getBinarySize() is the folded type's total alloc size (ops.cpp:97-118)."""
+
+    def __init__(self, result_type, contentAttr, swizzled=False, loc=None):
+        self._type, self._attr, self._swizzled, self.loc = result_type, contentAttr, bool(swizzled), loc
+        self.verify()
 
     def getContentAttr(self):
         return self._attr
 
     def getType(self):
-        return self._attr.getType()
+        return self._type
 
     def getContent(self):
         return self._attr.fold()
+
+    def fold(self):
+        """DeclareOp::fold: the op folds to its attribute."""
+        return self._attr
+
+    def verify(self):
+        attr_type, op_type = self._attr.getType(), self._type
+        # for a type with swizzling the shape check is skipped: the content may have been flattened
+        if not self._swizzled and tuple(op_type.shape) != tuple(attr_type.shape):
+            raise ConstError(f"'Const.Declare' has mismatch in value shape '{list(attr_type.shape)}' and result shape "
+                             f"'{list(op_type.shape)}'")
+        if op_type.getElementType() != attr_type.getElementType():
+            attr_is_integer = attr_type.quant is None and A.dtype_class(attr_type.dtype) in (A.CLS_INT, A.CLS_SINT, A.CLS_UINT)
+            if op_type.quant is None and not attr_is_integer:
+                raise ConstError(f"'Const.Declare' has mismatch in value element type '{attr_type.getElementType()}' and "
+                                 f"result element type '{op_type.getElementType()}'")
+        if tuple(op_type.order) != tuple(attr_type.order):
+            raise ConstError(f"'Const.Declare' has mismatch in value DimsOrder '{tuple(attr_type.order)}' and result "
+                             f"DimsOrder '{tuple(op_type.order)}'")
+
+    def getBinarySize(self):
+        return self.getContent().getType().getTotalAllocSize()
+
+    def serialize(self, section):
+        """Appends the constant's bytes to `section` (a bytearray): copyTo into a zero-initialised buffer of the
+        folded type's size."""
+        cnt = self.getContent()
+        buf = np.zeros(cnt.getType().getTotalAllocSize(), np.uint8)
+        cnt.copyTo(buf)
+        section += buf.tobytes()
+        return len(buf)
+
+
+def constant_folding_pass(ops):
+    """ConstantFoldingPass::safeRunOnFunc (src/vpux_compiler/src/dialect/const/passes/constant_folding.cpp:27-77):
+    every DeclareOp is replaced by one whose base content holds the folded bytes and whose list is empty -- except
+    for sub-byte element types (more than 1 and fewer than 8 bits), which a dense attribute cannot store: those
+    keep the packed bytes as a [1,1,1,N] ui8 base plus ChangeShapeAndElemType back to the original shape and
+    element type.  A quantised result is stored under its normalised storage integer type."""
+    out = []
+    for op in ops:
+        attr = op.getContentAttr()
+        content = op.getContent()
+        ctype = content.getType()
+        nbytes = ctype.getTotalAllocSize()
+        buf = np.zeros(nbytes, np.uint8)
+        content.copyTo(buf)
+        bits = ctype.getElemTypeSize()
+        if 1 < bits < 8:
+            base_type = NDType((1, 1, 1, nbytes), A.UI8, ctype.order)
+            orig = op.getType()
+            new_attr = ContentAttr.get(buf, base_type, is_splat=False, backend=attr._backend).changeShapeAndElemType(
+                orig.shape, orig.getElementType())
+        else:
+            base_type = NDType(ctype.shape, ctype.dtype, ctype.order)  # quantised: the normalised storage type
+            new_attr = ContentAttr.get(buf, base_type, is_splat=False, backend=attr._backend)
+        out.append(DeclareOp(op.getType(), new_attr, swizzled=op._swizzled, loc=op.loc))
+    return out

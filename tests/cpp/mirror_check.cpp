@@ -41,6 +41,29 @@ int main() {
         const NDType t = a.reorder(DimsOrder::NHWC()).padWithZero({0, 0, 0, 0}, {0, 16, 0, 0}).getType();
         EXPECT((t.shape == std::vector<int64_t>{2, 32, 3, 3}) && t.order == DimsOrder::NHWC(), "inferred type of reorder + pad");
     }
+    // ---- Const::DeclareOp verifier (ops.cpp:164-193), host only ----
+    {
+        std::vector<float> vals(12);
+        std::iota(vals.begin(), vals.end(), 0.0f);
+        auto a = ContentAttr::get(vals, NDType({3, 4}, B200C_F32));
+        auto throws = [&](const NDType& t, const ContentAttr& attr, bool swizzled = false) {
+            try {
+                DeclareOp op(t, attr, swizzled);
+            } catch (const Error& e) {
+                return e.code() == B200C_ERR_THROW;
+            }
+            return false;
+        };
+        EXPECT(throws(NDType({4, 3}, B200C_F32), a), "DeclareOp: shape mismatch");
+        EXPECT(throws(NDType({3, 4}, B200C_F16), a), "DeclareOp: element type mismatch");
+        EXPECT(throws(NDType({3, 4}, B200C_F32, DimsOrder::fromPermutation({1, 0})), a), "DeclareOp: order mismatch");
+        EXPECT(!throws(NDType({3, 4}, B200C_F32), a), "DeclareOp: matching type");
+        std::vector<uint8_t> bytes(100);
+        auto sw = ContentAttr::get(bytes, NDType({1, 100, 1, 1}, B200C_UI8)).swizzleConstant(5, 3);
+        EXPECT(throws(NDType({1, 100, 1, 1}, B200C_UI8), sw), "DeclareOp: flattened swizzled content needs the swizzled flag");
+        EXPECT(!throws(NDType({1, 100, 1, 1}, B200C_UI8), sw, true), "DeclareOp: swizzled result type skips the shape check");
+        EXPECT(DeclareOp(NDType({1, 100, 1, 1}, B200C_UI8), sw, true).getBinarySize() == 512, "getBinarySize of a swizzled constant");
+    }
     if (std::getenv("B200C_MIRROR_HOST_ONLY")) {
         std::printf("%s (host-only part)\n", failures ? "FAILED" : "OK");
         return failures ? 1 : 0;
@@ -126,6 +149,47 @@ int main() {
         const bool smaller = compress(be, x, &stream);
         EXPECT(smaller && stream.size() < x.size(), "codec shrinks a ramp of 16-byte runs");
         EXPECT(decompress(be, stream, x.size()) == x, "codec round trip");
+    }
+    // ---- the constant-folding pass on a 4-bit constant (constant_folding.cpp:45-68; lit
+    //      tests/lit/NPU/dialect/const/passes/constant_folding.mlir:212-222: bytes [16, 18], type 1x1x1x2xui8) ----
+    {
+        const DimsOrder YXOI = DimsOrder::fromPermutation({2, 3, 0, 1});
+        // f16 {1, 0, 1, 2}
+        const std::vector<uint16_t> vals{0x3C00, 0x0000, 0x3C00, 0x4000};
+        const QuantParams q = QuantParams::perTensor(B200C_F16, 0.0039215686274509803, 0, -8, 7);
+        auto attr = ContentAttr::get(vals, NDType({1, 4, 1, 1}, B200C_F16)).convertElemType(B200C_SI4).quantCast(q, B200C_SI4).reorder(YXOI);
+        NDType resultType({1, 4, 1, 1}, B200C_SI4, q);
+        resultType.order = YXOI;
+        const DeclareOp op(resultType, attr);
+        const DeclareOp folded = foldConstant(be, op);
+        const ContentAttr& fa = folded.getContentAttr();
+        EXPECT((fa.getBaseType().shape == std::vector<int64_t>{1, 1, 1, 2}) && fa.getBaseType().dtype == B200C_UI8 &&
+                       fa.getBaseType().order == YXOI,
+               "folded 4-bit constant is stored as 1x1x1x2xui8 in the original order");
+        EXPECT(fa.getNumTransformations() == 1 && fa.getTransformationKind(0) == B200C_X_CHANGE_SHAPE_AND_ELEM_TYPE,
+               "ChangeShapeAndElemType restores the shape and element type");
+        EXPECT((fa.getType().shape == std::vector<int64_t>{1, 4, 1, 1}) && fa.getType().dtype == B200C_SI4, "inferred type is the op's");
+        EXPECT((folded.getContent(be).getRawBytes() == std::vector<uint8_t>{16, 18}), "packed bytes [16, 18]");
+        std::vector<uint8_t> section{0xAB};
+        folded.serialize(be, section);
+        EXPECT((section == std::vector<uint8_t>{0xAB, 16, 18}), "serialize appends the constant's bytes");
+        // a byte-sized constant folds to an empty transformation list
+        std::vector<float> w(24);
+        std::iota(w.begin(), w.end(), 0.0f);
+        const DeclareOp plain(NDType({2, 3, 2, 2}, B200C_F16, DimsOrder::NHWC()),
+                              ContentAttr::get(w, NDType({2, 3, 2, 2}, B200C_F32)).convertElemType(B200C_F16).reorder(DimsOrder::NHWC()));
+        const DeclareOp pf = foldConstant(be, plain);
+        EXPECT(pf.getContentAttr().getNumTransformations() == 0 && pf.getContentAttr().getBaseType().dtype == B200C_F16,
+               "folded constant has an empty list and the folded element type");
+        EXPECT(pf.getContent(be).getRawBytes() == plain.getContent(be).getRawBytes(), "folding twice changes nothing");
+    }
+    // ---- splat detection of a raw buffer (content.cpp:103-137) ----
+    {
+        std::vector<uint32_t> same(100000, 0xDEADBEEFu), one_off = same;
+        one_off[77777] ^= 0x100u;
+        EXPECT(detectSplat(be, same.data(), same.size() * 4, 4), "all elements equal");
+        EXPECT(!detectSplat(be, one_off.data(), one_off.size() * 4, 4), "one element differs");
+        EXPECT(!detectSplat(be, same.data(), 0, 4), "empty data is not a splat");
     }
     std::printf("%s\n", failures ? "FAILED" : "OK");
     return failures ? 1 : 0;

@@ -1,0 +1,71 @@
+"""Const::DeclareOp and the constant-folding pass on the host mirror: the verifier's rules
+(src/vpux_compiler/src/dialect/const/ops.cpp:164-193), getContent / serialize / getBinarySize, and the pass's
+re-typing of folded constants including the sub-byte case the reference pins in
+tests/lit/NPU/dialect/const/passes/constant_folding.mlir:212-222 (bytes [16, 18] typed 1x1x1x2xui8)."""
+import numpy as np
+import pytest
+
+from npu_plugin_b200 import _cabi as A
+from npu_plugin_b200.const import (ConstError, ContentAttr, DeclareOp, DimsOrder, NDType, UniformQuantizedType,
+                                   constant_folding_pass)
+
+
+def test_constant_folding_of_a_4bit_constant(backend):
+    # ConstFoldI4: f16 {1,0,1,2} -> ConvertElemType<si4> -> QuantCast<i4:f16> -> Reorder<YXOI>
+    w = np.array([1.0, 0.0, 1.0, 2.0], np.float16).reshape(1, 4, 1, 1)
+    q = UniformQuantizedType(A.SI4, A.F16, 0.0039215686274509803, 0)
+    attr = ContentAttr.get(w, backend=backend).convertElemType(A.SI4).quantCast(q).reorder(DimsOrder.YXOI)
+    op = DeclareOp(NDType((1, 4, 1, 1), q, DimsOrder.YXOI), attr)
+    (folded,) = constant_folding_pass([op])
+    new_attr = folded.getContentAttr()
+    # the TYPE of the stored dense attribute: 1x1x1x2xui8 in YXOI order, holding the two packed bytes
+    assert new_attr._baseType.shape == (1, 1, 1, 2) and new_attr._baseType.dtype == A.UI8
+    assert tuple(new_attr._baseType.order) == tuple(DimsOrder.YXOI)
+    assert new_attr.getBaseContent().tolist() == [16, 18]
+    assert [t.kind for t in new_attr.getTransformations()] == [A.X_CHANGE_SHAPE_AND_ELEM_TYPE]
+    # the op keeps its result type, and the attribute infers back to it
+    assert folded.getType() == op.getType()
+    assert new_attr.getType().shape == (1, 4, 1, 1) and new_attr.getType().quant == q
+    assert folded.getContent().copyTo().tolist() == [16, 18]
+
+
+def test_constant_folding_of_plain_and_quantised_constants(backend):
+    # ConstFold: dense<-1.0> f32 splat -> f16 -> ui8?? would throw on -1; use the quantised u8 chain on 3.0 instead
+    q = UniformQuantizedType(A.UI8, A.F16, 0.5, 0)
+    a = (ContentAttr.get(np.array([3.0], np.float32), NDType((16, 3, 1, 1), A.F32), is_splat=True, backend=backend)
+         .convertElemType(A.F16).convertElemType(A.UI8).quantCast(q).dequantize().reorder(DimsOrder.YXOI))
+    op = DeclareOp(NDType((16, 3, 1, 1), A.F16, DimsOrder.YXOI), a)
+    (f,) = constant_folding_pass([op])
+    assert not f.getContentAttr().getTransformations()
+    assert f.getContentAttr()._baseType == NDType((16, 3, 1, 1), A.F16, DimsOrder.YXOI)
+    assert np.array_equal(f.getContent().copyTo().view(np.float16), np.full(48, 1.5, np.float16))
+    # a quantised result is stored under its storage integer type; the op keeps the quantised type
+    w = np.arange(24, dtype=np.uint8).reshape(2, 3, 2, 2)
+    aq = ContentAttr.get(w, backend=backend).quantCast(q).reorder(DimsOrder.NHWC)
+    (fq,) = constant_folding_pass([DeclareOp(NDType((2, 3, 2, 2), q, DimsOrder.NHWC), aq)])
+    assert fq.getContentAttr()._baseType == NDType((2, 3, 2, 2), A.UI8, DimsOrder.NHWC)
+    assert fq.getType().quant == q
+    assert np.array_equal(fq.getContent().copyTo().reshape(2, 2, 2, 3), np.transpose(w, (0, 2, 3, 1)))
+
+
+def test_declare_op_verifier_and_serialize(backend):
+    w = np.arange(12, dtype=np.float32).reshape(3, 4)
+    a = ContentAttr.get(w, backend=backend)
+    with pytest.raises(ConstError, match="mismatch in value shape"):
+        DeclareOp(NDType((4, 3), A.F32), a)
+    with pytest.raises(ConstError, match="mismatch in value element type"):
+        DeclareOp(NDType((3, 4), A.F16), a)
+    with pytest.raises(ConstError, match="mismatch in value DimsOrder"):
+        DeclareOp(NDType((3, 4), A.F32, (1, 0)), a)
+    # an integer attribute under a quantised result type is accepted; so is a shape mismatch of a swizzled constant
+    q = UniformQuantizedType(A.UI8, A.F16, 1.0, 0)
+    DeclareOp(NDType((3, 4), q), ContentAttr.get(w.astype(np.uint8), backend=backend))
+    sw = ContentAttr.get(np.arange(100, dtype=np.uint8).reshape(1, 100, 1, 1), backend=backend).swizzleConstant(5, 3)
+    with pytest.raises(ConstError):
+        DeclareOp(NDType((1, 100, 1, 1), A.UI8), sw)
+    op = DeclareOp(NDType((1, 100, 1, 1), A.UI8), sw, swizzled=True)
+    assert op.getBinarySize() == 512
+    section = bytearray(b"xyz")
+    assert op.serialize(section) == 512 and len(section) == 515
+    assert section[3:3 + 16] == bytes(range(16))
+    assert op.fold() is sw and op.getContentAttr() is sw
