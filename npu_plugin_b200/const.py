@@ -226,6 +226,18 @@ class Transform:
     def getTransformationName(self):
         return _NAMES[self.kind]
 
+    def key(self):
+        """Value identity of the transformation (MLIR attributes are uniqued by value)."""
+        e = self.elem
+        ek = (e.kind, e.storage, e.expressed, tuple(e.scales), tuple(e.zps), e.axis, e.qmin, e.qmax) if isinstance(e, Quant) else e
+        return (self.kind, self.a, self.b, self.f, self.i0, self.i1, ek, None if self.aux is None else tuple(self.aux))
+
+    def __eq__(self, o):
+        return isinstance(o, Transform) and self.key() == o.key()
+
+    def __hash__(self):
+        return hash(self.key())
+
     def __repr__(self):
         return f"#const.{_NAMES[self.kind]}"
 
@@ -308,6 +320,29 @@ class Content:
         return vals.astype(dt) if dt != vals.dtype else vals
 
 
+class ResidentContent:
+    """A folded constant whose bytes stay where the backend computes (device memory for the CUDA backend): the
+    folded type, the byte count copyTo writes, and the buffer.  to_content() brings the bytes to the host."""
+
+    def __init__(self, backend, ndtype, buf, nbytes, written):
+        self.backend, self.type, self.buf, self.nbytes, self.written = backend, ndtype, buf, int(nbytes), int(written)
+        self._released = False
+
+    def type_as_base(self):
+        """The type a base content of these bytes has: shape, storage element type and order (quantisation
+        parameters are not part of a base content; the next QuantCast of a chain re-attaches them)."""
+        return NDType(self.type.shape, self.type.dtype, self.type.order)
+
+    def to_content(self):
+        raw = self.backend.resident_to_host(self)
+        return Content(self.type, raw, self.written)
+
+    def release(self):
+        if not self._released:
+            self._released = True
+            self.backend.free_resident(self)
+
+
 # --------------------------------------------------------------------------- backend (CUDA library)
 class CudaBackend:
     """Calls libb200const.so; one b200c_ctx per backend object."""
@@ -368,6 +403,39 @@ class CudaBackend:
         raise_for(rc, self._err())
         t = NDType.from_c(ot)
         return Content(t, out[:max(t.getTotalAllocSize(), nb.value)], nb.value)
+
+    def fold_resident(self, base_type, data, is_splat, transforms):
+        """fold() + copyTo() with the result left in device memory.  `data` is a host array or a ResidentContent
+        (a cached folded prefix, read where it lies)."""
+        keep = []
+        bt = base_type.to_c(keep)
+        ch = chain_to_c(transforms, keep)
+        final = self.infer_type(base_type, transforms)
+        cap = max(final.getTotalAllocSize(), 1)
+        out = self.dev_alloc(cap)
+        ot = out_type_slot(max_q_of(base_type, transforms), keep)
+        nb = C.c_size_t()
+        try:
+            self.fill_zero(out, cap)
+            if isinstance(data, ResidentContent):
+                src, n, on_dev = data.buf, data.nbytes, 1
+            else:
+                buf = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+                src, n, on_dev = buf.ctypes.data, buf.size, 0
+            rc = self.lib.b200c_fold(self.ctx, C.byref(bt), src, n, int(is_splat), on_dev, ch, len(transforms), out, cap, 1,
+                                     C.byref(nb), C.byref(ot), 0)
+            raise_for(rc, self._err())
+        except Exception:
+            self.dev_free(out)
+            raise
+        t = NDType.from_c(ot)
+        return ResidentContent(self, t, out, max(t.getTotalAllocSize(), nb.value), nb.value)
+
+    def resident_to_host(self, rc):
+        return self.download(rc.buf, rc.nbytes)
+
+    def free_resident(self, rc):
+        self.dev_free(rc.buf)
 
     def count_nonsparse_per_oc(self, base_type, data, is_splat, transforms):
         keep = []
@@ -560,7 +628,35 @@ class ContentAttr:
         ts.insert(pos, t)
         out = ContentAttr(self._base, self._baseType, self._isSplat, ts, self._backend)
         out.getType()  # inferFinalType runs when the attribute is built; errors surface here
+        # with background folding enabled for this context, the new attribute is folded ahead of time (content.cpp:320-328)
+        from .cache import ConstantFoldingCacheManager, FoldingRequest
+        mgr = ConstantFoldingCacheManager.getInstance()
+        if mgr.contains(self._backend):
+            mgr.get(self._backend).enqueueRequest(FoldingRequest(out, t))
         return out
+
+    def key(self):
+        """Value identity: the base content object, its type and splat flag, and the transformation list."""
+        bt = self._baseType
+        return (id(self._base), bt.shape, bt.dtype, tuple(bt.order), self._isSplat, tuple(t.key() for t in self._transforms))
+
+    # -- ContentAttr::stripTransformationsFrom / getLastTransformationsFrom (content.cpp:342-369): the rightmost
+    #    occurrence of the transformation splits the list
+    def _rightmost(self, t):
+        for i in range(len(self._transforms) - 1, -1, -1):
+            if self._transforms[i] == t:
+                return i
+        return None
+
+    def stripTransformationsFrom(self, t):
+        i = self._rightmost(t)
+        if i is None:
+            return None
+        return ContentAttr(self._base, self._baseType, self._isSplat, self._transforms[:i], self._backend)
+
+    def getLastTransformationsFrom(self, t):
+        i = self._rightmost(t)
+        return [] if i is None else list(self._transforms[i:])
 
     # -- builder methods (attributes.td:72-107)
     def convertElemType(self, elem):
@@ -647,7 +743,16 @@ class ContentAttr:
         return None
 
     # -- ContentAttr::fold (content.cpp:167-193) + copyTo
-    def fold(self):
+    def fold(self, bypassCache=False):
+        if not bypassCache:
+            from .cache import ConstantFoldingCacheManager, FailedContent
+            mgr = ConstantFoldingCacheManager.getInstance()
+            if mgr.contains(self._backend):
+                hit = mgr.get(self._backend).getContent(self)
+                if isinstance(hit, FailedContent):
+                    raise hit.error
+                if hit is not None:
+                    return hit.to_content()
         return self._backend.fold(self._baseType, self._base, self._isSplat, self._transforms)
 
     def countNonSparseElementsPerOC(self):

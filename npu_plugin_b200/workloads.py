@@ -3,9 +3,8 @@
 Shapes, chains and value distributions follow the benchmark configurations: a conv weight folded to
 swizzled int8, an int4 weight-only linear layer with its dequantise leg, a 50 % sparse 1x1 conv weight
 (sparsity map + sparsify), a ResNet-50-shaped int8 weight set under the block codec and a 7B
-Llama-shaped decoder.  The chains are the ones the reference's passes build
-(src/vpux_compiler/src/dialect/VPU/utils/const_utils.cpp:101-119, sparsify_weights.cpp:108-164,
-src/vpux_translate_utils/src/hwtest/hwtest_utils.cpp:184-197), assembled by npu_plugin_b200.chains.
+Llama-shaped decoder, as plain descriptor lists (no data, no backend).  The reference's own chain-building
+call sites are restated in npu_plugin_b200.chains.
 No dataset is involved: every input comes from the counter-based generator behind b200c_synth_fill,
 keyed by (SEED, stream id of the constant).
 """

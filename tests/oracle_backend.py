@@ -141,6 +141,20 @@ class OracleBackend:
         K.raise_for(rc, self._err())
         return out[:n.value]
 
+    # resident contents: for the CPU oracle "resident" memory is host memory
+    def fold_resident(self, base_type, data, is_splat, transforms):
+        if isinstance(data, K.ResidentContent):
+            data = data.buf
+        c = self.fold(base_type, data, is_splat, transforms)
+        raw = np.array(c.copyTo(), copy=True)
+        return K.ResidentContent(self, c.getType(), raw, raw.size, c.bytesWritten)
+
+    def resident_to_host(self, rc):
+        return rc.buf
+
+    def free_resident(self, rc):
+        rc.buf = None
+
     def synth_fill(self, count, dtype, dist, p0, p1, seed, stream_id):
         """CPU twin of b200c_synth_fill: the same bytes as the device generator."""
         out = np.zeros(int(count) * A.dtype_bits(dtype) // 8, dtype=np.uint8)
