@@ -317,11 +317,15 @@ void Planner::apply(const Transformation& x) {
     if (_afterBitPack) throw NotBuilt("transformations after BitPack are not built");
     const TensorType outType = inferOne(x, _s.type);
     View& v = _s.view;
+    // only the metadata-only transformations below carry a deviating storage size on
+    const long long keepRaw = _s.rawBytes;
+    _s.rawBytes = -1;
 
     switch (x.kind) {
     case B200C_X_CONVERT_ELEM_TYPE:
     case B200C_X_QUANT_CAST:
         _s.type = outType;  // metadata only (convert_elem_type.cpp:79-81, quant_cast.cpp:81-83)
+        _s.rawBytes = keepRaw;
         return;
 
     case B200C_X_RESHAPE:
@@ -329,11 +333,16 @@ void Planner::apply(const Transformation& x) {
         // metadata only in the reference (reshape.cpp:82-84); the linear storage order is kept, so a
         // permuted view has to be made dense before its shape can be reinterpreted
         if (!_s.splat) materialize();
+        const int sbits = dtBits(_s.storage);
+        if (!_s.splat && sbits >= 8) {
+            const long long held = keepRaw >= 0 ? keepRaw : static_cast<long long>(_s.type.count()) * (sbits / 8);
+            if (held != static_cast<long long>(outType.count()) * (sbits / 8)) _s.rawBytes = held;
+        }
         _s.type = outType;
         setShape(v, outType.memShape());
         if (_s.splat) {
             for (int k = 0; k < v.rank; ++k) v.stride[k] = 0;
-        } else if (dtBits(_s.storage) >= 8) {
+        } else if (sbits >= 8) {
             contiguousStrides(v);
         }
         return;
@@ -1072,8 +1081,9 @@ size_t Planner::emitCopyTo(void* dst, size_t cap, int swizzleKey, int64_t totalB
             return static_cast<size_t>(alloc);
         }
         const int64_t storageBytes =
-                _afterBitPack ? n / 2
-                              : (static_cast<int64_t>(dtBits(_s.storage)) * n + 7) / 8;
+                _afterBitPack      ? n / 2
+                : _s.rawBytes >= 0 ? static_cast<int64_t>(_s.rawBytes)
+                                   : (static_cast<int64_t>(dtBits(_s.storage)) * n + 7) / 8;
         if (_afterBitPack) {
             // BitPack output: u8 storage of n/2 bytes, same size as the logical type -> memcpy branch
             if (tryFusedRowQuant(dst, 1, T_U8, -1, n / 2, n / 2)) return static_cast<size_t>(n / 2);

@@ -26,6 +26,10 @@ struct ContentState {
     int storage = 0;
     bool splat = false;
     View view;
+    // Bytes the storage really holds when a shape-and-element-type change left fewer storage elements
+    // than the logical type counts (packed sub-byte bytes kept as ui8); -1: count * storage element size.
+    // Content::copySubByteContent compares this size, not the element count, with the target's.
+    long long rawBytes = -1;
 };
 
 struct SideOutput {
