@@ -173,6 +173,20 @@ typedef struct b200c_xform {
 typedef struct b200c_ctx b200c_ctx;
 B200C_API int b200c_create(int device, b200c_ctx** out);
 B200C_API void b200c_destroy(b200c_ctx* ctx);
+/* Device memory for the library's own scratch.  The reference allocates every intermediate
+ * buffer of a fold on the host heap (Const::Content::allocTempBuffer,
+ * src/vpux_compiler/src/dialect/const/utils/content.cpp:32-47); here intermediates, staged inputs
+ * and launch tables live in a per-context arena of device blocks (64 MiB or more each, kept and
+ * reused across calls).  By default the blocks come from cudaMalloc; a host that runs its own
+ * device memory pool installs its allocator here.  alloc_fn returns a device pointer aligned to
+ * 256 bytes, or NULL when it has no memory -- the call in progress then fails with
+ * B200C_ERR_NOMEM and the context stays usable.  Both functions may be called from the
+ * library's planning threads, concurrently.  Installing (or removing, with two NULLs) an
+ * allocator waits for the context's stream and returns every block to the allocator it came
+ * from.  b200c_dev_alloc is not affected.                                      */
+typedef void* (*b200c_alloc_fn)(void* user, size_t bytes);
+typedef void (*b200c_free_fn)(void* user, void* ptr);
+B200C_API int b200c_set_allocator(b200c_ctx* ctx, b200c_alloc_fn alloc_fn, b200c_free_fn free_fn, void* user);
 /* Use `stream` (a cudaStream_t) for all later work of this context; NULL
  * restores the context's own stream.                                          */
 B200C_API int b200c_set_stream(b200c_ctx* ctx, void* stream);

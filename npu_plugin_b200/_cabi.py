@@ -111,6 +111,11 @@ class b200c_fold_item(C.Structure):
     ]
 
 
+# the caller's device allocator (b200c_set_allocator)
+ALLOC_FN = C.CFUNCTYPE(C.c_void_p, C.c_void_p, C.c_size_t)
+FREE_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p)
+
+
 class b200c_ipc_handle(C.Structure):
     _fields_ = [("handle", C.c_ubyte * 64), ("offset", C.c_uint64), ("size", C.c_uint64)]
 
@@ -124,6 +129,7 @@ _P = C.POINTER
 SYMBOLS = {
     "b200c_create": (C.c_int, [C.c_int, _P(C.c_void_p)]),
     "b200c_destroy": (None, [C.c_void_p]),
+    "b200c_set_allocator": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200c_set_stream": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200c_get_stream": (C.c_void_p, [C.c_void_p]),
     "b200c_synchronize": (C.c_int, [C.c_void_p]),

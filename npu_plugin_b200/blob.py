@@ -12,6 +12,8 @@ Descriptors are marshalled once (prepare) so that a step is only C ABI calls.
 """
 import ctypes as C
 
+import numpy as np
+
 from . import _cabi as A
 from .const import NDType, chain_to_c, out_type_slot, raise_for
 
@@ -96,6 +98,15 @@ class ShardFolder:
             it.chain = C.cast(ch, C.POINTER(A.b200c_xform))
             it.out_cap = self.folded_sizes[i]
         self.comp_idx = [i for i, d in enumerate(decls) if d.compress and self.folded_sizes[i] >= MIN_COMPRESS_BYTES]
+        # array views of the call arguments, so that a step costs no Python loop over the constants
+        self._in_ptrs_np = np.ctypeslib.as_array(C.cast(self._in_ptrs, C.POINTER(C.c_uint64)), (n,))
+        self._sizes_np = np.ctypeslib.as_array(C.cast(self._sizes, C.POINTER(C.c_uint64)), (n,))
+        self._out_size_np = np.ctypeslib.as_array(C.cast(self._out_size, C.POINTER(C.c_uint64)), (n,))
+        self._flag_np = np.ctypeslib.as_array(self._not_smaller)
+        self._comp_idx_np = np.asarray(self.comp_idx, dtype=np.int64)
+        self._offsets_np = np.asarray(self.folded_offsets, dtype=np.int64)
+        self._folded_sizes_np = np.asarray(self.folded_sizes, dtype=np.int64)
+        self._comp_marshalled = None
         self.blob_bound = sum((backend.btc_bound(self.folded_sizes[i]) + 31) // 32 * 32 for i in self.comp_idx) + 64
 
     def fold(self, data_ptrs, folded_ptr, data_on_device=True, side_ptrs=None, max_batch_bytes=None):
@@ -152,6 +163,7 @@ class ShardFolder:
         if k == 0:
             raise_for(self.lib.b200c_synchronize(self.ctx), self.lib.b200c_last_error())
             return []
+        self._comp_marshalled = None
         for j, i in enumerate(self.comp_idx):
             self._in_ptrs[j] = folded_ptr + self.folded_offsets[i]
             self._sizes[j] = self.folded_sizes[i]
@@ -164,21 +176,28 @@ class ShardFolder:
         """Compresses every eligible folded segment where it lies: a segment that shrinks is replaced
         by its stream (at the same offset), the others stay as they are.  The folded buffer then IS
         the blob.  Returns (decl index, offset, size, compressed flag) for every constant; synchronises."""
+        size, flag = self.compress_inplace_arrays(folded_ptr)
+        return list(zip(range(len(self.decls)), self.folded_offsets, size.tolist(), flag.tolist()))
+
+    def compress_inplace_arrays(self, folded_ptr):
+        """compress_inplace with the result as two arrays indexed like the constants: (live size in bytes,
+        compressed flag)."""
         k = len(self.comp_idx)
-        size = list(self.folded_sizes)
-        flag = [False] * len(self.decls)
+        size = self._folded_sizes_np.copy()
+        flag = np.zeros(len(self.decls), dtype=bool)
         if k:
-            for j, i in enumerate(self.comp_idx):
-                self._in_ptrs[j] = folded_ptr + self.folded_offsets[i]
-                self._sizes[j] = self.folded_sizes[i]
+            if self._comp_marshalled != folded_ptr:  # the same buffer as last time: the arrays are already filled in
+                self._in_ptrs_np[:k] = (self._offsets_np[self._comp_idx_np] + folded_ptr).astype(np.uint64)
+                self._sizes_np[:k] = self._folded_sizes_np[self._comp_idx_np].astype(np.uint64)
+                self._comp_marshalled = folded_ptr
             rc = self.lib.b200c_btc_compress_inplace_batch(self.ctx, k, self._in_ptrs, self._sizes, self._out_size,
                                                            self._not_smaller)
             raise_for(rc, self.lib.b200c_last_error())
-            for j, i in enumerate(self.comp_idx):
-                size[i], flag[i] = self._out_size[j], bool(self._not_smaller[j])
+            size[self._comp_idx_np] = self._out_size_np[:k].astype(np.int64)
+            flag[self._comp_idx_np] = self._flag_np[:k] != 0
         else:
             raise_for(self.lib.b200c_synchronize(self.ctx), self.lib.b200c_last_error())
-        return [(i, self.folded_offsets[i], size[i], flag[i]) for i in range(len(self.decls))]
+        return size, flag
 
 
 class PeerWindow:

@@ -217,14 +217,21 @@ B2_HD void layoutJobs(CodecJobDev* jobs, int njobs, const unsigned long long* ti
 }
 
 // single CTA: exclusive scan of the tile sums (the device prefix sum behind every record offset),
-// grand total at tileOffsets[ntiles], then the per-buffer layout
+// grand total at tileOffsets[ntiles], then the per-buffer layout, then the list of tiles whose buffer
+// gets a stream (emitTiles[0 .. *emitCount), in tile order), so that the emit launch can follow without
+// the host looking at the sizes first
 __global__ void __launch_bounds__(1024) codecScanKernel(const unsigned int* __restrict__ tileSums,
                                                         unsigned long long ntiles, unsigned long long* tileOffsets,
                                                         CodecJobDev* jobs, int njobs, unsigned long long outCap,
-                                                        int rawFallback, int* err) {
+                                                        int rawFallback, int* err, const unsigned int* __restrict__ tileJob,
+                                                        unsigned int* emitTiles, unsigned int* emitCount) {
     __shared__ unsigned long long warpSum[32];
     __shared__ unsigned long long carry;
-    if (threadIdx.x == 0) carry = 0;
+    __shared__ int anyFailed;
+    if (threadIdx.x == 0) {
+        carry = 0;
+        anyFailed = 0;
+    }
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (unsigned long long base = 0; base < ntiles; base += blockDim.x) {
@@ -297,15 +304,48 @@ __global__ void __launch_bounds__(1024) codecScanKernel(const unsigned int* __re
             job.outBase = before;
             job.outBytes = outBytes;
             if (!skip && before + outBytes > outCap) {
-                atomicCAS(err, E_NONE, E_CODEC);
+                // in place the "output" is the library's own capped scratch: the host lays the batch out again
+                if (rawFallback != 2) atomicCAS(err, E_NONE, E_CODEC);
                 job.outBytes = 0;
                 job.failed = 1;
+                anyFailed = 1;
             }
         }
         __syncthreads();
         if (threadIdx.x == blockDim.x - 1) carry = before + mine;
         __syncthreads();
     }
+    // tiles of the buffers that are emitted, compacted in order
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (unsigned long long base = 0; base < ntiles; base += blockDim.x) {
+        const unsigned long long t = base + threadIdx.x;
+        bool emits = false;
+        if (t < ntiles) {
+            const CodecJobDev& job = jobs[tileJob[t]];
+            emits = job.outBytes > 0 && !job.failed && !(rawFallback == 1 && job.notSmaller);
+        }
+        const unsigned int m = __ballot_sync(0xFFFFFFFFu, emits);
+        if (lane == 0) warpSum[warp] = __popc(m);
+        __syncthreads();
+        if (warp == 0) {
+            unsigned long long w = warpSum[lane];
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long x = __shfl_up_sync(0xFFFFFFFFu, w, o);
+                if (lane >= o) w += x;
+            }
+            warpSum[lane] = w;
+        }
+        __syncthreads();
+        const unsigned long long pos = carry + (warp ? warpSum[warp - 1] : 0) + __popc(m & ((1u << lane) - 1u));
+        if (emits) emitTiles[pos] = static_cast<unsigned int>(t);
+        const unsigned long long total = warpSum[31];
+        __syncthreads();
+        if (threadIdx.x == 0) carry += total;
+        __syncthreads();
+    }
+    // in place, a batch with a buffer that found no room is emitted as a whole on the second attempt
+    if (threadIdx.x == 0) *emitCount = (rawFallback == 2 && anyFailed) ? 0u : static_cast<unsigned int>(carry);
 }
 
 // In-place mode: every stream built in scratch memory goes over the head of its own input buffer.
@@ -313,8 +353,9 @@ __global__ void __launch_bounds__(1024) codecScanKernel(const unsigned int* __re
 __global__ void __launch_bounds__(256) codecCopyBackKernel(const CodecJobDev* __restrict__ jobs,
                                                            const unsigned int* __restrict__ tileJob,
                                                            const unsigned int* __restrict__ emitTiles,
-                                                           unsigned long long nEmitTiles,
+                                                           const unsigned int* __restrict__ emitCount,
                                                            const unsigned char* __restrict__ scratch) {
+    const unsigned long long nEmitTiles = *emitCount;
     for (unsigned long long e = blockIdx.x; e < nEmitTiles; e += gridDim.x) {
         const unsigned long long tile = emitTiles[e];
         const CodecJobDev& job = jobs[tileJob[tile]];
@@ -407,7 +448,7 @@ __device__ __forceinline__ void storeGroup(unsigned char* g8, unsigned long long
 __global__ void __launch_bounds__(kEmitThreads) codecEmitKernel(const CodecJobDev* __restrict__ jobs,
                                                        const unsigned int* __restrict__ tileJob,
                                                        const unsigned int* __restrict__ emitTiles,
-                                                       unsigned long long nEmitTiles,
+                                                       const unsigned int* __restrict__ emitCount,
                                                        const unsigned int* __restrict__ summary,
                                                        const unsigned long long* __restrict__ tileOffsets,
                                                        unsigned char* __restrict__ out) {
@@ -428,6 +469,7 @@ __global__ void __launch_bounds__(kEmitThreads) codecEmitKernel(const CodecJobDe
         compactSel[threadIdx.x] = sel;
     }
 
+    const unsigned long long nEmitTiles = *emitCount;
     for (unsigned long long e = blockIdx.x; e < nEmitTiles * kEmitSubsPerTile; e += gridDim.x) {
         const unsigned long long tile = emitTiles[e / kEmitSubsPerTile];
         const int sub = static_cast<int>(e % kEmitSubsPerTile);
@@ -661,56 +703,71 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
     unsigned int* tileSums = static_cast<unsigned int*>(ctx->arena.alloc(sizeof(unsigned int) * (ntiles + 1)));
     unsigned long long* tileOffsets =
             static_cast<unsigned long long*>(ctx->arena.alloc(sizeof(unsigned long long) * (ntiles + 1)));
+    unsigned int* emitDev = static_cast<unsigned int*>(ctx->arena.alloc(sizeof(unsigned int) * (ntiles + 1)));
+    unsigned int* emitCount = emitDev + ntiles;
     uploadSmall(ctx, jobsDev, jobs.data(), sizeof(CodecJobDev) * count);
     uploadSmall(ctx, tileJobDev, tileJob.data(), sizeof(unsigned int) * ntiles);
 
-    {
-        const int grid = static_cast<int>(std::max<unsigned long long>(1, std::min<unsigned long long>(ntiles, ctx->smCount * 8ULL)));
-        codecAnalyzeKernel<<<grid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, ntiles, summary, tileSums);
+    // In-place mode builds the streams in scratch memory and copies them over the head of their inputs.
+    // A stream is only kept when it is shorter than its buffer, so the buffers' total size bounds the
+    // scratch; it is capped, and a batch whose streams outgrow the cap is laid out again with the exact need.
+    size_t scratchCap = 0;
+    if (inPlace) {
+        size_t total = 64;
+        for (int j = 0; j < count; ++j) total += (bufs[j].n + 31) / 32 * 32;
+        scratchCap = std::min<size_t>(total, 1ull << 30);
+        outDev = static_cast<unsigned char*>(ctx->arena.alloc(scratchCap));
+        outCap = scratchCap;
+    }
+    // One pass of launches with a single wait at the end: analysis, the device prefix sum with the
+    // per-buffer layout and the list of tiles to emit, emission, (in place) the copy back.
+    const unsigned long long subs = ntiles * kEmitSubsPerTile;
+    const int agrid = static_cast<int>(std::max<unsigned long long>(1, std::min<unsigned long long>(ntiles, ctx->smCount * 8ULL)));
+    const int egrid = static_cast<int>(std::max<unsigned long long>(1, std::min<unsigned long long>(subs, ctx->smCount * 16ULL)));
+    const int cgrid = static_cast<int>(std::max<unsigned long long>(1, std::min<unsigned long long>(ntiles, ctx->smCount * 4ULL)));
+    codecAnalyzeKernel<<<agrid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, ntiles, summary, tileSums);
+    B2_CUDA(cudaGetLastError());
+    ++ctx->launches;
+    auto layoutAndEmit = [&] {
+        codecScanKernel<<<1, 1024, 0, ctx->stream>>>(tileSums, ntiles, tileOffsets, jobsDev, count, outCap, rawFallback,
+                                                     ctx->errWord, tileJobDev, emitDev, emitCount);
         B2_CUDA(cudaGetLastError());
-        codecScanKernel<<<1, 1024, 0, ctx->stream>>>(tileSums, ntiles, tileOffsets, jobsDev, count, outCap,
-                                                     rawFallback, ctx->errWord);
+        codecEmitKernel<<<egrid, kEmitThreads, 0, ctx->stream>>>(jobsDev, tileJobDev, emitDev, emitCount, summary, tileOffsets, outDev);
         B2_CUDA(cudaGetLastError());
         ctx->launches += 2;
-        copyD2H(ctx, jobs.data(), jobsDev, sizeof(CodecJobDev) * count);
-        syncStream(ctx);
-        checkDeviceError(ctx);
-        // buffers that do not shrink are stored as they are (a device-to-device copy); the others
-        // go through the emit kernel
-        std::vector<unsigned int> emitTiles;
         if (inPlace) {
-            // the streams are built in scratch memory and then copied over the head of their inputs
-            size_t need = 64;
-            for (int j = 0; j < count; ++j) need = std::max<size_t>(need, jobs[j].outBase + jobs[j].outBytes + 64);
-            outDev = static_cast<unsigned char*>(ctx->arena.alloc(need));
-        }
-        for (int j = 0; j < count; ++j) {
-            if (jobs[j].failed) throw Capacity("codec: output capacity exceeded");
-            if (jobs[j].outBytes == 0) continue;
-            if (rawFallback == 1 && jobs[j].notSmaller) {
-                copyD2D(ctx, outDev + jobs[j].outBase, jobs[j].in, jobs[j].n);
-                continue;
-            }
-            const unsigned long long t0 = jobs[j].firstBlock / kTileBlocks;
-            const unsigned long long t1 = t0 + (jobs[j].nblocks + kTileBlocks - 1) / kTileBlocks;
-            for (unsigned long long t = t0; t < t1; ++t) emitTiles.push_back(static_cast<unsigned int>(t));
-        }
-        if (!emitTiles.empty()) {
-            unsigned int* emitDev = static_cast<unsigned int*>(ctx->arena.alloc(sizeof(unsigned int) * emitTiles.size()));
-            uploadSmall(ctx, emitDev, emitTiles.data(), sizeof(unsigned int) * emitTiles.size());
-            const int egrid = static_cast<int>(std::min<unsigned long long>(emitTiles.size() * kEmitSubsPerTile, ctx->smCount * 16ULL));
-            const int cgrid = static_cast<int>(std::min<unsigned long long>(emitTiles.size(), ctx->smCount * 4ULL));
-            codecEmitKernel<<<egrid, kEmitThreads, 0, ctx->stream>>>(jobsDev, tileJobDev, emitDev, emitTiles.size(), summary,
-                                                            tileOffsets, outDev);
+            codecCopyBackKernel<<<cgrid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, emitDev, emitCount, outDev);
             B2_CUDA(cudaGetLastError());
             ++ctx->launches;
-            if (inPlace) {
-                codecCopyBackKernel<<<cgrid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, emitDev, emitTiles.size(), outDev);
-                B2_CUDA(cudaGetLastError());
-                ++ctx->launches;
-            }
-            syncStream(ctx);  // the call hands finished buffers back
         }
+        copyD2H(ctx, jobs.data(), jobsDev, sizeof(CodecJobDev) * count);
+        checkDeviceError(ctx);  // waits for the stream: the call hands finished buffers back
+    };
+    layoutAndEmit();
+    bool failed = false;
+    for (int j = 0; j < count; ++j) failed = failed || jobs[j].failed;
+    if (failed && inPlace) {
+        // the capped scratch was too small and nothing was emitted: lay the batch out again with room for
+        // every stream
+        size_t need = 64;
+        for (int j = 0; j < count; ++j) need += (std::min<size_t>(jobs[j].streamBytes, jobs[j].n) + 31) / 32 * 32;
+        outDev = static_cast<unsigned char*>(ctx->arena.alloc(need));
+        outCap = need;
+        layoutAndEmit();
+        failed = false;
+        for (int j = 0; j < count; ++j) failed = failed || jobs[j].failed;
+    }
+    if (failed) throw Capacity("codec: output capacity exceeded");
+    if (rawFallback == 1) {
+        // buffers that do not shrink are stored as they are
+        bool copied = false;
+        for (int j = 0; j < count; ++j) {
+            if (jobs[j].notSmaller && jobs[j].outBytes) {
+                copyD2D(ctx, outDev + jobs[j].outBase, jobs[j].in, jobs[j].n);
+                copied = true;
+            }
+        }
+        if (copied) syncStream(ctx);
     }
     for (int j = 0; j < count; ++j) {
         results[j].offset = inPlace ? 0 : jobs[j].outBase;
@@ -786,11 +843,12 @@ void codecCompressNoAlloc(int device, const unsigned char* inDev, size_t n, unsi
     unsigned int* tileSums = reinterpret_cast<unsigned int*>(scratch + 1024);
     unsigned long long* tileOffsets = reinterpret_cast<unsigned long long*>(scratch + 2048);
     int* errDev = reinterpret_cast<int*>(scratch + 3072);
+    unsigned int* emitCountDev = reinterpret_cast<unsigned int*>(scratch + 3072 + 64);
     unsigned int* summary = reinterpret_cast<unsigned int*>(scratch + kNoAllocSmall);
     // slots: job record [0, 256), tile table and emit list [256, 1024), tile sums [1024, 2048),
-    // tile offsets [2048, 3072), error word at 3072, summaries from kNoAllocSmall
+    // tile offsets [2048, 3072), error word at 3072, length of the emit list at 3136, summaries from kNoAllocSmall
     static_assert(sizeof(CodecJobDev) <= 256 && 2 * kNoAllocMaxTiles * 4 <= 768 && (kNoAllocMaxTiles + 1) * 4 <= 1024 &&
-                          (kNoAllocMaxTiles + 1) * 8 <= 1024 && kNoAllocSmall >= 3072 + sizeof(int) &&
+                          (kNoAllocMaxTiles + 1) * 8 <= 1024 && kNoAllocSmall >= 3072 + 64 + sizeof(int) &&
                           kNoAllocMaxTiles * kTileBlocks * kCodecBlock >= kNoAllocMaxInput,
                   "layout of the fixed scratch buffer");
 
@@ -803,24 +861,22 @@ void codecCompressNoAlloc(int device, const unsigned char* inDev, size_t n, unsi
     job.firstBlock = 0;
     const unsigned long long ntiles = (job.nblocks + kTileBlocks - 1) / kTileBlocks;
     unsigned int tileJob[kNoAllocMaxTiles] = {0};  // one buffer: every tile belongs to job 0
-    unsigned int emitTiles[kNoAllocMaxTiles];
-    for (unsigned long long t = 0; t < ntiles; ++t) emitTiles[t] = static_cast<unsigned int>(t);
 
     // The array keeps whatever the previous call left: everything read below is rewritten first --
     // the job record and tile table here, the error word by the memset, the per-block summaries and
-    // tile sums by the analysis kernel (including the zero sizes of the padding slots).
+    // tile sums by the analysis kernel (including the zero sizes of the padding slots), the emit list
+    // and its length by the scan kernel.
     B2_CUDA(cudaMemcpyAsync(jobDev, &job, sizeof(job), cudaMemcpyHostToDevice, stream));
     B2_CUDA(cudaMemcpyAsync(tileJobDev, tileJob, sizeof(unsigned int) * ntiles, cudaMemcpyHostToDevice, stream));
     B2_CUDA(cudaMemsetAsync(errDev, 0, sizeof(int), stream));
     const int grid = static_cast<int>(ntiles);
     codecAnalyzeKernel<<<grid, 256, 0, stream>>>(jobDev, tileJobDev, ntiles, summary, tileSums);
     B2_CUDA(cudaGetLastError());
-    codecScanKernel<<<1, 1024, 0, stream>>>(tileSums, ntiles, tileOffsets, jobDev, 1, cap, /*rawFallback=*/0, errDev);
+    // the scan also writes the list of tiles to emit (second half of the table slot) and its length
+    codecScanKernel<<<1, 1024, 0, stream>>>(tileSums, ntiles, tileOffsets, jobDev, 1, cap, /*rawFallback=*/0, errDev, tileJobDev,
+                                            tileJobDev + kNoAllocMaxTiles, emitCountDev);
     B2_CUDA(cudaGetLastError());
-    // the emit kernel reads its tile list from the table slot, which the analysis no longer needs
-    B2_CUDA(cudaMemcpyAsync(tileJobDev + kNoAllocMaxTiles, emitTiles, sizeof(unsigned int) * ntiles, cudaMemcpyHostToDevice,
-                            stream));
-    codecEmitKernel<<<grid * kEmitSubsPerTile, kEmitThreads, 0, stream>>>(jobDev, tileJobDev, tileJobDev + kNoAllocMaxTiles, ntiles,
+    codecEmitKernel<<<grid * kEmitSubsPerTile, kEmitThreads, 0, stream>>>(jobDev, tileJobDev, tileJobDev + kNoAllocMaxTiles, emitCountDev,
                                                                           summary, tileOffsets, outDev);
     B2_CUDA(cudaGetLastError());
     int err = 0;

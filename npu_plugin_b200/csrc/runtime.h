@@ -10,6 +10,7 @@
 #include <cstdint>
 #include <mutex>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 namespace b200c {
@@ -84,6 +85,24 @@ struct TileItem {
 };
 bool makeTileItem(const GenParams& p, TileItem* out);
 
+// A queued tile-kernel item of a batched fold: the launch parameters live once in device memory (a
+// "template": constants of the same type, chain and alignment share it), the item itself is only the
+// template's address, its own buffers and its tile count.
+struct TileRef {
+    const TileItem* templ;  // device
+    const void* src;
+    void* dst;
+    long long tiles;
+};
+// Templates are written into slabs of device memory reserved from the arena; the host copies wait in
+// the slab until the next flush uploads them with one copy per slab.
+struct TileSlab {
+    static constexpr int kCapacity = 64;
+    TileItem* dev = nullptr;
+    std::vector<TileItem> host;
+    size_t uploaded = 0;
+};
+
 // One GetSparsityMap of 8-bit elements written straight to its final place (sparsity_kernels.cu).
 struct MapItem {
     const unsigned char* src;
@@ -112,8 +131,27 @@ struct SparseItem {
 
 class PlanPool;
 
+// What planning one constant of a batched fold came to, when that was a single queued launch item and
+// nothing else: kept under a key made of the constant's descriptors so that the next constant with the
+// same base type, chain and buffer alignment (another layer of the same shape) reuses the item with its
+// own pointers instead of being planned again.  Entries live for one b200c_fold_batch call.
+struct PlanMemo {
+    int queue;  // 0: fused quantiser, 1: tile kernel, 2: sparsity map, 3: sparsify
+    RowQuantParams rq;
+    TileRef tile;
+    MapItem map;
+    SparseItem sparse;
+    size_t outBytes;
+    long long queuedBytes;
+};
+
 struct Context {
     int device = 0;
+    // device memory for the library's own scratch (arena blocks): the caller's allocator when one is
+    // installed with b200c_set_allocator, else cudaMalloc / cudaFree
+    b200c_alloc_fn allocFn = nullptr;
+    b200c_free_fn freeFn = nullptr;
+    void* allocUser = nullptr;
     cudaStream_t ownStream = nullptr;
     cudaStream_t stream = nullptr;
     std::mutex mu;
@@ -125,10 +163,14 @@ struct Context {
     size_t l2Bytes = 0;
     bool batching = false;                 // inside b200c_fold_batch: fused quantiser launches are queued
     std::vector<RowQuantParams> rqBatch;
-    std::vector<TileItem> tileBatch;
+    std::vector<TileRef> tileBatch;
+    std::vector<TileSlab> tileSlabs;       // templates of this call's tile items (reset with the arena)
     std::vector<MapItem> mapBatch;
     std::vector<SparseItem> sparseBatch;
     long long queuedBytes = 0;             // input bytes of the queued launches (drives early flushes)
+    long long directOps = 0;               // copies and fills issued straight to the stream (not queued items)
+    std::unordered_map<std::string, PlanMemo> planMemo;
+    std::string planKey;
     // planning threads of the batched entry point: each plans items into a context of its own
     // (same stream and error word, own scratch arena and launch queues)
     PlanPool* pool = nullptr;
@@ -231,6 +273,9 @@ void launchExpandDilated(Context* ctx, const void* src, void* dst, int es, long 
                          long long dky, long long dkx, long long d0, long long d1, unsigned long long fill);
 // queued while ctx->batching is set, launched by flushTileBatch
 void launchTile(Context* ctx, const TileItem& it);
+// uploads the templates `from` has gathered since its last upload (through `ctx`'s staging) and launches
+// what `ctx` has queued
+void uploadTileTemplates(Context* ctx, Context* from);
 void flushTileBatch(Context* ctx);
 // contiguous rows of 8-bit storage with one Dequantize and f16/f32 output (dequant_kernels.cu)
 bool tryLaunchDequantRows(Context* ctx, const GenParams& p);

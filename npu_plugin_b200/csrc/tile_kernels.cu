@@ -12,6 +12,7 @@
 #include "runtime.h"
 
 #include <algorithm>
+#include <cstddef>
 #include <cstring>
 
 namespace b200c {
@@ -320,17 +321,29 @@ __global__ void __launch_bounds__(kTileThreads) foldTileKernel(const __grid_cons
     }
 }
 
-__global__ void __launch_bounds__(kTileThreads) foldTileBatchKernel(const TileItem* __restrict__ items,
+__global__ void __launch_bounds__(kTileThreads) foldTileBatchKernel(const TileRef* __restrict__ refs,
                                                                     const long long* __restrict__ tileStart, int nitems) {
     __shared__ __align__(16) unsigned char smem[kTileSmemBytes];
     __shared__ TileItem it;
     const long long b = blockIdx.x;
     const int lo = findBatchItem(tileStart, nitems, b);
+    const TileRef ref = refs[lo];
     {
-        const int words = sizeof(TileItem) / 4;
-        const unsigned int* s = reinterpret_cast<const unsigned int*>(items + lo);
+        // the shared template, with this item's own buffers put in place of the template's
+        constexpr int words = sizeof(TileItem) / 4;
+        constexpr int srcWord = offsetof(TileItem, g.src) / 4, dstWord = offsetof(TileItem, g.dst) / 4;
+        const unsigned long long srcBits = reinterpret_cast<unsigned long long>(ref.src);
+        const unsigned long long dstBits = reinterpret_cast<unsigned long long>(ref.dst);
+        const unsigned int* s = reinterpret_cast<const unsigned int*>(ref.templ);
         unsigned int* d = reinterpret_cast<unsigned int*>(&it);
-        for (int i = threadIdx.x; i < words; i += kTileThreads) d[i] = s[i];
+        for (int i = threadIdx.x; i < words; i += kTileThreads) {
+            unsigned int v = __ldg(s + i);
+            if (i == srcWord) v = static_cast<unsigned int>(srcBits);
+            if (i == srcWord + 1) v = static_cast<unsigned int>(srcBits >> 32);
+            if (i == dstWord) v = static_cast<unsigned int>(dstBits);
+            if (i == dstWord + 1) v = static_cast<unsigned int>(dstBits >> 32);
+            d[i] = v;
+        }
     }
     __syncthreads();
     tileBody(it, b - tileStart[lo], smem);
@@ -458,7 +471,20 @@ bool makeTileItem(const GenParams& p, TileItem* out) {
 
 void launchTile(Context* ctx, const TileItem& it) {
     if (ctx->batching) {
-        ctx->tileBatch.push_back(it);
+        if (ctx->tileSlabs.empty() || ctx->tileSlabs.back().host.size() >= static_cast<size_t>(TileSlab::kCapacity)) {
+            TileSlab slab;
+            slab.dev = static_cast<TileItem*>(ctx->arena.alloc(sizeof(TileItem) * TileSlab::kCapacity));
+            slab.host.reserve(TileSlab::kCapacity);
+            ctx->tileSlabs.push_back(std::move(slab));
+        }
+        TileSlab& slab = ctx->tileSlabs.back();
+        TileRef ref;
+        ref.templ = slab.dev + slab.host.size();
+        ref.src = it.g.src;
+        ref.dst = it.g.dst;
+        ref.tiles = it.tiles;
+        slab.host.push_back(it);
+        ctx->tileBatch.push_back(ref);
         ctx->queuedBytes += it.g.outElems * it.esIn;
         return;
     }
@@ -468,8 +494,19 @@ void launchTile(Context* ctx, const TileItem& it) {
     ++ctx->launches;
 }
 
+void uploadTileTemplates(Context* ctx, Context* from) {
+    for (TileSlab& slab : from->tileSlabs) {
+        if (slab.uploaded < slab.host.size()) {
+            uploadSmall(ctx, slab.dev + slab.uploaded, slab.host.data() + slab.uploaded,
+                        sizeof(TileItem) * (slab.host.size() - slab.uploaded));
+            slab.uploaded = slab.host.size();
+        }
+    }
+}
+
 void flushTileBatch(Context* ctx) {
-    std::vector<TileItem> pending;
+    uploadTileTemplates(ctx, ctx);
+    std::vector<TileRef> pending;
     pending.swap(ctx->tileBatch);
     size_t first = 0;
     while (first < pending.size()) {
@@ -482,21 +519,14 @@ void flushTileBatch(Context* ctx) {
             ++last;
         }
         const int n = static_cast<int>(last - first);
-        if (n == 1) {
-            const bool was = ctx->batching;
-            ctx->batching = false;
-            launchTile(ctx, pending[first]);
-            ctx->batching = was;
-        } else {
-            TileItem* itemsDev = static_cast<TileItem*>(ctx->arena.alloc(sizeof(TileItem) * n));
-            appendCoarseIndex(start, total);
-            long long* startDev = static_cast<long long*>(ctx->arena.alloc(sizeof(long long) * start.size()));
-            uploadSmall(ctx, itemsDev, pending.data() + first, sizeof(TileItem) * n);
-            uploadSmall(ctx, startDev, start.data(), sizeof(long long) * start.size());
-            foldTileBatchKernel<<<static_cast<unsigned int>(total), kTileThreads, 0, ctx->stream>>>(itemsDev, startDev, n);
-            B2_CUDA(cudaGetLastError());
-            ++ctx->launches;
-        }
+        TileRef* refsDev = static_cast<TileRef*>(ctx->arena.alloc(sizeof(TileRef) * n));
+        appendCoarseIndex(start, total);
+        long long* startDev = static_cast<long long*>(ctx->arena.alloc(sizeof(long long) * start.size()));
+        uploadSmall(ctx, refsDev, pending.data() + first, sizeof(TileRef) * n);
+        uploadSmall(ctx, startDev, start.data(), sizeof(long long) * start.size());
+        foldTileBatchKernel<<<static_cast<unsigned int>(total), kTileThreads, 0, ctx->stream>>>(refsDev, startDev, n);
+        B2_CUDA(cudaGetLastError());
+        ++ctx->launches;
         first = last;
     }
 }

@@ -130,6 +130,9 @@ class ShardedFolder:
         for k, f in enumerate(self.folders):  # the folders' own slot arithmetic must agree with the layout's
             nxt = L.chunk_off[rank][k + 1] if k + 1 < len(self.folders) else L.region_bytes[rank]
             assert f.folded_bytes <= max(1, nxt - L.chunk_off[rank][k]), "slot layout mismatch"
+        # blob offset of every slot of every chunk of this rank
+        self._slot_off = [[L.region_off[rank] + L.chunk_off[rank][k] + off for off in f.folded_offsets]
+                          for k, f in enumerate(self.folders)]
         self.seq = 0
         self.local_base = transport.setup(self)
         self._rows = np.zeros((max(1, len(L.mine[rank])), Layout.TABLE_ROW), dtype=np.int64)
@@ -154,10 +157,16 @@ class ShardedFolder:
                    max_batch_bytes=max_batch_bytes)
             if hooks:
                 hooks("fold1", k)
-            segs = f.compress_inplace(base)  # synchronises: the chunk is complete
-            if hooks:
-                hooks("codec1", k)
-            chunk_rows = [(chunk[j], L.region_off[r] + L.chunk_off[r][k] + off, size, int(comp)) for j, off, size, comp in segs]
+            if hasattr(f, "compress_inplace_arrays"):  # no Python loop over the chunk's constants
+                size, comp = f.compress_inplace_arrays(base)  # synchronises: the chunk is complete
+                if hooks:
+                    hooks("codec1", k)
+                chunk_rows = list(zip(chunk, self._slot_off[k], size.tolist(), comp.astype(np.int64).tolist()))
+            else:
+                segs = f.compress_inplace(base)
+                if hooks:
+                    hooks("codec1", k)
+                chunk_rows = [(chunk[j], L.region_off[r] + L.chunk_off[r][k] + off, size, int(comp)) for j, off, size, comp in segs]
             if r != 0:
                 self.t.push_chunk(self, k, chunk_rows)
             rows += chunk_rows
@@ -206,8 +215,10 @@ class ShardedFolder:
         Raises ExchangeError when a wait runs out."""
         assert self.rank == 0
         rows = list(own_rows) + self.t.collect(self)
-        rows.sort(key=lambda x: x[0])
-        if [x[0] for x in rows] != list(range(len(self.decls))):
+        rows.sort()  # by constant index
+        n = len(self.decls)
+        if len(rows) != n or rows[0][0] != 0 or rows[-1][0] != n - 1 or \
+                (self.world > 1 and [x[0] for x in rows] != list(range(n))):
             raise ExchangeError("the gathered segment table does not cover every constant exactly once")
         return rows
 
