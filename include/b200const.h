@@ -330,6 +330,17 @@ B200C_API int b200c_btc_compress_batch(b200c_ctx* ctx, int count, const void* co
 B200C_API int b200c_btc_compress_inplace_batch(b200c_ctx* ctx, int count, void* const* bufs_dev, const size_t* sizes,
                                                size_t* out_sizes, int32_t* compressed);
 
+/* The same in two steps, for writers that fold the next group of constants while the device still
+ * compresses the previous one: _begin queues the work on the context's stream and returns a
+ * ticket at once; _end waits for that work only (not for anything queued after it) and hands
+ * the sizes back as b200c_btc_compress_inplace_batch does.  The buffers must not be touched by
+ * the caller between the two calls.  Up to 8 tickets may be open per context.  A device-side
+ * error of earlier work (the sticky error word) is reported by the next call that waits for the
+ * whole stream, e.g. b200c_synchronize.                                                           */
+B200C_API int b200c_btc_compress_inplace_begin(b200c_ctx* ctx, int count, void* const* bufs_dev, const size_t* sizes,
+                                               int* ticket);
+B200C_API int b200c_btc_compress_inplace_end(b200c_ctx* ctx, int ticket, size_t* out_sizes, int32_t* compressed);
+
 /* ---- splat detection -------------------------------------------------------------
  * "All elements equal" test of a raw buffer: detectSplatElementWise, which the reference runs when
  * it wraps a dense resource (src/vpux_compiler/src/dialect/const/attributes/content.cpp:103-137,

@@ -155,6 +155,8 @@ SYMBOLS = {
                                            C.c_size_t, _P(C.c_size_t), _P(C.c_size_t), _P(C.c_int32)]),
     "b200c_btc_compress_inplace_batch": (C.c_int, [C.c_void_p, C.c_int, _P(C.c_void_p), _P(C.c_size_t), _P(C.c_size_t),
                                                    _P(C.c_int32)]),
+    "b200c_btc_compress_inplace_begin": (C.c_int, [C.c_void_p, C.c_int, _P(C.c_void_p), _P(C.c_size_t), _P(C.c_int)]),
+    "b200c_btc_compress_inplace_end": (C.c_int, [C.c_void_p, C.c_int, _P(C.c_size_t), _P(C.c_int32)]),
     "b200c_synth_fill": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_double, C.c_double,
                                    C.c_uint64, C.c_uint64]),
     "b200c_detect_splat": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, _P(C.c_int)]),

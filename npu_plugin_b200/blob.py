@@ -179,6 +179,39 @@ class ShardFolder:
         size, flag = self.compress_inplace_arrays(folded_ptr)
         return list(zip(range(len(self.decls)), self.folded_offsets, size.tolist(), flag.tolist()))
 
+    def compress_inplace_begin(self, folded_ptr):
+        """First half of compress_inplace_arrays: queues the compression of this folder's slots and returns a
+        ticket at once, so that the caller can prepare the next group of constants while the device works.
+        Returns None when nothing is eligible."""
+        k = len(self.comp_idx)
+        if not k:
+            return None
+        self._marshal_compress(folded_ptr)
+        ticket = C.c_int()
+        rc = self.lib.b200c_btc_compress_inplace_begin(self.ctx, k, self._in_ptrs, self._sizes, C.byref(ticket))
+        raise_for(rc, self.lib.b200c_last_error())
+        return ticket.value
+
+    def compress_inplace_end(self, ticket):
+        """Second half: waits for the ticket's work only and returns (live sizes, compressed flags)."""
+        size = self._folded_sizes_np.copy()
+        flag = np.zeros(len(self.decls), dtype=bool)
+        if ticket is None:
+            return size, flag
+        k = len(self.comp_idx)
+        rc = self.lib.b200c_btc_compress_inplace_end(self.ctx, ticket, self._out_size, self._not_smaller)
+        raise_for(rc, self.lib.b200c_last_error())
+        size[self._comp_idx_np] = self._out_size_np[:k].astype(np.int64)
+        flag[self._comp_idx_np] = self._flag_np[:k] != 0
+        return size, flag
+
+    def _marshal_compress(self, folded_ptr):
+        if self._comp_marshalled != folded_ptr:  # the same buffer as last time: the arrays are already filled in
+            k = len(self.comp_idx)
+            self._in_ptrs_np[:k] = (self._offsets_np[self._comp_idx_np] + folded_ptr).astype(np.uint64)
+            self._sizes_np[:k] = self._folded_sizes_np[self._comp_idx_np].astype(np.uint64)
+            self._comp_marshalled = folded_ptr
+
     def compress_inplace_arrays(self, folded_ptr):
         """compress_inplace with the result as two arrays indexed like the constants: (live size in bytes,
         compressed flag)."""
@@ -186,10 +219,7 @@ class ShardFolder:
         size = self._folded_sizes_np.copy()
         flag = np.zeros(len(self.decls), dtype=bool)
         if k:
-            if self._comp_marshalled != folded_ptr:  # the same buffer as last time: the arrays are already filled in
-                self._in_ptrs_np[:k] = (self._offsets_np[self._comp_idx_np] + folded_ptr).astype(np.uint64)
-                self._sizes_np[:k] = self._folded_sizes_np[self._comp_idx_np].astype(np.uint64)
-                self._comp_marshalled = folded_ptr
+            self._marshal_compress(folded_ptr)
             rc = self.lib.b200c_btc_compress_inplace_batch(self.ctx, k, self._in_ptrs, self._sizes, self._out_size,
                                                            self._not_smaller)
             raise_for(rc, self.lib.b200c_last_error())

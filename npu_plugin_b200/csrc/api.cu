@@ -404,6 +404,10 @@ void b200c_destroy(b200c_ctx* h) {
     destroyPool(ctx);
     releaseExchange(ctx);
     releaseStage(ctx);
+    for (CodecPending& t : ctx->codecTickets) {
+        if (t.jobsHost) cudaFreeHost(t.jobsHost);
+        if (t.done) cudaEventDestroy(t.done);
+    }
     ctx->arena.releaseAll();  // frees the blocks while the device is still current
     if (ctx->ownStream) cudaStreamDestroy(ctx->ownStream);
     delete ctx;
@@ -940,6 +944,44 @@ int b200c_btc_compress_inplace_batch(b200c_ctx* h, int count, void* const* bufs_
         for (int i = 0; i < count; ++i) bufs[i] = CodecBuf{static_cast<const unsigned char*>(bufs_dev[i]), sizes[i]};
         std::vector<CodecResult> res(count);
         codecCompressBatch(ctx, count, bufs.data(), nullptr, 0, /*rawFallback=*/2, res.data());
+        for (int i = 0; i < count; ++i) {
+            out_sizes[i] = res[i].size;
+            if (compressed) compressed[i] = res[i].notSmaller ? 0 : 1;
+        }
+    });
+}
+
+int b200c_btc_compress_inplace_begin(b200c_ctx* h, int count, void* const* bufs_dev, const size_t* sizes, int* ticket) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        if (!ticket) throw BadArg("null ticket pointer");
+        if (count <= 0 || !bufs_dev || !sizes) throw BadArg("bad batch arguments");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        CallScope scope(ctx);
+        int slot = -1;
+        for (int k = 0; k < Context::kCodecTickets && slot < 0; ++k)
+            if (!ctx->codecTickets[k].open) slot = k;
+        if (slot < 0) throw BadArg("too many compressions are pending: collect one with b200c_btc_compress_inplace_end first");
+        std::vector<CodecBuf> bufs(count);
+        for (int i = 0; i < count; ++i) bufs[i] = CodecBuf{static_cast<const unsigned char*>(bufs_dev[i]), sizes[i]};
+        codecCompressBatch(ctx, count, bufs.data(), nullptr, 0, /*rawFallback=*/2, nullptr, &ctx->codecTickets[slot]);
+        *ticket = slot;
+    });
+}
+
+int b200c_btc_compress_inplace_end(b200c_ctx* h, int ticket, size_t* out_sizes, int32_t* compressed) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        if (ticket < 0 || ticket >= Context::kCodecTickets || !ctx->codecTickets[ticket].open) throw BadArg("not a pending compression");
+        if (!out_sizes) throw BadArg("null result pointer");
+        std::unique_lock<std::mutex> lock(ctx->mu);
+        B2_CUDA(cudaSetDevice(ctx->device));
+        CodecPending& pend = ctx->codecTickets[ticket];
+        std::vector<CodecResult> res(pend.count);
+        const int count = pend.count;
+        codecCollect(ctx, &pend, res.data());
+        if (pend.errCode != E_NONE) throw RefThrow(errText(pend.errCode));
         for (int i = 0; i < count; ++i) {
             out_sizes[i] = res[i].size;
             if (compressed) compressed[i] = res[i].notSmaller ? 0 : 1;

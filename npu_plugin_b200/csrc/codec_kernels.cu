@@ -675,9 +675,36 @@ __global__ void __launch_bounds__(kEmitThreads) codecEmitKernel(const CodecJobDe
     }
 }
 
+static void fillResults(const CodecJobDev* jobs, int count, bool inPlace, CodecResult* results) {
+    for (int j = 0; j < count; ++j) {
+        results[j].offset = inPlace ? 0 : jobs[j].outBase;
+        results[j].size = (inPlace && jobs[j].notSmaller) ? jobs[j].n : jobs[j].outBytes;
+        results[j].notSmaller = jobs[j].notSmaller != 0;
+    }
+}
+
+void codecCollect(Context* ctx, CodecPending* pending, CodecResult* results) {
+    B2_CUDA(cudaEventSynchronize(pending->done));
+    pending->open = false;
+    pending->errCode = *reinterpret_cast<const int*>(pending->jobsHost + pending->capacity);
+    if (pending->errCode != E_NONE) {
+        B2_CUDA(cudaMemsetAsync(ctx->errWord, 0, sizeof(int), ctx->stream));
+        return;  // the caller reports it; the buffers of this batch are not to be trusted
+    }
+    bool failed = false;
+    for (int j = 0; j < pending->count; ++j) failed = failed || pending->jobsHost[j].failed;
+    if (failed) {
+        // the capped scratch was too small and nothing was emitted: compress again, waiting for the result
+        codecCompressBatch(ctx, pending->count, pending->bufs.data(), nullptr, 0, /*rawFallback=*/2, results);
+        return;
+    }
+    fillResults(pending->jobsHost, pending->count, true, results);
+}
+
 void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned char* outDev, size_t outCap,
-                        int rawFallback, CodecResult* results) {
+                        int rawFallback, CodecResult* results, CodecPending* pending) {
     const bool inPlace = rawFallback == 2;  // streams replace the head of their own input buffer
+    if (pending && !inPlace) throw BadArg("only the in-place batch compression can be left pending");
     if (inPlace) outCap = ~static_cast<size_t>(0) >> 1;
     if (count <= 0) return;
     std::vector<CodecJobDev> jobs(count);
@@ -728,7 +755,7 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
     codecAnalyzeKernel<<<agrid, 256, 0, ctx->stream>>>(jobsDev, tileJobDev, ntiles, summary, tileSums);
     B2_CUDA(cudaGetLastError());
     ++ctx->launches;
-    auto layoutAndEmit = [&] {
+    auto layoutAndEmit = [&](bool wait) {
         codecScanKernel<<<1, 1024, 0, ctx->stream>>>(tileSums, ntiles, tileOffsets, jobsDev, count, outCap, rawFallback,
                                                      ctx->errWord, tileJobDev, emitDev, emitCount);
         B2_CUDA(cudaGetLastError());
@@ -740,10 +767,31 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
             B2_CUDA(cudaGetLastError());
             ++ctx->launches;
         }
+        if (!wait) {
+            copyD2H(ctx, pending->jobsHost, jobsDev, sizeof(CodecJobDev) * count);
+            copyD2H(ctx, pending->jobsHost + pending->capacity, ctx->errWord, sizeof(int));
+            B2_CUDA(cudaEventRecord(pending->done, ctx->stream));
+            return;
+        }
         copyD2H(ctx, jobs.data(), jobsDev, sizeof(CodecJobDev) * count);
         checkDeviceError(ctx);  // waits for the stream: the call hands finished buffers back
     };
-    layoutAndEmit();
+    if (pending) {
+        if (pending->capacity < static_cast<size_t>(count)) {
+            if (pending->jobsHost) cudaFreeHost(pending->jobsHost);
+            pending->jobsHost = nullptr;
+            pending->capacity = 0;
+            B2_CUDA(cudaMallocHost(&pending->jobsHost, sizeof(CodecJobDev) * (static_cast<size_t>(count) * 2 + 1)));
+            pending->capacity = static_cast<size_t>(count) * 2;
+        }
+        if (!pending->done) B2_CUDA(cudaEventCreateWithFlags(&pending->done, cudaEventDisableTiming));
+        pending->count = count;
+        pending->bufs.assign(bufs, bufs + count);
+        layoutAndEmit(false);
+        pending->open = true;
+        return;
+    }
+    layoutAndEmit(true);
     bool failed = false;
     for (int j = 0; j < count; ++j) failed = failed || jobs[j].failed;
     if (failed && inPlace) {
@@ -753,7 +801,7 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
         for (int j = 0; j < count; ++j) need += (std::min<size_t>(jobs[j].streamBytes, jobs[j].n) + 31) / 32 * 32;
         outDev = static_cast<unsigned char*>(ctx->arena.alloc(need));
         outCap = need;
-        layoutAndEmit();
+        layoutAndEmit(true);
         failed = false;
         for (int j = 0; j < count; ++j) failed = failed || jobs[j].failed;
     }
@@ -769,11 +817,7 @@ void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned 
         }
         if (copied) syncStream(ctx);
     }
-    for (int j = 0; j < count; ++j) {
-        results[j].offset = inPlace ? 0 : jobs[j].outBase;
-        results[j].size = (inPlace && jobs[j].notSmaller) ? jobs[j].n : jobs[j].outBytes;
-        results[j].notSmaller = jobs[j].notSmaller != 0;
-    }
+    fillResults(jobs.data(), count, inPlace, results);
 }
 
 // ---------------------------------------------------------------------------- allocation-free compress

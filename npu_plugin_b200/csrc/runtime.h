@@ -131,6 +131,34 @@ struct SparseItem {
 
 class PlanPool;
 
+// block codec (codec.h, codec_kernels.cu)
+struct CodecJobDev {
+    const unsigned char* in;
+    unsigned long long n, nblocks, nsuper, firstBlock;
+    unsigned long long recordsBytes, streamBytes, outBase, outBytes;
+    int notSmaller;
+    int failed;
+};
+struct CodecBuf {
+    const unsigned char* in;  // device
+    size_t n;
+};
+struct CodecResult {
+    size_t offset, size;
+    bool notSmaller;
+};
+// An in-place batch compression whose launches are queued and whose sizes have not been read yet: the
+// per-buffer records come back into pinned host memory behind `done`.
+struct CodecPending {
+    bool open = false;
+    int count = 0;
+    CodecJobDev* jobsHost = nullptr;  // pinned
+    size_t capacity = 0;              // records jobsHost can hold; one more slot behind them holds the error word
+    int errCode = 0;                  // device error word as it stood behind the queued work (set by codecCollect)
+    cudaEvent_t done = nullptr;
+    std::vector<CodecBuf> bufs;
+};
+
 // What planning one constant of a batched fold came to, when that was a single queued launch item and
 // nothing else: kept under a key made of the constant's descriptors so that the next constant with the
 // same base type, chain and buffer alignment (another layer of the same shape) reuses the item with its
@@ -168,6 +196,8 @@ struct Context {
     std::vector<MapItem> mapBatch;
     std::vector<SparseItem> sparseBatch;
     long long queuedBytes = 0;             // input bytes of the queued launches (drives early flushes)
+    static constexpr int kCodecTickets = 8;
+    CodecPending codecTickets[kCodecTickets];  // asynchronous in-place compressions not collected yet
     long long directOps = 0;               // copies and fills issued straight to the stream (not queued items)
     std::unordered_map<std::string, PlanMemo> planMemo;
     std::string planKey;
@@ -323,27 +353,15 @@ void launchSubViewBits(Context* ctx, const void* src, void* dst, int rank, const
 
 // block codec (codec.h, codec_kernels.cu)
 size_t codecBound(size_t n);
-struct CodecJobDev {
-    const unsigned char* in;
-    unsigned long long n, nblocks, nsuper, firstBlock;
-    unsigned long long recordsBytes, streamBytes, outBase, outBytes;
-    int notSmaller;
-    int failed;
-};
-struct CodecBuf {
-    const unsigned char* in;  // device
-    size_t n;
-};
-struct CodecResult {
-    size_t offset, size;
-    bool notSmaller;
-};
 // Compresses `count` device buffers into outDev; segment i starts at results[i].offset (32-byte
 // aligned).  With rawFallback a buffer whose stream would not be smaller is stored unchanged.
 // rawFallback 2: in place -- a buffer whose stream is smaller gets the stream written over its own
 // head (results[i].size = stream length), every other buffer is left untouched; outDev is unused.
+// With `pending` (in-place mode only) the call returns after queueing its launches; codecCollect waits for
+// them and delivers the results.
 void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned char* outDev, size_t outCap,
-                        int rawFallback, CodecResult* results);
+                        int rawFallback, CodecResult* results, CodecPending* pending = nullptr);
+void codecCollect(Context* ctx, CodecPending* pending, CodecResult* results);
 // allocation-free single-buffer variant (fixed scratch inside the library image)
 size_t codecNoAllocMaxInput();
 void codecCompressNoAlloc(int device, const unsigned char* inDev, size_t n, unsigned char* outDev, size_t cap,

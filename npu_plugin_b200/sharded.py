@@ -148,6 +148,16 @@ class ShardedFolder:
         self.seq += 1
         self.t.begin_step(self)
         rows, at = [], 0
+        pending = None  # (chunk number, ticket) of the compression queued last
+
+        def finish(k, ticket):
+            # sizes of chunk k are known once its compression has run: its table rows, and (peers) its push
+            size, comp = self.folders[k].compress_inplace_end(ticket)
+            chunk_rows = list(zip(self.my_chunks[k], self._slot_off[k], size.tolist(), comp.astype(np.int64).tolist()))
+            if r != 0:
+                self.t.push_chunk(self, k, chunk_rows)
+            return chunk_rows
+
         for k, (chunk, f) in enumerate(zip(self.my_chunks, self.folders)):
             n = len(chunk)
             base = self.local_base + L.chunk_off[r][k]
@@ -157,20 +167,26 @@ class ShardedFolder:
                    max_batch_bytes=max_batch_bytes)
             if hooks:
                 hooks("fold1", k)
-            if hasattr(f, "compress_inplace_arrays"):  # no Python loop over the chunk's constants
-                size, comp = f.compress_inplace_arrays(base)  # synchronises: the chunk is complete
+            if hasattr(f, "compress_inplace_begin"):
+                # The compression of chunk k is only queued here; the host goes on to plan the fold of chunk
+                # k + 1 while the device compresses, and reads the sizes of chunk k after that.
+                ticket = f.compress_inplace_begin(base)
                 if hooks:
-                    hooks("codec1", k)
-                chunk_rows = list(zip(chunk, self._slot_off[k], size.tolist(), comp.astype(np.int64).tolist()))
+                    hooks("codec1", k)  # on the stream: right behind the chunk's compression
+                if pending is not None:
+                    rows += finish(*pending)
+                pending = (k, ticket)
             else:
-                segs = f.compress_inplace(base)
+                segs = f.compress_inplace(base)  # synchronises: the chunk is complete
                 if hooks:
                     hooks("codec1", k)
                 chunk_rows = [(chunk[j], L.region_off[r] + L.chunk_off[r][k] + off, size, int(comp)) for j, off, size, comp in segs]
-            if r != 0:
-                self.t.push_chunk(self, k, chunk_rows)
-            rows += chunk_rows
+                if r != 0:
+                    self.t.push_chunk(self, k, chunk_rows)
+                rows += chunk_rows
             at += n
+        if pending is not None:
+            rows += finish(*pending)
         if r != 0:
             self.t.finish_step(self, len(self.folders))
         return rows
