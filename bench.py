@@ -171,10 +171,11 @@ class DeviceRun:
         self.sf = ShardedFolder(backend, decls, rank, world, transport, weights=weights, nchunks=args.chunks,
                                 rank0_chunks=rank0_chunks)
         self.mine = [decls[i] for i in self.sf.layout.mine[rank]]
-        self.inputs = [torch.empty(d.nbytes, dtype=torch.uint8, device="cuda") for d in self.mine]
-        for t, d in zip(self.inputs, self.mine):
-            W.fill_device(backend, d, t.data_ptr())
-        self.in_ptrs = [t.data_ptr() for t in self.inputs]
+        owner, owners = W.shared_inputs(self.mine)
+        self.inputs = {i: torch.empty(self.mine[i].nbytes, dtype=torch.uint8, device="cuda") for i in owners}
+        for i in owners:
+            W.fill_device(backend, self.mine[i], self.inputs[i].data_ptr())
+        self.in_ptrs = [self.inputs[o].data_ptr() for o in owner]
         hq = [W.has_quantizer(d) for d in self.mine]
         self.scales = [torch.empty(d.base_type.shape[0], dtype=torch.float32, device="cuda") if q else None
                        for d, q in zip(self.mine, hq)]
@@ -314,11 +315,13 @@ def run_e2e(torch, dist, backend, stream, decls, rank, world, comm, args, algori
     nchunks = max(1, min(16, (total_in // world + chunk_bytes - 1) // chunk_bytes))
     sf = ShardedFolder(backend, decls, rank, world, transport, weights=w, nchunks=nchunks, rank0_chunks=nchunks)
     mine = [decls[i] for i in sf.layout.mine[rank]]
-    host_in = [torch.empty(d.nbytes, dtype=torch.uint8, pin_memory=True) for d in mine]
+    owner, owners = W.shared_inputs(mine)
+    host_own = {i: torch.empty(mine[i].nbytes, dtype=torch.uint8, pin_memory=True) for i in owners}
     tmp = torch.empty(max([d.nbytes for d in mine] + [1]), dtype=torch.uint8, device="cuda")
-    for h, d in zip(host_in, mine):
-        W.fill_device(backend, d, tmp.data_ptr())
-        h.copy_(tmp[:d.nbytes])
+    for i in owners:
+        W.fill_device(backend, mine[i], tmp.data_ptr())
+        host_own[i].copy_(tmp[:mine[i].nbytes])
+    host_in = [host_own[o] for o in owner]
     torch.cuda.synchronize()
     del tmp
     hq = [W.has_quantizer(d) for d in mine]
@@ -396,7 +399,7 @@ def run_per_config(torch, dist, backend, stream, args, peak):
     for name in ("cfg1", "cfg2", "cfg3", "cfg4"):
         builder, n_inst, text, dtype_name, dominant = W.WORKLOADS[name]
         decls = builder(n_inst)
-        run = DeviceRun(torch, dist, backend, stream, decls, 0, 1, None, args)
+        run = DeviceRun(torch, dist, backend, stream, decls, 0, 1, None, args, rank0_chunks=W.PIPELINE_CHUNKS.get(name, 1))
         tm = run.timed(20, 3)
         fold_b, codec_b, n_comp, blob_b, folded_sizes = run.byte_counts()
         ms = tm["elapsed_ms"] / 20
@@ -502,7 +505,10 @@ def main():
 
     # The workload description holds millions of Python objects (per-channel scale lists); a cyclic
     # garbage collection walking them would stall the host in the middle of a step.
-    run = DeviceRun(torch, dist, backend, stream, decls, rank, world, comm, args, weights=weights)
+    # rank 0 cuts its share into chunks only where the compression of one chunk can hide the host's planning of
+    # the next (workloads of many small constants); its slots never travel
+    run = DeviceRun(torch, dist, backend, stream, decls, rank, world, comm, args, weights=weights,
+                    rank0_chunks=W.PIPELINE_CHUNKS.get(args.workload, 1))
     gc.collect()
     gc.freeze()
     sampler = ClockSampler(local_rank)

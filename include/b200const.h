@@ -404,6 +404,13 @@ B200C_API int b200c_ipc_close(b200c_ctx* ctx, void* mapped);
 B200C_API int b200c_copy_segments_async(b200c_ctx* ctx, const b200c_copy_seg* segs, int count, const uint64_t* wait_flag,
                                         uint64_t wait_value, uint64_t* done_flag, uint64_t done_value,
                                         unsigned timeout_ms, int mode, int ctas);
+/* The same copies, ordered after the work of a compression ticket (b200c_btc_compress_inplace_begin;
+ * the ticket may have been collected already, as long as no later _begin has reused it) instead
+ * of after everything queued on the context's stream: a chunk travels as soon as it is complete
+ * although the next chunk's kernels are queued behind it.                                          */
+B200C_API int b200c_copy_segments_after(b200c_ctx* ctx, int ticket, const b200c_copy_seg* segs, int count,
+                                        const uint64_t* wait_flag, uint64_t wait_value, uint64_t* done_flag,
+                                        uint64_t done_value, unsigned timeout_ms, int mode, int ctas);
 B200C_API int b200c_wait_flags(b200c_ctx* ctx, const uint64_t* flags_dev, int count, uint64_t value, unsigned timeout_ms,
                                int on_transfer_stream);
 B200C_API int b200c_signal_flags(b200c_ctx* ctx, uint64_t* const* targets, int count, uint64_t value);

@@ -166,6 +166,8 @@ SYMBOLS = {
     "b200c_ipc_close": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200c_copy_segments_async": (C.c_int, [C.c_void_p, _P(b200c_copy_seg), C.c_int, C.c_void_p, C.c_uint64, C.c_void_p,
                                             C.c_uint64, C.c_uint, C.c_int, C.c_int]),
+    "b200c_copy_segments_after": (C.c_int, [C.c_void_p, C.c_int, _P(b200c_copy_seg), C.c_int, C.c_void_p, C.c_uint64, C.c_void_p,
+                                            C.c_uint64, C.c_uint, C.c_int, C.c_int]),
     "b200c_wait_flags": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_uint64, C.c_uint, C.c_int]),
     "b200c_signal_flags": (C.c_int, [C.c_void_p, _P(C.c_void_p), C.c_int, C.c_uint64]),
     "b200c_exchange_status": (C.c_int, [C.c_void_p, _P(C.c_int)]),

@@ -548,12 +548,17 @@ class CudaBackend:
         self.lib.b200c_ipc_close(self.ctx, mapped)
 
     def copy_segments_async(self, segs, wait_flag=None, wait_value=0, done_flag=None, done_value=0, timeout_ms=5000,
-                            mode=0, ctas=64):
-        """segs: (src pointer, dst pointer, bytes) triples; see b200c_copy_segments_async."""
+                            mode=0, ctas=64, after_ticket=None):
+        """segs: (src pointer, dst pointer, bytes) triples; see b200c_copy_segments_async.  With after_ticket the
+        copies are ordered after that compression ticket only (b200c_copy_segments_after)."""
         n = len(segs)
         arr = (A.b200c_copy_seg * max(1, n))()
         for i, (src, dst, nb) in enumerate(segs):
             arr[i].src, arr[i].dst, arr[i].n = src, dst, nb
+        if after_ticket is not None:
+            raise_for(self.lib.b200c_copy_segments_after(self.ctx, after_ticket, arr, n, wait_flag, wait_value, done_flag,
+                                                         done_value, timeout_ms, mode, ctas), self._err())
+            return
         raise_for(self.lib.b200c_copy_segments_async(self.ctx, arr, n, wait_flag, wait_value, done_flag, done_value,
                                                      timeout_ms, mode, ctas), self._err())
 

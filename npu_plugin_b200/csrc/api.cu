@@ -1070,6 +1070,24 @@ int b200c_copy_segments_async(b200c_ctx* h, const b200c_copy_seg* segs, int coun
                      reinterpret_cast<unsigned long long*>(done_flag), done_value, timeout_ms, mode, ctas > 0 ? ctas : 64);
     });
 }
+int b200c_copy_segments_after(b200c_ctx* h, int ticket, const b200c_copy_seg* segs, int count, const uint64_t* wait_flag,
+                              uint64_t wait_value, uint64_t* done_flag, uint64_t done_value, unsigned timeout_ms, int mode,
+                              int ctas) {
+    return guarded([&] {
+        if (!h) throw BadArg("null context");
+        if (count < 0 || (count > 0 && !segs)) throw BadArg("bad segment list");
+        if (mode < 0 || mode > 2) throw BadArg("mode must be 0 (copy kernel), 1 (copy engine) or 2 (bulk-copy kernel)");
+        for (int i = 0; i < count; ++i)
+            if (segs[i].n && (!segs[i].src || !segs[i].dst)) throw BadArg("null segment pointer");
+        Context* ctx = reinterpret_cast<Context*>(h);
+        if (ticket < 0 || ticket >= Context::kCodecTickets || !ctx->codecTickets[ticket].done) throw BadArg("not a compression ticket");
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        B2_CUDA(cudaSetDevice(ctx->device));
+        pushSegments(ctx, segs, count, reinterpret_cast<const unsigned long long*>(wait_flag), wait_value,
+                     reinterpret_cast<unsigned long long*>(done_flag), done_value, timeout_ms, mode, ctas > 0 ? ctas : 64,
+                     ctx->codecTickets[ticket].done);
+    });
+}
 int b200c_wait_flags(b200c_ctx* h, const uint64_t* flags_dev, int count, uint64_t value, unsigned timeout_ms,
                      int on_transfer_stream) {
     return guarded([&] {

@@ -448,11 +448,17 @@ static void pushSegmentsBulk(Context* ctx, const b200c_copy_seg* segs, int count
 
 void pushSegments(Context* ctx, const b200c_copy_seg* segs, int count, const unsigned long long* waitFlag,
                   unsigned long long waitValue, unsigned long long* doneFlag, unsigned long long doneValue,
-                  unsigned int timeoutMs, int mode, int ctas) {
+                  unsigned int timeoutMs, int mode, int ctas, cudaEvent_t after) {
     ensureExchange(ctx);
-    // the pushed bytes are whatever the context's stream has produced so far
-    B2_CUDA(cudaEventRecord(ctx->xferEvent, ctx->stream));
-    B2_CUDA(cudaStreamWaitEvent(ctx->xferStream, ctx->xferEvent, 0));
+    if (after) {
+        // the pushed bytes were complete when `after` was recorded; work queued on the context's stream since
+        // then (the next chunk's kernels) does not hold the transfer back
+        B2_CUDA(cudaStreamWaitEvent(ctx->xferStream, after, 0));
+    } else {
+        // the pushed bytes are whatever the context's stream has produced so far
+        B2_CUDA(cudaEventRecord(ctx->xferEvent, ctx->stream));
+        B2_CUDA(cudaStreamWaitEvent(ctx->xferStream, ctx->xferEvent, 0));
+    }
     const unsigned long long timeoutNs = static_cast<unsigned long long>(timeoutMs) * 1000000ull;
     auto nextCounter = [&] { return ctx->xferCounters + (ctx->xferCounterNext++ % Context::kXferCounters); };
     if (mode == 2) {

@@ -857,6 +857,7 @@ void Planner::getSparsityMap(const TensorType& outType, int swizzleKey) {
         it.sparseByte = static_cast<unsigned int>(sparseBitsFor(sv, tag, false) & 0xFF);
         it.swizzleKey = swzNext ? static_cast<int>(static_cast<uint32_t>(_next->i0) % 6u) : -1;
         it.totalBytes = swzNext ? roundUp(static_cast<int64_t>(bytes), kSwizzleSizeAlign) : static_cast<int64_t>(bytes);
+        it.counts = nullptr;
         if (static_cast<size_t>(it.totalBytes) > _finalCap) throw Capacity("output buffer too small");
         launchMapItem(_ctx, it);
         dst = _finalDst;
@@ -935,6 +936,7 @@ void Planner::sparsify(const Transformation& x) {  // sparsify.cpp:115-186
         it.sparseByte = static_cast<unsigned int>(sbits & 0xFF);
         it.swizzleKey = swzNext ? static_cast<int>(static_cast<uint32_t>(_next->i0) % 6u) : -1;
         it.err = _ctx->errWord;
+        it.countsReady = 0;
         int64_t total = 0;
         if (x.hasAux) {
             for (int64_t n : x.aux) total += roundUp(n * eb, kWeightSetAlign);

@@ -112,6 +112,8 @@ struct MapItem {
     long long totalBytes;      // bytes to write: the map, then zeros up to the swizzle size alignment
     unsigned int sparseByte;
     int swizzleKey;
+    long long* counts;         // when a Sparsify of the same batch reads the same source: its per-channel counts,
+                               // written here as a by-product of the one read (else nullptr)
 };
 
 // One Sparsify of 8-bit elements written straight to its final place.
@@ -127,6 +129,7 @@ struct SparseItem {
     unsigned int sparseByte;
     int swizzleKey;        // -1: not swizzled
     int* err;
+    int countsReady;       // the sparsity-map kernel of the same batch has already counted this source
 };
 
 class PlanPool;
@@ -380,7 +383,7 @@ void* ipcOpen(Context* ctx, const unsigned char handle[64], unsigned long long o
 void ipcClose(Context* ctx, void* mapped);
 void pushSegments(Context* ctx, const b200c_copy_seg* segs, int count, const unsigned long long* waitFlag,
                   unsigned long long waitValue, unsigned long long* doneFlag, unsigned long long doneValue,
-                  unsigned int timeoutMs, int mode, int ctas);
+                  unsigned int timeoutMs, int mode, int ctas, cudaEvent_t after = nullptr);
 void waitFlags(Context* ctx, const unsigned long long* flagsDev, int count, unsigned long long value, unsigned int timeoutMs,
                bool onTransferStream);
 void signalFlags(Context* ctx, unsigned long long* const* targets, int count, unsigned long long value);

@@ -6,6 +6,7 @@
 #include "runtime.h"
 
 #include <algorithm>
+#include <unordered_map>
 #include <vector>
 
 namespace b200c {
@@ -272,26 +273,85 @@ __device__ __forceinline__ unsigned int neMask16(const uint4& v, unsigned int sv
 }
 
 constexpr int kMapUnitsPerCta = 2048;  // 16 input bytes -> 2 map bytes per unit, 8 units per thread
+constexpr int kMapMaxChanPerCta = 256;  // map rows are at least 16 bytes (8 units)
 
+// A CTA covers 2048 units (32 KB of elements -> 4 KB of map); in every round a warp loads 32 consecutive
+// units (512 coalesced bytes), the 16-bit masks of 8 neighbouring lanes are joined with shuffles and every
+// eighth lane stores one whole 16-byte chunk through the swizzle rotation.  Index arithmetic is 32-bit
+// relative to the CTA's first channel (a shift when the units per channel are a power of two).
+//
+// When a Sparsify of the same batch reads the same source (it.counts), the per-channel counts it needs
+// fall out of this pass: every unit adds the population count of its mask to a shared-memory counter
+// of its channel, and the CTA writes the counters of the channels it covers.  The host only asks for
+// this when CTAs cover whole channels (kMapUnitsPerCta is a multiple of the units per channel).
 __global__ void __launch_bounds__(256) sparsityMapBatchKernel(const MapItem* __restrict__ items,
                                                               const long long* __restrict__ ctaStart, int nitems) {
+    __shared__ int chanCount[kMapMaxChanPerCta];
     const int k = findBatchItem(ctaStart, nitems, blockIdx.x);
     const MapItem it = items[k];
     const unsigned int sv4 = it.sparseByte * 0x01010101u;
-    const long long unitsPerOC = it.outBytesPerOC / 2, dataUnitsPerOC = it.work / 16;
-    const long long units = (it.totalBytes + 1) / 2, mapUnits = it.oc * unitsPerOC;
+    const long long unitsPerOC = it.outBytesPerOC / 2;
+    const long long units = (it.totalBytes + 1) / 2, mapUnits = it.oc * unitsPerOC;  // both multiples of 8
     const long long first = (blockIdx.x - ctaStart[k]) * kMapUnitsPerCta;
+    const bool counting = it.counts != nullptr;
+    const long long oc0 = first / unitsPerOC;  // first channel of this CTA (counting: CTAs start on channel boundaries)
+    const unsigned int rem0 = static_cast<unsigned int>(first - oc0 * unitsPerOC);
+    const unsigned int upo = static_cast<unsigned int>(unitsPerOC);
+    const int upoShift = (upo & (upo - 1)) == 0 ? 31 - __clz(upo) : -1;
+    const unsigned int dataUnits = static_cast<unsigned int>(it.work / 16);
+    const unsigned int work = static_cast<unsigned int>(it.work);
+    // units of this CTA that belong to the map / that are written at all
+    const unsigned int liveMap = static_cast<unsigned int>(min(static_cast<long long>(kMapUnitsPerCta), max(0ll, mapUnits - first)));
+    const unsigned int liveAll = static_cast<unsigned int>(min(static_cast<long long>(kMapUnitsPerCta), max(0ll, units - first)));
+    const unsigned char* src0 = it.src + oc0 * it.work;
+    const int lane = threadIdx.x & 31;
+    if (counting) {
+        chanCount[threadIdx.x] = 0;
+        __syncthreads();
+    }
+    constexpr int R = kMapUnitsPerCta / 256;
+    uint4 x[R];
+    unsigned int chan[R];
 #pragma unroll
-    for (int r = 0; r < kMapUnitsPerCta / 256; ++r) {
-        const long long u = first + r * 256 + threadIdx.x;
-        if (u >= units) break;
-        unsigned int mask16 = 0;
-        if (u < mapUnits) {
-            const long long oc = u / unitsPerOC, j = u - oc * unitsPerOC;
-            if (j < dataUnitsPerOC) mask16 = neMask16(__ldg(reinterpret_cast<const uint4*>(it.src + oc * it.work) + j), sv4);
+    for (int r = 0; r < R; ++r) {  // all loads of the thread are issued before the first is used
+        const unsigned int local = r * 256 + threadIdx.x;
+        const unsigned int at = rem0 + local;
+        const unsigned int dc = upoShift >= 0 ? (at >> upoShift) : (at / upo);
+        const unsigned int j = at - dc * upo;
+        chan[r] = dc;
+        x[r] = make_uint4(sv4, sv4, sv4, sv4);  // padding units compare equal everywhere: mask 0
+        if (local < liveMap && j < dataUnits) {
+            x[r] = __ldg(reinterpret_cast<const uint4*>(src0 + static_cast<unsigned long long>(dc) * work) + j);
         }
-        // two output bytes; a 16-byte swizzle chunk is never split
-        *reinterpret_cast<unsigned short*>(it.dst + swizzleAddr(u * 2, it.swizzleKey)) = static_cast<unsigned short>(mask16);
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const unsigned int local = r * 256 + threadIdx.x;
+        const unsigned int mask16 = neMask16(x[r], sv4);
+        if (counting) {
+            const int n = __popc(mask16);
+            if (upo >= 32) {
+                // the 32 units of a warp lie in one channel (the units per channel are a multiple of 32)
+                const int total = __reduce_add_sync(0xFFFFFFFFu, n);
+                if (lane == 0 && total) atomicAdd(&chanCount[chan[r]], total);
+            } else if (n) {
+                atomicAdd(&chanCount[chan[r]], n);
+            }
+        }
+        // eight neighbouring lanes -> one 16-byte chunk in the first of them
+        const unsigned int m32 = mask16 | (__shfl_down_sync(0xFFFFFFFFu, mask16, 1) << 16);
+        const unsigned int b = __shfl_down_sync(0xFFFFFFFFu, m32, 2);
+        const unsigned int c = __shfl_down_sync(0xFFFFFFFFu, m32, 4);
+        const unsigned int d = __shfl_down_sync(0xFFFFFFFFu, b, 4);
+        if ((lane & 7) == 0 && local < liveAll) {
+            const long long a = (first + local) * 2;  // a 16-byte swizzle chunk is never split
+            *reinterpret_cast<uint4*>(it.dst + swizzleAddr(a, it.swizzleKey)) = make_uint4(m32, b, c, d);
+        }
+    }
+    if (counting) {
+        __syncthreads();
+        const long long oc = oc0 + threadIdx.x;
+        if (threadIdx.x < kMapUnitsPerCta / unitsPerOC && oc < it.oc) it.counts[oc] = chanCount[threadIdx.x];
     }
 }
 
@@ -315,6 +375,7 @@ __global__ void __launch_bounds__(256) sparseCountBatchKernel(const SparseItem* 
         if (ch >= nchan) break;
         k = nextItem(chanStart, nitems, k, ch);
         const SparseItem& it = items[k];
+        if (it.countsReady) continue;  // counted by the sparsity-map kernel of the same source
         const long long c = ch - chanStart[k];
         const unsigned int sv4 = it.sparseByte * 0x01010101u;
         const uint4* row = reinterpret_cast<const uint4*>(it.src + c * it.work);
@@ -547,6 +608,25 @@ void flushSparsityBatch(Context* ctx) {
     std::vector<SparseItem> sparse;
     maps.swap(ctx->mapBatch);
     sparse.swap(ctx->sparseBatch);
+    // A sparsity map and a Sparsify of the same source (the two constants of one sparse weight) need the
+    // same comparison of every element: the map kernel then leaves the per-channel counts behind and the
+    // Sparsify skips its counting pass, so the source is read twice instead of three times.
+    if (!maps.empty() && !sparse.empty()) {
+        std::unordered_map<const void*, size_t> bySrc;
+        for (size_t i = 0; i < sparse.size(); ++i) bySrc.emplace(sparse[i].src, i);
+        for (MapItem& m : maps) {
+            const auto hit = bySrc.find(m.src);
+            if (hit == bySrc.end()) continue;
+            SparseItem& sp = sparse[hit->second];
+            const long long unitsPerOC = m.outBytesPerOC / 2;
+            if (sp.countsReady || sp.oc != m.oc || sp.work != m.work || sp.sparseByte != m.sparseByte || unitsPerOC <= 0 ||
+                kMapUnitsPerCta % unitsPerOC != 0) {
+                continue;
+            }
+            m.counts = sp.counts;
+            sp.countsReady = 1;
+        }
+    }
     runMapItems(ctx, maps);
     runSparseItems(ctx, sparse);
 }

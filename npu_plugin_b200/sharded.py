@@ -155,7 +155,7 @@ class ShardedFolder:
             size, comp = self.folders[k].compress_inplace_end(ticket)
             chunk_rows = list(zip(self.my_chunks[k], self._slot_off[k], size.tolist(), comp.astype(np.int64).tolist()))
             if r != 0:
-                self.t.push_chunk(self, k, chunk_rows)
+                self.t.push_chunk(self, k, chunk_rows, after_ticket=ticket)
             return chunk_rows
 
         for k, (chunk, f) in enumerate(zip(self.my_chunks, self.folders)):
@@ -293,7 +293,7 @@ class PushTransport:
             sf.b.stream_join()
             self._row_at = 0
 
-    def push_chunk(self, sf, k, chunk_rows):
+    def push_chunk(self, sf, k, chunk_rows, after_ticket=None):
         b, L, rank = sf.b, sf.layout, sf.rank
         region = L.region_off[rank]
         segs = [(self.buffer + (off - region), self.mapped_blob + off, size) for _, off, size, _ in chunk_rows]
@@ -308,7 +308,8 @@ class PushTransport:
             self._row_at += n
         flag = self.mapped_blob + L.flags_off + (k * L.world + rank) * 8
         b.copy_segments_async(segs, wait_flag=self.release_word if k == 0 else None, wait_value=sf.seq - 1,
-                              done_flag=flag, done_value=sf.seq, timeout_ms=self.timeout_ms, mode=self.mode, ctas=self.ctas)
+                              done_flag=flag, done_value=sf.seq, timeout_ms=self.timeout_ms, mode=self.mode, ctas=self.ctas,
+                              after_ticket=after_ticket)
 
     def finish_step(self, sf, chunks_done):
         # chunks this rank does not have still owe their flag (the first of them waits for the release when

@@ -129,8 +129,24 @@ WORKLOADS = {
 }
 
 
+# chunks a single rank cuts the workload into: with several, the device compresses chunk k while the host plans
+# the fold of chunk k + 1 (worth it where the constants are small and every one of them is compressed)
+PIPELINE_CHUNKS = {}
+
+
 def has_quantizer(d):
     return any(t.kind == A.X_QUANTIZE_SYNTH for t in d.transforms)
+
+
+def shared_inputs(decls):
+    """Constants that hold the same values (same generator stream, type and size: the sparsity map and the
+    sparsified values of one weight) share one base content, as the two DeclareOps of a sparse weight share one
+    dense resource in the compiler.  Returns (owner index per constant, indices that own a buffer)."""
+    first, owner = {}, []
+    for i, d in enumerate(decls):
+        key = (d.stream, d.nbytes, tuple(d.synth), d.base_type.dtype)
+        owner.append(first.setdefault(key, i))
+    return owner, sorted(set(owner))
 
 
 def fill_device(backend, d, dev_ptr):

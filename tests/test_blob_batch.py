@@ -230,3 +230,57 @@ def test_two_contexts_fold_concurrently(oracle):
     assert not errors, errors
     for k in range(2):
         assert np.array_equal(results[k], build(oracle, ws[k]).fold().copyTo())
+
+
+@gpu_only
+def test_sparsity_batch_over_densities_and_shapes(gpu, oracle):
+    """GetSparsityMap and Sparsify of the same weights in one batch (the map kernel then also counts for the
+    Sparsify), over densities from all-sparse to all-dense, a non-zero sparse value, channel lengths with and
+    without the shared-count form, swizzled and plain, with and without numActualElements."""
+    from npu_plugin_b200.const import UniformQuantizedType
+    rng = np.random.default_rng(29)
+    cases = []  # (weights, zero point or None, swizzle)
+    for k, (oc, work, density, zp, swz) in enumerate([
+            (64, 1024, 0.5, None, True), (48, 1024, 0.0, None, True), (48, 1024, 1.0, None, True), (33, 1024, 0.05, None, False),
+            (40, 1024, 0.95, 7, True), (17, 16, 0.5, None, True), (24, 48, 0.4, None, False), (9, 2000, 0.5, None, True),
+            (5, 4096, 0.7, 3, True), (128, 128, 0.5, None, True), (31, 512, 0.02, None, True), (6, 3072, 0.5, None, True)]):
+        w = rng.integers(-127, 128, (oc, work, 1, 1)).astype(np.int8)
+        fill = 0 if zp is None else zp
+        w[w == fill] = fill + 1
+        w[rng.random(w.shape) >= density] = fill
+        cases.append((w, zp, swz))
+    decls, data = [], []
+    for k, (w, zp, swz) in enumerate(cases):
+        pre = [] if zp is None else [Transform(A.X_QUANT_CAST, elem=UniformQuantizedType(A.SI8, A.F16, 0.1, zp, -128, 127))]
+        tail = [Transform(A.X_SWIZZLE_CONSTANT, i0=5, i1=3)] if swz else []
+        bt = NDType(w.shape, A.SI8)
+        decls.append(ConstantDecl(f"map{k}", bt, pre + [Transform(A.X_GET_SPARSITY_MAP)] + tail, w.size, compress=False))
+        data.append(w)
+        if k % 2:  # numActualElements given: the per-channel counts of the data
+            counts = [int(c) for c in (w.reshape(w.shape[0], -1) != (0 if zp is None else zp)).sum(axis=1)]
+            sp = Transform(A.X_SPARSIFY, i0=1, aux=counts)
+        else:
+            sp = Transform(A.X_SPARSIFY, i0=0)
+        decls.append(ConstantDecl(f"vals{k}", bt, pre + [sp] + tail, w.size, compress=False))
+        data.append(w)
+    folder = ShardFolder(gpu, decls)
+    ins = [DevBuf(gpu, d.nbytes) for d in decls]
+    out = DevBuf(gpu, folder.folded_bytes)
+    try:
+        for b, x in zip(ins, data):
+            b.upload(x)
+        for _ in range(2):  # the second pass runs over a used arena and a dirty output buffer
+            gpu.upload(out.ptr, np.full(folder.folded_bytes, 0xCD, np.uint8))
+            folder.fold([b.ptr for b in ins], out.ptr, True)
+            gpu.synchronize()
+            got = out.download()
+            for i, (d, x) in enumerate(zip(decls, data)):
+                want = oracle.fold(d.base_type, x, False, d.transforms)
+                wb = want.copyTo().reshape(-1).view(np.uint8)
+                n = want.bytesWritten
+                off = folder.folded_offsets[i]
+                assert np.array_equal(got[off:off + n], wb[:n]), d.name
+    finally:
+        for b in ins:
+            b.free()
+        out.free()
