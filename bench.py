@@ -442,6 +442,7 @@ def main():
     ap.add_argument("--push-mode", type=int, default=2, choices=[0, 1, 2], help="0: copy kernel, 1: copy engine, 2: bulk-copy kernel")
     ap.add_argument("--push-ctas", type=int, default=32)
     ap.add_argument("--exchange-timeout-ms", type=int, default=20000)
+    ap.add_argument("--log-tensors", default=None, help="write one JSON line per constant of the final blob to this file")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -548,6 +549,15 @@ def main():
         gpu_digests = backend.digest64([blob + off for _, off, _, _ in run.table], [size for _, _, size, _ in run.table])
         digest = combine_digests(gpu_digests, run.table)
         gpu_results = {i: (dg, size, bool(comp)) for dg, (i, _, size, comp) in zip(gpu_digests, run.table)}
+        if args.log_tensors:
+            from npu_plugin_b200.sharded import tensor_log_lines
+            sizes = {}
+            for r in range(world):
+                for chunk in run.sf.layout.chunks[r]:
+                    for i in chunk:
+                        sizes[i] = backend.infer_type(decls[i].base_type, decls[i].transforms).getTotalAllocSize()
+            with open(args.log_tensors, "w") as f:
+                f.write("\n".join(tensor_log_lines(decls, run.table, sizes.get)) + "\n")
 
     # roofline of the dominant kernel
     peak, peak_kind = measured_peak()

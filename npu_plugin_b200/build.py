@@ -72,7 +72,7 @@ def build(force=False, verbose=False, out=LIB):
             sys.stderr.write(f"---- {src}\n{r.stderr}")
     if failed:
         raise RuntimeError("nvcc failed")
-    cmd = [NVCC, "-shared", "-cudart", "shared", "-ccbin", "/usr/bin/g++", "-o", out] + [_obj(s) for s in _sources()]
+    cmd = [NVCC, "-shared", "-cudart", "shared", "-ccbin", "/usr/bin/g++", "-o", out] + [_obj(s) for s in _sources()] + ["-ldl"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)

@@ -506,6 +506,7 @@ int b200c_fold(b200c_ctx* h, const b200c_type* base, const void* data, size_t nb
         if (!h) throw BadArg("null context");
         Context* ctx = reinterpret_cast<Context*>(h);
         CallScope scope(ctx);
+        TraceRange range("b200c_fold");
         if (!out && out_cap > 0) throw BadArg("null output pointer");
         const auto xs = chainFromC(chain, n);
         auto plan = makePlanner(ctx, base, data, nbytes, is_splat, data_on_device);
@@ -573,6 +574,7 @@ int b200c_fold_batch(b200c_ctx* h, b200c_fold_item* items, int count, int data_o
         if (count < 0 || (count > 0 && !items)) throw BadArg("bad item list");
         Context* ctx = reinterpret_cast<Context*>(h);
         CallScope scope(ctx);
+        TraceRange range("b200c_fold_batch");
         struct BatchGuard {
             Context* c;
             ~BatchGuard() {
@@ -723,6 +725,7 @@ int b200c_fold_batch(b200c_ctx* h, b200c_fold_item* items, int count, int data_o
         auto now = [] { return std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now().time_since_epoch()).count(); };
         while (first < count) {
             const double t0 = now();
+            TraceRange waveRange("fold_batch: plan and flush one wave");
             ++waves;
             int last = first;
             long long bytes = 0;

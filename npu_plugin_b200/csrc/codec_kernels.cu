@@ -703,6 +703,7 @@ void codecCollect(Context* ctx, CodecPending* pending, CodecResult* results) {
 
 void codecCompressBatch(Context* ctx, int count, const CodecBuf* bufs, unsigned char* outDev, size_t outCap,
                         int rawFallback, CodecResult* results, CodecPending* pending) {
+    TraceRange range("codec: compress batch");
     const bool inPlace = rawFallback == 2;  // streams replace the head of their own input buffer
     if (pending && !inPlace) throw BadArg("only the in-place batch compression can be left pending");
     if (inPlace) outCap = ~static_cast<size_t>(0) >> 1;

@@ -449,6 +449,7 @@ static void pushSegmentsBulk(Context* ctx, const b200c_copy_seg* segs, int count
 void pushSegments(Context* ctx, const b200c_copy_seg* segs, int count, const unsigned long long* waitFlag,
                   unsigned long long waitValue, unsigned long long* doneFlag, unsigned long long doneValue,
                   unsigned int timeoutMs, int mode, int ctas, cudaEvent_t after) {
+    TraceRange range("exchange: copy segments");
     ensureExchange(ctx);
     if (after) {
         // the pushed bytes were complete when `after` was recorded; work queued on the context's stream since

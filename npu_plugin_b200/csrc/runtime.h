@@ -6,6 +6,7 @@
 #include "view.h"
 
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <cstdint>
 #include <mutex>
@@ -24,6 +25,19 @@ namespace b200c {
     } while (0)
 
 struct Context;
+
+// Named range on the profiler's timeline (NVTX; a no-op when no tool is attached): the phases of a
+// batched fold -- planning, flushing, compression, exchange -- show up next to the kernels they launch.
+struct TraceRange {
+    explicit TraceRange(const char* name) {
+        nvtxRangePushA(name);
+    }
+    ~TraceRange() {
+        nvtxRangePop();
+    }
+    TraceRange(const TraceRange&) = delete;
+    TraceRange& operator=(const TraceRange&) = delete;
+};
 
 // Fused single-pass quantiser (rowquant_kernels.cu): rows are contiguous in the source; the output
 // keeps the row order and may permute elements inside a row.

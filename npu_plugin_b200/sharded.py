@@ -414,6 +414,23 @@ class SingleTransport:
         self.buffer = None
 
 
+def tensor_log_lines(decls, table, folded_size_of=None):
+    """One JSON line per constant of an assembled blob, in model order: name, transformation names, bytes in,
+    bytes stored in the blob, compressed flag and ratio -- the counterpart of the reference's per-constant trace
+    lines (the transformation trace of content.cpp:188, the compression ratio of compress_weights_btc.cpp:193-196)."""
+    import json
+    out = []
+    for (i, off, size, comp), d in zip(table, decls):
+        rec = {"constant": d.name, "transformations": [t.getTransformationName() for t in d.transforms],
+               "bytes_in": int(d.nbytes), "blob_offset": int(off), "bytes_stored": int(size), "compressed": bool(comp)}
+        if folded_size_of is not None:
+            folded = int(folded_size_of(i))
+            rec["bytes_folded"] = folded
+            rec["ratio"] = round(size / folded, 4) if folded else None
+        out.append(json.dumps(rec))
+    return out
+
+
 def blob_digest(backend, blob_ptr, table):
     """Digest of an assembled blob that does not depend on where the slots lie: the per-constant digests of
     the live bytes (b200c_digest64_batch), combined in model order with size and compressed flag."""

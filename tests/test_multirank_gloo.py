@@ -211,3 +211,16 @@ def test_rank_leaving_between_steps_gives_an_error_not_a_hang(tmp_path):
     outcome, seconds = open(tmp_path / "outcome.txt").read().split()
     assert outcome == "exchange-error"
     assert float(seconds) < 30.0
+
+
+def test_tensor_log_lines_describe_every_constant():
+    import json
+    from npu_plugin_b200.sharded import tensor_log_lines
+    decls = _model()
+    table = [(i, 512 * i, max(1, d.nbytes // 2), i % 2) for i, d in enumerate(decls)]
+    lines = tensor_log_lines(decls, table, lambda i: decls[i].nbytes)
+    assert len(lines) == len(decls)
+    first = json.loads(lines[0])
+    assert first["constant"] == decls[0].name and first["bytes_in"] == decls[0].nbytes
+    assert first["bytes_stored"] == table[0][2] and first["compressed"] is False
+    assert json.loads(lines[1])["compressed"] is True and 0 < json.loads(lines[1])["ratio"] <= 1
