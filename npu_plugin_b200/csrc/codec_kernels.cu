@@ -31,10 +31,6 @@ B2_HD void loadBlock(const CodecJobDev& job, unsigned long long blk, unsigned ch
 // One thread per 64-byte block: four 128-bit loads, min / max / zigzag-or / non-zero count with
 // byte-SIMD instructions, mode choice, and one packed 32-bit summary per block
 // (header | base << 8 | record size << 16), so consecutive threads store consecutive words.
-__device__ __forceinline__ unsigned int zigzag4(unsigned int x) {
-    return ((x << 1) & 0xFEFEFEFEu) ^ (((x >> 7) & 0x01010101u) * 0xFFu);
-}
-
 // Per-block statistics.  Byte min/max run on 16-bit lanes (bytes widened with one byte-permute per
 // half, then the native three-input u16x2 min/max); the packed-byte min/max intrinsics are emulated
 // with long instruction sequences on this architecture and made the kernel ALU-bound.
@@ -51,6 +47,11 @@ __device__ __forceinline__ unsigned int signMask4(unsigned int x) {
     unsigned int m;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(m) : "r"(x), "r"(0u), "r"(0xBA98u));
     return m;
+}
+
+// zigzag code of four int8 values at once: (b << 1) ^ (b >> 7, arithmetic), per byte
+__device__ __forceinline__ unsigned int zigzag4(unsigned int x) {
+    return ((x << 1) & 0xFEFEFEFEu) ^ signMask4(x);
 }
 
 __device__ __forceinline__ void statsAddPair(BlockStats& s, unsigned int a, unsigned int b) {
@@ -437,11 +438,80 @@ __device__ __forceinline__ unsigned long long packGroup(unsigned int a, unsigned
     return static_cast<unsigned long long>(qa) | (static_cast<unsigned long long>(qb) << (4 * w));
 }
 
-__device__ __forceinline__ void storeGroup(unsigned char* g8, unsigned long long packed, int w) {
-    const unsigned int plo = static_cast<unsigned int>(packed), phi = static_cast<unsigned int>(packed >> 32);
+// NW words (4 * NW bytes, byte 0 first) written to shared memory at a byte address of any alignment:
+// the words are shifted to the address's phase and stored as whole words; only the bytes of the first
+// and of the last, partly covered word are stored one by one (the neighbouring records own the rest of
+// those words).
+template <int NW>
+__device__ __forceinline__ void storeWords(unsigned char* at, const unsigned int (&w)[NW]) {
+    const unsigned int a = static_cast<unsigned int>(reinterpret_cast<uintptr_t>(at) & 3u);
+    unsigned int* base = reinterpret_cast<unsigned int*>(at - a);
+    const unsigned int sh = 8u * a;
 #pragma unroll
-    for (int j = 0; j < 7; ++j) {
-        if (j < w) g8[j] = static_cast<unsigned char>((j < 4 ? plo : phi) >> (8 * (j & 3)));
+    for (int k = 1; k < NW; ++k) base[k] = __funnelshift_l(w[k - 1], w[k], sh);
+    if (a == 0) {
+        base[0] = w[0];
+    } else {
+        // bytes a .. 3 of the first word: the low 4 - a bytes of w[0]
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            if (i < static_cast<int>(4u - a)) at[i] = static_cast<unsigned char>(w[0] >> (8 * i));
+        }
+        // bytes 0 .. a - 1 of the word behind the last whole one: the top a bytes of w[NW - 1]
+        const unsigned int top = w[NW - 1] >> (32u - sh);
+        unsigned char* tail = reinterpret_cast<unsigned char*>(base + NW);
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            if (i < static_cast<int>(a)) tail[i] = static_cast<unsigned char>(top >> (8 * i));
+        }
+    }
+}
+
+// payload of a PACKU / PACKS record with fields of W bits: eight groups of 8 * W bits, 2 * W words in all.
+// Field widths are compile-time constants here, so every shift below is an immediate.
+template <int W, bool SIGNED>
+__device__ __forceinline__ void packPayload(const unsigned int (&words)[16], unsigned int base, unsigned int (&p)[2 * W]) {
+    const unsigned int base4 = base * 0x01010101u, lowBase = base4 & 0x7F7F7F7Fu, notBase = ~base4;
+#pragma unroll
+    for (int i = 0; i < 2 * W; ++i) p[i] = 0;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const unsigned int lo = words[g * 2], hi = words[g * 2 + 1];
+        unsigned int flo, fhi;
+        if (SIGNED) {
+            flo = zigzag4(lo);
+            fhi = zigzag4(hi);
+        } else {
+            // (b - base) & 0xFF per byte without borrows across bytes
+            flo = ((lo | 0x80808080u) - lowBase) ^ ((lo ^ notBase) & 0x80808080u);
+            fhi = ((hi | 0x80808080u) - lowBase) ^ ((hi ^ notBase) & 0x80808080u);
+        }
+        const unsigned long long v = packGroup(flo, fhi, W);  // 8 * W bits
+        const unsigned int vlo = static_cast<unsigned int>(v), vhi = static_cast<unsigned int>(v >> 32);
+        const int bit = 8 * W * g, idx = bit >> 5, off = bit & 31;
+        if (off == 0) {
+            p[idx] |= vlo;
+            if (idx + 1 < 2 * W) p[idx + 1] |= vhi;
+        } else {
+            p[idx] |= vlo << off;
+            if (idx + 1 < 2 * W) p[idx + 1] |= __funnelshift_l(vlo, vhi, off);
+            if (idx + 2 < 2 * W) p[idx + 2] |= vhi >> (32 - off);
+        }
+    }
+}
+
+template <int W>
+__device__ __forceinline__ void emitPack(const unsigned int (&words)[16], int mode, unsigned int header, unsigned int base,
+                                         unsigned char* rec) {
+    unsigned int p[2 * W];
+    rec[0] = static_cast<unsigned char>(header);
+    if (mode == 2) {
+        rec[1] = static_cast<unsigned char>(base);
+        packPayload<W, false>(words, base, p);
+        storeWords<2 * W>(rec + 2, p);
+    } else {
+        packPayload<W, true>(words, 0u, p);
+        storeWords<2 * W>(rec + 1, p);
     }
 }
 
@@ -602,29 +672,24 @@ __global__ void __launch_bounds__(kEmitThreads) codecEmitKernel(const CodecJobDe
                 const unsigned int header = word & 0xFFu, base = (word >> 8) & 0xFFu;
                 const int mode = header >> 5, w = header & 31;
                 unsigned char* rec = window + phase + (relOff[it * kEmitThreads + bi] - winStart);
-                rec[0] = static_cast<unsigned char>(header);
                 if (mode == 0) {
-#pragma unroll
-                    for (int i = 0; i < 64; ++i) rec[1 + i] = static_cast<unsigned char>(words[i >> 2] >> (8 * (i & 3)));
+                    rec[0] = static_cast<unsigned char>(header);
+                    storeWords<16>(rec + 1, words);
                 } else if (mode == 1) {
+                    rec[0] = static_cast<unsigned char>(header);
                     rec[1] = static_cast<unsigned char>(base);
-                } else if (mode == 2) {
-                    rec[1] = static_cast<unsigned char>(base);
-                    const unsigned int base4 = base * 0x01010101u, lowBase = base4 & 0x7F7F7F7Fu, notBase = ~base4;
-#pragma unroll
-                    for (int gq = 0; gq < 8; ++gq) {  // eight 8-element groups, w bytes each
-                        // (b - base) & 0xFF per byte without borrows across bytes
-                        const unsigned int lo = words[gq * 2], hi = words[gq * 2 + 1];
-                        const unsigned int flo = ((lo | 0x80808080u) - lowBase) ^ ((lo ^ notBase) & 0x80808080u);
-                        const unsigned int fhi = ((hi | 0x80808080u) - lowBase) ^ ((hi ^ notBase) & 0x80808080u);
-                        storeGroup(rec + 2 + gq * w, packGroup(flo, fhi, w), w);
-                    }
-                } else if (mode == 3) {
-#pragma unroll
-                    for (int gq = 0; gq < 8; ++gq) {
-                        storeGroup(rec + 1 + gq * w, packGroup(zigzag4(words[gq * 2]), zigzag4(words[gq * 2 + 1]), w), w);
+                } else if (mode <= 3) {
+                    switch (w) {
+                    case 1: emitPack<1>(words, mode, header, base, rec); break;
+                    case 2: emitPack<2>(words, mode, header, base, rec); break;
+                    case 3: emitPack<3>(words, mode, header, base, rec); break;
+                    case 4: emitPack<4>(words, mode, header, base, rec); break;
+                    case 5: emitPack<5>(words, mode, header, base, rec); break;
+                    case 6: emitPack<6>(words, mode, header, base, rec); break;
+                    default: emitPack<7>(words, mode, header, base, rec); break;
                     }
                 } else {  // sparse: 8 mask bytes, then the non-zero bytes in order
+                    rec[0] = static_cast<unsigned char>(header);
                     unsigned char* nz = rec + 9;
 #pragma unroll
                     for (int q = 0; q < 8; ++q) {

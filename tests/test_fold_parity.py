@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 from npu_plugin_b200 import _cabi as A
-from npu_plugin_b200.const import (ConstError, ContentAttr, DimsOrder, NDType, UniformQuantizedPerAxisType,
+from npu_plugin_b200.const import (ConstError, ContentAttr, DimsOrder, NDType, Transform, UniformQuantizedPerAxisType,
                                    UniformQuantizedType)
 
 pytestmark = pytest.mark.gpu
@@ -245,6 +245,74 @@ def test_codec_parity_and_roundtrip(gpu, oracle, n, kind):
     assert np.array_equal(gpu.btc_decompress(sg, n), x)
     assert np.array_equal(oracle.btc_decompress(sg, n), x)
     assert ns_g == (n <= len(sg))
+
+
+def test_codec_every_mode_and_field_width(gpu, oracle):
+    """Blocks built so that every record form occurs -- RAW, CONST, PACKU and PACKS with each field width from 1 to 7,
+    SPARSE -- shuffled, so that the blocks of one iteration of the emit kernel mix all forms, at several lengths
+    (a ragged tail, block counts around the kernel's 128-block iterations and 1024-block shares)."""
+    rng = np.random.default_rng(99)
+    blocks = []
+    for rep in range(40):
+        for w in range(1, 8):
+            lo = int(rng.integers(40, 100)) if w < 7 else 100
+            blocks.append((lo + rng.integers(0, 1 << w, 64)).astype(np.uint8))            # PACKU, width w
+            blocks[-1][:2] = (lo, lo + (1 << w) - 1)
+            half = 1 << (w - 1)
+            b = rng.integers(-half, half, 64).astype(np.int8)
+            b[:2] = (-half, half - 1)
+            blocks.append(b.view(np.uint8))                                               # PACKS, width w
+        blocks.append(rng.integers(0, 256, 64).astype(np.uint8))                          # RAW
+        blocks.append(np.full(64, int(rng.integers(0, 256)), np.uint8))                   # CONST
+        sp = rng.integers(1, 256, 64).astype(np.uint8)
+        sp[rng.random(64) < 0.85] = 0
+        blocks.append(sp)                                                                 # SPARSE
+    order = rng.permutation(len(blocks))
+    x_all = np.concatenate([blocks[i] for i in order])
+    modes = set()
+    for n in (x_all.size, 64 * 127, 64 * 128 + 5, 64 * 1024, 64 * 1025 - 1, 64 * 300 + 37):
+        x = np.resize(x_all, n)
+        sg, ns_g = gpu.btc_compress(x)
+        so, ns_o = oracle.btc_compress(x)
+        assert ns_g == ns_o and np.array_equal(sg, so), f"stream of {n} bytes differs from the oracle encoder"
+        assert np.array_equal(gpu.btc_decompress(sg, n), x)
+        assert np.array_equal(oracle.btc_decompress(sg, n), x)
+    # the forms really occur: walk the records of the first stream
+    so, _ = oracle.btc_compress(x_all)
+    nblocks = (x_all.size + 63) // 64
+    nsuper = (nblocks + 63) // 64
+    at = 32 + 4 * nsuper
+    for _ in range(nblocks):
+        h = int(so[at])
+        mode, w = h >> 5, h & 31
+        modes.add((mode, w))
+        at += {0: 65, 1: 2, 2: 2 + 8 * w, 3: 1 + 8 * w}.get(mode, 9 + int(np.unpackbits(so[at + 1:at + 9]).sum()))
+    assert {(0, 0), (1, 0), (4, 0)} <= modes
+    assert {(2, w) for w in range(1, 8)} <= modes and {(3, w) for w in range(1, 8)} <= modes
+
+
+def test_truncated_and_malformed_streams_are_rejected(backend):
+    """A stream cut anywhere -- inside the header, the index, a record, the mask of a SPARSE record -- or with an
+    unassigned mode in a record header is reported as an error; the decoder looks at no byte behind the end of the
+    stream it was given (the size of a SPARSE record is only read once its mask is known to be inside)."""
+    from npu_plugin_b200.const import ConstError
+    rng = np.random.default_rng(5)
+    x = rng.integers(1, 256, 64 * 70).astype(np.uint8)
+    x[rng.random(x.size) < 0.85] = 0          # every block becomes a SPARSE record
+    stream, not_smaller = backend.btc_compress(x)
+    assert not not_smaller
+    assert np.array_equal(backend.btc_decompress(stream, x.size), x)
+    first_record = 32 + 4 * 2                  # header + two index entries (70 blocks)
+    assert stream[first_record] >> 5 == 4
+    for cut in (0, 10, 31, 33, first_record, first_record + 1, first_record + 5, first_record + 8, first_record + 9,
+                stream.size // 2, stream.size - 40):
+        with pytest.raises(ConstError):
+            backend.btc_decompress(stream[:cut].copy(), x.size)
+    for bad_mode in (5, 6, 7):
+        broken = stream.copy()
+        broken[first_record] = (bad_mode << 5) | (broken[first_record] & 31)
+        with pytest.raises(ConstError):
+            backend.btc_decompress(broken, x.size)
 
 
 # ------------------------------------------------------------------ random chains
@@ -516,3 +584,63 @@ def test_relocate_weights_table(gpu, oracle, offsets, ptrs, compressed):
     got = cg.getValues().reshape(OC, 4)
     assert np.array_equal(got[:, 2:], table[:, 0, 0, 2:])
     assert got[0, 0] == ptrs[0] and (got[10::5, 1] == 0xFFFFFF).all()
+
+
+# ------------------------------------------------------------------ exhaustive small reorders
+def _all_small_reorders():
+    import itertools
+    cases = []
+    for rank in range(1, 6):
+        shape = [2, 3, 4, 2, 3][:rank]
+        for perm in itertools.permutations(range(rank)):
+            cases.append((tuple(shape), perm))
+    return cases
+
+
+@pytest.mark.gpu
+def test_every_permutation_of_small_tensors(gpu, oracle):
+    """Every memory permutation of every rank up to 5 at extents of at most 4 (153 permutations), for 1-, 2- and
+    4-byte elements, plain and followed by SwizzleConstant, folded in one batched call and compared with the oracle
+    byte for byte -- the index arithmetic of the view composer and of the tile / generic kernels has no case left
+    that only large shapes would reach."""
+    from npu_plugin_b200.blob import ConstantDecl, ShardFolder
+    rng = np.random.default_rng(17)
+    decls, data = [], []
+    for (shape, perm), (dt, npdt) in itertools_product(_all_small_reorders(), [(A.UI8, np.uint8), (A.F16, np.float16), (A.SI32, np.int32)]):
+        x = rng.integers(0, 100, shape).astype(npdt)
+        for swz in (False, True):
+            chain = [Transform(A.X_REORDER, a=perm)] + ([Transform(A.X_SWIZZLE_CONSTANT, i0=5, i1=3)] if swz else [])
+            if swz:
+                # SwizzleConstant flattens to [N,1,1,1] under the input's order and the reference rejects the
+                # combinations where that order does not fit the new shape: those are not folds
+                try:
+                    oracle.infer_type(NDType(shape, dt), chain)
+                except ConstError:
+                    continue
+            decls.append(ConstantDecl(f"p{len(decls)}", NDType(shape, dt), chain, x.nbytes, compress=False))
+            data.append(x)
+    folder = ShardFolder(gpu, decls)
+    total_in = sum(x.nbytes for x in data)
+    src, out = gpu.dev_alloc(total_in + 16 * len(data)), gpu.dev_alloc(folder.folded_bytes)
+    try:
+        ptrs, at = [], 0
+        for x in data:
+            gpu.upload(src + at, x)
+            ptrs.append(src + at)
+            at += (x.nbytes + 15) // 16 * 16
+        gpu.fill_zero(out, folder.folded_bytes)
+        folder.fold(ptrs, out, True)
+        gpu.synchronize()
+        got = gpu.download(out, folder.folded_bytes)
+        for i, (d, x) in enumerate(zip(decls, data)):
+            want = oracle.fold(d.base_type, x, False, d.transforms).copyTo().reshape(-1).view(np.uint8)
+            off = folder.folded_offsets[i]
+            assert np.array_equal(got[off:off + want.size], want), f"{d.base_type.shape} perm {d.transforms[0].a} dtype {d.base_type.dtype}"
+    finally:
+        gpu.dev_free(src)
+        gpu.dev_free(out)
+
+
+def itertools_product(a, b):
+    import itertools
+    return itertools.product(a, b)
