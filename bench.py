@@ -122,6 +122,7 @@ def run_cpu(decls, steps, warmup, budget_elems, threads=None, want_digests=False
     cores = orc.set_threads(threads or (os.cpu_count() or 1))
     sample = cpu_sample_decls(decls, budget_elems)
     data = [orc.synth_of(decls[i], W.SEED) for i in sample]
+    slot_sizes = {i: orc.infer_type(decls[i].base_type, decls[i].transforms).getTotalAllocSize() for i in sample}
     for i in sample:
         for t in decls[i].transforms:
             if t.kind == A.X_QUANTIZE_SYNTH:
@@ -138,6 +139,13 @@ def run_cpu(decls, steps, warmup, budget_elems, threads=None, want_digests=False
             b += d.nbytes + folded.size
             if W.has_quantizer(d):
                 b += 4 * d.base_type.shape[0]
+            # the constant's buffer as the reference's writers hold it: pre-zeroed, of the type's size, with the
+            # content copied in (a Sparsify result is shorter than its type says)
+            slot_size = slot_sizes[i]
+            if folded.size < slot_size:
+                slot = np.zeros(slot_size, np.uint8)
+                slot[:folded.size] = folded
+                folded = slot
             live, comp = folded, False
             if d.compress and folded.size >= 4096:
                 stream, not_smaller = orc.btc_compress(folded)
@@ -250,10 +258,12 @@ class DeviceRun:
         """(fold bytes, codec bytes, compressed constants, blob bytes) of this rank's share."""
         own = {i: (size, comp) for i, _, size, comp in (self.table if self.rank == 0 else self.own_rows)}
         idx = self.sf.layout.mine[self.rank]
-        folded = [f for fl in self.sf.folders for f in fl.folded_sizes]
+        # bytes the fold really wrote (a Sparsify result is shorter than its slot) and the slot sizes the codec reads
+        written = [f for fl in self.sf.folders for f in fl.written_sizes()]
+        slots = [f for fl in self.sf.folders for f in fl.folded_sizes]
         streams = [own[i][0] if own[i][1] else None for i in idx]
-        fold_b, codec_b = W.algorithmic_bytes(self.mine, folded, streams)
-        return fold_b, codec_b, sum(1 for i in idx if own[i][1]), sum(own[i][0] for i in idx), folded
+        fold_b, codec_b = W.algorithmic_bytes(self.mine, written, streams, slots)
+        return fold_b, codec_b, sum(1 for i in idx if own[i][1]), sum(own[i][0] for i in idx), written
 
     def fold_launches(self):
         l0 = self.b.launch_count()

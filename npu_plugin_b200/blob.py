@@ -139,6 +139,12 @@ class ShardFolder:
                 raise_for(rc, lib.b200c_last_error())
             first = last
 
+    def written_sizes(self):
+        """Bytes the last fold() wrote per constant.  Equal to folded_sizes except for contents that are shorter
+        than their type says (Sparsify without numActualElements: the values end where the data decides, the
+        rest of the pre-zeroed slot is never touched)."""
+        return [int(self._items[i].out_bytes) for i in range(len(self.decls))]
+
     def fold_one_by_one(self, data_ptrs, folded_ptr, data_on_device=True, side_ptrs=None):
         """Same result through one b200c_fold call per constant."""
         lib, ctx = self.lib, self.ctx

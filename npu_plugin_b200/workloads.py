@@ -155,14 +155,15 @@ def fill_device(backend, d, dev_ptr):
     backend.synth_fill(dev_ptr, d.nbytes * 8 // A.dtype_bits(dt), dt, dist, p0, p1, SEED, d.stream)
 
 
-def algorithmic_bytes(decls, folded_sizes, stream_sizes):
-    """Read-once + write-once bytes of one step.  Fold: input + folded output (written straight into the blob
-    slot) + the quantiser's scale tables.  Codec: every constant offered to it is read once; only a stream that
-    is smaller than its constant is written (stream_sizes[i] is its length, else None)."""
+def algorithmic_bytes(decls, folded_sizes, stream_sizes, slot_sizes=None):
+    """Read-once + write-once bytes of one step.  Fold: input + folded output (the bytes really written into the
+    blob slot: folded_sizes) + the quantiser's scale tables.  Codec: every constant offered to it is read once
+    (its whole slot: slot_sizes, default folded_sizes); only a stream that is smaller than its constant is written
+    (stream_sizes[i] is its length, else None)."""
     fold = sum(d.nbytes for d in decls) + sum(folded_sizes)
     fold += sum(4 * d.base_type.shape[0] for d in decls if has_quantizer(d))
     codec = 0
-    for d, fs, ss in zip(decls, folded_sizes, stream_sizes):
+    for d, fs, ss in zip(decls, slot_sizes if slot_sizes is not None else folded_sizes, stream_sizes):
         if d.compress and fs >= 4096:
             codec += fs + (ss or 0)
     return fold, codec
