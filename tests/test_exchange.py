@@ -13,6 +13,8 @@ import time
 import numpy as np
 import pytest
 
+from npu_plugin_b200 import _cabi as A
+
 pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -141,3 +143,48 @@ def test_two_gpu_sharded_fold_equals_single_rank_blob(gpu, oracle, tmp_path):
         assert np.array_equal(blob[off:off + size], ref_blob[roff:roff + rsize]), f"constant {i}"
     want = combine_digests([oracle.digest64(ref_blob[o:o + s]) for _, o, s, _ in ref_table], ref_table)
     assert open(tmp_path / "digest.txt").read() == want
+
+
+def test_copy_ordered_behind_a_compression_ticket(gpu, oracle):
+    """The two-step in-place compression with a transfer ordered behind its ticket alone: the copy sees the
+    finished streams although more work was queued on the context's stream after the compression."""
+    import ctypes as C
+    from npu_plugin_b200.const import raise_for
+    rng = np.random.default_rng(21)
+    sizes = [300_000, 64 * 1024, 5000]
+    slots = [np.clip(np.rint(rng.laplace(0, 4, n)), -127, 127).astype(np.int8).view(np.uint8) for n in sizes]
+    slots[2] = rng.integers(0, 256, sizes[2], dtype=np.uint8)  # does not shrink: stays as it is
+    offs = [0, 512 * 600, 512 * 800]
+    total = 512 * 900
+    buf, mirror, flags, noise = gpu.dev_alloc(total), gpu.dev_alloc(total), gpu.dev_alloc(256), gpu.dev_alloc(1 << 24)
+    try:
+        for o, x in zip(offs, slots):
+            gpu.upload(buf + o, x)
+        gpu.fill_zero(mirror, total)
+        gpu.fill_zero(flags, 256)
+        ptrs = (C.c_void_p * 3)(*[buf + o for o in offs])
+        lens = (C.c_size_t * 3)(*sizes)
+        ticket = C.c_int()
+        raise_for(gpu.lib.b200c_btc_compress_inplace_begin(gpu.ctx, 3, ptrs, lens, C.byref(ticket)), gpu.lib.b200c_last_error())
+        # more work behind the compression on the same stream: the transfer must not wait for it to be correct
+        gpu.fill_zero(noise, 1 << 24)
+        out_sizes, comp = (C.c_size_t * 3)(), (C.c_int32 * 3)()
+        raise_for(gpu.lib.b200c_btc_compress_inplace_end(gpu.ctx, ticket.value, out_sizes, comp), gpu.lib.b200c_last_error())
+        assert list(comp) == [1, 1, 0] and out_sizes[2] == sizes[2]
+        segs = [(buf + o, mirror + o, int(n)) for o, n in zip(offs, out_sizes)]
+        gpu.copy_segments_async(segs, done_flag=flags, done_value=3, mode=2, ctas=8, after_ticket=ticket.value)
+        gpu.wait_flags(flags, 1, 3, timeout_ms=2000)
+        assert gpu.exchange_status() == 0
+        got = gpu.download(mirror, total)
+        for o, n, x, c in zip(offs, out_sizes, slots, comp):
+            live = got[o:o + n]
+            if c:
+                stream, not_smaller = oracle.btc_compress(x)
+                assert not not_smaller and np.array_equal(live, stream)
+            else:
+                assert np.array_equal(live, x)
+        # a ticket is spent once collected; an unknown ticket is an argument error
+        assert gpu.lib.b200c_btc_compress_inplace_end(gpu.ctx, ticket.value, out_sizes, comp) == A.ERR_INVALID
+    finally:
+        for p in (buf, mirror, flags, noise):
+            gpu.dev_free(p)
