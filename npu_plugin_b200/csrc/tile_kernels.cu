@@ -321,7 +321,7 @@ __global__ void __launch_bounds__(kTileThreads) foldTileKernel(const __grid_cons
     }
 }
 
-__global__ void __launch_bounds__(kTileThreads) foldTileBatchKernel(const TileRef* __restrict__ refs,
+__global__ void __launch_bounds__(kTileThreads, 5) foldTileBatchKernel(const TileRef* __restrict__ refs,
                                                                     const long long* __restrict__ tileStart, int nitems) {
     __shared__ __align__(16) unsigned char smem[kTileSmemBytes];
     __shared__ TileItem it;
