@@ -449,6 +449,9 @@ def main():
                     help="share of the constants rank 0 keeps when several ranks push into its blob (default: balances its "
                          "compute against its NVLink ingress)")
     ap.add_argument("--chunks", type=int, default=4, help="chunks a pushing rank cuts its share into")
+    ap.add_argument("--rank0-chunks", type=int, default=None,
+                    help="chunks rank 0 cuts its share into (default: per workload; more than one lets the device "
+                         "compress a chunk while the host plans the next)")
     ap.add_argument("--push-mode", type=int, default=2, choices=[0, 1, 2], help="0: copy kernel, 1: copy engine, 2: bulk-copy kernel")
     ap.add_argument("--push-ctas", type=int, default=32)
     ap.add_argument("--exchange-timeout-ms", type=int, default=20000)
@@ -519,7 +522,7 @@ def main():
     # rank 0 cuts its share into chunks only where the compression of one chunk can hide the host's planning of
     # the next (workloads of many small constants); its slots never travel
     run = DeviceRun(torch, dist, backend, stream, decls, rank, world, comm, args, weights=weights,
-                    rank0_chunks=W.PIPELINE_CHUNKS.get(args.workload, 1))
+                    rank0_chunks=args.rank0_chunks or W.PIPELINE_CHUNKS.get(args.workload, 1))
     gc.collect()
     gc.freeze()
     sampler = ClockSampler(local_rank)
