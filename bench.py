@@ -321,7 +321,7 @@ def run_e2e(torch, dist, backend, stream, decls, rank, world, comm, args, algori
     transport = PushTransport(comm, timeout_ms=args.exchange_timeout_ms, mode=args.push_mode, ctas=args.push_ctas) \
         if world > 1 else SingleTransport()
     total_in = sum(d.nbytes for d in decls)
-    chunk_bytes = 1_500_000_000
+    chunk_bytes = args.e2e_chunk_bytes
     nchunks = max(1, min(16, (total_in // world + chunk_bytes - 1) // chunk_bytes))
     sf = ShardedFolder(backend, decls, rank, world, transport, weights=w, nchunks=nchunks, rank0_chunks=nchunks)
     mine = [decls[i] for i in sf.layout.mine[rank]]
@@ -441,6 +441,8 @@ def main():
                          "configuration, batched")
     ap.add_argument("--instances", type=int, default=None, help="independent instances per step for cfg1..cfg4")
     ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--e2e-chunk-bytes", type=int, default=1_500_000_000,
+                    help="input bytes per chunk of the end-to-end leg (uploads, folds and downloads overlap chunk by chunk)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-per-config", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
