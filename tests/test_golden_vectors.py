@@ -456,3 +456,103 @@ def test_expand_dilated(backend):
     want = np.zeros((OC, IC, dK, dK), np.int32)
     want[:, :, ::d, ::d] = vals.reshape(OC, IC, KY, KX)
     assert np.array_equal(c.getValues().reshape(want.shape), want)
+
+
+# UT:119-134 FromEmptyDenseElementsAttr: a tensor with no elements folds to a content with no values
+def test_from_empty_dense(backend):
+    c = attr(backend, [], (0,), A.F32, np.float32).fold()
+    assert c.getType() == NDType((0,), A.F32)
+    assert c.getValues().size == 0 and c.copyTo().size == 0
+
+
+# UT:348-370 ConvertStorageElemType: getValues<int32_t>() of f32 storage converts element by element
+def test_convert_storage_elem_type(backend):
+    vals = iota(24, np.float32)
+    c = attr(backend, vals, (1, 2, 3, 4), A.F32).fold()
+    assert c.getType() == NDType((1, 2, 3, 4), A.F32)
+    assert list(c.getValues(np.int32)) == list(range(24))
+
+
+# UT:608-634 ConvertElemTypeSplat: the single stored element is converted, the content stays a splat of 24 elements
+def test_convert_elem_type_splat(backend):
+    c = attr(backend, [4.0], (1, 2, 3, 4), A.F32, np.float32, splat=True).convertElemType(A.SI32).fold()
+    assert c.getType() == NDType((1, 2, 3, 4), A.SI32)
+    assert list(c.getValues(np.int32)) == [4] * 24
+    assert c.copyTo().view(np.int32).tolist() == [4] * 24
+
+
+# UT:636-662 ConvertElemTypeSubByte: u8 {0,1,2} read as i1 gives {false,true,true}; three 1-bit elements do not fill
+# a byte, so copying them out is refused (Content::copySubByteContent: elements per byte must be a power of two)
+def test_convert_elem_type_sub_byte(backend):
+    a = attr(backend, [0, 1, 2], (3,), A.UI8, np.uint8).convertElemType(A.I1)
+    assert a.getType() == NDType((3,), A.I1)
+    with pytest.raises(ConstError, match="Invalid number of elements per byte"):
+        a.fold().copyTo()
+    # the same conversion on eight elements packs the low bit of each (getValues<int8_t>() & 1), first element in
+    # the most significant bit: 2 contributes 0, 7 contributes 1
+    c = attr(backend, [0, 1, 2, 0, 0, 7, 0, 1], (8,), A.UI8, np.uint8).convertElemType(A.I1).fold()
+    assert list(c.copyTo()) == [0b01000101]
+
+
+# UT:1482-1530 GetSparsityMapQuantized: the zero point (7) is the sparse value
+def test_get_sparsity_map_quantized(backend):
+    vals = [7, 0, 1, 2, 3, 4, 5, 6, 7, 8, 7, 10, 7, 12, 13, 14]
+    q = UniformQuantizedType(A.UI8, A.F32, 1.0, 7, 0, 14)
+    c = attr(backend, vals, (1, 1, 2, 8), A.UI8, np.uint8).quantCast(q).getSparsityMap().fold()
+    assert c.getType() == NDType((1, 1, 1, 128), A.I1)
+    out = c.copyTo()
+    assert out.size == 16 and list(out[:2]) == [0xFE, 0xEA] and not out[2:].any()
+
+
+# UT:1639-1667 ChangeShapeAndElemType: shape and (quantised) element type change, the values stay
+def test_change_shape_and_elem_type(backend):
+    vals = iota(16, np.uint8)
+    q = UniformQuantizedType(A.UI8, A.F32, 0.078431372549019607, 128, 0, 255)
+    a = attr(backend, vals, (2, 1, 1, 8), A.UI8).changeShapeAndElemType((1, 2, 1, 8), q)
+    assert a.getType() == NDType((1, 2, 1, 8), q)
+    c = a.fold()
+    assert c.getType() != NDType((2, 1, 1, 8), A.UI8)
+    assert list(c.getValues(np.uint8)) == list(range(16))
+
+
+# UT:1669-1711 ChangeShapeAndElemTypePerAxisQuant: the quantised axis moves with the reshape
+def test_change_shape_and_elem_type_per_axis(backend):
+    vals = iota(16, np.uint8)
+    q1 = UniformQuantizedPerAxisType(A.UI8, A.F16, [0.5, 0.5], [127, 127], 0, 0, 255)
+    q2 = UniformQuantizedPerAxisType(A.UI8, A.F16, [0.5, 0.5], [127, 127], 1, 0, 255)
+    a1 = attr(backend, vals, (2, 1, 1, 8), A.UI8).quantCast(q1)
+    a2 = a1.changeShapeAndElemType((1, 2, 1, 8), q2)
+    assert a1.getType() != a2.getType()
+    c1, c2 = a1.fold(), a2.fold()
+    assert c1.getType() == NDType((2, 1, 1, 8), q1) and c2.getType() == NDType((1, 2, 1, 8), q2)
+    assert list(c1.getValues(np.uint8)) == list(range(16)) and list(c2.getValues(np.uint8)) == list(range(16))
+
+
+# UT:1713-1737 ChangeShapeAndElemTypeFloat: f32 storage under an si32 type is converted when the values are read
+def test_change_shape_and_elem_type_float(backend):
+    vals = iota(16, np.float32)
+    a = attr(backend, vals, (2, 1, 1, 8), A.F32).changeShapeAndElemType((1, 2, 1, 8), A.SI32)
+    assert a.getType() == NDType((1, 2, 1, 8), A.SI32)
+    c = a.fold()
+    assert list(c.getValues(np.int32)) == list(range(16))
+    assert c.copyTo().view(np.int32).tolist() == list(range(16))
+
+
+# UT:1739-1765 GetTransformationsRange and :1767-1796 ...DuplicatedTransformations: the list is cut at the last
+# occurrence of a transformation (equal transformations are one uniqued object in the reference)
+def test_get_transformations_range(backend):
+    a = attr(backend, iota(10, np.float32), (10,), A.F32).add(1.0).reshape((2, 5)).subview((0, 0), (1, 5))
+    ts = a.getTransformations()
+    assert [t.getTransformationName() for t in ts] == ["Add", "Reshape", "SubView"]
+    head = a.stripTransformationsFrom(ts[1])
+    assert [t.getTransformationName() for t in head.getTransformations()] == ["Add"]
+    assert [t.getTransformationName() for t in a.getLastTransformationsFrom(ts[1])] == ["Reshape", "SubView"]
+    # the stripped attribute folds to the head's result, the full one to the first row of it
+    assert np.array_equal(head.fold().getValues(), iota(10, np.float32) + 1)
+    assert np.array_equal(a.fold().getValues(), (iota(10, np.float32) + 1)[:5])
+    d = attr(backend, iota(10, np.float32), (10,), A.F32).add(1.0).reshape((2, 5)).reshape((2, 5)).subview((0, 0), (1, 5))
+    ts = d.getTransformations()
+    assert len(ts) == 4 and ts[1] == ts[2]
+    for which in (ts[1], ts[2]):  # either Reshape reaches the same result
+        assert [t.getTransformationName() for t in d.stripTransformationsFrom(which).getTransformations()] == ["Add", "Reshape"]
+        assert [t.getTransformationName() for t in d.getLastTransformationsFrom(which)] == ["Reshape", "SubView"]
