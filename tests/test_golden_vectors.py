@@ -556,3 +556,20 @@ def test_get_transformations_range(backend):
     for which in (ts[1], ts[2]):  # either Reshape reaches the same result
         assert [t.getTransformationName() for t in d.stripTransformationsFrom(which).getTransformations()] == ["Add", "Reshape"]
         assert [t.getTransformationName() for t in d.getLastTransformationsFrom(which)] == ["Reshape", "SubView"]
+
+
+# LIT constant_folding.mlir:56-107 I1SubviewConstFold{Splat,NotSplat,NonSplat}: SubView on 1-bit content (bit k of a
+# byte is element k) -- a splat stays a splat, a dense one is cut bit by bit
+def test_lit_i1_subview(backend):
+    splat = ContentAttr.get(np.array([1], np.uint8), NDType((1, 32, 3, 3), A.I1), is_splat=True, backend=backend)
+    c = splat.subview((0, 16, 0, 0), (1, 16, 3, 3)).fold()
+    assert c.getType() == NDType((1, 16, 3, 3), A.I1)
+    assert list(c.copyTo()) == [0xFF] * 18  # dense<true> : tensor<1x16x3x3xi1>, 144 bits
+    row = np.packbits(np.array([1, 0, 1, 0], np.uint8), bitorder="little")
+    c = ContentAttr.get(row, NDType((1, 4), A.I1), is_splat=False, backend=backend).subview((0, 2), (1, 2)).fold()
+    assert list(np.unpackbits(c.copyTo(), bitorder="little")[:2]) == [1, 0]  # dense<[[true, false]]>
+    bits = np.array([0] * 8 + [1] * 8 + [0, 1] * 4 + [1, 0] * 4, np.uint8)
+    dense = ContentAttr.get(np.packbits(bits, bitorder="little"), NDType((1, 32, 1, 1), A.I1), is_splat=False, backend=backend)
+    c = dense.subview((0, 16, 0, 0), (1, 16, 1, 1)).fold()
+    assert c.getType() == NDType((1, 16, 1, 1), A.I1)
+    assert list(np.unpackbits(c.copyTo(), bitorder="little")) == [0, 1] * 4 + [1, 0] * 4
