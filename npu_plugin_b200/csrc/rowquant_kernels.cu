@@ -43,9 +43,13 @@ __device__ __forceinline__ Stats warpReduce(Stats s) {
     return s;
 }
 
+// the symmetric scheme takes its scale from max|w| alone: the signed extremes are not tracked for it
+template <int SCHEME>
 __device__ __forceinline__ void accum(Stats& s, float w) {
-    s.mx = fmaxf(s.mx, w);
-    s.mn = fminf(s.mn, w);
+    if (SCHEME != B200C_QSYNTH_SYM_I8) {
+        s.mx = fmaxf(s.mx, w);
+        s.mn = fminf(s.mn, w);
+    }
     const float aw = fabsf(w);
     s.amax = fmaxf(s.amax, aw);
     if (!(w == w) || (aw != 0.0f && aw < 1e-30f)) s.odd = 1.0f;
@@ -359,7 +363,7 @@ __device__ __forceinline__ void rowQuantRegBody(const RowQuantParams& p, long lo
             if (live && u < units) {
                 const float* f = reinterpret_cast<const float*>(&x[i][0]);
 #pragma unroll
-                for (int k = 0; k < 16; ++k) accum(s, f[k]);
+                for (int k = 0; k < 16; ++k) accum<SCHEME>(s, f[k]);
             }
         }
     }
@@ -452,14 +456,14 @@ __device__ __forceinline__ void rowQuantSmemBody(const RowQuantParams& p, long l
                     sm4[v + ((v * PER) >> p.padLog2)] = xv[r];  // padLog2 is 31 when the row is not padded
                     const T* e = reinterpret_cast<const T*>(&xv[r]);
 #pragma unroll
-                    for (int i = 0; i < PER; ++i) accum(s, elemToFloat<T>(e[i]));
+                    for (int i = 0; i < PER; ++i) accum<SCHEME>(s, elemToFloat<T>(e[i]));
                 }
             }
         } else {
             for (int j = t; j < L; j += TPR) {
                 const T xv = src[j];
                 rowSm[j] = xv;
-                accum(s, elemToFloat<T>(xv));
+                accum<SCHEME>(s, elemToFloat<T>(xv));
             }
         }
     }
