@@ -367,6 +367,31 @@ public:
     int getTransformationKind(size_t i) const {
         return _steps[i].x.kind;
     }
+    // Two transformations with equal parameters are one uniqued attribute object in the reference, so the two
+    // methods below cut the list at the LAST transformation equal to transformation i of this attribute
+    // (ContentAttr::stripTransformationsFrom / getLastTransformationsFrom, attributes.td:72-107).
+    bool sameTransformation(size_t i, size_t j) const {
+        const Step &a = _steps[i], &b = _steps[j];
+        const b200c_xform &x = a.x, &y = b.x;
+        if (x.kind != y.kind || x.n != y.n || x.f != y.f || x.i0 != y.i0 || x.i1 != y.i1) return false;
+        for (int k = 0; k < x.n; ++k)
+            if (x.a[k] != y.a[k] || x.b[k] != y.b[k]) return false;
+        const QuantParams &p = a.type.quant, &q = b.type.quant;
+        return a.type.dtype == b.type.dtype && p.kind == q.kind && p.axis == q.axis && p.expressed == q.expressed &&
+               p.qmin == q.qmin && p.qmax == q.qmax && p.scales == q.scales && p.zps == q.zps && a.aux == b.aux;
+    }
+    // the attribute without transformation i's last equal and everything behind it
+    ContentAttr stripTransformationsFrom(size_t i) const {
+        ContentAttr r = *this;
+        r._steps.erase(r._steps.begin() + static_cast<std::ptrdiff_t>(lastEqual(i)), r._steps.end());
+        return r;
+    }
+    // kinds of the transformations from transformation i's last equal on
+    std::vector<int> getLastTransformationsFrom(size_t i) const {
+        std::vector<int> kinds;
+        for (size_t k = lastEqual(i); k < _steps.size(); ++k) kinds.push_back(_steps[k].x.kind);
+        return kinds;
+    }
 
     // ContentAttr::getType(): inferFinalType over the list (pure host code in the library)
     NDType getType() const {
@@ -448,6 +473,13 @@ private:
             n += grow;
         }
         return static_cast<size_t>(std::min<int64_t>(n, int64_t(1) << 24) + 64);
+    }
+    size_t lastEqual(size_t i) const {
+        if (i >= _steps.size()) throw Error(B200C_ERR_INVALID, "transformation index out of range");
+        size_t last = i;
+        for (size_t k = i + 1; k < _steps.size(); ++k)
+            if (sameTransformation(i, k)) last = k;
+        return last;
     }
     // ContentAttr::addTransformation: insert at getInsertionPosition, then re-check the final type
     ContentAttr add(Step s) const {

@@ -64,6 +64,24 @@ int main() {
         EXPECT(!throws(NDType({1, 100, 1, 1}, B200C_UI8), sw, true), "DeclareOp: swizzled result type skips the shape check");
         EXPECT(DeclareOp(NDType({1, 100, 1, 1}, B200C_UI8), sw, true).getBinarySize() == 512, "getBinarySize of a swizzled constant");
     }
+    // ---- stripTransformationsFrom / getLastTransformationsFrom (content_tests.cpp:1739-1796), host only ----
+    {
+        std::vector<float> vals(10);
+        std::iota(vals.begin(), vals.end(), 0.0f);
+        auto a = ContentAttr::get(vals, NDType({10}, B200C_F32)).add(1.0).reshape({2, 5}).subview({0, 0}, {1, 5});
+        EXPECT(a.getNumTransformations() == 3, "Add, Reshape, SubView");
+        auto head = a.stripTransformationsFrom(1);
+        EXPECT(head.getNumTransformations() == 1 && head.getTransformationKind(0) == B200C_X_ADD, "head of the list is Add");
+        EXPECT((a.getLastTransformationsFrom(1) == std::vector<int>{B200C_X_RESHAPE, B200C_X_SUBVIEW}), "tail is Reshape, SubView");
+        // two equal Reshapes are one object in the reference: either of them cuts at the second
+        auto d = ContentAttr::get(vals, NDType({10}, B200C_F32)).add(1.0).reshape({2, 5}).reshape({2, 5}).subview({0, 0}, {1, 5});
+        EXPECT(d.getNumTransformations() == 4 && d.sameTransformation(1, 2), "duplicated Reshape");
+        for (size_t which : {size_t(1), size_t(2)}) {
+            auto h = d.stripTransformationsFrom(which);
+            EXPECT(h.getNumTransformations() == 2 && h.getTransformationKind(1) == B200C_X_RESHAPE, "head is Add, Reshape");
+            EXPECT((d.getLastTransformationsFrom(which) == std::vector<int>{B200C_X_RESHAPE, B200C_X_SUBVIEW}), "tail is Reshape, SubView");
+        }
+    }
     if (std::getenv("B200C_MIRROR_HOST_ONLY")) {
         std::printf("%s (host-only part)\n", failures ? "FAILED" : "OK");
         return failures ? 1 : 0;
