@@ -167,9 +167,12 @@ class ShardedFolder:
                    max_batch_bytes=max_batch_bytes)
             if hooks:
                 hooks("fold1", k)
-            if hasattr(f, "compress_inplace_begin"):
+            if hasattr(f, "compress_inplace_begin") and r == 0:
                 # The compression of chunk k is only queued here; the host goes on to plan the fold of chunk
-                # k + 1 while the device compresses, and reads the sizes of chunk k after that.
+                # k + 1 while the device compresses, and reads the sizes of chunk k after that.  Only the
+                # assembling rank works this way: a pushing rank sends chunk k the moment it is complete, and
+                # measured on four GPUs its pushes arrived later when the next chunk's kernels were already
+                # queued behind them (4.8 ms per step instead of 3.9).
                 ticket = f.compress_inplace_begin(base)
                 if hooks:
                     hooks("codec1", k)  # on the stream: right behind the chunk's compression
