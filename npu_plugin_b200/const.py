@@ -289,6 +289,42 @@ def max_q_of(base_type, transforms):
     return min(m, 1 << 24) + 64
 
 
+def quick_q_of(base_type, transforms):
+    """First guess for the parameter storage of a chain's output type: the longest parameter list that goes in,
+    or the largest extent named anywhere (a per-axis list is as long as one dimension)."""
+    m = max([1] + list(base_type.shape))
+    if base_type.quant is not None:
+        m = max(m, len(base_type.quant.scales))
+    for t in transforms:
+        for v in list(t.a) + list(t.b) + [t.i1]:
+            m = max(m, abs(int(v)))
+        if isinstance(t.elem, Quant):
+            m = max(m, len(t.elem.scales))
+    return min(m, 1 << 24) + 64
+
+
+def infer_type_through(entry, last_error, base_type, transforms):
+    """b200c_infer_type behind `entry`, with parameter storage sized by quick_q_of and, when the library answers
+    that the output type needs more (it reports how many in the type's nq), once more with that."""
+    n = quick_q_of(base_type, transforms)
+    for attempt in (0, 1):
+        keep = []
+        out = out_type_slot(n, keep)
+        bt = base_type.to_c(keep)
+        ch = chain_to_c(transforms, keep)
+        rc = entry(C.byref(bt), ch, len(transforms), C.byref(out))
+        if rc == A.ERR_CAPACITY and attempt == 0 and out.nq > n:
+            n = int(out.nq)
+            continue
+        raise_for(rc, last_error())
+        return NDType.from_c(out)
+
+
+def q_slots_of(ndtype):
+    """Parameter storage an output type slot needs when the type is already known."""
+    return max(1, len(ndtype.quant.scales)) if ndtype.quant is not None else 1
+
+
 # --------------------------------------------------------------------------- Content
 class Content:
     """Result of ContentAttr.fold(): the folded type plus the bytes Content::copyTo writes."""
@@ -372,12 +408,7 @@ class CudaBackend:
 
     # host-only entry points
     def infer_type(self, base_type, transforms):
-        keep = []
-        out = out_type_slot(max_q_of(base_type, transforms), keep)
-        bt = base_type.to_c(keep)
-        ch = chain_to_c(transforms, keep)
-        raise_for(self.lib.b200c_infer_type(C.byref(bt), ch, len(transforms), C.byref(out)), self._err())
-        return NDType.from_c(out)
+        return infer_type_through(self.lib.b200c_infer_type, self._err, base_type, transforms)
 
     def insert_position(self, kinds, new_kind):
         arr = (C.c_int32 * max(1, len(kinds)))(*kinds)
@@ -395,7 +426,7 @@ class CudaBackend:
         # (never: it is smaller); the inferred size is therefore a safe capacity.
         cap = max(final.getTotalAllocSize(), 1)
         out = np.zeros(cap, dtype=np.uint8)
-        ot = out_type_slot(max_q_of(base_type, transforms), keep)
+        ot = out_type_slot(max(q_slots_of(final), quick_q_of(base_type, transforms)), keep)
         nb = C.c_size_t()
         buf = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
         rc = self.lib.b200c_fold(self.ctx, C.byref(bt), buf.ctypes.data, buf.size, int(is_splat), 0, ch,
@@ -413,7 +444,7 @@ class CudaBackend:
         final = self.infer_type(base_type, transforms)
         cap = max(final.getTotalAllocSize(), 1)
         out = self.dev_alloc(cap)
-        ot = out_type_slot(max_q_of(base_type, transforms), keep)
+        ot = out_type_slot(max(q_slots_of(final), quick_q_of(base_type, transforms)), keep)
         nb = C.c_size_t()
         try:
             self.fill_zero(out, cap)

@@ -21,13 +21,7 @@ class HostOnly:
         self.lib = A.load()
 
     def infer_type(self, base_type, transforms):
-        import ctypes as C
-        keep = []
-        out = K.out_type_slot(K.max_q_of(base_type, transforms), keep)
-        bt = base_type.to_c(keep)
-        ch = K.chain_to_c(transforms, keep)
-        K.raise_for(self.lib.b200c_infer_type(C.byref(bt), ch, len(transforms), C.byref(out)), self.lib.b200c_last_error())
-        return NDType.from_c(out)
+        return K.infer_type_through(self.lib.b200c_infer_type, self.lib.b200c_last_error, base_type, transforms)
 
     def insert_position(self, kinds, new_kind):
         import ctypes as C
@@ -126,3 +120,22 @@ def test_errors_of_type_inference(oracle):
             backend.infer_type(base, [Transform(A.X_GET_SPARSITY_MAP)])
         with pytest.raises(K.ConstError):
             backend.infer_type(base, [Transform(A.X_QUANT_CAST, elem=UniformQuantizedType(A.UI8, A.F32, 1.0, 0))])
+
+
+def test_type_inference_asks_again_when_the_parameter_storage_is_short(oracle, monkeypatch):
+    """The library reports how many quantisation parameters the output type holds; the host layer's second call
+    brings exactly that storage, so a low first guess costs one more call and changes nothing in the result."""
+    host = HostOnly()
+    oc = 300
+    q = UniformQuantizedPerAxisType(A.SI8, A.F16, [0.5 + 0.001 * k for k in range(oc)], [3] * oc, 0, -128, 127)
+    base = NDType((oc, 16, 1, 1), A.SI8)
+    chain = [Transform(A.X_QUANT_CAST, elem=q), Transform(A.X_PAD_WITH_ZERO, a=(0, 0, 0, 0), b=(7, 0, 0, 0)),
+             Transform(A.X_REORDER, a=DimsOrder.NHWC)]
+    want = oracle.infer_type(base, chain)
+    assert len(want.quant.scales) == oc + 7
+    assert host.infer_type(base, chain) == want
+    calls = []
+    monkeypatch.setattr(K, "quick_q_of", lambda b, t: calls.append(1) or 1)
+    assert host.infer_type(base, chain) == want and calls
+    # an unquantised result needs no storage at all
+    assert host.infer_type(base, chain + [Transform(A.X_DEQUANTIZE)]) == oracle.infer_type(base, chain + [Transform(A.X_DEQUANTIZE)])
