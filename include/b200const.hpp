@@ -226,8 +226,27 @@ private:
 // getInsertionPosition gives it (content.cpp:268-299).
 class ContentAttr {
 public:
-    // ContentAttr::get(baseContent): `data` is copied
+    // ContentAttr::get(baseContent): `data` is copied.  The checks of ContentAttr::verify (content.cpp:61-99) run here:
+    // the buffer holds every element of the type, or exactly one (a splat -- taken as one even when isSplat was
+    // left false, the rule mlir::DenseElementsAttr::isValidRawBuffer applies to a dense resource; a single byte of
+    // one-bit elements only as 0x00 or 0xFF).  Sub-byte elements are held packed.
     static ContentAttr get(const void* data, size_t nbytes, NDType baseType, bool isSplat = false) {
+        if (data == nullptr) throw Error(B200C_ERR_THROW, "Got NULL 'baseContent' in 'ContentAttr'");
+        if (baseType.quant.kind != B200C_Q_NONE) {
+            throw Error(B200C_ERR_THROW, "Got unsupported element type for 'baseContent' in 'ContentAttr'");
+        }
+        const size_t bits = static_cast<size_t>(B200C_DTYPE_BITS(baseType.dtype));
+        const size_t count = static_cast<size_t>(baseType.getNumElements());
+        const size_t one = (bits + 7) / 8, all = (bits * count + 7) / 8;
+        bool valid = isSplat ? nbytes == one : nbytes == all;
+        if (!isSplat && !valid && nbytes == one && count != 1) {
+            const uint8_t byte = *static_cast<const uint8_t*>(data);
+            valid = isSplat = bits != 1 || byte == 0x00 || byte == 0xFF;
+        }
+        if (!valid) {
+            throw Error(B200C_ERR_THROW, "Size of dense resource buffer '" + std::to_string(nbytes) +
+                                                 "' in 'baseContent' doesn't match its type");
+        }
         ContentAttr a;
         a._base = std::move(baseType);
         a._data = std::make_shared<std::vector<uint8_t>>(static_cast<const uint8_t*>(data),

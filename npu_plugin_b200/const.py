@@ -620,6 +620,24 @@ def default_backend():
 
 
 # --------------------------------------------------------------------------- ContentAttr
+def valid_raw_buffer(base_type, raw):
+    """The buffer rule ContentAttr::verify applies to a dense resource (content.cpp:76-86, through
+    mlir::DenseElementsAttr::isValidRawBuffer): the bytes hold every element of the type, or exactly one element
+    (a splat).  One-bit elements are packed eight to a byte, and a single byte is a splat only when it is 0x00 or
+    0xFF.  Sub-byte elements wider than one bit are held packed here (the layout Content keeps them in), where
+    MLIR's attribute storage spends a byte on each.  Returns (valid, detected splat)."""
+    bits, n = base_type.getElemTypeSize(), base_type.getNumElements()
+    nbytes = int(raw.size) * raw.itemsize
+    splat = n == 1
+    if bits == 1:
+        if nbytes == 1 and int(raw.reshape(-1).view(np.uint8)[0]) in (0x00, 0xFF):
+            return True, True
+        return nbytes == (n + 7) // 8, splat
+    if nbytes == (bits + 7) // 8:
+        return True, True
+    return nbytes == (bits * n + 7) // 8, splat
+
+
 class ContentAttr:
     """Const::ContentAttr: base content + ordered transformation list + inferred final type."""
 
@@ -632,6 +650,8 @@ class ContentAttr:
     def get(base, base_type=None, is_splat=None, backend=None):
         """base: numpy array holding the dense (or single splat) element(s); base_type: NDType
         (defaults to the array's shape and dtype)."""
+        if base is None:
+            raise ConstError("Got NULL 'baseContent' in 'ContentAttr'")
         arr = np.ascontiguousarray(base)
         if base_type is None:
             m = {np.dtype(np.float32): A.F32, np.dtype(np.float16): A.F16, np.dtype(np.float64): A.F64,
@@ -639,8 +659,18 @@ class ContentAttr:
                  np.dtype(np.uint16): A.UI16, np.dtype(np.int32): A.SI32, np.dtype(np.uint32): A.UI32,
                  np.dtype(np.int64): A.SI64, np.dtype(np.uint64): A.UI64}
             base_type = NDType(arr.shape, m[arr.dtype])
+        if base_type.quant is not None:  # every plain element type here is an integer or a float
+            raise ConstError(f"Got unsupported element type for 'baseContent' in 'ContentAttr' : '{base_type.getElementType()}'")
+        valid, detected = valid_raw_buffer(base_type, arr)
+        nbytes, bits = arr.size * arr.itemsize, base_type.getElemTypeSize()
         if is_splat is None:
-            is_splat = (arr.size == 1 and base_type.getNumElements() != 1)
+            is_splat = detected and base_type.getNumElements() != 1
+        elif is_splat:  # the caller says one element: any value of it is taken
+            valid = nbytes == (bits + 7) // 8
+        else:
+            valid = nbytes == base_type.getTotalAllocSize()
+        if not valid:
+            raise ConstError(f"Size of dense resource buffer '{nbytes}' in 'baseContent' doesn't match its type '{base_type}'")
         return ContentAttr(arr, base_type, bool(is_splat), [], backend or default_backend())
 
     # -- accessors

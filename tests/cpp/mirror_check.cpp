@@ -64,6 +64,33 @@ int main() {
         EXPECT(!throws(NDType({1, 100, 1, 1}, B200C_UI8), sw, true), "DeclareOp: swizzled result type skips the shape check");
         EXPECT(DeclareOp(NDType({1, 100, 1, 1}, B200C_UI8), sw, true).getBinarySize() == 512, "getBinarySize of a swizzled constant");
     }
+    // ---- ContentAttr::verify on a dense resource (content.cpp:61-99; lit content.mlir:70-136), host only ----
+    {
+        auto refused = [&](const std::vector<uint32_t>& words, const NDType& t, const char* size) {
+            try {
+                ContentAttr::get(words, t);
+            } catch (const Error& e) {
+                return e.code() == B200C_ERR_THROW &&
+                       std::string(e.what()).find(std::string("Size of dense resource buffer '") + size + "'") != std::string::npos;
+            }
+            return false;
+        };
+        const NDType t({1, 3, 1, 1}, B200C_F32);
+        EXPECT(!ContentAttr::get(std::vector<uint32_t>{1, 2, 3}, t).isSplat(), "verify: a full dense resource");
+        EXPECT(refused({2, 3}, t, "8"), "verify: 8 bytes for three f32");
+        EXPECT(refused({1, 2, 3, 4}, t, "16"), "verify: 16 bytes for three f32");
+        EXPECT(ContentAttr::get(std::vector<uint32_t>{1}, NDType({2, 3, 1, 1}, B200C_F32)).isSplat(), "verify: one element is a splat");
+        EXPECT(!ContentAttr::get(std::vector<uint32_t>{1}, NDType({1}, B200C_F32)).isSplat(), "verify: a one-element type is no splat");
+        const NDType bits({4, 8}, B200C_I1);
+        EXPECT(ContentAttr::get(std::vector<uint8_t>{0xFF}, bits).isSplat(), "verify: 0xFF is a one-bit splat");
+        bool threw = false;
+        try {
+            ContentAttr::get(std::vector<uint8_t>{0x0F}, bits);
+        } catch (const Error&) {
+            threw = true;
+        }
+        EXPECT(threw, "verify: a lone byte of mixed bits is refused");
+    }
     // ---- stripTransformationsFrom / getLastTransformationsFrom (content_tests.cpp:1739-1796), host only ----
     {
         std::vector<float> vals(10);

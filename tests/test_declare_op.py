@@ -69,3 +69,37 @@ def test_declare_op_verifier_and_serialize(backend):
     assert op.serialize(section) == 512 and len(section) == 515
     assert section[3:3 + 16] == bytes(range(16))
     assert op.fold() is sw and op.getContentAttr() is sw
+
+
+# ContentAttr::verify (content.cpp:61-99) on the cases of tests/lit/NPU/dialect/const/passes/content.mlir:70-136: a dense
+# resource is accepted when it holds every element or exactly one (a splat), refused with the reference's text otherwise
+def test_content_attr_verifies_its_base_buffer(oracle):
+    from npu_plugin_b200.const import ConstError, UniformQuantizedType
+    t = NDType((1, 3, 1, 1), A.F32)
+    ok = ContentAttr.get(np.array([1, 2, 3], np.uint32).view(np.float32), t, backend=oracle)   # ParsePrintDenseResource
+    assert ok.getType() == t and not ok._isSplat
+    with pytest.raises(ConstError, match="Size of dense resource buffer '8' in 'baseContent' doesn't match its type"):
+        ContentAttr.get(np.array([2, 3], np.uint32), t, backend=oracle)                            # ...NoAlignment
+    with pytest.raises(ConstError, match="Size of dense resource buffer '16' in 'baseContent' doesn't match its type"):
+        ContentAttr.get(np.array([1, 2, 3, 4], np.uint32), t, backend=oracle)                      # ...WrongDataSize
+    splat = ContentAttr.get(np.array([1], np.uint32).view(np.float32), NDType((2, 3, 1, 1), A.F32), backend=oracle)
+    assert splat._isSplat                                                                          # ...Splat
+    raw = splat.fold().copyTo()
+    assert np.array_equal(raw.view(np.uint32), np.full(6, 1, np.uint32))
+    # one-bit elements: packed eight to a byte; a single byte is a splat only as 0x00 or 0xFF
+    bits = NDType((4, 8), A.I1)
+    assert not ContentAttr.get(np.array([1, 2, 3, 4], np.uint8), bits, backend=oracle)._isSplat
+    assert ContentAttr.get(np.array([0xFF], np.uint8), bits, backend=oracle)._isSplat
+    with pytest.raises(ConstError, match="Size of dense resource buffer '1'"):
+        ContentAttr.get(np.array([0x0F], np.uint8), bits, backend=oracle)
+    # a type of one element is never flagged as a splat; a missing or quantised base is refused
+    assert not ContentAttr.get(np.array([5.0], np.float32), backend=oracle)._isSplat
+    with pytest.raises(ConstError, match="Got NULL 'baseContent'"):
+        ContentAttr.get(None, t, backend=oracle)
+    with pytest.raises(ConstError, match="Got unsupported element type"):
+        ContentAttr.get(np.zeros(3, np.uint8), NDType((3,), UniformQuantizedType(A.UI8, A.F32, 1.0, 0)), backend=oracle)
+    # the caller's own splat flag is checked against the size as well
+    with pytest.raises(ConstError, match="Size of dense resource buffer '12'"):
+        ContentAttr.get(np.zeros(3, np.float32), t, is_splat=True, backend=oracle)
+    with pytest.raises(ConstError, match="Size of dense resource buffer '4'"):
+        ContentAttr.get(np.zeros(1, np.float32), t, is_splat=False, backend=oracle)
