@@ -68,6 +68,7 @@ class ShardFolder:
         self._keep = []
         self._prepared = []
         self._marshalled = None
+        self._group_cache = {}
         self.folded_offsets, self.folded_sizes = [], []
         at = 0
         for d in decls:
@@ -127,17 +128,27 @@ class ShardFolder:
                         if ch[k].kind == A.X_QUANTIZE_SYNTH:
                             ch[k].side0, ch[k].side1 = side_ptrs[i]
             self._marshalled = key
-        first = 0
-        while first < n:
-            last, total = first, 0
-            while last < n and (last == first or max_batch_bytes is None or total + self.decls[last].nbytes <= max_batch_bytes):
-                total += self.decls[last].nbytes
-                last += 1
+        for first, last in self._groups(max_batch_bytes):
             at = C.cast(C.addressof(self._items) + first * C.sizeof(A.b200c_fold_item), C.POINTER(A.b200c_fold_item))
             rc = lib.b200c_fold_batch(ctx, at, last - first, int(data_on_device), 1, A.FOLD_ASYNC)
             if rc != A.OK:
                 raise_for(rc, lib.b200c_last_error())
-            first = last
+
+    def _groups(self, max_batch_bytes):
+        """[first, last) ranges of consecutive constants whose input bytes stay within max_batch_bytes (one range
+        for all of them without a limit; a constant above the limit goes alone).  Worked out once per limit: a
+        step must not pay a Python loop over the constants."""
+        if max_batch_bytes not in self._group_cache:
+            n, out, first = len(self.decls), [], 0
+            while first < n:
+                last, total = first, 0
+                while last < n and (last == first or max_batch_bytes is None or total + self.decls[last].nbytes <= max_batch_bytes):
+                    total += self.decls[last].nbytes
+                    last += 1
+                out.append((first, last))
+                first = last
+            self._group_cache[max_batch_bytes] = out
+        return self._group_cache[max_batch_bytes]
 
     def written_sizes(self):
         """Bytes the last fold() wrote per constant.  Equal to folded_sizes except for contents that are shorter
@@ -234,53 +245,3 @@ class ShardFolder:
         else:
             raise_for(self.lib.b200c_synchronize(self.ctx), self.lib.b200c_last_error())
         return size, flag
-
-
-class PeerWindow:
-    """Another rank's blob buffer mapped into this process through CUDA IPC, so that rank 0 can pull
-    slots with plain device-to-device copies (the copy engines move them over NVLink; no kernel runs on
-    either GPU, unlike a send/recv pair whose copy loops compete with the fold kernels for SMs)."""
-
-    @staticmethod
-    def export(tensor):
-        """A picklable description of a 1-D uint8 CUDA tensor's memory (sent to the pulling rank)."""
-        return tuple(tensor.untyped_storage()._share_cuda_()) + (int(tensor.storage_offset()), int(tensor.numel()))
-
-    @staticmethod
-    def open(desc):
-        """The exporting rank's tensor as seen from this process (lives on the exporter's device)."""
-        import torch
-        *share, offset, numel = desc
-        storage = torch.UntypedStorage._new_shared_cuda(*share)
-        whole = torch.empty(0, dtype=torch.uint8, device=storage.device).set_(storage)
-        return whole[offset:offset + numel]
-
-
-def gather_segments(dist, blob, used, rank, world, gathered=None):
-    """The one exchange of the multi-GPU fold: every rank's blob prefix (`used` bytes of the 1-D uint8
-    tensor `blob`) is appended on rank 0 in rank order.  Sizes travel with an all_gather, the bytes with
-    point-to-point send/recv (NCCL over NVLink on GPUs, gloo on CPU).  Returns (per-rank sizes,
-    the assembled tensor on rank 0 or None elsewhere); `gathered` is reused when large enough."""
-    import torch
-    mine = torch.tensor([int(used)], dtype=torch.int64, device=blob.device)
-    sizes = [torch.zeros(1, dtype=torch.int64, device=blob.device) for _ in range(world)]
-    dist.all_gather(sizes, mine)
-    sizes = [int(s.item()) for s in sizes]
-    if rank != 0:
-        if used:
-            dist.send(blob[:used], dst=0)
-        return sizes, None
-    total = sum(sizes)
-    if gathered is None or gathered.numel() < total:
-        gathered = torch.empty(int(total * 1.05) + 1024, dtype=torch.uint8, device=blob.device)
-    at = sizes[0]
-    if at:
-        gathered[:at].copy_(blob[:at])
-    reqs = []
-    for r in range(1, world):
-        if sizes[r]:
-            reqs.append(dist.irecv(gathered[at:at + sizes[r]], src=r))
-        at += sizes[r]
-    for q in reqs:
-        q.wait()
-    return sizes, gathered
