@@ -278,17 +278,6 @@ def chain_to_c(transforms, keep):
     return arr
 
 
-def max_q_of(base_type, transforms):
-    m = base_type.getNumElements() if base_type.rank else 1
-    m = max([m, 1] + list(base_type.shape))
-    for t in transforms:
-        for v in list(t.a) + list(t.b) + [t.i1]:
-            m = max(m, abs(int(v)))
-        if isinstance(t.elem, Quant):
-            m = max(m, len(t.elem.scales))
-    return min(m, 1 << 24) + 64
-
-
 def quick_q_of(base_type, transforms):
     """First guess for the parameter storage of a chain's output type: the longest parameter list that goes in,
     or the largest extent named anywhere (a per-axis list is as long as one dimension)."""

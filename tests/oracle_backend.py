@@ -65,12 +65,18 @@ class OracleBackend:
         return self.lib.orc_set_threads(n)
 
     def infer_type(self, base_type, transforms):
-        keep = []
-        out = K.out_type_slot(K.max_q_of(base_type, transforms), keep)
-        bt = base_type.to_c(keep)
-        ch = K.chain_to_c(transforms, keep)
-        K.raise_for(self.lib.orc_infer_type(C.byref(bt), ch, len(transforms), C.byref(out)), self._err())
-        return K.NDType.from_c(out)
+        n = K.quick_q_of(base_type, transforms)
+        for attempt in (0, 1):
+            keep = []
+            out = K.out_type_slot(n, keep)
+            bt = base_type.to_c(keep)
+            ch = K.chain_to_c(transforms, keep)
+            rc = self.lib.orc_infer_type(C.byref(bt), ch, len(transforms), C.byref(out))
+            if rc != A.OK and attempt == 0 and out.nq > n:  # the type needs more room than the first guess: it says how much
+                n = int(out.nq)
+                continue
+            K.raise_for(rc, self._err())
+            return K.NDType.from_c(out)
 
     def insert_position(self, kinds, new_kind):
         arr = (C.c_int32 * max(1, len(kinds)))(*kinds)
@@ -85,7 +91,7 @@ class OracleBackend:
         final = self.infer_type(base_type, transforms)
         cap = max(final.getTotalAllocSize(), 1)
         out = np.zeros(cap, dtype=np.uint8)
-        ot = K.out_type_slot(K.max_q_of(base_type, transforms), keep)
+        ot = K.out_type_slot(max(K.q_slots_of(final), K.quick_q_of(base_type, transforms)), keep)
         nb = C.c_size_t()
         buf = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
         rc = self.lib.orc_fold(C.byref(bt), buf.ctypes.data, buf.size, int(is_splat), ch, len(transforms),

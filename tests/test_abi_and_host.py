@@ -137,5 +137,6 @@ def test_type_inference_asks_again_when_the_parameter_storage_is_short(oracle, m
     calls = []
     monkeypatch.setattr(K, "quick_q_of", lambda b, t: calls.append(1) or 1)
     assert host.infer_type(base, chain) == want and calls
+    assert oracle.infer_type(base, chain) == want  # the oracle's binding asks again the same way
     # an unquantised result needs no storage at all
     assert host.infer_type(base, chain + [Transform(A.X_DEQUANTIZE)]) == oracle.infer_type(base, chain + [Transform(A.X_DEQUANTIZE)])
