@@ -374,6 +374,20 @@ public:
         return add(std::move(s));
     }
 
+    // Every Sparsify of the list rewritten in place to Sparsify<true, numElems>, so that the attribute's type is the
+    // flat compressed one (compressConstWeightsType,
+    // src/vpux_compiler/src/dialect/VPUIP/passes/flatten_sparse_weights_types.cpp:41-73)
+    ContentAttr withCompressedSparsify(const std::vector<int64_t>& numElems) const {
+        ContentAttr r = *this;
+        for (Step& s : r._steps) {
+            if (s.x.kind == B200C_X_SPARSIFY) {
+                s.x.i0 = 1;
+                s.aux = numElems;
+            }
+        }
+        return r;
+    }
+
     const NDType& getBaseType() const {
         return _base;
     }
@@ -636,6 +650,115 @@ inline std::vector<uint8_t> decompress(const Backend& be, const std::vector<uint
     out.resize(n);
     return out;
 }
+
+// The chain builders: the callers of the ContentAttr API that assemble the transformation lists the hot path folds.
+// Each function restates one call site of the reference compiler on the ContentAttr mirror above.
+namespace chains {
+
+constexpr int64_t VPU_WEIGHT_SET_BYTE_ALIGNMENT = 16;  // nce_invariant.hpp:39
+
+// getAlignedConstWeights (src/vpux_compiler/src/dialect/VPU/utils/const_utils.cpp:101-119): depthwise weights
+// flattened to flatShape and padded along dim 1
+inline ContentAttr alignDepthwiseWeights(const ContentAttr& weights, const std::vector<int64_t>& flatShape, int64_t padding) {
+    return weights.reorder(DimsOrder::NCHW())
+            .reshape(flatShape)
+            .padWithZero({0, 0, 0, 0}, {0, padding, 0, 0})
+            .reorder(DimsOrder::NHWC());
+}
+
+// alignConvWeightsTensor (const_utils.cpp:246-283): [OC, IC, KY, KX] whose IC*KY*KX is not a multiple of the
+// alignment becomes [OC, 1, 1, aligned]; returned unchanged when no padding is needed
+inline ContentAttr alignConvolutionWeights(const ContentAttr& weights, int64_t alignment = VPU_WEIGHT_SET_BYTE_ALIGNMENT,
+                                           bool isCMajorConv = false) {
+    const std::vector<int64_t> shape = weights.getType().shape;
+    if (shape.size() != 4 || alignment <= 0) throw Error(B200C_ERR_INVALID, "alignConvolutionWeights: 4D weights and a positive alignment");
+    const int64_t row = shape[1] * shape[2] * shape[3];
+    const int64_t remainder = row % alignment;
+    if (remainder == 0) return weights;
+    const std::vector<int64_t> flat{shape[0], 1, 1, row};
+    ContentAttr a = isCMajorConv ? weights.reorder(DimsOrder::NCHW()).reshape(flat) : weights.reshape(flat);
+    a = a.padWithZero({0, 0, 0, 0}, {0, 0, 0, alignment - remainder});
+    return isCMajorConv ? a.reorder(DimsOrder::NHWC()) : a;
+}
+
+// ConvertWeightsToU8 ConstRewriter (src/vpux_compiler/src/dialect/IE/passes/convert_weights_to_u8.cpp:85-101):
+// signed quantised weights re-based to unsigned; newQuant is the u8 type with the shifted zero points
+inline ContentAttr weightsToU8(const ContentAttr& weights, const QuantParams& newQuant) {
+    const NDType t = weights.getType();
+    if (t.quant.kind == B200C_Q_NONE) throw Error(B200C_ERR_INVALID, "weightsToU8: the constant is not quantised");
+    return weights.quantCast()
+            .convertElemType(B200C_SI32)
+            .add(static_cast<double>(-t.quant.qmin))
+            .convertElemType(B200C_UI8)
+            .quantCast(newQuant, B200C_UI8);
+}
+
+struct SparseWeights {
+    ContentAttr values;           // ...Sparsify<false>
+    ContentAttr map;              // ...GetSparsityMap
+    std::vector<int64_t> counts;  // countNonSparseElementsPerOC, for the compression scheme
+};
+
+// SparsifyWeightsPass (src/vpux_compiler/src/dialect/VPU/transforms/passes/sparsify_weights.cpp:108-164): the
+// original list is folded first and its bytes become the base of a fresh attribute (later passes do not fold it
+// again); a quantised result keeps its type through quantCast
+inline SparseWeights sparsifyWeights(const Backend& be, const ContentAttr& weights) {
+    const Content content = weights.fold(be);
+    const NDType& folded = content.getType();
+    std::vector<int64_t> counts = weights.countNonSparseElementsPerOC(be);
+    const size_t size = static_cast<size_t>(folded.getTotalAllocSize());
+    std::vector<uint8_t> buf(size, 0);
+    content.copyTo(buf.data(), size);
+    ContentAttr fresh = ContentAttr::get(buf.data(), size, NDType(folded.shape, folded.dtype, folded.order));
+    if (folded.quant.kind != B200C_Q_NONE) fresh = fresh.quantCast(folded.quant, folded.dtype);
+    return SparseWeights{fresh.sparsify(false), fresh.getSparsityMap(), std::move(counts)};
+}
+
+// compressConstWeightsType (flatten_sparse_weights_types.cpp:41-73); an attribute without Sparsify comes back as it is
+inline ContentAttr flattenSparseWeights(const ContentAttr& attr, const std::vector<int64_t>& numElems) {
+    return attr.withCompressedSparsify(numElems);
+}
+
+// createFilter (src/vpux_compiler/src/dialect/VPU/transforms/passes/lower_sparsity_ops.cpp:209-250): ones on the
+// diagonal of an [OC, IC, 1, 1] f32 constant -> (ui8 + quantCast | f16) -> reorder -> Sparsify<false>, with its
+// sparsity map and counts.  quant != nullptr: a quantised ui8 filter; otherwise dtype is B200C_F16 or B200C_F32.
+inline SparseWeights sparseIdentityFilter(const Backend& be, int64_t OC, int64_t IC, int dtype, const QuantParams* quant = nullptr,
+                                          const DimsOrder& order = DimsOrder::OYXI()) {
+    std::vector<float> content(static_cast<size_t>(OC * IC), 0.0f);
+    for (int64_t oc = 0; oc < OC; ++oc) {
+        if (oc * IC + oc < OC * IC) content[static_cast<size_t>(oc * IC + oc)] = 1.0f;
+    }
+    ContentAttr attr = ContentAttr::get(content, NDType({OC, IC, 1, 1}, B200C_F32));
+    if (quant != nullptr) {
+        attr = attr.convertElemType(B200C_UI8).quantCast(*quant, B200C_UI8);
+    } else if (dtype == B200C_F16) {
+        attr = attr.convertElemType(B200C_F16);
+    }
+    if (!(order == DimsOrder::identity(4))) attr = attr.reorder(order);
+    return SparseWeights{attr.sparsify(false), attr.getSparsityMap(), attr.countNonSparseElementsPerOC(be)};
+}
+
+// generateDefaultWeightsAttr (src/vpux_translate_utils/src/hwtest/hwtest_utils.cpp:184-197): reorder(OYXI) ->
+// quantCast(the type, under the constant's own storage) -> bitPack(4) when the type's storage has 4 bits
+inline ContentAttr hwtestDefaultWeights(const ContentAttr& weights, const QuantParams* quant = nullptr, int quantStorage = 0) {
+    ContentAttr a = weights.reorder(DimsOrder::OYXI());
+    if (quant != nullptr) {
+        a = a.quantCast(*quant, a.getType().dtype);
+        if (B200C_DTYPE_BITS(quantStorage) == 4) a = a.bitPack(4);
+    }
+    return a;
+}
+
+// Swizzling::attachSwizzleTransformation (src/vpux_compiler/src/dialect/VPUIP/passes/swizzling.cpp:469-500): a
+// constant shared by several NCE tasks gets the transformation once
+inline ContentAttr attachSwizzle(const ContentAttr& attr, uint64_t swizzleKey = 5, uint64_t arch = 3) {
+    for (size_t i = 0; i < attr.getNumTransformations(); ++i) {
+        if (attr.getTransformationKind(i) == B200C_X_SWIZZLE_CONSTANT) return attr;
+    }
+    return attr.swizzleConstant(swizzleKey, arch);
+}
+
+}  // namespace chains
 
 }  // namespace Const
 }  // namespace b200

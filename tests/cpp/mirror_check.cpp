@@ -109,6 +109,70 @@ int main() {
             EXPECT((d.getLastTransformationsFrom(which) == std::vector<int>{B200C_X_RESHAPE, B200C_X_SUBVIEW}), "tail is Reshape, SubView");
         }
     }
+    // ---- chain builders (const_utils.cpp:101-119,246-283; convert_weights_to_u8.cpp:85-101; hwtest_utils.cpp:184-197;
+    //      swizzling.cpp:469-500; flatten_sparse_weights_types.cpp:41-73): lists and inferred types, host only ----
+    {
+        auto kinds = [](const ContentAttr& a) {
+            std::vector<int> k;
+            for (size_t i = 0; i < a.getNumTransformations(); ++i) k.push_back(a.getTransformationKind(i));
+            return k;
+        };
+        std::vector<int8_t> w(8 * 3 * 3 * 3);
+        for (size_t i = 0; i < w.size(); ++i) w[i] = static_cast<int8_t>(i % 101) - 50;
+        const auto base = ContentAttr::get(w, NDType({8, 3, 3, 3}, B200C_SI8));
+        const auto a = chains::alignConvolutionWeights(base, 16);
+        EXPECT((kinds(a) == std::vector<int>{B200C_X_RESHAPE, B200C_X_PAD_WITH_ZERO}), "aligned weights: Reshape, PadWithZero");
+        EXPECT((a.getType().shape == std::vector<int64_t>{8, 1, 1, 32}), "aligned weights: [8,1,1,32]");
+        const auto c = chains::alignConvolutionWeights(base, 16, true);
+        EXPECT((kinds(c) == std::vector<int>{B200C_X_REORDER, B200C_X_RESHAPE, B200C_X_PAD_WITH_ZERO, B200C_X_REORDER}),
+               "C-major aligned weights: Reorder, Reshape, PadWithZero, Reorder");
+        EXPECT((c.getType().shape == std::vector<int64_t>{8, 1, 1, 32}) && c.getType().order == DimsOrder::NHWC(), "C-major aligned weights: NHWC");
+        std::vector<int8_t> w16(4 * 16);
+        EXPECT(chains::alignConvolutionWeights(ContentAttr::get(w16, NDType({4, 16, 1, 1}, B200C_SI8))).getNumTransformations() == 0,
+               "aligned already: untouched");
+        std::vector<uint16_t> dw(6 * 9);
+        const auto d = chains::alignDepthwiseWeights(ContentAttr::get(dw, NDType({6, 1, 3, 3}, B200C_F16)), {6, 9, 1, 1}, 7);
+        EXPECT((d.getType().shape == std::vector<int64_t>{6, 16, 1, 1}) && d.getType().order == DimsOrder::NHWC(), "depthwise weights: [6,16,1,1] NHWC");
+        // i8 -> u8
+        std::vector<int8_t> q8(4 * 8);
+        const QuantParams qs = QuantParams::perTensor(B200C_F16, 0.02, -3, -128, 127), qu = QuantParams::perTensor(B200C_F16, 0.02, 125, 0, 255);
+        const auto u = chains::weightsToU8(ContentAttr::get(q8, NDType({4, 8, 1, 1}, B200C_SI8)).quantCast(qs, B200C_SI8), qu);
+        EXPECT((kinds(u) == std::vector<int>{B200C_X_QUANT_CAST, B200C_X_QUANT_CAST, B200C_X_CONVERT_ELEM_TYPE, B200C_X_ADD,
+                                             B200C_X_CONVERT_ELEM_TYPE, B200C_X_QUANT_CAST}),
+               "weights to u8: QuantCast, ConvertElemType, Add, ConvertElemType, QuantCast behind the constant's own QuantCast");
+        const NDType ut = u.getType();
+        EXPECT(ut.dtype == B200C_UI8 && ut.quant.kind == B200C_Q_PER_TENSOR && ut.quant.zps == qu.zps && ut.quant.scales == qu.scales,
+               "weights to u8: the new quantised type");
+        bool threw = false;
+        try {
+            chains::weightsToU8(ContentAttr::get(q8, NDType({4, 8, 1, 1}, B200C_SI8)), qu);
+        } catch (const Error&) {
+            threw = true;
+        }
+        EXPECT(threw, "weights to u8 needs a quantised constant");
+        // hardware-test weights
+        std::vector<uint8_t> hw(2 * 4 * 1 * 2);
+        const QuantParams q4 = QuantParams::perTensor(B200C_F16, 0.5, 0, 0, 15);
+        const auto h = chains::hwtestDefaultWeights(ContentAttr::get(hw, NDType({2, 4, 1, 2}, B200C_UI8)), &q4, B200C_UI4);
+        EXPECT((kinds(h) == std::vector<int>{B200C_X_REORDER, B200C_X_QUANT_CAST, B200C_X_BIT_PACK}), "hw-test weights: Reorder, QuantCast, BitPack");
+        EXPECT((kinds(chains::hwtestDefaultWeights(ContentAttr::get(hw, NDType({2, 4, 1, 2}, B200C_UI8)))) == std::vector<int>{B200C_X_REORDER}),
+               "hw-test weights without a quantised type: Reorder");
+        // swizzle once
+        std::vector<uint8_t> sw(1024);
+        const auto s1 = chains::attachSwizzle(ContentAttr::get(sw, NDType({4, 256, 1, 1}, B200C_UI8)));
+        EXPECT((kinds(s1) == std::vector<int>{B200C_X_SWIZZLE_CONSTANT}) && kinds(chains::attachSwizzle(s1)) == kinds(s1), "SwizzleConstant is attached once");
+        // Sparsify<false> -> Sparsify<true, numElems>: the flat compressed type
+        std::vector<int8_t> sp(16 * 32);
+        const auto vals = ContentAttr::get(sp, NDType({16, 32, 1, 1}, B200C_SI8)).sparsify(false);
+        std::vector<int64_t> counts(16);
+        int64_t total = 0;
+        for (int o = 0; o < 16; ++o) {
+            counts[o] = o + 1;
+            total += (counts[o] + 15) / 16 * 16;
+        }
+        EXPECT((chains::flattenSparseWeights(vals, counts).getType().shape == std::vector<int64_t>{total, 1, 1, 1}), "flattened sparse weights: [sum of 16-byte aligned runs,1,1,1]");
+        EXPECT((vals.getType().shape == std::vector<int64_t>{16, 32, 1, 1}), "Sparsify<false> keeps the shape");
+    }
     if (std::getenv("B200C_MIRROR_HOST_ONLY")) {
         std::printf("%s (host-only part)\n", failures ? "FAILED" : "OK");
         return failures ? 1 : 0;
@@ -235,6 +299,61 @@ int main() {
         EXPECT(detectSplat(be, same.data(), same.size() * 4, 4), "all elements equal");
         EXPECT(!detectSplat(be, one_off.data(), one_off.size() * 4, 4), "one element differs");
         EXPECT(!detectSplat(be, same.data(), 0, 4), "empty data is not a splat");
+    }
+    // ---- sparsify-weights and the identity filter of a lowered sparsity op (sparsify_weights.cpp:108-164,
+    //      lower_sparsity_ops.cpp:209-250) ----
+    {
+        std::mt19937 rng(11);
+        std::vector<int8_t> w(16 * 32);
+        for (auto& v : w) v = (rng() % 10 < 4) ? static_cast<int8_t>(static_cast<int>(rng() % 254) - 127) : 0;
+        for (auto& v : w)
+            if (v == 0 && (rng() % 64) == 0) v = 1;  // keep a few small survivors
+        const QuantParams q = QuantParams::perAxis(B200C_F16, std::vector<double>(16, 0.1), std::vector<int64_t>(16, 0), 0, -128, 127);
+        const auto base = ContentAttr::get(w, NDType({16, 32, 1, 1}, B200C_SI8)).quantCast(q, B200C_SI8).reorder(DimsOrder::OYXI());
+        const chains::SparseWeights sw = chains::sparsifyWeights(be, base);
+        EXPECT(sw.values.getNumTransformations() == 2 && sw.values.getTransformationKind(0) == B200C_X_QUANT_CAST &&
+                       sw.values.getTransformationKind(1) == B200C_X_SPARSIFY,
+               "sparsified weights: a fresh base, QuantCast, Sparsify");
+        EXPECT(sw.map.getNumTransformations() == 2 && sw.map.getTransformationKind(1) == B200C_X_GET_SPARSITY_MAP, "sparsity map: QuantCast, GetSparsityMap");
+        const auto raw = sw.values.fold(be).getRawBytes();
+        const auto map = sw.map.fold(be).getRawBytes();
+        bool ok = sw.counts.size() == 16 && map.size() == 16 * 16;
+        size_t at = 0;
+        for (int oc = 0; ok && oc < 16; ++oc) {
+            int64_t n = 0;
+            for (int j = 0; j < 32; ++j) {
+                const bool nz = w[oc * 32 + j] != 0;
+                ok = ok && (((map[oc * 16 + j / 8] >> (j % 8)) & 1) == (nz ? 1 : 0));
+                if (nz) {
+                    ok = ok && at + n < raw.size() && static_cast<int8_t>(raw[at + n]) == w[oc * 32 + j];
+                    ++n;
+                }
+            }
+            ok = ok && sw.counts[oc] == n;
+            at += static_cast<size_t>((n + 15) / 16 * 16);
+        }
+        EXPECT(ok, "sparsify-weights: counts, map bits and compacted runs of a quantised OYXI weight");
+        const auto flat = chains::flattenSparseWeights(sw.values, sw.counts);
+        EXPECT((flat.getType().shape == std::vector<int64_t>{static_cast<int64_t>(at), 1, 1, 1}), "flattened type holds the aligned runs");
+        const auto flatRaw = flat.fold(be).getRawBytes();
+        EXPECT(flatRaw.size() >= at && raw.size() >= at && std::memcmp(flatRaw.data(), raw.data(), at) == 0, "flattened content equals the runs");
+
+        const chains::SparseWeights id = chains::sparseIdentityFilter(be, 16, 16, B200C_F16);
+        EXPECT((id.counts == std::vector<int64_t>(16, 1)), "identity filter: one survivor per channel");
+        const auto idv = id.values.fold(be).getValues<uint16_t>();
+        const auto idm = id.map.fold(be).getRawBytes();
+        bool idok = idv.size() >= 16 * 8 && idm.size() == 16 * 16;
+        for (int oc = 0; idok && oc < 16; ++oc) {
+            idok = idv[static_cast<size_t>(oc) * 8] == 0x3C00;  // f16 1.0 at the head of every 16-byte run
+            for (int j = 0; idok && j < 16; ++j) idok = (((idm[oc * 16 + j / 8] >> (j % 8)) & 1) == (j == oc ? 1 : 0));
+        }
+        EXPECT(idok, "identity filter: values and map");
+        const QuantParams qi = QuantParams::perTensor(B200C_F16, 1.0, 0, 0, 255);
+        const chains::SparseWeights idq = chains::sparseIdentityFilter(be, 16, 16, B200C_UI8, &qi);
+        const auto idqv = idq.values.fold(be).getRawBytes();
+        bool qok = idq.counts == std::vector<int64_t>(16, 1) && idqv.size() >= 16 * 16;
+        for (int oc = 0; qok && oc < 16; ++oc) qok = idqv[static_cast<size_t>(oc) * 16] == 1;
+        EXPECT(qok, "quantised identity filter");
     }
     std::printf("%s\n", failures ? "FAILED" : "OK");
     return failures ? 1 : 0;
