@@ -221,6 +221,15 @@ private:
     std::vector<uint8_t> _bytes;
 };
 
+// Result of constant fusion: the [1,1,1,N] ui8 or f16 constant that replaces the weight table, weights, weights
+// sparsity map and activation window of one NCE task; views[k] = (offset, size) in elements of the fused type where
+// part k lives -- the SubView that replaces it -- or (-1, -1) for an absent part.
+struct FusedConstant {
+    NDType type;
+    std::vector<uint8_t> data;
+    std::vector<std::pair<int64_t, int64_t>> views;
+};
+
 // vpux::Const::ContentAttr: a base content plus an ordered transformation list.  The builder methods
 // return a new attribute, as the reference's do; a transformation is inserted at the position
 // getInsertionPosition gives it (content.cpp:268-299).
@@ -454,6 +463,77 @@ public:
         return Content(finalType, std::move(out));
     }
 
+    // FuseConstants (src/vpux_compiler/src/dialect/VPUIP/passes/fuse_constants.cpp:82-176,
+    // src/vpux_compiler/src/utils/constant_fusion.cpp): parts[k] is the weight table, the weights, the weights sparsity
+    // map and the activation window (nullptr = absent).  The reference folds each part and appends its values to a byte
+    // vector; here ONE batched call folds the parts into adjacent ranges of the fused buffer on the device and one copy
+    // brings the bytes back.  The fused type is f16 when f16 parts hold more than half of the bytes, else ui8.
+    static FusedConstant fuse(const Backend& be, const std::vector<const ContentAttr*>& parts) {
+        std::vector<const ContentAttr*> present;
+        for (const ContentAttr* p : parts)
+            if (p != nullptr) present.push_back(p);
+        std::vector<Marshalled> descs;
+        descs.reserve(present.size());  // the items point into these
+        std::vector<size_t> sizes;
+        size_t total = 0, f16Bytes = 0;
+        for (const ContentAttr* p : present) {
+            const NDType t = p->getType();
+            const int bits = B200C_DTYPE_BITS(t.dtype);
+            const bool known = t.quant.kind != B200C_Q_NONE || t.dtype == B200C_UI8 || t.dtype == B200C_I8 || t.dtype == B200C_F16 ||
+                               t.dtype == B200C_SI32 || bits == 1;
+            if (!known) throw Error(B200C_ERR_THROW, "Unsupported data type for constant");
+            const size_t size = static_cast<size_t>(t.getTotalAllocSize());
+            if (t.quant.kind == B200C_Q_NONE && t.dtype == B200C_F16) f16Bytes += size;
+            sizes.push_back(size);
+            total += size;
+            descs.emplace_back(*p);
+        }
+        struct DeviceBuffer {
+            b200c_ctx* ctx;
+            void* ptr = nullptr;
+            ~DeviceBuffer() {
+                if (ptr) b200c_dev_free(ctx, ptr);
+            }
+        } fused{be.ctx()};
+        check(b200c_dev_alloc(be.ctx(), total ? total : 1, &fused.ptr));
+        check(b200c_dev_memset(be.ctx(), fused.ptr, 0, total ? total : 1));
+        std::vector<b200c_fold_item> items(present.size());
+        size_t at = 0;
+        for (size_t k = 0; k < present.size(); ++k) {
+            b200c_fold_item& it = items[k];
+            std::memset(&it, 0, sizeof(it));
+            it.base = &descs[k].base;
+            it.data = present[k]->_data->data();
+            it.nbytes = present[k]->_data->size();
+            it.is_splat = present[k]->_splat ? 1 : 0;
+            it.n = static_cast<int32_t>(descs[k].chain.size());
+            it.chain = descs[k].chain.data();
+            it.out = static_cast<uint8_t*>(fused.ptr) + at;
+            it.out_cap = sizes[k];
+            at += sizes[k];
+        }
+        if (!items.empty()) {
+            check(b200c_fold_batch(be.ctx(), items.data(), static_cast<int>(items.size()), /*data_on_device=*/0, /*out_on_device=*/1, 0));
+        }
+        FusedConstant r;
+        r.data.resize(total);
+        if (total) check(b200c_memcpy_d2h(be.ctx(), r.data.data(), fused.ptr, total));
+        const size_t es = f16Bytes * 2 > total ? 2 : 1;
+        r.type = NDType({1, 1, 1, static_cast<int64_t>(total / es)}, es == 2 ? B200C_F16 : B200C_UI8);
+        int64_t off = 0;
+        size_t j = 0;
+        for (const ContentAttr* p : parts) {
+            if (p == nullptr) {
+                r.views.emplace_back(-1, -1);
+                continue;
+            }
+            const int64_t n = static_cast<int64_t>(sizes[j++] / es);
+            r.views.emplace_back(off, n);
+            off += n;
+        }
+        return r;
+    }
+
     // vpux::countNonSparseElementsPerOC on the folded content
     std::vector<int64_t> countNonSparseElementsPerOC(const Backend& be) const {
         Marshalled m(*this);
@@ -649,6 +729,26 @@ inline std::vector<uint8_t> decompress(const Backend& be, const std::vector<uint
     check(b200c_btc_decompress(be.ctx(), stream.data(), stream.size(), 0, out.data(), originalSize, 0, &n));
     out.resize(n);
     return out;
+}
+
+inline FusedConstant fuseConstants(const Backend& be, const ContentAttr* weightTable, const ContentAttr* weights,
+                                   const ContentAttr* weightsSparsityMap, const ContentAttr* activationWindow) {
+    return ContentAttr::fuse(be, {weightTable, weights, weightsSparsityMap, activationWindow});
+}
+
+// The constants section of a blob: every op's bytes (DeclareOp::serialize) one after the other, each start aligned
+// to `align` bytes and the gap zero-filled -- 8 for the graph-schema writer (serializeBinaryData,
+// src/vpux_compiler/src/dialect/VPUIP/graph-schema/export.cpp:465-479), 1 for the ELF writer (ops.cpp:97-108).
+// offsets receives where every constant starts.
+inline std::vector<uint8_t> writeSection(const Backend& be, const std::vector<DeclareOp>& ops, size_t align, std::vector<size_t>* offsets) {
+    std::vector<uint8_t> section;
+    if (offsets) offsets->clear();
+    for (const DeclareOp& op : ops) {
+        if (offsets) offsets->push_back(section.size());
+        op.serialize(be, section);
+        if (align > 1) section.resize((section.size() + align - 1) / align * align, 0);
+    }
+    return section;
 }
 
 // The chain builders: the callers of the ContentAttr API that assemble the transformation lists the hot path folds.

@@ -355,6 +355,53 @@ int main() {
         for (int oc = 0; qok && oc < 16; ++oc) qok = idqv[static_cast<size_t>(oc) * 16] == 1;
         EXPECT(qok, "quantised identity filter");
     }
+    // ---- constant fusion (fuse_constants.cpp:82-176) and the constants-section writers (export.cpp:465-479,
+    //      ops.cpp:97-108): the fused bytes are the parts' folded bytes one after the other ----
+    {
+        std::vector<int32_t> table(4 * 4);
+        for (size_t i = 0; i < table.size(); ++i) table[i] = static_cast<int32_t>(1000 + 17 * i);
+        std::vector<uint8_t> w(4 * 16);
+        for (size_t i = 0; i < w.size(); ++i) w[i] = (i % 3 == 0) ? 0 : static_cast<uint8_t>(i + 1);
+        const auto wt = ContentAttr::get(table, NDType({4, 1, 1, 4}, B200C_SI32));
+        const auto weights = ContentAttr::get(w, NDType({4, 16, 1, 1}, B200C_UI8)).reorder(DimsOrder::OYXI());
+        const auto sm = ContentAttr::get(w, NDType({4, 16, 1, 1}, B200C_UI8)).getSparsityMap();
+        auto view = [](int64_t offset, int64_t size) { return std::pair<int64_t, int64_t>(offset, size); };
+        const FusedConstant f = fuseConstants(be, &wt, &weights, &sm, nullptr);
+        std::vector<uint8_t> want;
+        for (const ContentAttr* p : {&wt, &weights, &sm}) {
+            const Content c = p->fold(be);
+            std::vector<uint8_t> part(static_cast<size_t>(c.getType().getTotalAllocSize()), 0);
+            c.copyTo(part.data(), part.size());
+            want.insert(want.end(), part.begin(), part.end());
+        }
+        EXPECT(f.data == want && want.size() == 64 + 64 + 4 * 16, "fused bytes: table, weights, sparsity map");
+        EXPECT(f.type.dtype == B200C_UI8 && (f.type.shape == std::vector<int64_t>{1, 1, 1, static_cast<int64_t>(want.size())}), "fused type: [1,1,1,N] ui8");
+        EXPECT(f.views.size() == 4 && f.views[0] == view(0, 64) && f.views[1] == view(64, 64) &&
+                       f.views[2] == view(128, 64) && f.views[3].first == -1,
+               "fused views");
+        // f16 weights hold most of the bytes: the fused constant is f16
+        std::vector<uint16_t> hw(8 * 16, 0x3C00);
+        const auto hweights = ContentAttr::get(hw, NDType({8, 16, 1, 1}, B200C_F16));
+        const FusedConstant g = fuseConstants(be, &wt, &hweights, nullptr, nullptr);
+        EXPECT(g.type.dtype == B200C_F16 && (g.type.shape == std::vector<int64_t>{1, 1, 1, (64 + 256) / 2}) && g.data.size() == 320, "fused type: f16 majority");
+        EXPECT(g.views[0] == view(0, 32) && g.views[1] == view(32, 128) && g.views[2].first == -1,
+               "fused views in f16 elements");
+        bool tail = true;
+        for (size_t i = 64; i < g.data.size(); i += 2) tail = tail && g.data[i] == 0x00 && g.data[i + 1] == 0x3C;
+        EXPECT(tail && std::memcmp(g.data.data(), table.data(), 64) == 0, "fused f16 bytes");
+
+        std::vector<uint8_t> five{1, 2, 3, 4, 5};
+        std::vector<uint8_t> twelve(12, 9);
+        const std::vector<DeclareOp> ops{DeclareOp(NDType({5}, B200C_UI8), ContentAttr::get(five, NDType({5}, B200C_UI8))),
+                                         DeclareOp(NDType({12}, B200C_UI8), ContentAttr::get(twelve, NDType({12}, B200C_UI8)))};
+        std::vector<size_t> offs;
+        const auto schema = writeSection(be, ops, 8, &offs);
+        EXPECT(schema.size() == 24 && (offs == std::vector<size_t>{0, 8}) && std::memcmp(schema.data(), five.data(), 5) == 0 && schema[5] == 0 &&
+                       schema[7] == 0 && schema[8] == 9 && schema[19] == 9 && schema[20] == 0,
+               "graph-schema section: 8-byte aligned, zero padded");
+        const auto elf = writeSection(be, ops, 1, &offs);
+        EXPECT(elf.size() == 17 && (offs == std::vector<size_t>{0, 5}) && elf[4] == 5 && elf[5] == 9, "ELF section: no padding");
+    }
     std::printf("%s\n", failures ? "FAILED" : "OK");
     return failures ? 1 : 0;
 }
