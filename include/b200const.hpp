@@ -787,7 +787,7 @@ inline ContentAttr weightsToU8(const ContentAttr& weights, const QuantParams& ne
     const NDType t = weights.getType();
     if (t.quant.kind == B200C_Q_NONE) throw Error(B200C_ERR_INVALID, "weightsToU8: the constant is not quantised");
     return weights.quantCast()
-            .convertElemType(B200C_SI32)
+            .convertElemType(B200C_I32)  // signless, as the reference's getInt32Type
             .add(static_cast<double>(-t.quant.qmin))
             .convertElemType(B200C_UI8)
             .quantCast(newQuant, B200C_UI8);

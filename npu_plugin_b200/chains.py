@@ -45,13 +45,14 @@ def align_convolution_weights(weights, alignment=16, is_cmajor_conv=False):
 
 
 def weights_to_u8(weights, new_quant):
-    """Signed-int8 quantised weights re-based to unsigned: quantCast() -> convertElemType(si32) -> add(-storageMin)
-    -> convertElemType(ui8) -> quantCast(new type).  `new_quant` is the u8 quantised type (zero points shifted by
-    -storageMin by the caller's type converter)."""
+    """Signed-int8 quantised weights re-based to unsigned: quantCast() -> convertElemType(i32, signless as the
+    reference's getInt32Type) -> add(-storageMin) -> convertElemType(ui8) -> quantCast(new type).  `new_quant` is the
+    u8 quantised type (zero points shifted by -storageMin by the caller's type converter).  The list is the one
+    tests/lit/NPU/dialect/IE/passes/convert_weights_to_u8.mlir:25-32 checks."""
     old = weights.getType().quant
     if old is None:
         raise ValueError("weights_to_u8: the constant is not quantised")
-    return (weights.quantCast().convertElemType(A.SI32).add(float(-old.qmin)).convertElemType(A.UI8).quantCast(new_quant))
+    return (weights.quantCast().convertElemType(A.I32).add(float(-old.qmin)).convertElemType(A.UI8).quantCast(new_quant))
 
 
 def sparsify_weights(weights, backend=None):

@@ -103,3 +103,25 @@ def test_attach_swizzle_once(backend):
     assert kinds(a) == [A.X_SWIZZLE_CONSTANT]
     assert chains.attach_swizzle(a) is a
     assert a.fold().copyTo().size == 1024
+
+
+# tests/lit/NPU/dialect/IE/passes/convert_weights_to_u8.mlir:9-32 (@Conv): dense<-1.0> 3x3x3x3 f16 with
+# [ConvertElemType<si8>, QuantCast<i8<-127:127> per axis 0>] becomes u8<0:254> with zero points 127 through
+# [..., QuantCast<>, ConvertElemType<i32>, Add<127.0>, ConvertElemType<ui8>, QuantCast<new type>]
+def test_weights_to_u8_on_the_lit_case(oracle):
+    scales = [0.010680671751968504, 0.0081200787401574797, 0.010596087598425197]
+    q_old = UniformQuantizedPerAxisType(A.SI8, A.F16, scales, [0, 0, 0], 0, -127, 127)
+    q_new = UniformQuantizedPerAxisType(A.UI8, A.F16, scales, [127, 127, 127], 0, 0, 254)
+    base = ContentAttr.get(np.array([-1.0], np.float16), NDType((3, 3, 3, 3), A.F16), backend=oracle)
+    assert base._isSplat
+    a = chains.weights_to_u8(base.convertElemType(A.SI8).quantCast(q_old), q_new)
+    ts = a.getTransformations()
+    assert [t.getTransformationName() for t in ts] == ["ConvertElemType", "QuantCast", "QuantCast", "ConvertElemType", "Add",
+                                                        "ConvertElemType", "QuantCast"]
+    assert ts[0].elem == A.SI8 and ts[2].elem is None and ts[3].elem == A.I32 and ts[4].f == 127.0 and ts[5].elem == A.UI8
+    assert a.getType() == NDType((3, 3, 3, 3), q_new)
+    raw = a.fold().copyTo()
+    assert raw.size == 81 and (raw == 126).all()  # -1 - (-127)
+    # the library's own type inference (host code) accepts the same list
+    from test_abi_and_host import HostOnly
+    assert HostOnly().infer_type(base._baseType, ts) == a.getType()
