@@ -125,3 +125,37 @@ def test_weights_to_u8_on_the_lit_case(oracle):
     # the library's own type inference (host code) accepts the same list
     from test_abi_and_host import HostOnly
     assert HostOnly().infer_type(base._baseType, ts) == a.getType()
+
+
+# tests/lit/NPU/conversion/passes/IE2VPU/convert_IE_to_VPU_NCE_37XX.mlir:210-229 (@ConvToNCE4channels): weights
+# 16x4x1x1 f16 NHWC become 16x1x1x16 through [Reorder<NHWC>, Reshape<[16,1,1,4]>, PadWithZero<[0,0,0,0],[0,0,0,12]>]
+def test_align_convolution_weights_on_the_lit_case(oracle):
+    base = ContentAttr.get(np.array([1.0], np.float16), NDType((16, 4, 1, 1), A.F16), backend=oracle).reorder(DimsOrder.NHWC)
+    a = chains.align_convolution_weights(base, alignment=chains.VPU_WEIGHT_SET_BYTE_ALIGNMENT)
+    ts = a.getTransformations()
+    assert [t.getTransformationName() for t in ts] == ["Reorder", "Reshape", "PadWithZero"]
+    assert ts[1].b == (16, 1, 1, 4) and ts[2].a == (0, 0, 0, 0) and ts[2].b == (0, 0, 0, 12)
+    assert a.getType() == NDType((16, 1, 1, 16), A.F16, DimsOrder.NHWC)
+    got = a.fold().copyTo().view(np.float16).reshape(16, 16)
+    assert (got[:, :4] == 1.0).all() and (got[:, 4:] == 0.0).all()
+
+
+# tests/lit/NPU/dialect/VPU/passes/sparsify_weights_30XX.mlir:30-51 (@SparsifyPaddedConv): 16x15x1x1 f16 ones padded
+# to 16x32x1x1 NHWC -> folded base + [Sparsify<false>], a 16x1x1x128 i1 map from [GetSparsityMap], numElems = 15
+def test_sparsify_weights_on_the_lit_case(oracle):
+    base = (ContentAttr.get(np.array([1.0], np.float16), NDType((16, 15, 1, 1), A.F16), backend=oracle)
+            .reorder(DimsOrder.NHWC).padWithZero((0, 0, 0, 0), (0, 17, 0, 0)))
+    vals, smap, counts = chains.sparsify_weights(base)
+    assert counts == [15] * 16
+    assert [t.getTransformationName() for t in vals.getTransformations()] == ["Sparsify"]
+    assert [t.getTransformationName() for t in smap.getTransformations()] == ["GetSparsityMap"]
+    assert vals._baseType == NDType((16, 32, 1, 1), A.F16, DimsOrder.NHWC) and not vals._isSplat
+    assert vals.getType() == NDType((16, 32, 1, 1), A.F16, DimsOrder.NHWC)
+    assert smap.getType() == NDType((16, 1, 1, 128), A.I1)
+    bits = np.unpackbits(smap.fold().copyTo().reshape(16, 16), axis=1, bitorder="little")
+    assert (bits[:, :15] == 1).all() and (bits[:, 15:] == 0).all()
+    raw = vals.fold().copyTo().view(np.float16)
+    assert raw.size >= 16 * 16 and (raw[:16 * 16].reshape(16, 16)[:, :15] == 1.0).all() and (raw[:16 * 16].reshape(16, 16)[:, 15] == 0.0).all()
+    # late in the pipeline the type becomes the flat compressed one: 16 runs of 15 f16 = 30 bytes, each padded to 32
+    flat = chains.flatten_sparse_weights(vals, counts)
+    assert flat.getType().shape == (16 * 32, 1, 1, 1) and flat.getType().dtype == A.UI8
