@@ -159,3 +159,20 @@ def test_sparsify_weights_on_the_lit_case(oracle):
     # late in the pipeline the type becomes the flat compressed one: 16 runs of 15 f16 = 30 bytes, each padded to 32
     flat = chains.flatten_sparse_weights(vals, counts)
     assert flat.getType().shape == (16 * 32, 1, 1, 1) and flat.getType().dtype == A.UI8
+
+
+# tests/lit/NPU/dialect/VPU/passes/lower_unaligned_sparsity_ops_37XX.mlir:28-33,74-79: the identity filter of a lowered
+# sparsity op is an f32 16x16x1x1 constant with [ConvertElemType<ui8>, QuantCast<q>, Reorder<NHWC>, Sparsify<false>]
+# (or [ConvertElemType<f16>, Reorder<NHWC>, Sparsify<false>]), its map 16x1x1x128 i1, numElems = 1 per channel
+def test_sparse_identity_filter_on_the_lit_cases(oracle):
+    names = lambda a: [t.getTransformationName() for t in a.getTransformations()]
+    q = UniformQuantizedType(A.UI8, A.F16, 1.0, 0)
+    vals, smap, counts = chains.sparse_identity_filter(16, 16, q, order=DimsOrder.NHWC, backend=oracle)
+    assert names(vals) == ["ConvertElemType", "QuantCast", "Reorder", "Sparsify"]
+    assert names(smap) == ["ConvertElemType", "QuantCast", "Reorder", "GetSparsityMap"]
+    assert vals._baseType == NDType((16, 16, 1, 1), A.F32) and counts == [1] * 16
+    assert vals.getType() == NDType((16, 16, 1, 1), q, DimsOrder.NHWC) and smap.getType() == NDType((16, 1, 1, 128), A.I1)
+    vals, smap, counts = chains.sparse_identity_filter(16, 16, A.F16, order=DimsOrder.NHWC, backend=oracle)
+    assert names(vals) == ["ConvertElemType", "Reorder", "Sparsify"] and names(smap) == ["ConvertElemType", "Reorder", "GetSparsityMap"]
+    assert vals.getType() == NDType((16, 16, 1, 1), A.F16, DimsOrder.NHWC) and smap.getType() == NDType((16, 1, 1, 128), A.I1)
+    assert counts == [1] * 16
