@@ -1,4 +1,4 @@
-"""The multi-rank whole-model fold on CPU ranks (gloo, world size 2 and 3).
+"""The multi-rank whole-model fold on CPU ranks (gloo, world sizes 2, 3 and 8).
 
 The routine under test is npu_plugin_b200.sharded.ShardedFolder -- the same partition, chunking, slot
 layout, segment table and step/collect/release sequence the benchmark runs on GPUs.  Only the two parts
@@ -176,7 +176,7 @@ def _single_rank_reference():
     return sf.t.buf[:sf.layout.blob_bytes].copy(), table
 
 
-@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("world", [2, 3, 8])
 def test_sharded_fold_assembles_the_single_rank_blob(tmp_path, world):
     import torch.multiprocessing as mp
     port = 29500 + (os.getpid() % 2000) + world
