@@ -662,6 +662,27 @@ class ContentAttr:
             raise ConstError(f"Size of dense resource buffer '{nbytes}' in 'baseContent' doesn't match its type '{base_type}'")
         return ContentAttr(arr, base_type, bool(is_splat), [], backend or default_backend())
 
+    @staticmethod
+    def getDenseResource(raw, base_type, backend=None):
+        """A dense resource (mlir::DenseResourceElementsAttr) as base content.  Its blob is opaque to MLIR, so the
+        reference looks at the bytes itself (detectSplatManually, content.cpp:120-137): empty data is no splat, a
+        buffer of exactly one element is one, and otherwise all elements are compared with the first
+        (detectSplatElementWise, content.cpp:103-118) -- here by the backend's probe, a device kernel on the CUDA
+        backend.  A splat keeps its first element only, as the reference's take_front(elementSize)."""
+        backend = backend or default_backend()
+        if raw is None:
+            raise ConstError("Got NULL 'baseContent' in 'ContentAttr'")
+        arr = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+        attr = ContentAttr.get(arr, base_type, backend=backend)  # the size check; a one-element buffer is a splat already
+        bits = base_type.getElemTypeSize()
+        if attr._isSplat or arr.size == 0 or bits % 8 != 0:
+            return attr
+        elem = bits // 8
+        if backend.detect_splat(arr, elem):
+            splat = base_type.getNumElements() != 1
+            return ContentAttr(arr[:elem].copy(), base_type, splat, [], backend)
+        return attr
+
     # -- accessors
     def getBaseContent(self):
         return self._base

@@ -78,6 +78,18 @@ class OracleBackend:
             K.raise_for(rc, self._err())
             return K.NDType.from_c(out)
 
+    def detect_splat(self, data, elem_bytes):
+        """detectSplatElementWise (content.cpp:103-118) in numpy."""
+        buf = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        if buf.size == 0:
+            return False
+        if buf.size < elem_bytes:
+            raise K.ConstError("The data must contain at least one element")
+        if buf.size % elem_bytes:
+            raise K.ConstError("The data array has unexpected length")
+        rows = buf.reshape(-1, elem_bytes)
+        return bool((rows == rows[0]).all())
+
     def insert_position(self, kinds, new_kind):
         arr = (C.c_int32 * max(1, len(kinds)))(*kinds)
         pos = C.c_int()

@@ -103,3 +103,30 @@ def test_content_attr_verifies_its_base_buffer(oracle):
         ContentAttr.get(np.zeros(3, np.float32), t, is_splat=True, backend=oracle)
     with pytest.raises(ConstError, match="Size of dense resource buffer '4'"):
         ContentAttr.get(np.zeros(1, np.float32), t, is_splat=False, backend=oracle)
+
+
+# tests/unit/vpux_compiler/dialect/const/content_tests.cpp:160-320: a dense resource that holds every element is no
+# splat, one that holds a single element or only equal elements is (and folds to that value everywhere), an empty one
+# is not
+def test_dense_resource_splat_detection(oracle):
+    t = NDType((1, 2, 3, 4), A.F32)
+    vals = np.arange(24, dtype=np.float32)
+    dense = ContentAttr.getDenseResource(vals, t, backend=oracle)
+    assert not dense._isSplat and np.array_equal(dense.fold().copyTo().view(np.float32), vals)
+    one = ContentAttr.getDenseResource(np.array([4.0], np.float32), t, backend=oracle)
+    assert one._isSplat and (one.fold().copyTo().view(np.float32) == 4.0).all() and one.fold().copyTo().size == 96
+    equal = ContentAttr.getDenseResource(np.full(24, -4.0, np.float32), t, backend=oracle)
+    assert equal._isSplat and equal.getBaseContent().size == 4
+    assert (equal.fold().copyTo().view(np.float32) == -4.0).all() and equal.fold().copyTo().size == 96
+    empty = ContentAttr.getDenseResource(np.zeros(0, np.float32), NDType((0,), A.F32), backend=oracle)
+    assert not empty._isSplat and empty.getType() == NDType((0,), A.F32)
+    # equal bytes are not equal elements: 0x0101 0x0101 ... is a splat of 16-bit elements, 0x01 0x02 0x01 0x02 too,
+    # but a single differing byte is noticed
+    pat = np.tile(np.array([1, 2], np.uint8), 50)
+    assert ContentAttr.getDenseResource(pat, NDType((50,), A.UI16), backend=oracle)._isSplat
+    pat[37] = 3
+    assert not ContentAttr.getDenseResource(pat, NDType((50,), A.UI16), backend=oracle)._isSplat
+    # a splat behaves as one downstream: BitPack refuses it (bit_pack.cpp:109)
+    from npu_plugin_b200.const import ConstError
+    with pytest.raises(ConstError, match="splat"):
+        ContentAttr.getDenseResource(np.full(8, 3, np.int8), NDType((8,), A.SI8), backend=oracle).bitPack(4).fold()
